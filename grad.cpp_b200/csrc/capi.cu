@@ -1,0 +1,287 @@
+// extern "C" surface declared in include/gradb.h. Exceptions stop here and
+// become status codes plus a thread-local message.
+#include <cstring>
+
+#include "session.cuh"
+
+using namespace gradb;
+
+namespace {
+thread_local std::string g_error;
+
+template <typename F>
+gradb_status guarded(F&& f) {
+    try {
+        f();
+        return GRADB_OK;
+    } catch (const Error& e) {
+        g_error = e.what();
+        return e.status;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return GRADB_ERR_INVALID;
+    }
+}
+
+}  // namespace
+
+struct gradb_model {
+    DeviceModel* impl;
+};
+struct gradb_session {
+    Session* impl;
+};
+
+extern "C" {
+
+const char* gradb_last_error(void) { return g_error.c_str(); }
+const char* gradb_version(void) { return "gradb 0.1 (sm_100a)"; }
+
+gradb_status gradb_device_count(int* count_out) {
+    int n = 0;
+    const cudaError_t e = cudaGetDeviceCount(&n);
+    if (count_out) *count_out = e == cudaSuccess ? n : 0;
+    if (e != cudaSuccess || n == 0) {
+        g_error = "no CUDA device available; this library has no CPU path";
+        return GRADB_ERR_NO_DEVICE;
+    }
+    return GRADB_OK;
+}
+
+gradb_status gradb_checkpoint_inspect(const char* path, gradb_model_desc* desc_out) {
+    try {
+        const Checkpoint ck = read_checkpoint(path, false);
+        if (desc_out) *desc_out = ck.desc;
+        return GRADB_OK;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return GRADB_ERR_CHECKPOINT;
+    }
+}
+
+gradb_status gradb_tensor_count(const gradb_model_desc* desc, int* count_out) {
+    return guarded([&] {
+        if (!desc || !count_out) throw Error(GRADB_ERR_INVALID, "null argument");
+        gradb_model_desc d = *desc;
+        d.d_ff = resolve_d_ff(d.d_model, d.arch == GRADB_ARCH_MODERN);
+        *count_out = tensor_index(d).count;
+    });
+}
+
+gradb_status gradb_tensor_shape(const gradb_model_desc* desc, int index, int* rows_out, int* cols_out) {
+    return guarded([&] {
+        if (!desc) throw Error(GRADB_ERR_INVALID, "null argument");
+        gradb_model_desc d = *desc;
+        d.d_ff = resolve_d_ff(d.d_model, d.arch == GRADB_ARCH_MODERN);
+        const auto shapes = tensor_shapes(d);
+        if (index < 0 || index >= (int)shapes.size()) throw Error(GRADB_ERR_INVALID, "tensor index out of range");
+        if (rows_out) *rows_out = shapes[index].rows;
+        if (cols_out) *cols_out = shapes[index].cols;
+    });
+}
+
+gradb_status gradb_checkpoint_write(const char* path, const gradb_model_desc* desc, const float* const* tensors_host,
+                                    int n_tensors) {
+    return guarded([&] {
+        if (!path || !desc || !tensors_host) throw Error(GRADB_ERR_INVALID, "null argument");
+        gradb_model_desc d = *desc;
+        d.d_ff = resolve_d_ff(d.d_model, d.arch == GRADB_ARCH_MODERN);
+        std::string err;
+        if (!write_checkpoint(path, d, tensors_host, n_tensors, err)) throw Error(GRADB_ERR_IO, err);
+    });
+}
+
+gradb_status gradb_model_load(const char* path, int device, int precision, gradb_model** model_out) {
+    if (!path || !model_out) {
+        g_error = "null argument";
+        return GRADB_ERR_INVALID;
+    }
+    Checkpoint ck;
+    try {
+        ck = read_checkpoint(path, true);
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return GRADB_ERR_CHECKPOINT;
+    }
+    return guarded([&] {
+        std::vector<const float*> ptrs;
+        for (const auto& t : ck.tensors) ptrs.push_back(t.data());
+        DeviceModel* m = upload_model(ck.desc, ptrs.data(), (int)ptrs.size(), device, precision);
+        *model_out = new gradb_model{m};
+    });
+}
+
+gradb_status gradb_model_from_host(const gradb_model_desc* desc, const float* const* tensors_host, int n_tensors,
+                                   int device, int precision, gradb_model** model_out) {
+    return guarded([&] {
+        if (!desc || !tensors_host || !model_out) throw Error(GRADB_ERR_INVALID, "null argument");
+        DeviceModel* m = upload_model(*desc, tensors_host, n_tensors, device, precision);
+        *model_out = new gradb_model{m};
+    });
+}
+
+gradb_status gradb_model_save(const gradb_model* model, const char* path) {
+    return guarded([&] {
+        if (!model || !path) throw Error(GRADB_ERR_INVALID, "null argument");
+        const DeviceModel* m = model->impl;
+        GRADB_CUDA(cudaSetDevice(m->device));
+        const auto shapes = tensor_shapes(m->desc);
+        std::vector<std::vector<float>> host(shapes.size());
+        std::vector<const float*> ptrs(shapes.size());
+        for (size_t i = 0; i < shapes.size(); i++) {
+            host[i].resize((size_t)shapes[i].rows * shapes[i].cols);
+            GRADB_CUDA(cudaMemcpy(host[i].data(), m->blob + m->offsets[i], host[i].size() * sizeof(float),
+                                  cudaMemcpyDeviceToHost));
+            ptrs[i] = host[i].data();
+        }
+        std::string err;
+        if (!write_checkpoint(path, m->desc, ptrs.data(), (int)ptrs.size(), err)) throw Error(GRADB_ERR_IO, err);
+    });
+}
+
+gradb_status gradb_model_describe(const gradb_model* model, gradb_model_desc* desc_out) {
+    if (!model || !desc_out) {
+        g_error = "null argument";
+        return GRADB_ERR_INVALID;
+    }
+    *desc_out = model->impl->desc;
+    return GRADB_OK;
+}
+
+void gradb_model_free(gradb_model* model) {
+    if (!model) return;
+    free_model(model->impl);
+    delete model;
+}
+
+gradb_status gradb_session_create(const gradb_model* model, int max_batch, int max_len, void* stream,
+                                  gradb_session** session_out) {
+    return guarded([&] {
+        if (!model || !session_out) throw Error(GRADB_ERR_INVALID, "null argument");
+        *session_out = new gradb_session{create_session(model->impl, max_batch, max_len, stream)};
+    });
+}
+
+void gradb_session_free(gradb_session* session) {
+    if (!session) return;
+    destroy_session(session->impl);
+    delete session;
+}
+
+gradb_status gradb_session_reset(gradb_session* session) {
+    return guarded([&] {
+        if (!session) throw Error(GRADB_ERR_INVALID, "null session");
+        reset_session(session->impl);
+        GRADB_CUDA(cudaStreamSynchronize(session->impl->stream));
+    });
+}
+
+gradb_status gradb_session_position(const gradb_session* session, int seq, int* position_out) {
+    if (!session || !position_out || seq < 0 || seq >= session->impl->B) {
+        g_error = "bad argument";
+        return GRADB_ERR_INVALID;
+    }
+    *position_out = session->impl->h_pos[seq];
+    return GRADB_OK;
+}
+int gradb_session_capacity(const gradb_session* session) { return session ? session->impl->T : 0; }
+int gradb_session_vocab(const gradb_session* session) { return session ? session->impl->V : 0; }
+int gradb_session_max_batch(const gradb_session* session) { return session ? session->impl->B : 0; }
+
+gradb_status gradb_step(gradb_session* session, const int32_t* tokens_host, int n_seq, float* logits_host) {
+    return guarded([&] {
+        if (!session || !tokens_host) throw Error(GRADB_ERR_INVALID, "null argument");
+        session_step(session->impl, tokens_host, n_seq, logits_host);
+    });
+}
+
+gradb_status gradb_prefill(gradb_session* session, const int32_t* tokens_host, const int32_t* offsets_host, int n_seq,
+                           float* logits_host) {
+    return guarded([&] {
+        if (!session || !tokens_host || !offsets_host) throw Error(GRADB_ERR_INVALID, "null argument");
+        session_prefill(session->impl, tokens_host, offsets_host, n_seq, logits_host);
+    });
+}
+
+gradb_status gradb_select(gradb_session* session, const gradb_sampling* params, const float* uniforms_host, int n_seq,
+                          int32_t* tokens_host) {
+    return guarded([&] {
+        if (!session || !params || !tokens_host) throw Error(GRADB_ERR_INVALID, "null argument");
+        session_select(session->impl, *params, nullptr, uniforms_host, n_seq, tokens_host, nullptr);
+    });
+}
+
+gradb_status gradb_session_set_history(gradb_session* session, int seq, const int32_t* ids_host, int n) {
+    return guarded([&] {
+        if (!session || (!ids_host && n > 0)) throw Error(GRADB_ERR_INVALID, "null argument");
+        session_set_history(session->impl, seq, ids_host, n);
+    });
+}
+
+gradb_status gradb_select_from_logits(gradb_session* session, const gradb_sampling* params, const float* logits_host,
+                                      const float* uniforms_host, int n_seq, int32_t* tokens_host, float* probs_host) {
+    return guarded([&] {
+        if (!session || !params || !logits_host || !tokens_host) throw Error(GRADB_ERR_INVALID, "null argument");
+        session_select(session->impl, *params, logits_host, uniforms_host, n_seq, tokens_host, probs_host);
+    });
+}
+
+gradb_status gradb_generate(gradb_session* session, const int32_t* prompts_host, const int32_t* offsets_host, int n_seq,
+                            const gradb_sampling* params, int max_new, const float* uniforms_host,
+                            int32_t* out_ids_host, int out_stride, int32_t* out_len_host, float* step_ms_host,
+                            float* prefill_ms_host) {
+    return guarded([&] {
+        if (!session || !prompts_host || !offsets_host || !params || !out_ids_host || !out_len_host) {
+            throw Error(GRADB_ERR_INVALID, "null argument");
+        }
+        session_generate(session->impl, prompts_host, offsets_host, n_seq, *params, max_new, uniforms_host,
+                         out_ids_host, out_stride, out_len_host, step_ms_host, prefill_ms_host);
+    });
+}
+
+gradb_status gradb_session_last_ms(const gradb_session* session, float* ms_out) {
+    if (!session || !ms_out) {
+        g_error = "null argument";
+        return GRADB_ERR_INVALID;
+    }
+    *ms_out = session->impl->last_ms;
+    return GRADB_OK;
+}
+
+gradb_status gradb_session_cache_row(gradb_session* session, int seq, int layer, int which, int pos, float* row_host) {
+    return guarded([&] {
+        if (!session || !row_host) throw Error(GRADB_ERR_INVALID, "null argument");
+        session_cache_row(session->impl, seq, layer, which, pos, row_host);
+    });
+}
+
+gradb_status gradb_session_set_profiling(gradb_session* session, int on) {
+    return guarded([&] {
+        if (!session) throw Error(GRADB_ERR_INVALID, "null session");
+        session_set_profiling(session->impl, on != 0);
+    });
+}
+
+int gradb_kernel_class_count(void) { return kKernelClasses; }
+
+const char* gradb_kernel_class_name(int cls) {
+    static const char* const names[kKernelClasses] = {"embed",    "norm_qkv_rope", "attn_decode", "attn_out_proj", "norm_ffn_up",
+                                                      "ffn_down", "norm_logits",   "advance",     "select"};
+    return cls >= 0 && cls < kKernelClasses ? names[cls] : "";
+}
+
+gradb_status gradb_session_profile(const gradb_session* session, double* ms_out, uint64_t* launches_out) {
+    if (!session || !ms_out || !launches_out) {
+        g_error = "null argument";
+        return GRADB_ERR_INVALID;
+    }
+    for (int i = 0; i < kKernelClasses; i++) {
+        ms_out[i] = session->impl->class_ms[i];
+        launches_out[i] = session->impl->class_launches[i];
+    }
+    return GRADB_OK;
+}
+
+uint64_t gradb_kernel_launches(void) { return g_kernel_launches.load(); }
+
+}  // extern "C"

@@ -1,0 +1,69 @@
+// Shared declarations of the decode engine's CUDA translation units.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/gradb.h"
+#include "checkpoint.h"
+
+namespace gradb {
+
+struct Error : std::runtime_error {
+    gradb_status status;
+    Error(gradb_status s, const std::string& what) : std::runtime_error(what), status(s) {}
+};
+
+#define GRADB_CUDA(expr)                                                                          \
+    do {                                                                                          \
+        cudaError_t _e = (expr);                                                                  \
+        if (_e != cudaSuccess) {                                                                  \
+            throw ::gradb::Error(GRADB_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+        }                                                                                         \
+    } while (0)
+
+extern std::atomic<uint64_t> g_kernel_launches;
+// Set by the thread that is capturing a CUDA graph.
+extern thread_local bool g_capturing;
+inline void count_launch(uint64_t n = 1) { g_kernel_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// Sequences whose current token id is negative take no part in a step.
+constexpr int kSkip = -1;
+// Width of the repetition-penalty window (text_gen.cpp:22).
+constexpr int kPenaltyWindow = 50;
+
+// Per-layer device pointers. fp32 masters are always present; the bf16 copies
+// only in GRADB_BF16 mode. Linear weights are (in, out) row-major as in the
+// checkpoint (inference.cpp:13).
+struct LayerWeights {
+    const float *wq, *wk, *wv, *wo, *bq, *bk, *bv, *bo;
+    const float *gate, *w1, *b1, *w2, *b2;
+    const float *n1g, *n1b, *n2g, *n2b;
+    const __nv_bfloat16 *wq16, *wk16, *wv16, *wo16, *gate16, *w116, *w216;
+};
+
+struct DeviceModel {
+    gradb_model_desc desc{};
+    int device = 0;
+    int precision = GRADB_FP32;
+    float* blob = nullptr;           // every tensor, file order, fp32
+    std::vector<size_t> offsets;     // element offset of each tensor in blob
+    __nv_bfloat16* blob16 = nullptr; // bf16 copies of the matrices (BF16 mode)
+    const float *emb = nullptr, *pos = nullptr, *fng = nullptr, *fnb = nullptr;
+    const __nv_bfloat16* emb16 = nullptr;
+    std::vector<LayerWeights> layers;
+    float* rope_cos = nullptr;  // [max_len][hs/2], host-computed with the reference's expressions
+    float* rope_sin = nullptr;
+    int sm_count = 148;
+};
+
+DeviceModel* upload_model(const gradb_model_desc& desc, const float* const* tensors, int n_tensors, int device,
+                          int precision);
+void free_model(DeviceModel* m);
+
+}  // namespace gradb

@@ -1,0 +1,122 @@
+// Places a model's weights in HBM.
+#include <cmath>
+
+#include "common.cuh"
+
+namespace gradb {
+
+std::atomic<uint64_t> g_kernel_launches{0};
+thread_local bool g_capturing = false;
+
+namespace {
+__global__ void to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
+    size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
+}
+}  // namespace
+
+DeviceModel* upload_model(const gradb_model_desc& desc_in, const float* const* tensors, int n_tensors, int device,
+                          int precision) {
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        throw Error(GRADB_ERR_NO_DEVICE, "no CUDA device available; this library has no CPU path");
+    }
+    if (device < 0 || device >= ndev) throw Error(GRADB_ERR_INVALID, "device index out of range");
+    if (precision != GRADB_FP32 && precision != GRADB_BF16) throw Error(GRADB_ERR_INVALID, "unknown precision mode");
+    gradb_model_desc desc = desc_in;
+    const bool modern = desc.arch == GRADB_ARCH_MODERN;
+    desc.d_ff = resolve_d_ff(desc.d_model, modern);
+    const int d = desc.d_model, hs = d / desc.num_heads;
+    if (d % 4 != 0 || desc.d_ff % 4 != 0) throw Error(GRADB_ERR_INVALID, "d_model must be a multiple of 4");
+    if (hs % 2 != 0 || hs > 256) throw Error(GRADB_ERR_INVALID, "head size must be even and at most 256");
+    const std::vector<TensorShape> shapes = tensor_shapes(desc);
+    if ((int)shapes.size() != n_tensors) throw Error(GRADB_ERR_INVALID, "wrong tensor count for this model shape");
+
+    GRADB_CUDA(cudaSetDevice(device));
+    auto* m = new DeviceModel();
+    try {
+        m->desc = desc;
+        m->device = device;
+        m->precision = precision;
+        cudaDeviceProp prop{};
+        GRADB_CUDA(cudaGetDeviceProperties(&prop, device));
+        m->sm_count = prop.multiProcessorCount;
+
+        // Every tensor starts on a 256-byte boundary so vector loads and bulk copies are aligned.
+        size_t total = 0;
+        m->offsets.resize(shapes.size());
+        for (size_t i = 0; i < shapes.size(); i++) {
+            m->offsets[i] = total;
+            total += ((size_t)shapes[i].rows * shapes[i].cols + 63) / 64 * 64;
+        }
+        GRADB_CUDA(cudaMalloc(&m->blob, total * sizeof(float)));
+        for (size_t i = 0; i < shapes.size(); i++) {
+            GRADB_CUDA(cudaMemcpy(m->blob + m->offsets[i], tensors[i],
+                                  sizeof(float) * (size_t)shapes[i].rows * shapes[i].cols, cudaMemcpyHostToDevice));
+        }
+        if (precision == GRADB_BF16) {
+            GRADB_CUDA(cudaMalloc(&m->blob16, total * sizeof(__nv_bfloat16)));
+            to_bf16_kernel<<<1024, 256>>>(m->blob, m->blob16, total);
+            count_launch();
+            GRADB_CUDA(cudaGetLastError());
+        }
+        const TensorIndex ix = tensor_index(desc);
+        auto P = [&](int i) -> const float* { return i < 0 ? nullptr : m->blob + m->offsets[i]; };
+        auto H = [&](int i) -> const __nv_bfloat16* {
+            return (i < 0 || !m->blob16) ? nullptr : m->blob16 + m->offsets[i];
+        };
+        m->emb = P(ix.emb);
+        m->emb16 = H(ix.emb);
+        m->pos = P(ix.pos);
+        m->fng = P(ix.final_g);
+        m->fnb = P(ix.final_b);
+        m->layers.resize(desc.num_layers);
+        for (int l = 0; l < desc.num_layers; l++) {
+            const int b = ix.layer0 + l * ix.per_layer;
+            auto at = [&](int o) { return o < 0 ? -1 : b + o; };
+            LayerWeights& w = m->layers[l];
+            w.wq = P(at(ix.wq)); w.wk = P(at(ix.wk)); w.wv = P(at(ix.wv)); w.wo = P(at(ix.wo));
+            w.bq = P(at(ix.bq)); w.bk = P(at(ix.bk)); w.bv = P(at(ix.bv)); w.bo = P(at(ix.bo));
+            w.gate = P(at(ix.gate)); w.w1 = P(at(ix.w1)); w.b1 = P(at(ix.b1));
+            w.w2 = P(at(ix.w2)); w.b2 = P(at(ix.b2));
+            w.n1g = P(at(ix.n1g)); w.n1b = P(at(ix.n1b)); w.n2g = P(at(ix.n2g)); w.n2b = P(at(ix.n2b));
+            w.wq16 = H(at(ix.wq)); w.wk16 = H(at(ix.wk)); w.wv16 = H(at(ix.wv)); w.wo16 = H(at(ix.wo));
+            w.gate16 = H(at(ix.gate)); w.w116 = H(at(ix.w1)); w.w216 = H(at(ix.w2));
+        }
+        if (modern) {
+            // RoPE angles, computed with the reference's own float expressions
+            // (inference.cpp:169-175) on the host so that cos/sin bits are libm's.
+            const int half = hs / 2;
+            std::vector<float> c((size_t)desc.max_len * half), s((size_t)desc.max_len * half);
+            for (int p = 0; p < desc.max_len; p++) {
+                for (int j = 0; j < half; j++) {
+                    const float theta = std::pow(10000.0f, -2.0f * static_cast<float>(j) / static_cast<float>(hs));
+                    c[(size_t)p * half + j] = std::cos(static_cast<float>(p) * theta);
+                    s[(size_t)p * half + j] = std::sin(static_cast<float>(p) * theta);
+                }
+            }
+            GRADB_CUDA(cudaMalloc(&m->rope_cos, c.size() * sizeof(float)));
+            GRADB_CUDA(cudaMalloc(&m->rope_sin, s.size() * sizeof(float)));
+            GRADB_CUDA(cudaMemcpy(m->rope_cos, c.data(), c.size() * sizeof(float), cudaMemcpyHostToDevice));
+            GRADB_CUDA(cudaMemcpy(m->rope_sin, s.data(), s.size() * sizeof(float), cudaMemcpyHostToDevice));
+        }
+        GRADB_CUDA(cudaDeviceSynchronize());
+        return m;
+    } catch (...) {
+        free_model(m);
+        throw;
+    }
+}
+
+void free_model(DeviceModel* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    cudaFree(m->blob);
+    cudaFree(m->blob16);
+    cudaFree(m->rope_cos);
+    cudaFree(m->rope_sin);
+    delete m;
+}
+
+}  // namespace gradb

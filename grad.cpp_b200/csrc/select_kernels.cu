@@ -1,0 +1,454 @@
+// The selection stage of TextGen on the device: repetition penalty, greedy
+// argmax, and sample_from_logits (temperature, top-k, softmax, top-p, draw).
+// Reference: src/transformer/text_gen.cpp:14-33, 52-60, 135-209 and
+// Tensor::softmax, src/transformer/tensor.cpp:421-452.
+//
+// The goal is the reference's result bit for bit on identical logits and
+// draws, which constrains three things:
+//  * exp must return libm's expf bits. The host libm (glibc) implements the
+//    published table-driven algorithm (32-entry 2^(i/32) table, cubic
+//    polynomial, evaluated in double); expf_libm below restates it with
+//    non-contracted IEEE double operations.
+//  * the sums the reference accumulates sequentially in fp32 (softmax
+//    denominator, top-p running sum in sorted order, kept mass, draw scan) are
+//    order dependent. seq_scan below reproduces the sequential result exactly
+//    with a block-wide scan: inside one binade the running sum is an integer
+//    count of ulps, so "round(a/ulp)" increments compose associatively; the
+//    scan restarts whenever the sum enters the next binade.
+//  * the quirks are kept: ties at the top-k / top-p thresholds survive, the
+//    -1e10 sentinel, cutoff index 0 when the running sum never reaches p,
+//    the last id when the draw exceeds the total mass.
+#include "select_kernels.cuh"
+
+#include "exact_sum.h"
+
+namespace gradb {
+
+namespace {
+
+constexpr int kSelThreads = 1024;
+constexpr int kSelWarps = kSelThreads / 32;
+
+// 2^(i/32) as IEEE double bits with i<<47 subtracted, so that adding ki<<47
+// both selects the binade and restores the entry (the usual trick of the
+// published algorithm).
+__constant__ uint64_t c_exp2_tab[32] = {
+    0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
+    0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
+    0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull,
+    0x3feebfdad5362a27ull, 0x3feeb42b569d4f82ull, 0x3feeab07dd485429ull, 0x3feea47eb03a5585ull,
+    0x3feea09e667f3bcdull, 0x3fee9f75e8ec5f74ull, 0x3feea11473eb0187ull, 0x3feea589994cce13ull,
+    0x3feeace5422aa0dbull, 0x3feeb737b0cdc5e5ull, 0x3feec49182a3f090ull, 0x3feed503b23e255dull,
+    0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull,
+    0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull};
+
+// expf with the bits of the host C library's, for finite x <= ~88.
+__device__ __forceinline__ float expf_libm(float x) {
+    if (x < -0x1.9fe368p6f) return 0.0f;     // underflows to zero (also -inf, -1e10 - max)
+    if (x != x) return x;
+    if (x > 0x1.62e42ep6f) return INFINITY;
+    const double InvLn2N = 0x1.71547652b82fep+0 * 32.0;
+    const double Shift = 0x1.8p52;
+    const double C0 = 0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0;
+    const double C1 = 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0;
+    const double C2 = 0x1.62e42ff0c52d6p-1 / 32.0;
+    const double xd = (double)x;
+    double z = __dmul_rn(InvLn2N, xd);
+    double kd = __dadd_rn(z, Shift);
+    const uint64_t ki = (uint64_t)__double_as_longlong(kd);
+    kd = __dsub_rn(kd, Shift);
+    const double r = __dsub_rn(z, kd);
+    const uint64_t t = c_exp2_tab[ki & 31] + (ki << 47);
+    const double s = __longlong_as_double((long long)t);
+    z = __dadd_rn(__dmul_rn(C0, r), C1);
+    const double r2 = __dmul_rn(r, r);
+    double y = __dadd_rn(__dmul_rn(C2, r), 1.0);
+    y = __dadd_rn(__dmul_rn(z, r2), y);
+    y = __dmul_rn(y, s);
+    return __double2float_rn(y);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ---------------------------------------------------------------------------
+// Exact sequential fp32 accumulation of non-negative terms, in parallel.
+//
+// The reference computes s = fl(s + a[i]) for i = 0, 1, 2, ... While s stays in
+// one binade [2^e, 2^(e+1)) it is an integer multiple S of u = 2^(e-23), and
+// fl(s + a) = (S + inc) * u with inc = a/u rounded to nearest, ties resolved
+// towards an even S + inc. Only a tie looks at the running sum, and only at
+// its parity, so each term acts on (S mod 2) as a map parity -> increment, and
+// maps compose associatively: a prefix scan gives every running sum. The scan
+// is valid up to the first term that lifts the sum out of the binade; that
+// term is added natively and the scan restarts in the new binade.
+//
+// Thread t owns terms [t*per, (t+1)*per). `term(i)` yields a[i]. Stops early
+// at the first index whose running sum s satisfies `hit(s)`.
+struct ScanResult {
+    float sum;   // running sum after the last term consumed
+    int hit;     // first index whose running sum satisfied the predicate, or n
+};
+
+// sh: room for kSelWarps IncPair.
+template <typename Term, typename Hit>
+__device__ ScanResult seq_scan(int n, Term term, Hit hit, uint32_t* sh) {
+    __shared__ float s_sum;
+    __shared__ int s_next, s_hit, s_stop;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    IncPair* wtot = reinterpret_cast<IncPair*>(sh);
+    if (tid == 0) {
+        s_sum = 0.0f;
+        s_next = 0;
+        s_hit = n;
+        s_stop = n;
+    }
+    __syncthreads();
+    // Every pass consumes at least one term, so the bound is never the exit in practice.
+    for (int guard = 0; guard < 8192; guard++) {
+        const int start = s_next;
+        const float s0 = s_sum;
+        if (start >= n || s_hit < n) break;
+        const int per = (n - start + kSelThreads - 1) / kSelThreads;
+        const int beg = min(n, start + tid * per), end = min(n, beg + per);
+        const uint32_t sb = __float_as_uint(s0);
+        const int sex = (int)(sb >> 23);
+
+        if (s0 == 0.0f) {
+            // Zeros leave the sum at zero: jump to the first non-zero term.
+            if (hit(0.0f)) {
+                if (tid == 0) s_hit = start;
+                __syncthreads();
+                break;
+            }
+            int first = n;
+            for (int i = beg; i < end; i++) {
+                if (term(i) != 0.0f) {
+                    first = i;
+                    break;
+                }
+            }
+            if (first < n) atomicMin(&s_stop, first);
+            __syncthreads();
+            if (tid == 0) {
+                const int j = s_stop;
+                s_stop = n;
+                if (j >= n) {
+                    s_next = n;
+                } else {
+                    const float v = term(j);
+                    s_sum = v;
+                    s_next = j + 1;
+                    if (hit(v)) s_hit = j;
+                }
+            }
+            __syncthreads();
+            continue;
+        }
+        if (sex < 30 || sex >= 254) {
+            // Tiny or huge running sum: add a stretch natively.
+            if (tid == 0) {
+                float s = s0;
+                int i = start;
+                const int stop = min(n, start + 64);
+                while (i < stop) {
+                    s = __fadd_rn(s, term(i));
+                    i++;
+                    if (hit(s)) {
+                        s_hit = i - 1;
+                        break;
+                    }
+                    const int e2 = (int)(__float_as_uint(s) >> 23);
+                    if (e2 >= 30 && e2 < 254) break;
+                }
+                s_sum = s;
+                s_next = i;
+            }
+            __syncthreads();
+            continue;
+        }
+
+        const int ue = sex - 150;                          // u = 2^(sex-127-23)
+        const uint32_t S0 = (sb & 0x7fffffu) | 0x800000u;  // s0 = S0 * u
+        IncPair loc = {0u, 0u};
+        for (int i = beg; i < end; i++) loc = compose(loc, term_inc(__float_as_uint(term(i)), ue));
+        // inclusive scan of the per-thread maps across the warp, then across warps
+        IncPair inc = loc;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            IncPair prev;
+            prev.e = __shfl_up_sync(0xffffffffu, inc.e, o);
+            prev.o = __shfl_up_sync(0xffffffffu, inc.o, o);
+            if (lane >= o) inc = compose(prev, inc);
+        }
+        if (lane == 31) wtot[w] = inc;
+        __syncthreads();
+        IncPair ahead = {0u, 0u};  // everything before this warp
+        for (int i = 0; i < w; i++) ahead = compose(ahead, wtot[i]);
+        {
+            IncPair pl;  // everything before this lane inside the warp
+            pl.e = __shfl_up_sync(0xffffffffu, inc.e, 1);
+            pl.o = __shfl_up_sync(0xffffffffu, inc.o, 1);
+            if (lane == 0) pl.e = pl.o = 0u;
+            ahead = compose(ahead, pl);
+        }
+        // Walk this thread's terms from its now-known starting S.
+        uint32_t S = step_S(S0, ahead);
+        int my_stop = n;  // where this thread wants the pass to stop
+        int my_kind = 0;  // 1: predicate holds after term my_stop; 2: term my_stop leaves the binade
+        if (S < kBinadeEnd) {
+            for (int i = beg; i < end; i++) {
+                const uint32_t Sn = step_S(S, term_inc(__float_as_uint(term(i)), ue));
+                if (Sn >= kBinadeEnd) {
+                    my_stop = i;
+                    my_kind = 2;
+                    break;
+                }
+                S = Sn;
+                if (hit(__uint_as_float(((uint32_t)sex << 23) | (S & 0x7fffffu)))) {
+                    my_stop = i;
+                    my_kind = 1;
+                    break;
+                }
+            }
+        }
+        if (my_kind != 0) atomicMin(&s_stop, my_stop);
+        __syncthreads();
+        const int stop = s_stop;
+        __syncthreads();
+        const float sv = __uint_as_float(((uint32_t)sex << 23) | (S & 0x7fffffu));
+        if (stop < n) {
+            if (my_kind != 0 && my_stop == stop) {  // exactly one thread owns that term
+                s_stop = n;
+                s_next = stop + 1;
+                if (my_kind == 1) {
+                    s_hit = stop;
+                    s_sum = sv;
+                } else {
+                    const float s2 = __fadd_rn(sv, term(stop));  // into the next binade, natively
+                    s_sum = s2;
+                    if (hit(s2)) s_hit = stop;
+                }
+            }
+        } else if (end == n && beg < end) {  // the owner of the last term holds the total
+            s_sum = sv;
+            s_next = n;
+        }
+        __syncthreads();
+    }
+    ScanResult r;
+    r.sum = s_sum;
+    r.hit = s_hit;
+    __syncthreads();
+    return r;
+}
+
+// Bitonic sort, descending, of n_pad (power of two) floats in shared memory.
+__device__ void sort_desc(float* a, int n_pad) {
+    for (int k = 2; k <= n_pad; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < n_pad; i += blockDim.x) {
+                const int ixj = i ^ j;
+                if (ixj > i) {
+                    const float x = a[i], y = a[ixj];
+                    const bool desc = (i & k) == 0;
+                    if (desc ? (x < y) : (x > y)) {
+                        a[i] = y;
+                        a[ixj] = x;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams p) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ uint32_t scan_sh[2 * kSelWarps + 4];
+    __shared__ float red_v[kSelWarps];
+    __shared__ int red_i[kSelWarps];
+    __shared__ int s_pick;
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int V = p.V;
+    if (p.loop_mode && p.done[b]) return;
+
+    float* x = smem;           // [V]
+    float* sorted = smem + V;  // [n_pad]
+    const float* lg = p.logits + (size_t)b * V;
+    for (int i = tid; i < V; i += kSelThreads) x[i] = lg[i];
+    __syncthreads();
+
+    // ---- repetition penalty: last min(50, n) ids, once per occurrence, in order (text_gen.cpp:20-31)
+    int* hist = p.hist + (size_t)b * p.hist_stride;
+    const int hlen = p.hist_len[b];
+    if (p.penalty != 1.0f && tid == 0) {
+        const int window = min(kPenaltyWindow, hlen);
+        for (int k = hlen - window; k < hlen; k++) {
+            const int id = hist[k];
+            if (x[id] > 0) x[id] = __fdiv_rn(x[id], p.penalty);
+            else x[id] = __fmul_rn(x[id], p.penalty);
+        }
+    }
+    __syncthreads();
+
+    int pick = 0;
+    if (p.greedy) {
+        // first index of the maximum, strict > (text_gen.cpp:52-60)
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = tid; i < V; i += kSelThreads) {
+            const float v = x[i];
+            if (v > bv || (v == bv && i < bi)) {
+                bv = v;
+                bi = i;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) {
+            red_v[w] = bv;
+            red_i[w] = bi;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            for (int i = 1; i < kSelWarps; i++) {
+                if (red_v[i] > bv || (red_v[i] == bv && red_i[i] < bi)) {
+                    bv = red_v[i];
+                    bi = red_i[i];
+                }
+            }
+            // a NaN in slot 0 is never displaced by the reference's comparison
+            s_pick = (x[0] != x[0] || bi == 0x7fffffff) ? 0 : bi;
+        }
+        __syncthreads();
+        pick = s_pick;
+    } else {
+        const float inv_t = __fdiv_rn(1.0f, p.temperature);  // text_gen.cpp:136
+        const bool use_k = p.top_k > 0 && p.top_k < V;
+        const bool use_p = p.top_p < 1.0f;
+        const int n_pad = p.n_pad;
+        for (int i = tid; i < V; i += kSelThreads) x[i] = __fmul_rn(x[i], inv_t);
+        __syncthreads();
+        float kth = -INFINITY;
+        float mx;
+        if (use_k || use_p) {
+            for (int i = tid; i < n_pad; i += kSelThreads) sorted[i] = i < V ? x[i] : -INFINITY;
+            __syncthreads();
+            sort_desc(sorted, n_pad);
+            mx = sorted[0];
+            if (use_k) {  // text_gen.cpp:138-154: below the k-th largest value -> -1e10, ties kept
+                kth = sorted[p.top_k - 1];
+                for (int i = tid; i < V; i += kSelThreads) {
+                    if (x[i] < kth) x[i] = -1e10f;
+                }
+            }
+        } else {
+            float m = -INFINITY;
+            for (int i = tid; i < V; i += kSelThreads) m = fmaxf(m, x[i]);
+            m = warp_max(m);
+            if (lane == 0) red_v[w] = m;
+            __syncthreads();
+            m = red_v[0];
+            for (int i = 1; i < kSelWarps; i++) m = fmaxf(m, red_v[i]);
+            mx = m;
+        }
+        __syncthreads();
+        // softmax (tensor.cpp:434-448): exp(x - max), sequential sum in index order, times 1/sum
+        for (int i = tid; i < V; i += kSelThreads) x[i] = expf_libm(__fsub_rn(x[i], mx));
+        __syncthreads();
+        const ScanResult den = seq_scan(V, [&](int i) { return x[i]; }, [](float) { return false; }, scan_sh);
+        const float inv_sum = __fdiv_rn(1.0f, den.sum);
+        for (int i = tid; i < V; i += kSelThreads) x[i] = __fmul_rn(x[i], inv_sum);
+        __syncthreads();
+
+        if (use_p) {  // text_gen.cpp:158-193
+            // The sorted probabilities are the same map applied to the sorted logits (it is monotone).
+            for (int i = tid; i < V; i += kSelThreads) {
+                float v = sorted[i];
+                if (use_k && v < kth) v = -1e10f;
+                sorted[i] = __fmul_rn(expf_libm(__fsub_rn(v, mx)), inv_sum);
+            }
+            __syncthreads();
+            const float top_p = p.top_p;
+            const ScanResult cut = seq_scan(V, [&](int i) { return sorted[i]; },
+                                            [top_p](float s) { return s >= top_p; }, scan_sh);
+            const int cutoff = cut.hit < V ? cut.hit : 0;  // never reached: index stays 0
+            const float cutoff_prob = sorted[cutoff];
+            __syncthreads();
+            for (int i = tid; i < V; i += kSelThreads) {
+                if (x[i] < cutoff_prob) x[i] = 0.0f;
+            }
+            __syncthreads();
+            const ScanResult kept = seq_scan(V, [&](int i) { return x[i]; }, [](float) { return false; }, scan_sh);
+            if (kept.sum > 0.0f) {
+                const float tk = kept.sum;
+                for (int i = tid; i < V; i += kSelThreads) x[i] = __fdiv_rn(x[i], tk);
+            }
+            __syncthreads();
+        }
+        if (p.probs_out) {
+            for (int i = tid; i < V; i += kSelThreads) p.probs_out[(size_t)b * V + i] = x[i];
+        }
+        // draw (text_gen.cpp:199-208): first index with u <= running sum, else the last id
+        const float u = p.uniforms[(size_t)b * p.u_stride + (p.loop_mode ? p.gen[b] : 0)];
+        const ScanResult dr = seq_scan(V, [&](int i) { return x[i]; }, [u](float s) { return u <= s; }, scan_sh);
+        pick = dr.hit < V ? dr.hit : V - 1;
+    }
+
+    if (tid == 0) {
+        if (hlen < p.hist_stride) hist[hlen] = pick;
+        p.hist_len[b] = hlen + 1;
+        if (p.out_tok) p.out_tok[b] = pick;
+        if (p.loop_mode) {
+            // text_gen.cpp:48-63: push the id, stop when the context is full or max_tokens ids were emitted
+            const int g = p.gen[b] + 1;
+            p.gen[b] = g;
+            const bool stop = p.pos[b] >= p.capacity || g >= p.max_new;
+            p.cur_tok[b] = stop ? kSkip : pick;
+            if (stop) p.done[b] = 1;
+        }
+    }
+}
+
+}  // namespace
+
+size_t select_smem_bytes(int V, int* n_pad_out) {
+    int n_pad = 1;
+    while (n_pad < V) n_pad <<= 1;
+    if (n_pad_out) *n_pad_out = n_pad;
+    return ((size_t)V + n_pad) * sizeof(float);
+}
+
+void configure_select(int V) {
+    const size_t bytes = select_smem_bytes(V, nullptr);
+    if (bytes > 48 * 1024 && bytes <= 200 * 1024) {
+        GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    }
+}
+
+void launch_select(const SelectParams& p_in, int B, cudaStream_t st) {
+    SelectParams p = p_in;
+    const size_t bytes = select_smem_bytes(p.V, &p.n_pad);
+    if (bytes > 200 * 1024) {
+        throw Error(GRADB_ERR_INVALID, "vocabulary too large for the on-device selection stage (limit ~24k ids)");
+    }
+    if (bytes > 48 * 1024 && !g_capturing) {
+        GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    }
+    select_kernel<<<B, kSelThreads, bytes, st>>>(p);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+}  // namespace gradb

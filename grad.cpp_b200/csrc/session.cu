@@ -1,0 +1,589 @@
+#include "session.cuh"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+
+namespace gradb {
+
+namespace {
+
+template <typename T>
+void dalloc(T** p, size_t n) {
+    GRADB_CUDA(cudaMalloc(reinterpret_cast<void**>(p), std::max<size_t>(n, 1) * sizeof(T)));
+}
+
+size_t layer_cache_elems(const Session* s) { return (size_t)s->B * s->H * s->T * s->hs; }
+
+// Brackets one launch with events when profiling is on.
+struct Timed {
+    Session* s;
+    int idx = -1;
+    Timed(Session* s_, int cls) : s(s_) {
+        if (!s->profiling || g_capturing) return;
+        auto take = [&] {
+            cudaEvent_t e;
+            if (s->event_pool.empty()) {
+                GRADB_CUDA(cudaEventCreate(&e));
+            } else {
+                e = s->event_pool.back();
+                s->event_pool.pop_back();
+            }
+            return e;
+        };
+        Session::Span sp{cls, take(), take()};
+        cudaEventRecord(sp.a, s->stream);
+        idx = (int)s->spans.size();
+        s->spans.push_back(sp);
+    }
+    ~Timed() {
+        if (idx >= 0) cudaEventRecord(s->spans[idx].b, s->stream);
+    }
+};
+
+// After a stream synchronise: fold the recorded spans into per-class totals.
+void collect_spans(Session* s) {
+    for (const Session::Span& sp : s->spans) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) {
+            s->class_ms[sp.cls] += ms;
+            s->class_launches[sp.cls] += 1;
+        }
+        s->event_pool.push_back(sp.a);
+        s->event_pool.push_back(sp.b);
+    }
+    s->spans.clear();
+}
+
+// Enqueues one decode step for rows 0..n_seq-1. tok_dev: current ids (<0 = skip row).
+// logit_tok_dev: same convention, selects which rows get logits (the prompt feed
+// only needs them at each sequence's last position).
+void enqueue_step(Session* s, int n_seq, const int* tok_dev, const int* logit_tok_dev, bool append_history) {
+    const DeviceModel* m = s->m;
+    const bool modern = m->desc.arch == GRADB_ARCH_MODERN;
+    const bool bf16 = m->precision == GRADB_BF16;
+    cudaStream_t st = s->stream;
+    {
+        Timed t(s, KC_EMBED);
+        launch_embed(m->emb, modern ? nullptr : m->pos, tok_dev, s->pos, s->x, s->d, n_seq, st);
+    }
+    const int pro = modern ? PRO_RMSNORM : PRO_LAYERNORM;
+    for (int l = 0; l < s->L; l++) {
+        const LayerWeights& w = m->layers[l];
+        GemvParams g{};
+        g.tok = tok_dev;
+        g.pos = s->pos;
+        g.B = n_seq;
+        g.eps = 1e-5f;  // layer_norm.h:18
+        // norm1 + Q/K/V projections (+ RoPE), K and V rows go straight into the cache
+        g.X = s->x; g.ldx = s->d; g.K = s->d; g.N = s->d;
+        g.W[0] = bf16 ? (const void*)w.wq16 : w.wq;
+        g.W[1] = bf16 ? (const void*)w.wk16 : w.wk;
+        g.W[2] = bf16 ? (const void*)w.wv16 : w.wv;
+        g.bias[0] = w.bq; g.bias[1] = w.bk; g.bias[2] = w.bv;
+        g.gamma = w.n1g; g.beta = w.n1b;
+        g.Y = s->q; g.ldy = s->d;
+        g.kcache = s->kcache + (size_t)l * layer_cache_elems(s);
+        g.vcache = s->vcache + (size_t)l * layer_cache_elems(s);
+        g.rope_cos = modern ? m->rope_cos : nullptr;
+        g.rope_sin = modern ? m->rope_sin : nullptr;
+        g.H = s->H; g.hs = s->hs; g.T = s->T;
+        {
+            Timed t(s, KC_QKV);
+            launch_gemv(g, pro, EPI_QKV, bf16, m->sm_count, st);
+        }
+
+        AttnParams a{};
+        a.q = s->q; a.kcache = g.kcache; a.vcache = g.vcache; a.tok = tok_dev; a.pos = s->pos;
+        a.out = s->attn; a.partial = s->attn_partial; a.counters = s->attn_counters;
+        a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = s->d;
+        a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));  // inference.cpp:184
+        {
+            Timed t(s, KC_ATTN);
+            launch_attention(a, n_seq, s->attn_splits, st);
+        }
+
+        // x += attn @ Wo + bo
+        GemvParams o = g;
+        o.X = s->attn; o.K = s->d; o.N = s->d;
+        o.W[0] = bf16 ? (const void*)w.wo16 : w.wo;
+        o.bias[0] = w.bo;
+        o.Y = s->x; o.ldy = s->d;
+        {
+            Timed t(s, KC_OPROJ);
+            launch_gemv(o, PRO_NONE, EPI_RESID, bf16, m->sm_count, st);
+        }
+
+        // norm2 + FFN
+        GemvParams u = g;
+        u.X = s->x; u.K = s->d; u.N = s->dff;
+        u.gamma = w.n2g; u.beta = w.n2b;
+        u.Y = s->ffn; u.ldy = s->dff;
+        GemvParams dn = g;
+        dn.X = s->ffn; dn.ldx = s->dff; dn.K = s->dff; dn.N = s->d;
+        dn.W[0] = bf16 ? (const void*)w.w216 : w.w2;
+        dn.Y = s->x; dn.ldy = s->d;
+        if (modern) {
+            u.W[0] = bf16 ? (const void*)w.gate16 : w.gate;
+            u.W[1] = bf16 ? (const void*)w.w116 : w.w1;
+            u.bias[0] = u.bias[1] = nullptr;
+            {
+                Timed t(s, KC_FFN_UP);
+                launch_gemv(u, PRO_RMSNORM, EPI_SWIGLU, bf16, m->sm_count, st);
+            }
+            dn.bias[0] = nullptr;
+        } else {
+            u.W[0] = bf16 ? (const void*)w.w116 : w.w1;
+            u.bias[0] = w.b1;
+            {
+                Timed t(s, KC_FFN_UP);
+                launch_gemv(u, PRO_LAYERNORM, EPI_GELU, bf16, m->sm_count, st);
+            }
+            dn.bias[0] = w.b2;
+        }
+        {
+            Timed t(s, KC_FFN_DOWN);
+            launch_gemv(dn, PRO_NONE, EPI_RESID, bf16, m->sm_count, st);
+        }
+    }
+    LogitsParams lp{};
+    lp.X = s->x;
+    lp.E = bf16 ? (const void*)m->emb16 : m->emb;
+    lp.gamma = m->fng; lp.beta = m->fnb; lp.eps = 1e-5f; lp.rms = modern;
+    lp.tok = logit_tok_dev; lp.logits = s->logits;
+    lp.B = n_seq; lp.d = s->d; lp.V = s->V;
+    {
+        Timed t(s, KC_LOGITS);
+        launch_logits(lp, bf16, st);
+    }
+    Timed t(s, KC_ADVANCE);
+    launch_advance(tok_dev, s->pos, append_history ? s->hist : nullptr, s->hist_len, s->hist_stride, n_seq, st);
+}
+
+SelectParams make_select(Session* s, const gradb_sampling& sp) {
+    SelectParams p{};
+    p.logits = s->logits;
+    p.V = s->V;
+    p.greedy = sp.greedy;
+    p.temperature = sp.temperature;
+    p.penalty = sp.repetition_penalty;
+    p.top_k = sp.top_k;
+    p.top_p = sp.top_p;
+    p.uniforms = s->uniforms;
+    p.u_stride = 1;
+    p.hist = s->hist;
+    p.hist_stride = s->hist_stride;
+    p.hist_len = s->hist_len;
+    p.out_tok = s->out_tok;
+    p.gen = s->gen;
+    p.cur_tok = s->tok;
+    p.done = s->done;
+    p.pos = s->pos;
+    p.capacity = s->T;
+    return p;
+}
+
+void ensure_uniforms(Session* s, size_t n) {
+    if (n > s->uniforms_cap) {
+        cudaFree(s->uniforms);
+        s->uniforms = nullptr;
+        dalloc(&s->uniforms, n);
+        s->uniforms_cap = n;
+    }
+}
+
+void validate_sampling(const gradb_sampling& sp) {
+    if (!sp.greedy && !(sp.temperature > 0.0f)) throw Error(GRADB_ERR_INVALID, "temperature must be positive");
+}
+
+// Token matrix for the prompt feed: row t holds token t of every sequence (or
+// kSkip once a prompt is exhausted), followed by the row that says which
+// sequences need logits at step t (their last prompt position).
+int upload_prompt_matrix(Session* s, const int32_t* tokens, const int32_t* offsets, int n_seq) {
+    int steps = 0;
+    for (int b = 0; b < n_seq; b++) {
+        const int len = offsets[b + 1] - offsets[b];
+        if (len < 0) throw Error(GRADB_ERR_INVALID, "prompt offsets must be non-decreasing");
+        if (s->h_pos[b] + len > s->T) {
+            throw Error(GRADB_ERR_CONTEXT_FULL, "InferenceSession: context exceeds max_len");
+        }
+        for (int i = offsets[b]; i < offsets[b + 1]; i++) {
+            if (tokens[i] < 0 || tokens[i] >= s->V) {
+                throw Error(GRADB_ERR_BAD_TOKEN, "InferenceSession: token id out of vocab range");
+            }
+        }
+        steps = std::max(steps, len);
+    }
+    const size_t need = (size_t)steps * 2 * n_seq;
+    if (need > s->tok_matrix_cap) {
+        cudaFree(s->tok_matrix);
+        s->tok_matrix = nullptr;
+        dalloc(&s->tok_matrix, need);
+        s->tok_matrix_cap = need;
+    }
+    std::vector<int> host(need, kSkip);
+    for (int b = 0; b < n_seq; b++) {
+        const int len = offsets[b + 1] - offsets[b];
+        for (int t = 0; t < len; t++) {
+            host[(size_t)t * 2 * n_seq + b] = tokens[offsets[b] + t];
+            if (t == len - 1) host[(size_t)t * 2 * n_seq + n_seq + b] = tokens[offsets[b] + t];
+        }
+    }
+    if (need) {
+        GRADB_CUDA(cudaMemcpyAsync(s->tok_matrix, host.data(), need * sizeof(int), cudaMemcpyHostToDevice, s->stream));
+        GRADB_CUDA(cudaStreamSynchronize(s->stream));  // host vector goes out of scope
+    }
+    return steps;
+}
+
+void enqueue_prompt_feed(Session* s, int steps, int n_seq) {
+    for (int t = 0; t < steps; t++) {
+        const int* row = s->tok_matrix + (size_t)t * 2 * n_seq;
+        enqueue_step(s, n_seq, row, row + n_seq, true);
+    }
+}
+
+}  // namespace
+
+Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* stream) {
+    if (!m) throw Error(GRADB_ERR_INVALID, "null model");
+    if (max_batch < 1 || max_batch > 65535) throw Error(GRADB_ERR_INVALID, "max_batch must be in [1, 65535]");
+    if (max_len == 0) max_len = m->desc.max_len;
+    if (max_len < 1 || max_len > m->desc.max_len) {
+        throw Error(GRADB_ERR_INVALID, "session max_len must be in [1, model max_len]");
+    }
+    GRADB_CUDA(cudaSetDevice(m->device));
+    auto* s = new Session();
+    try {
+        s->m = m;
+        s->B = max_batch;
+        s->T = max_len;
+        s->V = m->desc.vocab_size;
+        s->d = m->desc.d_model;
+        s->H = m->desc.num_heads;
+        s->hs = s->d / s->H;
+        s->dff = m->desc.d_ff;
+        s->L = m->desc.num_layers;
+        s->hist_stride = s->T + 2;
+        if (stream) {
+            s->stream = static_cast<cudaStream_t>(stream);
+        } else {
+            GRADB_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+            s->own_stream = true;
+        }
+        const char* ng = std::getenv("GRADB_NO_GRAPH");
+        s->use_graph = !(ng && ng[0] == '1');
+        // Enough attention CTAs to cover the SMs about twice, at most 16 splits of the context.
+        const int want = (2 * m->sm_count + s->B * s->H - 1) / (s->B * s->H);
+        s->attn_splits = std::max(1, std::min({want, 16, (s->T + 31) / 32}));
+        const size_t B = s->B;
+        dalloc(&s->x, B * s->d);
+        dalloc(&s->q, B * s->d);
+        dalloc(&s->attn, B * s->d);
+        dalloc(&s->ffn, B * s->dff);
+        dalloc(&s->logits, B * s->V);
+        const size_t cache = (size_t)s->L * layer_cache_elems(s);
+        dalloc(&s->kcache, cache);
+        dalloc(&s->vcache, cache);
+        dalloc(&s->attn_partial, B * s->H * s->attn_splits * (s->hs + 2));
+        dalloc(&s->attn_counters, B * s->H);
+        dalloc(&s->tok, B);
+        dalloc(&s->pos, B);
+        dalloc(&s->hist, B * s->hist_stride);
+        dalloc(&s->hist_len, B);
+        dalloc(&s->gen, B);
+        dalloc(&s->done, B);
+        dalloc(&s->out_tok, B);
+        GRADB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&s->h_stage), sizeof(int) * 4 * B));
+        GRADB_CUDA(cudaEventCreate(&s->ev_begin));
+        GRADB_CUDA(cudaEventCreate(&s->ev_end));
+        s->h_pos.assign(B, 0);
+        // The reference zero-fills its caches at construction (inference.cpp:130-135).
+        GRADB_CUDA(cudaMemsetAsync(s->kcache, 0, cache * sizeof(float), s->stream));
+        GRADB_CUDA(cudaMemsetAsync(s->vcache, 0, cache * sizeof(float), s->stream));
+        GRADB_CUDA(cudaMemsetAsync(s->attn_counters, 0, B * s->H * sizeof(int), s->stream));
+        reset_session(s);
+        return s;
+    } catch (...) {
+        destroy_session(s);
+        throw;
+    }
+}
+
+void destroy_session(Session* s) {
+    if (!s) return;
+    cudaSetDevice(s->m->device);
+    if (s->stream) cudaStreamSynchronize(s->stream);
+    if (s->graph) cudaGraphExecDestroy(s->graph);
+    for (cudaEvent_t e : s->step_events) cudaEventDestroy(e);
+    for (cudaEvent_t e : s->event_pool) cudaEventDestroy(e);
+    for (const Session::Span& sp : s->spans) {
+        cudaEventDestroy(sp.a);
+        cudaEventDestroy(sp.b);
+    }
+    if (s->ev_begin) cudaEventDestroy(s->ev_begin);
+    if (s->ev_end) cudaEventDestroy(s->ev_end);
+    cudaFree(s->x); cudaFree(s->q); cudaFree(s->attn); cudaFree(s->ffn); cudaFree(s->logits);
+    cudaFree(s->kcache); cudaFree(s->vcache); cudaFree(s->attn_partial); cudaFree(s->attn_counters);
+    cudaFree(s->tok); cudaFree(s->pos); cudaFree(s->hist); cudaFree(s->hist_len);
+    cudaFree(s->gen); cudaFree(s->done); cudaFree(s->out_tok); cudaFree(s->tok_matrix);
+    cudaFree(s->uniforms); cudaFree(s->probs);
+    if (s->h_stage) cudaFreeHost(s->h_stage);
+    if (s->own_stream && s->stream) cudaStreamDestroy(s->stream);
+    delete s;
+}
+
+void reset_session(Session* s) {
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    const size_t B = s->B;
+    GRADB_CUDA(cudaMemsetAsync(s->pos, 0, B * sizeof(int), s->stream));
+    GRADB_CUDA(cudaMemsetAsync(s->hist_len, 0, B * sizeof(int), s->stream));
+    GRADB_CUDA(cudaMemsetAsync(s->gen, 0, B * sizeof(int), s->stream));
+    GRADB_CUDA(cudaMemsetAsync(s->done, 0, B * sizeof(int), s->stream));
+    GRADB_CUDA(cudaMemsetAsync(s->tok, 0xff, B * sizeof(int), s->stream));
+    std::fill(s->h_pos.begin(), s->h_pos.end(), 0);
+}
+
+void session_step(Session* s, const int32_t* tokens, int n_seq, float* logits_host) {
+    if (n_seq < 1 || n_seq > s->B) throw Error(GRADB_ERR_INVALID, "n_seq out of range for this session");
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    // Same order as the reference: context check, then the id range (inference.cpp:151-156).
+    for (int b = 0; b < n_seq; b++) {
+        if (tokens[b] < 0) continue;
+        if (s->h_pos[b] >= s->T) throw Error(GRADB_ERR_CONTEXT_FULL, "InferenceSession: context exceeds max_len");
+    }
+    for (int b = 0; b < n_seq; b++) {
+        if (tokens[b] >= s->V) throw Error(GRADB_ERR_BAD_TOKEN, "InferenceSession: token id out of vocab range");
+    }
+    for (int b = 0; b < n_seq; b++) s->h_stage[b] = tokens[b] < 0 ? kSkip : tokens[b];
+    GRADB_CUDA(cudaEventRecord(s->ev_begin, s->stream));
+    GRADB_CUDA(cudaMemcpyAsync(s->tok, s->h_stage, n_seq * sizeof(int), cudaMemcpyHostToDevice, s->stream));
+    enqueue_step(s, n_seq, s->tok, s->tok, true);
+    if (logits_host) {
+        GRADB_CUDA(cudaMemcpyAsync(logits_host, s->logits, (size_t)n_seq * s->V * sizeof(float),
+                                   cudaMemcpyDeviceToHost, s->stream));
+    }
+    GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+    collect_spans(s);
+    GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
+    for (int b = 0; b < n_seq; b++) {
+        if (tokens[b] >= 0) s->h_pos[b]++;
+    }
+}
+
+void session_prefill(Session* s, const int32_t* tokens, const int32_t* offsets, int n_seq, float* logits_host) {
+    if (n_seq < 1 || n_seq > s->B) throw Error(GRADB_ERR_INVALID, "n_seq out of range for this session");
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    const int steps = upload_prompt_matrix(s, tokens, offsets, n_seq);
+    GRADB_CUDA(cudaEventRecord(s->ev_begin, s->stream));
+    enqueue_prompt_feed(s, steps, n_seq);
+    GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
+    if (logits_host) {
+        GRADB_CUDA(cudaMemcpyAsync(logits_host, s->logits, (size_t)n_seq * s->V * sizeof(float),
+                                   cudaMemcpyDeviceToHost, s->stream));
+    }
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+    collect_spans(s);
+    GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
+    for (int b = 0; b < n_seq; b++) s->h_pos[b] += offsets[b + 1] - offsets[b];
+}
+
+void session_set_history(Session* s, int seq, const int32_t* ids, int n) {
+    if (seq < 0 || seq >= s->B || n < 0 || n > s->hist_stride) throw Error(GRADB_ERR_INVALID, "bad history");
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    GRADB_CUDA(cudaMemcpyAsync(s->hist + (size_t)seq * s->hist_stride, ids, n * sizeof(int), cudaMemcpyHostToDevice,
+                               s->stream));
+    GRADB_CUDA(cudaMemcpyAsync(s->hist_len + seq, &n, sizeof(int), cudaMemcpyHostToDevice, s->stream));
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+}
+
+void session_select(Session* s, const gradb_sampling& sp, const float* logits_host, const float* uniforms,
+                    int n_seq, int32_t* tokens_out, float* probs_host) {
+    if (n_seq < 1 || n_seq > s->B) throw Error(GRADB_ERR_INVALID, "n_seq out of range for this session");
+    validate_sampling(sp);
+    if (!sp.greedy && !uniforms) throw Error(GRADB_ERR_INVALID, "sampling needs one uniform draw per sequence");
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    if (logits_host) {
+        GRADB_CUDA(cudaMemcpyAsync(s->logits, logits_host, (size_t)n_seq * s->V * sizeof(float),
+                                   cudaMemcpyHostToDevice, s->stream));
+    }
+    ensure_uniforms(s, n_seq);
+    if (!sp.greedy) {
+        GRADB_CUDA(cudaMemcpyAsync(s->uniforms, uniforms, n_seq * sizeof(float), cudaMemcpyHostToDevice, s->stream));
+    }
+    SelectParams p = make_select(s, sp);
+    p.loop_mode = 0;
+    if (probs_host && !sp.greedy) {
+        if (!s->probs) dalloc(&s->probs, (size_t)s->B * s->V);
+        p.probs_out = s->probs;
+    }
+    launch_select(p, n_seq, s->stream);
+    GRADB_CUDA(cudaMemcpyAsync(tokens_out, s->out_tok, n_seq * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
+    if (p.probs_out) {
+        GRADB_CUDA(cudaMemcpyAsync(probs_host, s->probs, (size_t)n_seq * s->V * sizeof(float), cudaMemcpyDeviceToHost,
+                                   s->stream));
+    }
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+}
+
+void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets, int n_seq,
+                      const gradb_sampling& sp, int max_new, const float* uniforms, int32_t* out_ids,
+                      int out_stride, int32_t* out_len, float* step_ms, float* prefill_ms) {
+    if (n_seq < 1 || n_seq > s->B) throw Error(GRADB_ERR_INVALID, "n_seq out of range for this session");
+    if (max_new < 0) throw Error(GRADB_ERR_INVALID, "max_new must not be negative");
+    validate_sampling(sp);
+    if (!sp.greedy && max_new > 0 && !uniforms) {
+        throw Error(GRADB_ERR_INVALID, "sampling needs n_seq*max_new uniform draws");
+    }
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    reset_session(s);
+    // How many ids each sequence emits: max_new, or fewer when its context fills first; the id
+    // chosen when the context is full is still emitted (text_gen.cpp:61-63).
+    int emit_max = 0;
+    std::vector<int> emit(n_seq, 0);
+    for (int b = 0; b < n_seq; b++) {
+        const int len = offsets[b + 1] - offsets[b];
+        if (len <= 0) continue;  // empty prompt: nothing is generated (text_gen.cpp:40)
+        emit[b] = std::min(max_new, s->T - len + 1);
+        if (len + emit[b] > out_stride) throw Error(GRADB_ERR_INVALID, "out_stride too small for prompt + new ids");
+        emit_max = std::max(emit_max, emit[b]);
+    }
+    const int steps = upload_prompt_matrix(s, prompts, offsets, n_seq);
+    if (!sp.greedy && max_new > 0) {
+        ensure_uniforms(s, (size_t)n_seq * max_new);
+        GRADB_CUDA(cudaMemcpyAsync(s->uniforms, uniforms, (size_t)n_seq * max_new * sizeof(float),
+                                   cudaMemcpyHostToDevice, s->stream));
+    }
+    // Sequences with an empty prompt never run.
+    bool any_empty = false;
+    for (int b = 0; b < n_seq; b++) {
+        s->h_stage[b] = (offsets[b + 1] - offsets[b]) <= 0 ? 1 : 0;
+        any_empty = any_empty || s->h_stage[b];
+    }
+    if (any_empty) {
+        GRADB_CUDA(cudaMemcpyAsync(s->done, s->h_stage, n_seq * sizeof(int), cudaMemcpyHostToDevice, s->stream));
+    }
+
+    GRADB_CUDA(cudaEventRecord(s->ev_begin, s->stream));
+    enqueue_prompt_feed(s, steps, n_seq);
+    GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
+
+    SelectParams p = make_select(s, sp);
+    p.loop_mode = 1;
+    p.u_stride = max_new;
+    p.max_new = max_new;
+    p.out_tok = nullptr;
+
+    while ((int)s->step_events.size() < emit_max + 1) {
+        cudaEvent_t e;
+        GRADB_CUDA(cudaEventCreate(&e));
+        s->step_events.push_back(e);
+    }
+    const bool graph_ok = s->use_graph && !s->profiling && emit_max > 1;
+    if (graph_ok) {
+        const bool same = s->graph && s->graph_nseq == n_seq && s->graph_max_new == max_new &&
+                          std::memcmp(&s->graph_params, &sp, sizeof(sp)) == 0;
+        if (!same) {
+            if (s->graph) {
+                cudaGraphExecDestroy(s->graph);
+                s->graph = nullptr;
+            }
+            // One decode iteration = choose ids from the current logits, then feed them.
+            // Everything it reads lives at fixed device addresses, so one graph serves every token.
+            // The prompt feed has already run every step kernel eagerly, so their launch
+            // attributes are in place before capture starts.
+            cudaGraph_t g = nullptr;
+            configure_select(s->V);
+            GRADB_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+            g_capturing = true;
+            try {
+                launch_select(p, n_seq, s->stream);
+                enqueue_step(s, n_seq, s->tok, s->tok, false);
+            } catch (...) {
+                g_capturing = false;
+                cudaStreamEndCapture(s->stream, &g);
+                if (g) cudaGraphDestroy(g);
+                throw;
+            }
+            g_capturing = false;
+            GRADB_CUDA(cudaStreamEndCapture(s->stream, &g));
+            const cudaError_t e = cudaGraphInstantiate(&s->graph, g, 0);
+            cudaGraphDestroy(g);
+            if (e != cudaSuccess) throw Error(GRADB_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+            s->graph_params = sp;
+            s->graph_nseq = n_seq;
+            s->graph_max_new = max_new;
+        }
+    }
+    for (int i = 0; i < emit_max; i++) {
+        GRADB_CUDA(cudaEventRecord(s->step_events[i], s->stream));
+        if (i == emit_max - 1) {
+            Timed t(s, KC_SELECT);
+            launch_select(p, n_seq, s->stream);  // the last ids need no further step
+        } else if (graph_ok) {
+            GRADB_CUDA(cudaGraphLaunch(s->graph, s->stream));
+            count_launch(4 + 5 * s->L);  // kernels inside the graph
+        } else {
+            {
+                Timed t(s, KC_SELECT);
+                launch_select(p, n_seq, s->stream);
+            }
+            enqueue_step(s, n_seq, s->tok, s->tok, false);
+        }
+    }
+    GRADB_CUDA(cudaEventRecord(s->step_events[emit_max], s->stream));
+
+    std::vector<int> lens(n_seq);
+    GRADB_CUDA(cudaMemcpyAsync(lens.data(), s->hist_len, n_seq * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
+    std::vector<int> hist((size_t)n_seq * s->hist_stride);
+    GRADB_CUDA(cudaMemcpyAsync(hist.data(), s->hist, hist.size() * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+    collect_spans(s);
+    for (int b = 0; b < n_seq; b++) {
+        const int len = offsets[b + 1] - offsets[b];
+        const int n = len <= 0 ? 0 : std::min(lens[b], out_stride);
+        out_len[b] = n;
+        std::memcpy(out_ids + (size_t)b * out_stride, hist.data() + (size_t)b * s->hist_stride, n * sizeof(int));
+        s->h_pos[b] = len <= 0 ? 0 : std::min(s->T, len + std::max(0, emit[b] - 1));
+    }
+    float ms = 0.f;
+    GRADB_CUDA(cudaEventElapsedTime(&ms, s->ev_begin, s->ev_end));
+    if (prefill_ms) *prefill_ms = ms;
+    float total = 0.f;
+    for (int i = 0; i < emit_max; i++) {
+        float t = 0.f;
+        GRADB_CUDA(cudaEventElapsedTime(&t, s->step_events[i], s->step_events[i + 1]));
+        if (step_ms) step_ms[i] = t;
+        total += t;
+    }
+    s->last_ms = total;
+}
+
+void session_set_profiling(Session* s, bool on) {
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+    collect_spans(s);
+    s->profiling = on;
+    for (int i = 0; i < kKernelClasses; i++) {
+        s->class_ms[i] = 0.0;
+        s->class_launches[i] = 0;
+    }
+}
+
+void session_cache_row(Session* s, int seq, int layer, int which, int pos, float* row_host) {
+    if (seq < 0 || seq >= s->B || layer < 0 || layer >= s->L || pos < 0 || pos >= s->T || which < 0 || which > 1) {
+        throw Error(GRADB_ERR_INVALID, "cache row index out of range");
+    }
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    const float* base = (which ? s->vcache : s->kcache) + (size_t)layer * layer_cache_elems(s);
+    for (int h = 0; h < s->H; h++) {
+        const float* src = base + (((size_t)seq * s->H + h) * s->T + pos) * s->hs;
+        GRADB_CUDA(cudaMemcpyAsync(row_host + (size_t)h * s->hs, src, s->hs * sizeof(float), cudaMemcpyDeviceToHost,
+                                   s->stream));
+    }
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+}
+
+}  // namespace gradb

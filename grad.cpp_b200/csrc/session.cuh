@@ -1,0 +1,73 @@
+// Decode session: KV caches, scratch and the per-token launch sequence for a
+// batch of independent sequences (InferenceSession, inference.h:16-57, widened
+// to many sequences; TextGen's loops, text_gen.cpp:37-120).
+#pragma once
+#include "common.cuh"
+#include "select_kernels.cuh"
+#include "step_kernels.cuh"
+
+namespace gradb {
+
+enum KernelClass { KC_EMBED = 0, KC_QKV, KC_ATTN, KC_OPROJ, KC_FFN_UP, KC_FFN_DOWN, KC_LOGITS, KC_ADVANCE, KC_SELECT,
+                   kKernelClasses };
+
+struct Session {
+    const DeviceModel* m = nullptr;
+    int B = 0;  // max_batch
+    int T = 0;  // capacity (max_len)
+    int V = 0, d = 0, H = 0, hs = 0, dff = 0, L = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    int attn_splits = 1;
+    int hist_stride = 0;
+
+    // device buffers
+    float *x = nullptr, *q = nullptr, *attn = nullptr, *ffn = nullptr, *logits = nullptr;
+    float *kcache = nullptr, *vcache = nullptr;  // [L][B][H][T][hs]
+    float* attn_partial = nullptr;
+    int* attn_counters = nullptr;
+    int *tok = nullptr, *pos = nullptr, *hist = nullptr, *hist_len = nullptr;
+    int *gen = nullptr, *done = nullptr, *out_tok = nullptr;
+    int* tok_matrix = nullptr;  // prompt feed: [steps][2][B] (token rows, logits-mask rows)
+    size_t tok_matrix_cap = 0;
+    float* uniforms = nullptr;
+    size_t uniforms_cap = 0;
+    float* probs = nullptr;  // [B][V], allocated on first use
+
+    // host mirrors / staging (pinned)
+    std::vector<int> h_pos;
+    int* h_stage = nullptr;  // pinned, >= 4*B ints
+    float last_ms = 0.f;
+    cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+    std::vector<cudaEvent_t> step_events;
+
+    // decode-step graph (select + step), rebuilt when its parameters change
+    cudaGraphExec_t graph = nullptr;
+    gradb_sampling graph_params{};
+    int graph_nseq = -1, graph_max_new = -1, graph_u_stride = -1;
+    bool use_graph = true;
+
+    // Optional per-kernel-class device timing (events around every launch; graphs off).
+    bool profiling = false;
+    struct Span { int cls; cudaEvent_t a, b; };
+    std::vector<Span> spans;
+    std::vector<cudaEvent_t> event_pool;
+    double class_ms[kKernelClasses] = {};
+    uint64_t class_launches[kKernelClasses] = {};
+};
+
+Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* stream);
+void destroy_session(Session* s);
+void reset_session(Session* s);
+void session_step(Session* s, const int32_t* tokens, int n_seq, float* logits_host);
+void session_prefill(Session* s, const int32_t* tokens, const int32_t* offsets, int n_seq, float* logits_host);
+void session_select(Session* s, const gradb_sampling& sp, const float* logits_host, const float* uniforms,
+                    int n_seq, int32_t* tokens_out, float* probs_host);
+void session_set_history(Session* s, int seq, const int32_t* ids, int n);
+void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets, int n_seq,
+                      const gradb_sampling& sp, int max_new, const float* uniforms, int32_t* out_ids,
+                      int out_stride, int32_t* out_len, float* step_ms, float* prefill_ms);
+void session_set_profiling(Session* s, bool on);
+void session_cache_row(Session* s, int seq, int layer, int which, int pos, float* row_host);
+
+}  // namespace gradb

@@ -1,0 +1,680 @@
+// Kernels of one decode step (InferenceSession::step, src/transformer/inference.cpp:150-258)
+// for a batch of independent sequences.
+//
+// All of them are bandwidth-bound streaming kernels:
+//   embed        x = E[token] (+ P[pos])                                  inference.cpp:159-182
+//   fused_gemv   y = epilogue(norm(x) @ W + b), W (in,out) row-major      inference.cpp:14-58, 193-199, 228-247
+//                  - thread-block clusters split the reduction dimension; partial sums meet in
+//                    distributed shared memory in a fixed order (deterministic results)
+//   attn_decode  softmax(q K^T / sqrt(hs)) V over the cached positions     inference.cpp:208-225
+//                  - split along the context with a ticket-elected combiner
+//   logits       final norm + h @ E^T                                     inference.cpp:251-254
+#include <cooperative_groups.h>
+
+#include "step_kernels.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace gradb {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kTileN = 128;  // columns per CTA: 32 lanes x 4
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sums v[m] over the block; every thread gets the totals. Partial sums are
+// combined in warp order, so the result does not depend on scheduling.
+template <int MB>
+__device__ __forceinline__ void block_sum(float (&v)[MB], float* sh) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+    for (int m = 0; m < MB; m++) {
+        v[m] = warp_sum(v[m]);
+        if (lane == 0) sh[w * MB + m] = v[m];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int m = 0; m < MB; m++) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < kWarps; i++) s += sh[i * MB + m];
+        v[m] = s;
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ float4 load_w4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 load_w4(const __nv_bfloat16* p) {
+    const uint2 r = __ldg(reinterpret_cast<const uint2*>(p));
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    const float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
+    return make_float4(fa.x, fa.y, fb.x, fb.y);
+}
+
+// ------------------------------------------------------------------ embed
+
+__global__ void embed_kernel(const float* __restrict__ E, const float* __restrict__ P, const int* __restrict__ tok,
+                             const int* __restrict__ pos, float* __restrict__ x, int d) {
+    const int b = blockIdx.x;
+    const int t = tok[b];
+    if (t < 0) return;
+    const float4* e = reinterpret_cast<const float4*>(E + (size_t)t * d);
+    const float4* p = P ? reinterpret_cast<const float4*>(P + (size_t)pos[b] * d) : nullptr;
+    float4* o = reinterpret_cast<float4*>(x + (size_t)b * d);
+    for (int j = threadIdx.x; j < d / 4; j += blockDim.x) {
+        float4 v = __ldg(e + j);
+        // The reference multiplies by the embedding scale 1.0 first (token_embedding.h:12): a no-op in fp32.
+        if (p) {
+            const float4 q = __ldg(p + j);
+            v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+        }
+        o[j] = v;
+    }
+}
+
+// End of a step: positions move on; optionally the fed ids join the history the
+// repetition penalty reads.
+__global__ void advance_kernel(const int* __restrict__ tok, int* __restrict__ pos, int* __restrict__ hist,
+                               int* __restrict__ hist_len, int hist_stride, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B || tok[b] < 0) return;
+    pos[b] += 1;
+    if (hist) {
+        const int n = hist_len[b];
+        if (n < hist_stride) hist[(size_t)b * hist_stride + n] = tok[b];
+        hist_len[b] = n + 1;
+    }
+}
+
+// ------------------------------------------------------------- fused gemv
+
+// Shared-memory layout (floats): xs[MB][Kc] | xfull[K] (norm prologue only) | red[kWarps][NW][MB][128]
+//                                | part[NW][MB][128] | sh[kWarps*MB]
+template <int MB, typename WT, int PRO, int EPI, int NW>
+__global__ void __launch_bounds__(kThreads) fused_gemv_kernel(const GemvParams p) {
+    extern __shared__ __align__(16) float smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int KS = (int)cluster.dim_blocks().y;
+    const int kr = (int)cluster.block_index().y;
+    const int Kc = p.K / KS, k0 = kr * Kc;
+
+    float* xs = smem;
+    float* xfull = xs + MB * Kc;
+    float* red = xfull + (PRO != PRO_NONE ? p.K : 0);
+    float* part = red + kWarps * NW * MB * kTileN;
+    float* sh = part + NW * MB * kTileN;
+
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int row0 = blockIdx.z * MB;
+    const int tile = blockIdx.x;
+    int which = 0, n0 = tile * kTileN;
+    if (EPI == EPI_QKV) {
+        const int tiles_per = (p.N + kTileN - 1) / kTileN;
+        which = tile / tiles_per;
+        n0 = (tile % tiles_per) * kTileN;
+    }
+
+    // ---- prologue: stage (normalised) input rows in shared memory
+    bool live[MB];
+#pragma unroll
+    for (int m = 0; m < MB; m++) live[m] = (row0 + m < p.B) && (p.tok[row0 + m] >= 0);
+
+    if (PRO == PRO_NONE) {
+#pragma unroll
+        for (int m = 0; m < MB; m++) {
+            const float* xr = p.X + (size_t)(row0 + m) * p.ldx + k0;
+            for (int k = threadIdx.x; k < Kc; k += kThreads) xs[m * Kc + k] = live[m] ? xr[k] : 0.f;
+        }
+    } else {
+        for (int m = 0; m < MB; m++) {
+            if (!live[m]) {  // uniform across the block
+                for (int k = threadIdx.x; k < Kc; k += kThreads) xs[m * Kc + k] = 0.f;
+                continue;
+            }
+            const float* xr = p.X + (size_t)(row0 + m) * p.ldx;
+            float s[1] = {0.f};
+            for (int k = threadIdx.x; k < p.K; k += kThreads) {
+                const float v = xr[k];
+                xfull[k] = v;
+                s[0] += (PRO == PRO_RMSNORM) ? v * v : v;
+            }
+            block_sum<1>(s, sh);
+            if (PRO == PRO_RMSNORM) {
+                // inference.cpp:33-41
+                const float r = 1.0f / sqrtf(s[0] / (float)p.K + p.eps);
+                for (int k = threadIdx.x; k < Kc; k += kThreads) xs[m * Kc + k] = p.gamma[k0 + k] * xfull[k0 + k] * r;
+            } else {
+                // inference.cpp:44-57: mean, then the variance of the centred values
+                const float mean = s[0] / (float)p.K;
+                float v2[1] = {0.f};
+                for (int k = threadIdx.x; k < p.K; k += kThreads) {
+                    const float dlt = xfull[k] - mean;
+                    v2[0] += dlt * dlt;
+                }
+                block_sum<1>(v2, sh);
+                const float inv_std = 1.0f / sqrtf(v2[0] / (float)p.K + p.eps);
+                for (int k = threadIdx.x; k < Kc; k += kThreads) {
+                    xs[m * Kc + k] = p.gamma[k0 + k] * (xfull[k0 + k] - mean) * inv_std + p.beta[k0 + k];
+                }
+            }
+            __syncthreads();
+        }
+    }
+    __syncthreads();
+
+    // ---- main loop: each warp streams rows k0 + 4*(w + 8i) .. +3 of its 128-column tile
+    float acc[NW][MB][4];
+#pragma unroll
+    for (int a = 0; a < NW; a++)
+#pragma unroll
+        for (int m = 0; m < MB; m++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) acc[a][m][c] = 0.f;
+
+    const int col = n0 + lane * 4;
+    if (col < p.N) {
+        const WT* Wp[NW];
+#pragma unroll
+        for (int a = 0; a < NW; a++) {
+            const WT* base = static_cast<const WT*>(p.W[EPI == EPI_QKV ? which : a]);
+            Wp[a] = base + (size_t)k0 * p.N + col;
+        }
+        const int groups = Kc / 4;
+#pragma unroll 2
+        for (int g = w; g < groups; g += kWarps) {
+            const int k = 4 * g;
+            float4 wv[NW][4];
+#pragma unroll
+            for (int a = 0; a < NW; a++)
+#pragma unroll
+                for (int r = 0; r < 4; r++) wv[a][r] = load_w4(Wp[a] + (size_t)(k + r) * p.N);
+#pragma unroll
+            for (int m = 0; m < MB; m++) {
+                const float4 xv = *reinterpret_cast<const float4*>(&xs[m * Kc + k]);
+#pragma unroll
+                for (int a = 0; a < NW; a++) {
+                    acc[a][m][0] += xv.x * wv[a][0].x + xv.y * wv[a][1].x + xv.z * wv[a][2].x + xv.w * wv[a][3].x;
+                    acc[a][m][1] += xv.x * wv[a][0].y + xv.y * wv[a][1].y + xv.z * wv[a][2].y + xv.w * wv[a][3].y;
+                    acc[a][m][2] += xv.x * wv[a][0].z + xv.y * wv[a][1].z + xv.z * wv[a][2].z + xv.w * wv[a][3].z;
+                    acc[a][m][3] += xv.x * wv[a][0].w + xv.y * wv[a][1].w + xv.z * wv[a][2].w + xv.w * wv[a][3].w;
+                }
+            }
+        }
+    }
+
+    // ---- reduce over the block's warps, then over the cluster's K slices
+#pragma unroll
+    for (int a = 0; a < NW; a++)
+#pragma unroll
+        for (int m = 0; m < MB; m++) {
+            *reinterpret_cast<float4*>(&red[((w * NW + a) * MB + m) * kTileN + lane * 4]) =
+                make_float4(acc[a][m][0], acc[a][m][1], acc[a][m][2], acc[a][m][3]);
+        }
+    __syncthreads();
+    for (int i = threadIdx.x; i < NW * MB * kTileN; i += kThreads) {
+        float s = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < kWarps; ww++) s += red[ww * NW * MB * kTileN + i];
+        part[i] = s;
+    }
+    cluster.sync();
+
+    // Each CTA of the cluster finishes a 128/KS-column slice of the tile.
+    const int cslice = kTileN / KS;
+    const int pairs = cslice / 2;
+    for (int i = threadIdx.x; i < MB * pairs; i += kThreads) {
+        const int m = i / pairs, c = kr * cslice + (i % pairs) * 2;
+        const int b = row0 + m, n = n0 + c;
+        float v[NW][2];
+#pragma unroll
+        for (int a = 0; a < NW; a++) v[a][0] = v[a][1] = 0.f;
+        for (int r = 0; r < KS; r++) {
+            const float* rp = cluster.map_shared_rank(part, r);
+#pragma unroll
+            for (int a = 0; a < NW; a++) {
+                const float2 t = *reinterpret_cast<const float2*>(&rp[(a * MB + m) * kTileN + c]);
+                v[a][0] += t.x;
+                v[a][1] += t.y;
+            }
+        }
+        if (n >= p.N || !live[m]) continue;
+        if (EPI == EPI_RESID) {
+            // x += h @ W + b (inference.cpp:22-28)
+            float* y = p.Y + (size_t)b * p.ldy + n;
+            const float b0 = p.bias[0] ? p.bias[0][n] : 0.f, b1 = p.bias[0] ? p.bias[0][n + 1] : 0.f;
+            y[0] += v[0][0] + b0;
+            y[1] += v[0][1] + b1;
+        } else if (EPI == EPI_GELU) {
+            // inference.cpp:69-80
+            float* y = p.Y + (size_t)b * p.ldy + n;
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const float t = v[0][e] + p.bias[0][n + e];
+                const float u = 0.79788456f * (t + 0.044715f * t * t * t);
+                y[e] = 0.5f * t * (1.0f + tanhf(u));
+            }
+        } else if (EPI == EPI_SWIGLU) {
+            // silu(gate) * up (inference.cpp:82-91, 234-239)
+            float* y = p.Y + (size_t)b * p.ldy + n;
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const float g = v[0][e];
+                const float sg = g / (1.0f + expf(-g));
+                y[e] = v[1][e] * sg;
+            }
+        } else {  // EPI_QKV
+            float a0 = v[0][0] + p.bias[which][n], a1 = v[0][1] + p.bias[which][n + 1];
+            const int position = p.pos[b];
+            const int h = n / p.hs, c_in = n % p.hs;
+            if (p.rope_cos && which < 2) {
+                // inference.cpp:101-115: pairs (2j, 2j+1) inside each head
+                const float cs = p.rope_cos[(size_t)position * (p.hs / 2) + c_in / 2];
+                const float sn = p.rope_sin[(size_t)position * (p.hs / 2) + c_in / 2];
+                const float r0 = a0 * cs - a1 * sn, r1 = a0 * sn + a1 * cs;
+                a0 = r0;
+                a1 = r1;
+            }
+            if (which == 0) {
+                *reinterpret_cast<float2*>(p.Y + (size_t)b * p.ldy + n) = make_float2(a0, a1);
+            } else {
+                float* cache = which == 1 ? p.kcache : p.vcache;
+                const size_t off = (((size_t)b * p.H + h) * p.T + position) * p.hs + c_in;
+                *reinterpret_cast<float2*>(cache + off) = make_float2(a0, a1);
+            }
+        }
+    }
+    cluster.sync();
+}
+
+// ----------------------------------------------------------------- logits
+
+// One warp per vocabulary row: lanes stride the row in float4, then a shuffle
+// reduction. E is (vocab, d) row-major, used transposed (inference.cpp:254).
+template <int MB, typename WT>
+__global__ void __launch_bounds__(kThreads) logits_kernel(const LogitsParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float* hs_ = smem;                 // [MB][d] normalised rows
+    float* sh = hs_ + MB * p.d;        // reduction scratch
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int row0 = blockIdx.y * MB;
+    bool live[MB];
+    bool any = false;
+#pragma unroll
+    for (int m = 0; m < MB; m++) {
+        live[m] = (row0 + m < p.B) && (p.tok[row0 + m] >= 0);
+        any = any || live[m];
+    }
+    if (!any) return;
+
+    for (int m = 0; m < MB; m++) {
+        if (!live[m]) {
+            for (int k = threadIdx.x; k < p.d; k += kThreads) hs_[m * p.d + k] = 0.f;
+            continue;
+        }
+        const float* xr = p.X + (size_t)(row0 + m) * p.d;
+        float s[1] = {0.f};
+        for (int k = threadIdx.x; k < p.d; k += kThreads) {
+            const float v = xr[k];
+            s[0] += p.rms ? v * v : v;
+        }
+        block_sum<1>(s, sh);
+        if (p.rms) {
+            const float r = 1.0f / sqrtf(s[0] / (float)p.d + p.eps);
+            for (int k = threadIdx.x; k < p.d; k += kThreads) hs_[m * p.d + k] = p.gamma[k] * xr[k] * r;
+        } else {
+            const float mean = s[0] / (float)p.d;
+            float v2[1] = {0.f};
+            for (int k = threadIdx.x; k < p.d; k += kThreads) {
+                const float dlt = xr[k] - mean;
+                v2[0] += dlt * dlt;
+            }
+            block_sum<1>(v2, sh);
+            const float inv_std = 1.0f / sqrtf(v2[0] / (float)p.d + p.eps);
+            for (int k = threadIdx.x; k < p.d; k += kThreads) {
+                hs_[m * p.d + k] = p.gamma[k] * (xr[k] - mean) * inv_std + p.beta[k];
+            }
+        }
+    }
+    __syncthreads();
+
+    const WT* E = static_cast<const WT*>(p.E);
+    const int rows_per_block = kWarps * p.rows_per_warp;
+    const int vbeg = blockIdx.x * rows_per_block + w * p.rows_per_warp;
+    for (int v = vbeg; v < vbeg + p.rows_per_warp && v < p.V; v++) {
+        const WT* er = E + (size_t)v * p.d;
+        float acc[MB];
+#pragma unroll
+        for (int m = 0; m < MB; m++) acc[m] = 0.f;
+        for (int k = lane * 4; k < p.d; k += 128) {
+            const float4 e = load_w4(er + k);
+#pragma unroll
+            for (int m = 0; m < MB; m++) {
+                const float4 hv = *reinterpret_cast<const float4*>(&hs_[m * p.d + k]);
+                acc[m] += hv.x * e.x + hv.y * e.y + hv.z * e.z + hv.w * e.w;
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MB; m++) {
+            const float t = warp_sum(acc[m]);
+            if (lane == 0 && live[m]) p.logits[(size_t)(row0 + m) * p.V + v] = t;
+        }
+    }
+}
+
+// -------------------------------------------------------------- attention
+
+// Head size 64. grid (splits, heads, batch); 4 warps per CTA take 32-position
+// tiles of the CTA's context range round-robin, each with a running softmax.
+// Eight lanes share a K row (two float4 each); for P@V each lane owns two
+// output columns.
+constexpr int kAttnWarps = 4;
+
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode64_kernel(const AttnParams p) {
+    constexpr int HS = 64;
+    const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    if (p.tok[b] < 0) return;
+    const int S = gridDim.x;
+    const int ctx = p.pos[b] + 1;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int ntiles = (ctx + 31) / 32;
+    const int tps = (ntiles + S - 1) / S;
+    const int tile_beg = split * tps, tile_end = min(ntiles, tile_beg + tps);
+
+    const size_t head_base = (((size_t)b * p.H + h) * p.T) * HS;
+    const float* K = p.kcache + head_base;
+    const float* V = p.vcache + head_base;
+    const int sub = lane & 7, rin = lane >> 3;
+
+    const float4 q0 = *reinterpret_cast<const float4*>(p.q + (size_t)b * p.d + h * HS + sub * 8);
+    const float4 q1 = *reinterpret_cast<const float4*>(p.q + (size_t)b * p.d + h * HS + sub * 8 + 4);
+
+    float m_run = -INFINITY, l_run = 0.f, o0 = 0.f, o1 = 0.f;
+    for (int t = tile_beg + w; t < tile_end; t += kAttnWarps) {
+        const int r0 = t * 32;
+        const int nrows = min(32, ctx - r0);
+        float sc[8];
+#pragma unroll
+        for (int pp = 0; pp < 8; pp++) {
+            const int r = pp * 4 + rin;
+            float dsum = 0.f;
+            if (r < nrows) {
+                const float4* kr = reinterpret_cast<const float4*>(K + (size_t)(r0 + r) * HS + sub * 8);
+                const float4 k0 = __ldcs(kr), k1 = __ldcs(kr + 1);
+                dsum = q0.x * k0.x + q0.y * k0.y + q0.z * k0.z + q0.w * k0.w + q1.x * k1.x + q1.y * k1.y +
+                       q1.z * k1.z + q1.w * k1.w;
+            }
+            dsum += __shfl_xor_sync(0xffffffffu, dsum, 1);
+            dsum += __shfl_xor_sync(0xffffffffu, dsum, 2);
+            dsum += __shfl_xor_sync(0xffffffffu, dsum, 4);
+            sc[pp] = dsum;
+        }
+        float mine = 0.f;
+#pragma unroll
+        for (int pp = 0; pp < 8; pp++) {
+            const float v = __shfl_sync(0xffffffffu, sc[pp], (lane & 3) * 8);
+            if ((lane >> 2) == pp) mine = v;
+        }
+        mine = lane < nrows ? mine * p.scale : -INFINITY;
+        const float m_new = fmaxf(m_run, warp_max(mine));
+        const float corr = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
+        const float pr = lane < nrows ? expf(mine - m_new) : 0.f;
+        l_run = l_run * corr + warp_sum(pr);
+        o0 *= corr;
+        o1 *= corr;
+        m_run = m_new;
+        const float2* vr = reinterpret_cast<const float2*>(V + (size_t)r0 * HS) + lane;
+#pragma unroll 8
+        for (int r = 0; r < nrows; r++) {
+            const float pv = __shfl_sync(0xffffffffu, pr, r);
+            const float2 vv = __ldcs(vr + (size_t)r * (HS / 2));
+            o0 += pv * vv.x;
+            o1 += pv * vv.y;
+        }
+    }
+
+    // combine the CTA's warps (fixed order)
+    __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps], sm_o[kAttnWarps][HS];
+    __shared__ int sm_last;
+    if (lane == 0) {
+        sm_m[w] = m_run;
+        sm_l[w] = l_run;
+    }
+    sm_o[w][2 * lane] = o0;
+    sm_o[w][2 * lane + 1] = o1;
+    __syncthreads();
+    if (w != 0) {
+        if (S == 1) return;
+    }
+    float M = -INFINITY, Lsum = 0.f, a0 = 0.f, a1 = 0.f;
+    if (w == 0) {
+#pragma unroll
+        for (int i = 0; i < kAttnWarps; i++) M = fmaxf(M, sm_m[i]);
+#pragma unroll
+        for (int i = 0; i < kAttnWarps; i++) {
+            const float f = sm_m[i] == -INFINITY ? 0.f : expf(sm_m[i] - M);
+            Lsum += sm_l[i] * f;
+            a0 += sm_o[i][2 * lane] * f;
+            a1 += sm_o[i][2 * lane + 1] * f;
+        }
+        if (S == 1) {
+            const float inv = 1.0f / Lsum;
+            *reinterpret_cast<float2*>(p.out + (size_t)b * p.d + h * HS + 2 * lane) = make_float2(a0 * inv, a1 * inv);
+            return;
+        }
+        float* part = p.partial + ((size_t)(b * p.H + h) * S + split) * (HS + 2);
+        part[2 * lane] = a0;
+        part[2 * lane + 1] = a1;
+        if (lane == 0) {
+            part[HS] = M;
+            part[HS + 1] = Lsum;
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+            const int ticket = atomicAdd(p.counters + b * p.H + h, 1);
+            sm_last = (ticket == S - 1);
+        }
+    }
+    __syncthreads();
+    if (w != 0 || !sm_last) return;
+    // Last split to arrive combines all of them, in split order.
+    __threadfence();
+    const float* base = p.partial + (size_t)(b * p.H + h) * S * (HS + 2);
+    float Mt = -INFINITY;
+    for (int s = 0; s < S; s++) Mt = fmaxf(Mt, __ldcg(base + s * (HS + 2) + HS));
+    float Lt = 0.f, c0 = 0.f, c1 = 0.f;
+    for (int s = 0; s < S; s++) {
+        const float ms = __ldcg(base + s * (HS + 2) + HS);
+        const float f = ms == -INFINITY ? 0.f : expf(ms - Mt);
+        Lt += __ldcg(base + s * (HS + 2) + HS + 1) * f;
+        c0 += __ldcg(base + s * (HS + 2) + 2 * lane) * f;
+        c1 += __ldcg(base + s * (HS + 2) + 2 * lane + 1) * f;
+    }
+    const float inv = 1.0f / Lt;
+    *reinterpret_cast<float2*>(p.out + (size_t)b * p.d + h * HS + 2 * lane) = make_float2(c0 * inv, c1 * inv);
+    if (lane == 0) p.counters[b * p.H + h] = 0;
+}
+
+// Any head size: one CTA per (head, sequence), scores kept in shared memory.
+// Mirrors the reference loop structure directly (inference.cpp:208-225).
+__global__ void __launch_bounds__(128) attn_decode_generic_kernel(const AttnParams p) {
+    extern __shared__ float scores[];
+    __shared__ float sh[4];
+    const int h = blockIdx.y, b = blockIdx.z;
+    if (p.tok[b] < 0) return;
+    const int ctx = p.pos[b] + 1, hs = p.hs;
+    const size_t head_base = (((size_t)b * p.H + h) * p.T) * hs;
+    const float* K = p.kcache + head_base;
+    const float* V = p.vcache + head_base;
+    const float* q = p.q + (size_t)b * p.d + h * hs;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+
+    float mx = -INFINITY;
+    for (int t = threadIdx.x; t < ctx; t += blockDim.x) {
+        float dsum = 0.f;
+        for (int j = 0; j < hs; j++) dsum += q[j] * K[(size_t)t * hs + j];
+        dsum *= p.scale;
+        scores[t] = dsum;
+        mx = fmaxf(mx, dsum);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) sh[w] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(sh[0], sh[1]), fmaxf(sh[2], sh[3]));
+    __syncthreads();
+    float sum = 0.f;
+    for (int t = threadIdx.x; t < ctx; t += blockDim.x) {
+        const float e = expf(scores[t] - mx);
+        scores[t] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) sh[w] = sum;
+    __syncthreads();
+    const float inv = 1.0f / (((sh[0] + sh[1]) + sh[2]) + sh[3]);
+    for (int c = threadIdx.x; c < hs; c += blockDim.x) {
+        float o = 0.f;
+        for (int t = 0; t < ctx; t++) o += scores[t] * inv * V[(size_t)t * hs + c];
+        p.out[(size_t)b * p.d + h * hs + c] = o;
+    }
+}
+
+// Opt-in to more than 48 KB of dynamic shared memory. Skipped while a stream is
+// being captured: every kernel has by then run once eagerly with the same size.
+template <typename K>
+void set_smem(K kernel, size_t bytes) {
+    if (bytes > 48 * 1024 && !g_capturing) {
+        GRADB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    }
+}
+
+template <int MB, typename WT, int PRO, int EPI, int NW>
+void launch_gemv_t(const GemvParams& p, int n_tiles, int KS, cudaStream_t st) {
+    const size_t floats = (size_t)MB * (p.K / KS) + (PRO != PRO_NONE ? p.K : 0) +
+                          (size_t)(kWarps + 1) * NW * MB * kTileN + kWarps * MB;
+    const size_t bytes = floats * sizeof(float);
+    auto kernel = fused_gemv_kernel<MB, WT, PRO, EPI, NW>;
+    set_smem(kernel, bytes);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(n_tiles, KS, (p.B + MB - 1) / MB);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = KS;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    GRADB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+    count_launch();
+}
+
+template <int MB, typename WT>
+void launch_gemv_mb(const GemvParams& p, int pro, int epi, int n_tiles, int KS, cudaStream_t st) {
+    if (epi == EPI_QKV) {
+        if (pro == PRO_RMSNORM) launch_gemv_t<MB, WT, PRO_RMSNORM, EPI_QKV, 1>(p, n_tiles, KS, st);
+        else launch_gemv_t<MB, WT, PRO_LAYERNORM, EPI_QKV, 1>(p, n_tiles, KS, st);
+    } else if (epi == EPI_RESID) {
+        launch_gemv_t<MB, WT, PRO_NONE, EPI_RESID, 1>(p, n_tiles, KS, st);
+    } else if (epi == EPI_GELU) {
+        launch_gemv_t<MB, WT, PRO_LAYERNORM, EPI_GELU, 1>(p, n_tiles, KS, st);
+    } else {
+        launch_gemv_t<MB, WT, PRO_RMSNORM, EPI_SWIGLU, 2>(p, n_tiles, KS, st);
+    }
+}
+
+int pick_mb(int B) { return B >= 8 ? 8 : (B >= 4 ? 4 : (B >= 2 ? 2 : 1)); }
+
+}  // namespace
+
+void launch_embed(const float* E, const float* P, const int* tok, const int* pos, float* x, int d, int B,
+                  cudaStream_t st) {
+    embed_kernel<<<B, 128, 0, st>>>(E, P, tok, pos, x, d);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+void launch_advance(const int* tok, int* pos, int* hist, int* hist_len, int hist_stride, int B, cudaStream_t st) {
+    advance_kernel<<<(B + 127) / 128, 128, 0, st>>>(tok, pos, hist, hist_len, hist_stride, B);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+void launch_gemv(const GemvParams& p, int pro, int epi, bool bf16, int sm_count, cudaStream_t st) {
+    const int tiles_per = (p.N + kTileN - 1) / kTileN;
+    const int n_tiles = epi == EPI_QKV ? 3 * tiles_per : tiles_per;
+    const int MB = pick_mb(p.B);
+    const int row_groups = (p.B + MB - 1) / MB;
+    // Split the reduction dimension across a cluster until the grid covers the SMs.
+    int KS = 1;
+    while (KS < 8 && n_tiles * row_groups * KS < sm_count && p.K % (8 * KS) == 0 && p.K / (2 * KS) >= 32) KS *= 2;
+#define GRADB_MB_CASE(M)                                                                     \
+    case M:                                                                                  \
+        if (bf16) launch_gemv_mb<M, __nv_bfloat16>(p, pro, epi, n_tiles, KS, st);            \
+        else launch_gemv_mb<M, float>(p, pro, epi, n_tiles, KS, st);                         \
+        break;
+    switch (MB) {
+        GRADB_MB_CASE(1)
+        GRADB_MB_CASE(2)
+        GRADB_MB_CASE(4)
+        GRADB_MB_CASE(8)
+    }
+#undef GRADB_MB_CASE
+}
+
+void launch_logits(const LogitsParams& p_in, bool bf16, cudaStream_t st) {
+    LogitsParams p = p_in;
+    const int MB = pick_mb(p.B);
+    p.rows_per_warp = 4;
+    const int rows_per_block = kWarps * p.rows_per_warp;
+    const dim3 grid((p.V + rows_per_block - 1) / rows_per_block, (p.B + MB - 1) / MB);
+    const size_t bytes = ((size_t)MB * p.d + kWarps * MB) * sizeof(float);
+#define GRADB_MB_CASE(M)                                                              \
+    case M:                                                                           \
+        if (bf16) {                                                                   \
+            set_smem(logits_kernel<M, __nv_bfloat16>, bytes);                         \
+            logits_kernel<M, __nv_bfloat16><<<grid, kThreads, bytes, st>>>(p);        \
+        } else {                                                                      \
+            set_smem(logits_kernel<M, float>, bytes);                                 \
+            logits_kernel<M, float><<<grid, kThreads, bytes, st>>>(p);                \
+        }                                                                             \
+        break;
+    switch (MB) {
+        GRADB_MB_CASE(1)
+        GRADB_MB_CASE(2)
+        GRADB_MB_CASE(4)
+        GRADB_MB_CASE(8)
+    }
+#undef GRADB_MB_CASE
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+void launch_attention(const AttnParams& p, int B, int splits, cudaStream_t st) {
+    if (p.hs == 64) {
+        attn_decode64_kernel<<<dim3(splits, p.H, B), kAttnWarps * 32, 0, st>>>(p);
+    } else {
+        const size_t bytes = (size_t)p.T * sizeof(float);
+        set_smem(attn_decode_generic_kernel, bytes);
+        attn_decode_generic_kernel<<<dim3(1, p.H, B), 128, bytes, st>>>(p);
+    }
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+}  // namespace gradb

@@ -1,0 +1,57 @@
+// Launchers of the decode-step kernels (step_kernels.cu).
+#pragma once
+#include "common.cuh"
+
+namespace gradb {
+
+enum { PRO_NONE = 0, PRO_LAYERNORM = 1, PRO_RMSNORM = 2 };
+enum { EPI_QKV = 0, EPI_RESID = 1, EPI_GELU = 2, EPI_SWIGLU = 3 };
+
+struct GemvParams {
+    const float* X;  // [B][ldx] input rows
+    int ldx;
+    int B, K, N;           // N = columns of ONE matrix
+    const void* W[3];      // QKV: Wq, Wk, Wv. SwiGLU: gate, up. Others: W[0]
+    const float* bias[3];  // may be null (bias-free projections)
+    const float *gamma, *beta;
+    float eps;
+    const int *tok, *pos;  // per-sequence current token (<0: skip) and position
+    float* Y;              // q / residual stream / FFN activation
+    int ldy;
+    // EPI_QKV only
+    float *kcache, *vcache;  // this layer's caches: [B][H][T][hs]
+    const float *rope_cos, *rope_sin;  // [max_len][hs/2] or null (GPT-2)
+    int H, hs, T;
+};
+
+struct LogitsParams {
+    const float* X;  // [B][d] residual stream
+    const void* E;   // (V, d) embedding table, fp32 or bf16
+    const float *gamma, *beta;
+    float eps;
+    int rms;
+    const int* tok;
+    float* logits;  // [B][V]
+    int B, d, V;
+    int rows_per_warp;
+};
+
+struct AttnParams {
+    const float* q;  // [B][d]
+    const float *kcache, *vcache;
+    const int *tok, *pos;
+    float* out;       // [B][d]
+    float* partial;   // [B][H][S][hs+2] split results: o[hs], max, sum
+    int* counters;    // [B][H] arrival tickets, zero between launches
+    int H, hs, T, d;
+    float scale;
+};
+
+void launch_embed(const float* E, const float* P, const int* tok, const int* pos, float* x, int d, int B,
+                  cudaStream_t st);
+void launch_advance(const int* tok, int* pos, int* hist, int* hist_len, int hist_stride, int B, cudaStream_t st);
+void launch_gemv(const GemvParams& p, int pro, int epi, bool bf16, int sm_count, cudaStream_t st);
+void launch_logits(const LogitsParams& p, bool bf16, cudaStream_t st);
+void launch_attention(const AttnParams& p, int B, int splits, cudaStream_t st);
+
+}  // namespace gradb
