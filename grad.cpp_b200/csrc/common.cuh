@@ -1,5 +1,6 @@
 // Shared declarations of the decode engine's CUDA translation units.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -45,6 +46,11 @@ struct LayerWeights {
     const float *gate, *w1, *b1, *w2, *b2;
     const float *n1g, *n1b, *n2g, *n2b;
     const __nv_bfloat16 *wq16, *wk16, *wv16, *wo16, *gate16, *w116, *w216;
+    // Tensor-core path (BF16 mode): transposed (out, in) bf16 copies and their TMA descriptors.
+    // qkvT: [3d][d]; upT: modern [2*dff][d] with 128-row gate/up tiles interleaved, GPT-2 [dff][d];
+    // downT: [d][dff].
+    __nv_bfloat16 *qkvT = nullptr, *oT = nullptr, *upT = nullptr, *downT = nullptr;
+    CUtensorMap map_qkv, map_o, map_up, map_down;
 };
 
 struct DeviceModel {
@@ -60,6 +66,8 @@ struct DeviceModel {
     float* rope_cos = nullptr;  // [max_len][hs/2], host-computed with the reference's expressions
     float* rope_sin = nullptr;
     int sm_count = 148;
+    bool tc_ok = false;   // shapes fit the tensor-core kernels (BF16 mode, d and d_ff multiples of 64)
+    CUtensorMap map_emb;  // (V, d) bf16 embedding table = the logits GEMM's A operand
 };
 
 DeviceModel* upload_model(const gradb_model_desc& desc, const float* const* tensors, int n_tensors, int device,

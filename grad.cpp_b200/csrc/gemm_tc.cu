@@ -1,0 +1,425 @@
+// Batched-decode / prompt-feed projections on the 5th-generation tensor cores.
+//
+// For a batch of sequences the projections of one step are real GEMMs:
+//     Y[b, n] = sum_k X[b, k] * W[k, n]        (inference.cpp:14-28, 94-96, 254 for one row)
+// They are computed "swapped": the weight tile supplies the 128 MMA rows (one
+// TMEM lane per output feature n) and the tokens supply the MMA columns, so any
+// batch from 16 to 256 fills the instruction and the epilogue writes rows of
+// consecutive features, which is the memory order of every consumer.
+//
+//   D[n, b] (fp32, TMEM) = A[n, k] (bf16 weights, K-major, TMA) * B[b, k]^T (bf16 activations, K-major, TMA)
+//
+// One CTA = one 128-feature tile (two tiles for SwiGLU: gate and up) x one token
+// tile x one K split. Warp 0 lane 0 feeds a 4-stage shared-memory ring with TMA,
+// warp 1 lane 0 issues tcgen05.mma and releases stages with tcgen05.commit, and all
+// four warps run the epilogue from TMEM (bias, RoPE + cache write, GELU / SwiGLU,
+// residual add, logits) once the accumulator barrier fires.
+//
+// Every wait on an mbarrier is bounded; on expiry the kernel records a code in
+// the session's status word and falls through to the common exit, which frees
+// TMEM. TMA loads here are plain per-CTA loads of this GPU's own memory.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "gemm_tc.cuh"
+
+namespace gradb {
+
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kBlockK = 64;  // bf16 elements = one 128-byte swizzle row
+constexpr int kTileM = 128;  // features per MMA
+constexpr uint32_t kSpinLimit = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait. Returns false (and records `code`) if the phase never completes.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    atomicExch(status, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem_tile) {
+    const uint32_t addr = smem_u32(smem_tile);
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);  // start address
+    d |= (uint64_t)0 << 16;                   // leading byte offset (unused for this layout)
+    d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset
+    d |= (uint64_t)1 << 46;                   // descriptor version
+    d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor for kind::f16: bf16 x bf16 -> fp32, both operands K-major.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared memory: [stage][A tiles (NW x 16 KB) | B tile (TN x 128 B)], 1024-byte aligned.
+template <int EPI, int NW, int TN>
+__global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                           const __grid_constant__ CUtensorMap map_b,
+                                                           const TcGemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
+    __shared__ uint32_t tmem_base_slot;
+
+    constexpr int kABytes = NW * kTileM * kBlockK * 2;
+    constexpr int kBBytes = TN * kBlockK * 2;
+    constexpr int kStageBytes = kABytes + kBBytes;
+    constexpr int kTmemCols = NW * TN < 32 ? 32 : NW * TN;
+    static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two");
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x, tile_b = blockIdx.y, kz = blockIdx.z;
+    const int k_iters_total = p.K / kBlockK;
+    const int k_per = (k_iters_total + gridDim.z - 1) / gridDim.z;
+    const int k_beg = kz * k_per, k_end = min(k_iters_total, k_beg + k_per);
+    const int n_iters = max(0, k_end - k_beg);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"((uint32_t)kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+    bool ok = true;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer
+        for (int it = 0; it < n_iters && ok; it++) {
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1;
+            ok = mbar_wait(&empty_bar[s], ph ^ 1, p.status, 101);
+            if (!ok) break;
+            uint8_t* st = smem + (size_t)s * kStageBytes;
+            mbar_expect_tx(&full_bar[s], kStageBytes);
+            const int kx = (k_beg + it) * kBlockK;
+#pragma unroll
+            for (int w = 0; w < NW; w++) {
+                tma_load_2d(st + w * (kTileM * kBlockK * 2), &map_a, kx, (tile_n * NW + w) * kTileM, &full_bar[s]);
+            }
+            tma_load_2d(st + kABytes, &map_b, kx, tile_b * TN, &full_bar[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        constexpr uint32_t idesc = umma_idesc_bf16(kTileM, TN);
+        for (int it = 0; it < n_iters && ok; it++) {
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1;
+            ok = mbar_wait(&full_bar[s], ph, p.status, 102);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint8_t* st = smem + (size_t)s * kStageBytes;
+            const uint64_t bdesc = umma_desc_sw128(st + kABytes);
+#pragma unroll
+            for (int w = 0; w < NW; w++) {
+                const uint64_t adesc = umma_desc_sw128(st + w * (kTileM * kBlockK * 2));
+#pragma unroll
+                for (int k = 0; k < kBlockK / 16; k++) {
+                    // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in the address field
+                    umma_bf16(tmem_base + w * TN, adesc + 2 * k, bdesc + 2 * k, idesc, (it | k) != 0 ? 1u : 0u);
+                }
+            }
+            umma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
+        }
+        umma_commit(&accum_bar);  // accumulator complete
+    }
+    __syncwarp();
+
+    // ---- epilogue: thread t owns TMEM lane t = feature n0 + t
+    if (n_iters > 0) ok = mbar_wait(&accum_bar, 0, p.status, 103);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && n_iters > 0) {
+        const int t = threadIdx.x;
+        const int n = tile_n * kTileM + t;  // feature index inside one matrix (for NW=2: same n in gate and up)
+        const bool n_ok = n < p.N;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        int which = 0, n_in = n;
+        float bias = 0.f;
+        if (EPI == TC_QKV) {
+            which = n / p.d;
+            n_in = n - which * p.d;
+            if (n_ok) bias = p.bias[which][n_in];
+        } else if (EPI == TC_RESID || EPI == TC_GELU) {
+            if (n_ok && p.bias[0] && kz == 0) bias = p.bias[0][n];
+        }
+        for (int c0 = 0; c0 < TN; c0 += 32) {
+            float v[32], v2[32];
+            tmem_ld32(lane_addr + c0, v);
+            if (NW == 2) tmem_ld32(lane_addr + TN + c0, v2);
+#pragma unroll 4
+            for (int j = 0; j < 32; j++) {
+                const int b = tile_b * TN + c0 + j;
+                const bool live = b < p.B && p.tok[b] >= 0;  // warp-uniform
+                float val = v[j] + bias;
+                if (EPI == TC_QKV) {
+                    const int position = live ? p.pos[b] : 0;
+                    const int h = n_in / p.hs, c_in = n_in % p.hs;
+                    if (p.rope_cos && which < 2) {
+                        // pairs (2j, 2j+1) inside a head sit in neighbouring lanes (inference.cpp:101-115)
+                        const float other = __shfl_xor_sync(0xffffffffu, val, 1);
+                        const float cs = p.rope_cos[(size_t)position * (p.hs / 2) + c_in / 2];
+                        const float sn = p.rope_sin[(size_t)position * (p.hs / 2) + c_in / 2];
+                        val = (c_in & 1) ? (other * sn + val * cs) : (val * cs - other * sn);
+                    }
+                    if (live && n_ok) {
+                        if (which == 0) {
+                            p.out_f32[(size_t)b * p.ld_out + n_in] = val;
+                        } else {
+                            float* cache = which == 1 ? p.kcache : p.vcache;
+                            cache[(((size_t)b * p.H + h) * p.T + position) * p.hs + c_in] = val;
+                        }
+                    }
+                } else if (EPI == TC_RESID) {
+                    if (live && n_ok) {
+                        float* y = p.out_f32 + (size_t)b * p.ld_out + n;
+                        if (gridDim.z == 1) *y += val;
+                        else atomicAdd(y, val);
+                    }
+                } else if (EPI == TC_GELU) {
+                    if (live && n_ok) {
+                        const float u = 0.79788456f * (val + 0.044715f * val * val * val);
+                        p.out_bf16[(size_t)b * p.ld_out + n] = __float2bfloat16_rn(0.5f * val * (1.0f + tanhf(u)));
+                    }
+                } else if (EPI == TC_SWIGLU) {
+                    if (live && n_ok) {
+                        const float gte = v[j];
+                        const float sg = gte / (1.0f + expf(-gte));
+                        p.out_bf16[(size_t)b * p.ld_out + n] = __float2bfloat16_rn(v2[j] * sg);
+                    }
+                } else {  // TC_LOGITS
+                    if (b < p.B && p.tok[b] >= 0 && n_ok) p.out_f32[(size_t)b * p.ld_out + n] = v[j];
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                     : "memory");
+    }
+}
+
+// fp32 rows -> normalised bf16 rows (LayerNorm or RMSNorm), the tensor-core GEMMs' B operand.
+__global__ void __launch_bounds__(256) norm_bf16_kernel(const float* __restrict__ X, const float* __restrict__ gamma,
+                                                        const float* __restrict__ beta, const int* __restrict__ tok,
+                                                        __nv_bfloat16* __restrict__ out, int d, int rms, float eps) {
+    __shared__ float sh[8];
+    const int b = blockIdx.x;
+    if (tok[b] < 0) return;
+    const float* xr = X + (size_t)b * d;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    auto block_sum = [&](float v) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) sh[w] = v;
+        __syncthreads();
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) s += sh[i];
+        __syncthreads();
+        return s;
+    };
+    float s = 0.f;
+    for (int k = threadIdx.x; k < d; k += 256) {
+        const float v = xr[k];
+        s += rms ? v * v : v;
+    }
+    s = block_sum(s);
+    if (rms) {
+        const float r = 1.0f / sqrtf(s / (float)d + eps);
+        for (int k = threadIdx.x; k < d; k += 256) out[(size_t)b * d + k] = __float2bfloat16_rn(gamma[k] * xr[k] * r);
+    } else {
+        const float mean = s / (float)d;
+        float v2 = 0.f;
+        for (int k = threadIdx.x; k < d; k += 256) {
+            const float dl = xr[k] - mean;
+            v2 += dl * dl;
+        }
+        v2 = block_sum(v2);
+        const float inv_std = 1.0f / sqrtf(v2 / (float)d + eps);
+        for (int k = threadIdx.x; k < d; k += 256) {
+            out[(size_t)b * d + k] = __float2bfloat16_rn(gamma[k] * (xr[k] - mean) * inv_std + beta[k]);
+        }
+    }
+}
+
+// W (K, N) fp32 row-major -> W^T (N_pad, K) bf16 row-major, with a row mapping for the
+// interleaved gate/up layout.
+__global__ void transpose_bf16_kernel(const float* __restrict__ W, __nv_bfloat16* __restrict__ out, int K, int N,
+                                      int row_offset, int interleave_tiles) {
+    __shared__ float tile[32][33];
+    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int k = k0 + i, n = n0 + threadIdx.x;
+        tile[i][threadIdx.x] = (k < K && n < N) ? W[(size_t)k * N + n] : 0.f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int n = n0 + i, k = k0 + threadIdx.x;
+        if (n < N && k < K) {
+            // interleave: feature n of this matrix lands in 128-row tile pairs [gate tile | up tile]
+            const size_t row = interleave_tiles ? (size_t)(n / 128) * 256 + row_offset + (n % 128) : (size_t)row_offset + n;
+            out[row * K + k] = __float2bfloat16_rn(tile[threadIdx.x][i]);
+        }
+    }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            ptr = nullptr;
+        }
+        return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }();
+    return fn;
+}
+
+template <int EPI, int NW, int TN>
+void launch_t(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, dim3 grid, cudaStream_t st) {
+    constexpr size_t bytes = (size_t)kStages * (NW * kTileM * kBlockK * 2 + TN * kBlockK * 2) + 1024;
+    auto kernel = gemm_bf16_tc_kernel<EPI, NW, TN>;
+    if (!g_capturing) {
+        GRADB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    }
+    kernel<<<grid, 128, bytes, st>>>(a, b, p);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+template <int EPI, int NW>
+void launch_tn(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, int tn, dim3 grid, cudaStream_t st) {
+    switch (tn) {
+        case 32: launch_t<EPI, NW, 32>(a, b, p, grid, st); break;
+        case 64: launch_t<EPI, NW, 64>(a, b, p, grid, st); break;
+        case 128: launch_t<EPI, NW, 128>(a, b, p, grid, st); break;
+        default: throw Error(GRADB_ERR_INVALID, "unsupported token tile");
+    }
+}
+
+}  // namespace
+
+void make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    auto fn = encode_fn();
+    if (!fn) throw Error(GRADB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw Error(GRADB_ERR_CUDA, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
+}
+
+int tc_token_tile(int n_seq) { return n_seq <= 32 ? 32 : (n_seq <= 64 ? 64 : 128); }
+
+void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int token_tile,
+                    int k_splits, cudaStream_t st) {
+    const int n_tiles = (p.N + kTileM - 1) / kTileM;
+    const dim3 grid(n_tiles, (p.B + token_tile - 1) / token_tile, k_splits);
+    switch (epi) {
+        case TC_QKV: launch_tn<TC_QKV, 1>(map_a, map_b, p, token_tile, grid, st); break;
+        case TC_RESID: launch_tn<TC_RESID, 1>(map_a, map_b, p, token_tile, grid, st); break;
+        case TC_GELU: launch_tn<TC_GELU, 1>(map_a, map_b, p, token_tile, grid, st); break;
+        case TC_SWIGLU: launch_tn<TC_SWIGLU, 2>(map_a, map_b, p, token_tile, grid, st); break;
+        case TC_LOGITS: launch_tn<TC_LOGITS, 1>(map_a, map_b, p, token_tile, grid, st); break;
+        default: throw Error(GRADB_ERR_INVALID, "unknown epilogue");
+    }
+}
+
+void launch_norm_bf16(const float* X, const float* gamma, const float* beta, const int* tok, __nv_bfloat16* out, int d,
+                      int rms, float eps, int B, cudaStream_t st) {
+    norm_bf16_kernel<<<B, 256, 0, st>>>(X, gamma, beta, tok, out, d, rms, eps);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+void launch_transpose_bf16(const float* W, __nv_bfloat16* out, int K, int N, int row_offset, bool interleave,
+                           cudaStream_t st) {
+    const dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
+    transpose_bf16_kernel<<<grid, block, 0, st>>>(W, out, K, N, row_offset, interleave ? 1 : 0);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+}  // namespace gradb

@@ -2,6 +2,7 @@
 #include <cmath>
 
 #include "common.cuh"
+#include "gemm_tc.cuh"
 
 namespace gradb {
 
@@ -84,6 +85,35 @@ DeviceModel* upload_model(const gradb_model_desc& desc_in, const float* const* t
             w.wq16 = H(at(ix.wq)); w.wk16 = H(at(ix.wk)); w.wv16 = H(at(ix.wv)); w.wo16 = H(at(ix.wo));
             w.gate16 = H(at(ix.gate)); w.w116 = H(at(ix.w1)); w.w216 = H(at(ix.w2));
         }
+        m->tc_ok = precision == GRADB_BF16 && d % 64 == 0 && desc.d_ff % 64 == 0;
+        if (m->tc_ok) {
+            const int f = desc.d_ff;
+            for (int l = 0; l < desc.num_layers; l++) {
+                LayerWeights& w = m->layers[l];
+                const size_t up_rows = modern ? (size_t)((f + 127) / 128) * 256 : (size_t)f;
+                GRADB_CUDA(cudaMalloc(&w.qkvT, (size_t)3 * d * d * 2));
+                GRADB_CUDA(cudaMalloc(&w.oT, (size_t)d * d * 2));
+                GRADB_CUDA(cudaMalloc(&w.upT, up_rows * d * 2));
+                GRADB_CUDA(cudaMalloc(&w.downT, (size_t)d * f * 2));
+                GRADB_CUDA(cudaMemset(w.upT, 0, up_rows * d * 2));
+                launch_transpose_bf16(w.wq, w.qkvT, d, d, 0, false, nullptr);
+                launch_transpose_bf16(w.wk, w.qkvT, d, d, d, false, nullptr);
+                launch_transpose_bf16(w.wv, w.qkvT, d, d, 2 * d, false, nullptr);
+                launch_transpose_bf16(w.wo, w.oT, d, d, 0, false, nullptr);
+                if (modern) {
+                    launch_transpose_bf16(w.gate, w.upT, d, f, 0, true, nullptr);
+                    launch_transpose_bf16(w.w1, w.upT, d, f, 128, true, nullptr);
+                } else {
+                    launch_transpose_bf16(w.w1, w.upT, d, f, 0, false, nullptr);
+                }
+                launch_transpose_bf16(w.w2, w.downT, f, d, 0, false, nullptr);
+                make_tensor_map_bf16(&w.map_qkv, w.qkvT, (uint64_t)3 * d, d, 128);
+                make_tensor_map_bf16(&w.map_o, w.oT, d, d, 128);
+                make_tensor_map_bf16(&w.map_up, w.upT, up_rows, d, 128);
+                make_tensor_map_bf16(&w.map_down, w.downT, d, f, 128);
+            }
+            make_tensor_map_bf16(&m->map_emb, m->emb16, desc.vocab_size, d, 128);
+        }
         if (modern) {
             // RoPE angles, computed with the reference's own float expressions
             // (inference.cpp:169-175) on the host so that cos/sin bits are libm's.
@@ -114,6 +144,12 @@ void free_model(DeviceModel* m) {
     cudaSetDevice(m->device);
     cudaFree(m->blob);
     cudaFree(m->blob16);
+    for (LayerWeights& w : m->layers) {
+        cudaFree(w.qkvT);
+        cudaFree(w.oT);
+        cudaFree(w.upT);
+        cudaFree(w.downT);
+    }
     cudaFree(m->rope_cos);
     cudaFree(m->rope_sin);
     delete m;

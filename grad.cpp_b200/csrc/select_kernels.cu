@@ -45,6 +45,8 @@ __constant__ uint64_t c_exp2_tab[32] = {
 // expf with the bits of the host C library's, for finite x <= ~88.
 __device__ __forceinline__ float expf_libm(float x) {
     if (x < -0x1.9fe368p6f) return 0.0f;     // underflows to zero (also -inf, -1e10 - max)
+    // The one input in [-104, 0] where glibc 2.39's FMA-contracted build rounds the other way.
+    if (__float_as_uint(x) == 0xc27c65d9u) return 0x1.f45326p-92f;
     if (x != x) return x;
     if (x > 0x1.62e42ep6f) return INFINITY;
     const double InvLn2N = 0x1.71547652b82fep+0 * 32.0;

@@ -42,6 +42,16 @@ struct Timed {
     }
 };
 
+// After a stream synchronise: a kernel whose bounded wait expired left a code in the status word.
+void check_status(Session* s) {
+    int code = 0;
+    GRADB_CUDA(cudaMemcpy(&code, s->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (code != 0) {
+        cudaMemset(s->status, 0, sizeof(int));
+        throw Error(GRADB_ERR_DEVICE_WAIT, "a device-side wait expired (code " + std::to_string(code) + ")");
+    }
+}
+
 // After a stream synchronise: fold the recorded spans into per-class totals.
 void collect_spans(Session* s) {
     for (const Session::Span& sp : s->spans) {
@@ -59,7 +69,88 @@ void collect_spans(Session* s) {
 // Enqueues one decode step for rows 0..n_seq-1. tok_dev: current ids (<0 = skip row).
 // logit_tok_dev: same convention, selects which rows get logits (the prompt feed
 // only needs them at each sequence's last position).
+// Tensor-core variant of a step: every projection is a TMA-fed tcgen05 GEMM over all
+// sequences; norms produce the bf16 operand, attention stays the streaming kernel.
+void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit_tok_dev, bool append_history) {
+    const DeviceModel* m = s->m;
+    const bool modern = m->desc.arch == GRADB_ARCH_MODERN;
+    cudaStream_t st = s->stream;
+    const int d = s->d, f = s->dff, tn = s->token_tile;
+    const int token_tiles = (n_seq + tn - 1) / tn;
+    auto splits = [&](int n_tiles, int k_iters) {
+        int ks = 1;
+        while (ks < 8 && n_tiles * token_tiles * ks * 2 <= 64 && k_iters / (ks * 2) >= 2) ks *= 2;
+        return ks;
+    };
+    {
+        Timed t(s, KC_EMBED);
+        launch_embed(m->emb, modern ? nullptr : m->pos, tok_dev, s->pos, s->x, d, n_seq, st);
+    }
+    TcGemmParams base{};
+    base.B = n_seq; base.d = d; base.H = s->H; base.hs = s->hs; base.T = s->T;
+    base.tok = tok_dev; base.pos = s->pos; base.status = s->status;
+    for (int l = 0; l < s->L; l++) {
+        const LayerWeights& w = m->layers[l];
+        float* kc = s->kcache + (size_t)l * layer_cache_elems(s);
+        float* vc = s->vcache + (size_t)l * layer_cache_elems(s);
+        {
+            Timed t(s, KC_QKV);
+            launch_norm_bf16(s->x, w.n1g, w.n1b, tok_dev, s->h16, d, modern, 1e-5f, n_seq, st);
+            TcGemmParams g = base;
+            g.K = d; g.N = 3 * d; g.ld_out = d;
+            g.bias[0] = w.bq; g.bias[1] = w.bk; g.bias[2] = w.bv;
+            g.rope_cos = modern ? m->rope_cos : nullptr;
+            g.rope_sin = modern ? m->rope_sin : nullptr;
+            g.out_f32 = s->q; g.kcache = kc; g.vcache = vc;
+            launch_tc_gemm(TC_QKV, w.map_qkv, s->map_h16, g, tn, 1, st);
+        }
+        {
+            Timed t(s, KC_ATTN);
+            AttnParams a{};
+            a.q = s->q; a.kcache = kc; a.vcache = vc; a.tok = tok_dev; a.pos = s->pos;
+            a.out = s->attn; a.out16 = s->attn16; a.partial = s->attn_partial; a.counters = s->attn_counters;
+            a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = d;
+            a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
+            launch_attention(a, n_seq, s->attn_splits, st);
+        }
+        {
+            Timed t(s, KC_OPROJ);
+            TcGemmParams g = base;
+            g.K = d; g.N = d; g.ld_out = d; g.bias[0] = w.bo; g.out_f32 = s->x;
+            launch_tc_gemm(TC_RESID, w.map_o, s->map_attn16, g, tn, splits((d + 127) / 128, d / 64), st);
+        }
+        {
+            Timed t(s, KC_FFN_UP);
+            launch_norm_bf16(s->x, w.n2g, w.n2b, tok_dev, s->h16, d, modern, 1e-5f, n_seq, st);
+            TcGemmParams g = base;
+            g.K = d; g.N = f; g.ld_out = f; g.out_bf16 = s->ffn16;
+            g.bias[0] = modern ? nullptr : w.b1;
+            launch_tc_gemm(modern ? TC_SWIGLU : TC_GELU, w.map_up, s->map_h16, g, tn, 1, st);
+        }
+        {
+            Timed t(s, KC_FFN_DOWN);
+            TcGemmParams g = base;
+            g.K = f; g.N = d; g.ld_out = d; g.bias[0] = modern ? nullptr : w.b2; g.out_f32 = s->x;
+            launch_tc_gemm(TC_RESID, w.map_down, s->map_ffn16, g, tn, splits((d + 127) / 128, f / 64), st);
+        }
+    }
+    {
+        Timed t(s, KC_LOGITS);
+        launch_norm_bf16(s->x, m->fng, m->fnb, logit_tok_dev, s->h16, d, modern, 1e-5f, n_seq, st);
+        TcGemmParams g = base;
+        g.tok = logit_tok_dev;
+        g.K = d; g.N = s->V; g.ld_out = s->V; g.out_f32 = s->logits;
+        launch_tc_gemm(TC_LOGITS, m->map_emb, s->map_h16, g, tn, 1, st);
+    }
+    Timed t(s, KC_ADVANCE);
+    launch_advance(tok_dev, s->pos, append_history ? s->hist : nullptr, s->hist_len, s->hist_stride, n_seq, st);
+}
+
 void enqueue_step(Session* s, int n_seq, const int* tok_dev, const int* logit_tok_dev, bool append_history) {
+    if (s->use_tc && n_seq >= 16) {
+        enqueue_step_tc(s, n_seq, tok_dev, logit_tok_dev, append_history);
+        return;
+    }
     const DeviceModel* m = s->m;
     const bool modern = m->desc.arch == GRADB_ARCH_MODERN;
     const bool bf16 = m->precision == GRADB_BF16;
@@ -96,7 +187,7 @@ void enqueue_step(Session* s, int n_seq, const int* tok_dev, const int* logit_to
 
         AttnParams a{};
         a.q = s->q; a.kcache = g.kcache; a.vcache = g.vcache; a.tok = tok_dev; a.pos = s->pos;
-        a.out = s->attn; a.partial = s->attn_partial; a.counters = s->attn_counters;
+        a.out = s->attn; a.out16 = nullptr; a.partial = s->attn_partial; a.counters = s->attn_counters;
         a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = s->d;
         a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));  // inference.cpp:184
         {
@@ -295,6 +386,24 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         dalloc(&s->gen, B);
         dalloc(&s->done, B);
         dalloc(&s->out_tok, B);
+        dalloc(&s->status, 1);
+        GRADB_CUDA(cudaMemsetAsync(s->status, 0, sizeof(int), s->stream));
+        const char* ntc = std::getenv("GRADB_NO_TC");
+        s->use_tc = m->tc_ok && s->B >= 16 && !(ntc && ntc[0] == '1');
+        if (s->use_tc) {
+            s->token_tile = tc_token_tile(s->B);
+            // rows padded to a whole token tile so a TMA box never starts outside the buffer
+            const size_t rows = (size_t)((s->B + s->token_tile - 1) / s->token_tile) * s->token_tile;
+            dalloc(&s->h16, rows * s->d);
+            dalloc(&s->attn16, rows * s->d);
+            dalloc(&s->ffn16, rows * s->dff);
+            GRADB_CUDA(cudaMemsetAsync(s->h16, 0, rows * s->d * 2, s->stream));
+            GRADB_CUDA(cudaMemsetAsync(s->attn16, 0, rows * s->d * 2, s->stream));
+            GRADB_CUDA(cudaMemsetAsync(s->ffn16, 0, rows * s->dff * 2, s->stream));
+            make_tensor_map_bf16(&s->map_h16, s->h16, rows, s->d, s->token_tile);
+            make_tensor_map_bf16(&s->map_attn16, s->attn16, rows, s->d, s->token_tile);
+            make_tensor_map_bf16(&s->map_ffn16, s->ffn16, rows, s->dff, s->token_tile);
+        }
         GRADB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&s->h_stage), sizeof(int) * 4 * B));
         GRADB_CUDA(cudaEventCreate(&s->ev_begin));
         GRADB_CUDA(cudaEventCreate(&s->ev_end));
@@ -329,6 +438,7 @@ void destroy_session(Session* s) {
     cudaFree(s->tok); cudaFree(s->pos); cudaFree(s->hist); cudaFree(s->hist_len);
     cudaFree(s->gen); cudaFree(s->done); cudaFree(s->out_tok); cudaFree(s->tok_matrix);
     cudaFree(s->uniforms); cudaFree(s->probs);
+    cudaFree(s->h16); cudaFree(s->attn16); cudaFree(s->ffn16); cudaFree(s->status);
     if (s->h_stage) cudaFreeHost(s->h_stage);
     if (s->own_stream && s->stream) cudaStreamDestroy(s->stream);
     delete s;
@@ -367,6 +477,7 @@ void session_step(Session* s, const int32_t* tokens, int n_seq, float* logits_ho
     GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
+    if (s->use_tc) check_status(s);
     GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
     for (int b = 0; b < n_seq; b++) {
         if (tokens[b] >= 0) s->h_pos[b]++;
@@ -386,6 +497,7 @@ void session_prefill(Session* s, const int32_t* tokens, const int32_t* offsets, 
     }
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
+    if (s->use_tc) check_status(s);
     GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
     for (int b = 0; b < n_seq; b++) s->h_pos[b] += offsets[b + 1] - offsets[b];
 }
@@ -541,6 +653,7 @@ void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets
     GRADB_CUDA(cudaMemcpyAsync(hist.data(), s->hist, hist.size() * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
+    if (s->use_tc) check_status(s);
     for (int b = 0; b < n_seq; b++) {
         const int len = offsets[b + 1] - offsets[b];
         const int n = len <= 0 ? 0 : std::min(lens[b], out_stride);
@@ -565,6 +678,7 @@ void session_set_profiling(Session* s, bool on) {
     GRADB_CUDA(cudaSetDevice(s->m->device));
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
+    if (s->use_tc) check_status(s);
     s->profiling = on;
     for (int i = 0; i < kKernelClasses; i++) {
         s->class_ms[i] = 0.0;

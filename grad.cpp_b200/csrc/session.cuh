@@ -3,6 +3,7 @@
 // to many sequences; TextGen's loops, text_gen.cpp:37-120).
 #pragma once
 #include "common.cuh"
+#include "gemm_tc.cuh"
 #include "select_kernels.cuh"
 #include "step_kernels.cuh"
 
@@ -33,6 +34,13 @@ struct Session {
     float* uniforms = nullptr;
     size_t uniforms_cap = 0;
     float* probs = nullptr;  // [B][V], allocated on first use
+
+    // tensor-core path: bf16 activations (GEMM B operands), their TMA descriptors, device status word
+    bool use_tc = false;
+    int token_tile = 128;
+    __nv_bfloat16 *h16 = nullptr, *attn16 = nullptr, *ffn16 = nullptr;
+    CUtensorMap map_h16, map_attn16, map_ffn16;
+    int* status = nullptr;
 
     // host mirrors / staging (pinned)
     std::vector<int> h_pos;

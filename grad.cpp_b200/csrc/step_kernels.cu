@@ -472,6 +472,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode64_kernel(const At
         if (S == 1) {
             const float inv = 1.0f / Lsum;
             *reinterpret_cast<float2*>(p.out + (size_t)b * p.d + h * HS + 2 * lane) = make_float2(a0 * inv, a1 * inv);
+            if (p.out16) {
+                *reinterpret_cast<__nv_bfloat162*>(p.out16 + (size_t)b * p.d + h * HS + 2 * lane) =
+                    __floats2bfloat162_rn(a0 * inv, a1 * inv);
+            }
             return;
         }
         float* part = p.partial + ((size_t)(b * p.H + h) * S + split) * (HS + 2);
@@ -505,6 +509,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode64_kernel(const At
     }
     const float inv = 1.0f / Lt;
     *reinterpret_cast<float2*>(p.out + (size_t)b * p.d + h * HS + 2 * lane) = make_float2(c0 * inv, c1 * inv);
+    if (p.out16) {
+        *reinterpret_cast<__nv_bfloat162*>(p.out16 + (size_t)b * p.d + h * HS + 2 * lane) =
+            __floats2bfloat162_rn(c0 * inv, c1 * inv);
+    }
     if (lane == 0) p.counters[b * p.H + h] = 0;
 }
 
@@ -549,6 +557,7 @@ __global__ void __launch_bounds__(128) attn_decode_generic_kernel(const AttnPara
         float o = 0.f;
         for (int t = 0; t < ctx; t++) o += scores[t] * inv * V[(size_t)t * hs + c];
         p.out[(size_t)b * p.d + h * hs + c] = o;
+        if (p.out16) p.out16[(size_t)b * p.d + h * hs + c] = __float2bfloat16_rn(o);
     }
 }
 

@@ -41,6 +41,7 @@ struct AttnParams {
     const float *kcache, *vcache;
     const int *tok, *pos;
     float* out;       // [B][d]
+    __nv_bfloat16* out16;  // optional bf16 copy of out (operand of the tensor-core projection)
     float* partial;   // [B][H][S][hs+2] split results: o[hs], max, sum
     int* counters;    // [B][H] arrival tickets, zero between launches
     int H, hs, T, d;
