@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
     __shared__ uint32_t tmem_base_slot;
+    __shared__ int s_tok[TN], s_pos[TN];
 
     constexpr int kABytes = NW * kTileM * kBlockK * 2;
     constexpr int kBBytes = TN * kBlockK * 2;
@@ -137,6 +138,12 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
     const int k_beg = kz * k_per, k_end = min(k_iters_total, k_beg + k_per);
     const int n_iters = max(0, k_end - k_beg);
 
+    for (int c = threadIdx.x; c < TN; c += blockDim.x) {
+        const int b = blockIdx.y * TN + c;
+        const int tk = b < p.B ? p.tok[b] : kSkip;
+        s_tok[c] = tk;
+        s_pos[c] = tk >= 0 ? p.pos[b] : 0;
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) {
             mbar_init(&full_bar[s], 1);
@@ -217,52 +224,72 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
         } else if (EPI == TC_RESID || EPI == TC_GELU) {
             if (n_ok && p.bias[0] && kz == 0) bias = p.bias[0][n];
         }
+        const int h = n_in / p.hs, c_in = n_in % p.hs, half = p.hs / 2;
+        const bool rope = EPI == TC_QKV && p.rope_cos != nullptr && which < 2;
+        float* cache = which == 1 ? p.kcache : p.vcache;
         for (int c0 = 0; c0 < TN; c0 += 32) {
             float v[32], v2[32];
             tmem_ld32(lane_addr + c0, v);
             if (NW == 2) tmem_ld32(lane_addr + TN + c0, v2);
-#pragma unroll 4
-            for (int j = 0; j < 32; j++) {
-                const int b = tile_b * TN + c0 + j;
-                const bool live = b < p.B && p.tok[b] >= 0;  // warp-uniform
-                float val = v[j] + bias;
-                if (EPI == TC_QKV) {
-                    const int position = live ? p.pos[b] : 0;
-                    const int h = n_in / p.hs, c_in = n_in % p.hs;
-                    if (p.rope_cos && which < 2) {
-                        // pairs (2j, 2j+1) inside a head sit in neighbouring lanes (inference.cpp:101-115)
-                        const float other = __shfl_xor_sync(0xffffffffu, val, 1);
-                        const float cs = p.rope_cos[(size_t)position * (p.hs / 2) + c_in / 2];
-                        const float sn = p.rope_sin[(size_t)position * (p.hs / 2) + c_in / 2];
-                        val = (c_in & 1) ? (other * sn + val * cs) : (val * cs - other * sn);
+            // Eight tokens at a time: first every load the group needs (so they are all in
+            // flight together), then the arithmetic and the stores.
+#pragma unroll
+            for (int j0 = 0; j0 < 32; j0 += 8) {
+                float aux0[8], aux1[8];
+                int posn[8];
+                bool live[8];
+#pragma unroll
+                for (int jj = 0; jj < 8; jj++) {
+                    const int c = c0 + j0 + jj;
+                    live[jj] = s_tok[c] >= 0;  // warp-uniform; rows past the batch were staged as skipped
+                    posn[jj] = s_pos[c];
+                    aux0[jj] = aux1[jj] = 0.f;
+                    if (rope) {
+                        aux0[jj] = __ldg(p.rope_cos + (size_t)posn[jj] * half + c_in / 2);
+                        aux1[jj] = __ldg(p.rope_sin + (size_t)posn[jj] * half + c_in / 2);
                     }
-                    if (live && n_ok) {
-                        if (which == 0) {
-                            p.out_f32[(size_t)b * p.ld_out + n_in] = val;
-                        } else {
-                            float* cache = which == 1 ? p.kcache : p.vcache;
-                            cache[(((size_t)b * p.H + h) * p.T + position) * p.hs + c_in] = val;
+                    if (EPI == TC_RESID && gridDim.z == 1 && live[jj] && n_ok) {
+                        aux0[jj] = p.out_f32[(size_t)(tile_b * TN + c) * p.ld_out + n];
+                    }
+                }
+#pragma unroll
+                for (int jj = 0; jj < 8; jj++) {
+                    const int j = j0 + jj;
+                    const int b = tile_b * TN + c0 + j;
+                    float val = v[j] + bias;
+                    if (EPI == TC_QKV) {
+                        if (rope) {
+                            // pairs (2j, 2j+1) inside a head sit in neighbouring lanes (inference.cpp:101-115)
+                            const float other = __shfl_xor_sync(0xffffffffu, val, 1);
+                            val = (c_in & 1) ? (other * aux1[jj] + val * aux0[jj]) : (val * aux0[jj] - other * aux1[jj]);
                         }
+                        if (live[jj] && n_ok) {
+                            if (which == 0) {
+                                p.out_f32[(size_t)b * p.ld_out + n_in] = val;
+                            } else {
+                                cache[(((size_t)b * p.H + h) * p.T + posn[jj]) * p.hs + c_in] = val;
+                            }
+                        }
+                    } else if (EPI == TC_RESID) {
+                        if (live[jj] && n_ok) {
+                            float* y = p.out_f32 + (size_t)b * p.ld_out + n;
+                            if (gridDim.z == 1) *y = aux0[jj] + val;
+                            else atomicAdd(y, val);
+                        }
+                    } else if (EPI == TC_GELU) {
+                        if (live[jj] && n_ok) {
+                            const float u = 0.79788456f * (val + 0.044715f * val * val * val);
+                            p.out_bf16[(size_t)b * p.ld_out + n] = __float2bfloat16_rn(0.5f * val * (1.0f + tanhf(u)));
+                        }
+                    } else if (EPI == TC_SWIGLU) {
+                        if (live[jj] && n_ok) {
+                            const float gte = v[j];
+                            const float sg = gte / (1.0f + __expf(-gte));
+                            p.out_bf16[(size_t)b * p.ld_out + n] = __float2bfloat16_rn(v2[j] * sg);
+                        }
+                    } else {  // TC_LOGITS
+                        if (live[jj] && n_ok) p.out_f32[(size_t)b * p.ld_out + n] = v[j];
                     }
-                } else if (EPI == TC_RESID) {
-                    if (live && n_ok) {
-                        float* y = p.out_f32 + (size_t)b * p.ld_out + n;
-                        if (gridDim.z == 1) *y += val;
-                        else atomicAdd(y, val);
-                    }
-                } else if (EPI == TC_GELU) {
-                    if (live && n_ok) {
-                        const float u = 0.79788456f * (val + 0.044715f * val * val * val);
-                        p.out_bf16[(size_t)b * p.ld_out + n] = __float2bfloat16_rn(0.5f * val * (1.0f + tanhf(u)));
-                    }
-                } else if (EPI == TC_SWIGLU) {
-                    if (live && n_ok) {
-                        const float gte = v[j];
-                        const float sg = gte / (1.0f + expf(-gte));
-                        p.out_bf16[(size_t)b * p.ld_out + n] = __float2bfloat16_rn(v2[j] * sg);
-                    }
-                } else {  // TC_LOGITS
-                    if (b < p.B && p.tok[b] >= 0 && n_ok) p.out_f32[(size_t)b * p.ld_out + n] = v[j];
                 }
             }
         }
@@ -391,7 +418,15 @@ void make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
     if (r != CUDA_SUCCESS) throw Error(GRADB_ERR_CUDA, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
 }
 
-int tc_token_tile(int n_seq) { return n_seq <= 32 ? 32 : (n_seq <= 64 ? 64 : 128); }
+// Largest token tile that still yields enough CTAs to occupy most of the SMs: these GEMMs
+// are short, so CTA count (latency hiding across SMs) matters more than MMA width.
+int tc_token_tile(int n_seq, int n_tiles, int want_ctas) {
+    for (int tn : {128, 64, 32}) {
+        if (tn > 32 && tn >= 2 * n_seq) continue;  // do not pad a small batch to a wide tile
+        if (n_tiles * ((n_seq + tn - 1) / tn) >= want_ctas || tn == 32) return tn;
+    }
+    return 32;
+}
 
 void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int token_tile,
                     int k_splits, cudaStream_t st) {

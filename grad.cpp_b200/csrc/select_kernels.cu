@@ -95,56 +95,197 @@ struct ScanResult {
     int hit;     // first index whose running sum satisfied the predicate, or n
 };
 
+constexpr int kSerialPrefix = 128;   // terms one thread adds natively before the block-wide passes start
+constexpr int kMaxPer = 16;          // terms per thread per pass (register resident)
+constexpr int kMaxRange = kMaxPer * kSelThreads;
+
+// One block-wide pass over terms [start, pend) with PER terms per thread. Returns nothing;
+// the outcome is left in the shared scan state.
+struct ScanShared {
+    float sum;
+    int next, hit, stop, range;
+};
+
+template <int PER, typename Term, typename Hit>
+__device__ __forceinline__ void scan_pass(Term& term, Hit& hit, ScanShared* st, IncPair* wtot, int start, int pend,
+                                          float s0, int n) {
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int len = pend - start;
+    const int beg = min(pend, start + tid * PER), end = min(pend, beg + PER);
+    const uint32_t sb = __float_as_uint(s0);
+    const int sex = (int)(sb >> 23);
+    const int ue = sex - 150;                          // u = 2^(sex-127-23)
+    const uint32_t S0 = (sb & 0x7fffffu) | 0x800000u;  // s0 = S0 * u
+    IncPair tinc[PER];
+    IncPair loc = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        tinc[i].e = tinc[i].o = 0u;
+        if (beg + i < end) tinc[i] = term_inc(__float_as_uint(term(beg + i)), ue);
+        loc = compose(loc, tinc[i]);
+    }
+    // inclusive scan of the per-thread maps across the warp, then across warps
+    IncPair inc = loc;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        IncPair prev;
+        prev.e = __shfl_up_sync(0xffffffffu, inc.e, o);
+        prev.o = __shfl_up_sync(0xffffffffu, inc.o, o);
+        if (lane >= o) inc = compose(prev, inc);
+    }
+    if (lane == 31) wtot[w] = inc;
+    __syncthreads();
+    // scan of the 32 warp totals by every warp (lane i holds warp i's total)
+    IncPair wt = wtot[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        IncPair prev;
+        prev.e = __shfl_up_sync(0xffffffffu, wt.e, o);
+        prev.o = __shfl_up_sync(0xffffffffu, wt.o, o);
+        if (lane >= o) wt = compose(prev, wt);
+    }
+    IncPair ahead;  // everything before this warp
+    ahead.e = __shfl_sync(0xffffffffu, wt.e, (w + 31) & 31);
+    ahead.o = __shfl_sync(0xffffffffu, wt.o, (w + 31) & 31);
+    if (w == 0) ahead.e = ahead.o = 0u;
+    {
+        IncPair pl;  // everything before this lane inside the warp
+        pl.e = __shfl_up_sync(0xffffffffu, inc.e, 1);
+        pl.o = __shfl_up_sync(0xffffffffu, inc.o, 1);
+        if (lane == 0) pl.e = pl.o = 0u;
+        ahead = compose(ahead, pl);
+    }
+    // Walk this thread's terms from its now-known starting S.
+    uint32_t S = step_S(S0, ahead);
+    int my_stop = 0x7fffffff;  // where this thread wants the pass to stop
+    int my_kind = 0;           // 1: predicate holds after term my_stop; 2: term my_stop leaves the binade
+    if (S < kBinadeEnd) {
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            if (my_kind == 0 && beg + i < end) {
+                const uint32_t Sn = step_S(S, tinc[i]);
+                if (Sn >= kBinadeEnd) {
+                    my_stop = beg + i;
+                    my_kind = 2;
+                } else {
+                    S = Sn;
+                    if (hit(__uint_as_float(((uint32_t)sex << 23) | (S & 0x7fffffu)))) {
+                        my_stop = beg + i;
+                        my_kind = 1;
+                    }
+                }
+            }
+        }
+    }
+    if (my_kind != 0) atomicMin(&st->stop, my_stop);
+    __syncthreads();
+    const int stop = st->stop;
+    __syncthreads();
+    const float sv = __uint_as_float(((uint32_t)sex << 23) | (S & 0x7fffffu));
+    if (stop != 0x7fffffff) {
+        if (my_kind != 0 && my_stop == stop) {  // exactly one thread owns that term
+            st->stop = 0x7fffffff;
+            st->next = stop + 1;
+            st->range = max(kSelThreads, min(2 * (stop + 1 - start), kMaxRange));
+            if (my_kind == 1) {
+                st->hit = stop;
+                st->sum = sv;
+            } else {
+                const float s2 = __fadd_rn(sv, term(stop));  // into the next binade, natively
+                st->sum = s2;
+                if (hit(s2)) st->hit = stop;
+            }
+        }
+    } else if (end == pend && beg < end) {  // the owner of the pass's last term holds the sum so far
+        st->sum = sv;
+        st->next = pend;
+        st->range = min(2 * len, kMaxRange);
+    }
+    (void)n;
+}
+
 // sh: room for kSelWarps IncPair.
+//
+// Pass structure: a running sum that starts at zero crosses binades quickly at
+// first (1, 2, 4, ... terms apart), so one thread adds the first kSerialPrefix
+// terms natively. After that every pass covers an adaptive range (about twice
+// what the previous binade consumed, at most kMaxRange terms): each thread keeps
+// up to kMaxPer consecutive terms in registers, composes their maps, the block
+// scans the per-thread maps, and each thread walks its terms from its now-known
+// start looking for the predicate or for the term that leaves the binade.
 template <typename Term, typename Hit>
 __device__ ScanResult seq_scan(int n, Term term, Hit hit, uint32_t* sh) {
-    __shared__ float s_sum;
-    __shared__ int s_next, s_hit, s_stop;
+    __shared__ ScanShared st;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     IncPair* wtot = reinterpret_cast<IncPair*>(sh);
     if (tid == 0) {
-        s_sum = 0.0f;
-        s_next = 0;
-        s_hit = n;
-        s_stop = n;
+        float s = 0.0f;
+        int i = 0, h = n;
+        const int stop = min(n, kSerialPrefix);
+        while (i + 4 <= stop && h == n) {  // loads of a group are issued together, adds stay in order
+            const float a0 = term(i), a1 = term(i + 1), a2 = term(i + 2), a3 = term(i + 3);
+            const float s1 = __fadd_rn(s, a0), s2 = __fadd_rn(s1, a1), s3 = __fadd_rn(s2, a2), s4 = __fadd_rn(s3, a3);
+            if (hit(s4)) {  // monotone predicate: the first hit is somewhere in this group
+                if (hit(s1)) { h = i; s = s1; i += 1; }
+                else if (hit(s2)) { h = i + 1; s = s2; i += 2; }
+                else if (hit(s3)) { h = i + 2; s = s3; i += 3; }
+                else { h = i + 3; s = s4; i += 4; }
+            } else {
+                s = s4;
+                i += 4;
+            }
+        }
+        while (i < stop && h == n) {
+            s = __fadd_rn(s, term(i));
+            i++;
+            if (hit(s)) h = i - 1;
+        }
+        st.sum = s;
+        st.next = i;
+        st.hit = h;
+        st.stop = 0x7fffffff;
+        st.range = kSelThreads;
     }
     __syncthreads();
     // Every pass consumes at least one term, so the bound is never the exit in practice.
     for (int guard = 0; guard < 8192; guard++) {
-        const int start = s_next;
-        const float s0 = s_sum;
-        if (start >= n || s_hit < n) break;
-        const int per = (n - start + kSelThreads - 1) / kSelThreads;
-        const int beg = min(n, start + tid * per), end = min(n, beg + per);
+        const int start = st.next;
+        const float s0 = st.sum;
+        if (start >= n || st.hit < n) break;
+        const int len = min(st.range, n - start);
+        const int pend = start + len;
+        const int per = (len + kSelThreads - 1) / kSelThreads;  // <= kMaxPer
+        const int beg = min(pend, start + tid * per), end = min(pend, beg + per);
         const uint32_t sb = __float_as_uint(s0);
         const int sex = (int)(sb >> 23);
 
         if (s0 == 0.0f) {
-            // Zeros leave the sum at zero: jump to the first non-zero term.
+            // Zeros leave the sum at zero: jump to the first non-zero term of the range.
             if (hit(0.0f)) {
-                if (tid == 0) s_hit = start;
+                if (tid == 0) st.hit = start;
                 __syncthreads();
                 break;
             }
-            int first = n;
+            int first = 0x7fffffff;
             for (int i = beg; i < end; i++) {
                 if (term(i) != 0.0f) {
                     first = i;
                     break;
                 }
             }
-            if (first < n) atomicMin(&s_stop, first);
+            if (first != 0x7fffffff) atomicMin(&st.stop, first);
             __syncthreads();
             if (tid == 0) {
-                const int j = s_stop;
-                s_stop = n;
-                if (j >= n) {
-                    s_next = n;
+                const int j = st.stop;
+                st.stop = 0x7fffffff;
+                if (j == 0x7fffffff) {
+                    st.next = pend;
+                    st.range = min(2 * len, kMaxRange);
                 } else {
                     const float v = term(j);
-                    s_sum = v;
-                    s_next = j + 1;
-                    if (hit(v)) s_hit = j;
+                    st.sum = v;
+                    st.next = j + 1;
+                    if (hit(v)) st.hit = j;
                 }
             }
             __syncthreads();
@@ -160,90 +301,30 @@ __device__ ScanResult seq_scan(int n, Term term, Hit hit, uint32_t* sh) {
                     s = __fadd_rn(s, term(i));
                     i++;
                     if (hit(s)) {
-                        s_hit = i - 1;
+                        st.hit = i - 1;
                         break;
                     }
                     const int e2 = (int)(__float_as_uint(s) >> 23);
                     if (e2 >= 30 && e2 < 254) break;
                 }
-                s_sum = s;
-                s_next = i;
+                st.sum = s;
+                st.next = i;
             }
             __syncthreads();
             continue;
         }
 
-        const int ue = sex - 150;                          // u = 2^(sex-127-23)
-        const uint32_t S0 = (sb & 0x7fffffu) | 0x800000u;  // s0 = S0 * u
-        IncPair loc = {0u, 0u};
-        for (int i = beg; i < end; i++) loc = compose(loc, term_inc(__float_as_uint(term(i)), ue));
-        // inclusive scan of the per-thread maps across the warp, then across warps
-        IncPair inc = loc;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            IncPair prev;
-            prev.e = __shfl_up_sync(0xffffffffu, inc.e, o);
-            prev.o = __shfl_up_sync(0xffffffffu, inc.o, o);
-            if (lane >= o) inc = compose(prev, inc);
-        }
-        if (lane == 31) wtot[w] = inc;
-        __syncthreads();
-        IncPair ahead = {0u, 0u};  // everything before this warp
-        for (int i = 0; i < w; i++) ahead = compose(ahead, wtot[i]);
-        {
-            IncPair pl;  // everything before this lane inside the warp
-            pl.e = __shfl_up_sync(0xffffffffu, inc.e, 1);
-            pl.o = __shfl_up_sync(0xffffffffu, inc.o, 1);
-            if (lane == 0) pl.e = pl.o = 0u;
-            ahead = compose(ahead, pl);
-        }
-        // Walk this thread's terms from its now-known starting S.
-        uint32_t S = step_S(S0, ahead);
-        int my_stop = n;  // where this thread wants the pass to stop
-        int my_kind = 0;  // 1: predicate holds after term my_stop; 2: term my_stop leaves the binade
-        if (S < kBinadeEnd) {
-            for (int i = beg; i < end; i++) {
-                const uint32_t Sn = step_S(S, term_inc(__float_as_uint(term(i)), ue));
-                if (Sn >= kBinadeEnd) {
-                    my_stop = i;
-                    my_kind = 2;
-                    break;
-                }
-                S = Sn;
-                if (hit(__uint_as_float(((uint32_t)sex << 23) | (S & 0x7fffffu)))) {
-                    my_stop = i;
-                    my_kind = 1;
-                    break;
-                }
-            }
-        }
-        if (my_kind != 0) atomicMin(&s_stop, my_stop);
-        __syncthreads();
-        const int stop = s_stop;
-        __syncthreads();
-        const float sv = __uint_as_float(((uint32_t)sex << 23) | (S & 0x7fffffu));
-        if (stop < n) {
-            if (my_kind != 0 && my_stop == stop) {  // exactly one thread owns that term
-                s_stop = n;
-                s_next = stop + 1;
-                if (my_kind == 1) {
-                    s_hit = stop;
-                    s_sum = sv;
-                } else {
-                    const float s2 = __fadd_rn(sv, term(stop));  // into the next binade, natively
-                    s_sum = s2;
-                    if (hit(s2)) s_hit = stop;
-                }
-            }
-        } else if (end == n && beg < end) {  // the owner of the last term holds the total
-            s_sum = sv;
-            s_next = n;
-        }
+        // terms per thread this pass: the smallest of 1, 2, 4, 8, 16 that covers the range
+        if (per <= 1) scan_pass<1>(term, hit, &st, wtot, start, pend, s0, n);
+        else if (per <= 2) scan_pass<2>(term, hit, &st, wtot, start, pend, s0, n);
+        else if (per <= 4) scan_pass<4>(term, hit, &st, wtot, start, pend, s0, n);
+        else if (per <= 8) scan_pass<8>(term, hit, &st, wtot, start, pend, s0, n);
+        else scan_pass<16>(term, hit, &st, wtot, start, pend, s0, n);
         __syncthreads();
     }
     ScanResult r;
-    r.sum = s_sum;
-    r.hit = s_hit;
+    r.sum = st.sum;
+    r.hit = st.hit;
     __syncthreads();
     return r;
 }
@@ -268,10 +349,89 @@ __device__ void sort_desc(float* a, int n_pad) {
     }
 }
 
+constexpr int kBuckets = 4096;
+constexpr int kBucketMax = 96;  // larger buckets fall back to the bitonic sort
+
+// Descending sort of src[0..n) into dst[0..n) by value buckets: a monotone map
+// sends each key to one of kBuckets ranges, a histogram + prefix sum places the
+// ranges, and each (small) range is finished by insertion. Returns false, with
+// dst unspecified, when the keys are too clustered for that (many equal values)
+// or not finite; the caller then sorts bitonically.
+__device__ bool bucket_sort_desc(const float* src, float* dst, int n, float mn, float mx, int* hist) {
+    __shared__ int s_bad;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    if (tid == 0) s_bad = 0;
+    for (int i = tid; i < kBuckets; i += kSelThreads) hist[i] = 0;
+    __syncthreads();
+    const float span = mx - mn;
+    if (!(span > 0.0f) || !(span < 3.0e38f)) return false;  // all equal, NaN or infinite keys
+    const float scale = (float)(kBuckets - 1) / span;
+    auto bucket_of = [&](float v) {
+        int bkt = (int)((mx - v) * scale);  // monotone in v: larger keys land in lower buckets
+        return min(max(bkt, 0), kBuckets - 1);
+    };
+    for (int i = tid; i < n; i += kSelThreads) atomicAdd(&hist[bucket_of(src[i])], 1);
+    __syncthreads();
+    // exclusive prefix sum of the histogram: 4 consecutive buckets per thread
+    constexpr int kPer = kBuckets / kSelThreads;
+    int c[kPer], tot = 0;
+#pragma unroll
+    for (int i = 0; i < kPer; i++) {
+        c[i] = hist[tid * kPer + i];
+        if (c[i] > kBucketMax) s_bad = 1;
+        tot += c[i];
+    }
+    int inc = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+    }
+    __shared__ int wsum[kSelWarps];
+    if (lane == 31) wsum[w] = inc;
+    __syncthreads();
+    int wv = wsum[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, wv, o);
+        if (lane >= o) wv += v;
+    }
+    int base = __shfl_sync(0xffffffffu, wv, (w + 31) & 31);
+    if (w == 0) base = 0;
+    base += inc - tot;
+    if (s_bad) return false;  // uniform: s_bad was written before the barrier above
+#pragma unroll
+    for (int i = 0; i < kPer; i++) {
+        hist[tid * kPer + i] = base;  // becomes the write cursor of the bucket
+        base += c[i];
+    }
+    __syncthreads();
+    for (int i = tid; i < n; i += kSelThreads) {
+        const float v = src[i];
+        dst[atomicAdd(&hist[bucket_of(v)], 1)] = v;
+    }
+    __syncthreads();
+    // hist[b] is now the END of bucket b; finish each bucket by insertion (descending)
+    for (int bkt = tid; bkt < kBuckets; bkt += kSelThreads) {
+        const int lo = bkt == 0 ? 0 : hist[bkt - 1], hi = hist[bkt];
+        for (int i = lo + 1; i < hi; i++) {
+            const float v = dst[i];
+            int j = i - 1;
+            while (j >= lo && dst[j] < v) {
+                dst[j + 1] = dst[j];
+                j--;
+            }
+            dst[j + 1] = v;
+        }
+    }
+    __syncthreads();
+    return true;
+}
+
 __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams p) {
     extern __shared__ __align__(16) float smem[];
     __shared__ uint32_t scan_sh[2 * kSelWarps + 4];
-    __shared__ float red_v[kSelWarps];
+    __shared__ float red_v[kSelWarps], red_lo[kSelWarps];
     __shared__ int red_i[kSelWarps];
     __shared__ int s_pick;
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -345,9 +505,31 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         float kth = -INFINITY;
         float mx;
         if (use_k || use_p) {
-            for (int i = tid; i < n_pad; i += kSelThreads) sorted[i] = i < V ? x[i] : -INFINITY;
+            float m = -INFINITY, lo = INFINITY;
+            for (int i = tid; i < V; i += kSelThreads) {
+                m = fmaxf(m, x[i]);
+                lo = fminf(lo, x[i]);
+            }
+            m = warp_max(m);
+            lo = -warp_max(-lo);
+            if (lane == 0) {
+                red_v[w] = m;
+                red_lo[w] = lo;
+            }
             __syncthreads();
-            sort_desc(sorted, n_pad);
+            m = red_v[0];
+            lo = red_lo[0];
+            for (int i = 1; i < kSelWarps; i++) {
+                m = fmaxf(m, red_v[i]);
+                lo = fminf(lo, red_lo[i]);
+            }
+            __syncthreads();
+            if (!bucket_sort_desc(x, sorted, V, lo, m, reinterpret_cast<int*>(sorted + n_pad))) {
+                __syncthreads();
+                for (int i = tid; i < n_pad; i += kSelThreads) sorted[i] = i < V ? x[i] : -INFINITY;
+                __syncthreads();
+                sort_desc(sorted, n_pad);
+            }
             mx = sorted[0];
             if (use_k) {  // text_gen.cpp:138-154: below the k-th largest value -> -1e10, ties kept
                 kth = sorted[p.top_k - 1];
@@ -429,7 +611,7 @@ size_t select_smem_bytes(int V, int* n_pad_out) {
     int n_pad = 1;
     while (n_pad < V) n_pad <<= 1;
     if (n_pad_out) *n_pad_out = n_pad;
-    return ((size_t)V + n_pad) * sizeof(float);
+    return ((size_t)V + n_pad) * sizeof(float) + kBuckets * sizeof(int);
 }
 
 void configure_select(int V) {

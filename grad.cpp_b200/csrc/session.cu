@@ -75,11 +75,14 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
     const DeviceModel* m = s->m;
     const bool modern = m->desc.arch == GRADB_ARCH_MODERN;
     cudaStream_t st = s->stream;
-    const int d = s->d, f = s->dff, tn = s->token_tile;
-    const int token_tiles = (n_seq + tn - 1) / tn;
-    auto splits = [&](int n_tiles, int k_iters) {
+    const int d = s->d, f = s->dff;
+    const int want = m->sm_count * 3 / 4;
+    auto tile_for = [&](int n_features) { return tc_token_tile(n_seq, (n_features + 127) / 128, want); };
+    auto map_idx = [](int tn) { return tn == 32 ? 0 : (tn == 64 ? 1 : 2); };
+    auto splits = [&](int n_features, int tn, int k_iters) {
+        const int ctas = ((n_features + 127) / 128) * ((n_seq + tn - 1) / tn);
         int ks = 1;
-        while (ks < 8 && n_tiles * token_tiles * ks * 2 <= 64 && k_iters / (ks * 2) >= 2) ks *= 2;
+        while (ks < 8 && ctas * ks * 2 <= m->sm_count * 3 / 2 && k_iters / (ks * 2) >= 2) ks *= 2;
         return ks;
     };
     {
@@ -102,7 +105,8 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
             g.rope_cos = modern ? m->rope_cos : nullptr;
             g.rope_sin = modern ? m->rope_sin : nullptr;
             g.out_f32 = s->q; g.kcache = kc; g.vcache = vc;
-            launch_tc_gemm(TC_QKV, w.map_qkv, s->map_h16, g, tn, 1, st);
+            const int tn = tile_for(3 * d);
+            launch_tc_gemm(TC_QKV, w.map_qkv, s->map_h16[map_idx(tn)], g, tn, 1, st);
         }
         {
             Timed t(s, KC_ATTN);
@@ -117,7 +121,8 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
             Timed t(s, KC_OPROJ);
             TcGemmParams g = base;
             g.K = d; g.N = d; g.ld_out = d; g.bias[0] = w.bo; g.out_f32 = s->x;
-            launch_tc_gemm(TC_RESID, w.map_o, s->map_attn16, g, tn, splits((d + 127) / 128, d / 64), st);
+            const int tn = tile_for(d);
+            launch_tc_gemm(TC_RESID, w.map_o, s->map_attn16[map_idx(tn)], g, tn, splits(d, tn, d / 64), st);
         }
         {
             Timed t(s, KC_FFN_UP);
@@ -125,13 +130,15 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
             TcGemmParams g = base;
             g.K = d; g.N = f; g.ld_out = f; g.out_bf16 = s->ffn16;
             g.bias[0] = modern ? nullptr : w.b1;
-            launch_tc_gemm(modern ? TC_SWIGLU : TC_GELU, w.map_up, s->map_h16, g, tn, 1, st);
+            const int tn = tile_for(f);
+            launch_tc_gemm(modern ? TC_SWIGLU : TC_GELU, w.map_up, s->map_h16[map_idx(tn)], g, tn, 1, st);
         }
         {
             Timed t(s, KC_FFN_DOWN);
             TcGemmParams g = base;
             g.K = f; g.N = d; g.ld_out = d; g.bias[0] = modern ? nullptr : w.b2; g.out_f32 = s->x;
-            launch_tc_gemm(TC_RESID, w.map_down, s->map_ffn16, g, tn, splits((d + 127) / 128, f / 64), st);
+            const int tn = tile_for(d);
+            launch_tc_gemm(TC_RESID, w.map_down, s->map_ffn16[map_idx(tn)], g, tn, splits(d, tn, f / 64), st);
         }
     }
     {
@@ -140,7 +147,8 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
         TcGemmParams g = base;
         g.tok = logit_tok_dev;
         g.K = d; g.N = s->V; g.ld_out = s->V; g.out_f32 = s->logits;
-        launch_tc_gemm(TC_LOGITS, m->map_emb, s->map_h16, g, tn, 1, st);
+        const int tn = tile_for(s->V);
+        launch_tc_gemm(TC_LOGITS, m->map_emb, s->map_h16[map_idx(tn)], g, tn, 1, st);
     }
     Timed t(s, KC_ADVANCE);
     launch_advance(tok_dev, s->pos, append_history ? s->hist : nullptr, s->hist_len, s->hist_stride, n_seq, st);
@@ -391,18 +399,20 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         const char* ntc = std::getenv("GRADB_NO_TC");
         s->use_tc = m->tc_ok && s->B >= 16 && !(ntc && ntc[0] == '1');
         if (s->use_tc) {
-            s->token_tile = tc_token_tile(s->B);
-            // rows padded to a whole token tile so a TMA box never starts outside the buffer
-            const size_t rows = (size_t)((s->B + s->token_tile - 1) / s->token_tile) * s->token_tile;
+            // rows padded to a whole 128-row tile so a TMA box never starts outside the buffer
+            const size_t rows = (size_t)((s->B + 127) / 128) * 128;
             dalloc(&s->h16, rows * s->d);
             dalloc(&s->attn16, rows * s->d);
             dalloc(&s->ffn16, rows * s->dff);
             GRADB_CUDA(cudaMemsetAsync(s->h16, 0, rows * s->d * 2, s->stream));
             GRADB_CUDA(cudaMemsetAsync(s->attn16, 0, rows * s->d * 2, s->stream));
             GRADB_CUDA(cudaMemsetAsync(s->ffn16, 0, rows * s->dff * 2, s->stream));
-            make_tensor_map_bf16(&s->map_h16, s->h16, rows, s->d, s->token_tile);
-            make_tensor_map_bf16(&s->map_attn16, s->attn16, rows, s->d, s->token_tile);
-            make_tensor_map_bf16(&s->map_ffn16, s->ffn16, rows, s->dff, s->token_tile);
+            for (int i = 0; i < 3; i++) {
+                const uint32_t tn = 32u << i;
+                make_tensor_map_bf16(&s->map_h16[i], s->h16, rows, s->d, tn);
+                make_tensor_map_bf16(&s->map_attn16[i], s->attn16, rows, s->d, tn);
+                make_tensor_map_bf16(&s->map_ffn16[i], s->ffn16, rows, s->dff, tn);
+            }
         }
         GRADB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&s->h_stage), sizeof(int) * 4 * B));
         GRADB_CUDA(cudaEventCreate(&s->ev_begin));

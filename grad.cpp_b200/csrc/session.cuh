@@ -37,9 +37,8 @@ struct Session {
 
     // tensor-core path: bf16 activations (GEMM B operands), their TMA descriptors, device status word
     bool use_tc = false;
-    int token_tile = 128;
     __nv_bfloat16 *h16 = nullptr, *attn16 = nullptr, *ffn16 = nullptr;
-    CUtensorMap map_h16, map_attn16, map_ffn16;
+    CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];  // token tiles of 32, 64, 128 rows
     int* status = nullptr;
 
     // host mirrors / staging (pinned)
