@@ -266,7 +266,7 @@ int gradb_kernel_class_count(void) { return kKernelClasses; }
 
 const char* gradb_kernel_class_name(int cls) {
     static const char* const names[kKernelClasses] = {"embed",    "norm_qkv_rope", "attn_decode", "attn_out_proj", "norm_ffn_up",
-                                                      "ffn_down", "norm_logits",   "advance",     "select"};
+                                                      "ffn_down", "norm_logits",   "advance",     "select",        "decode_step_b1"};
     return cls >= 0 && cls < kKernelClasses ? names[cls] : "";
 }
 

@@ -53,6 +53,8 @@ struct LayerWeights {
     CUtensorMap map_qkv, map_o, map_up, map_down;
 };
 
+struct B1Plan;
+
 struct DeviceModel {
     gradb_model_desc desc{};
     int device = 0;
@@ -68,6 +70,7 @@ struct DeviceModel {
     int sm_count = 148;
     bool tc_ok = false;   // shapes fit the tensor-core kernels (BF16 mode, d and d_ff multiples of 64)
     CUtensorMap map_emb;  // (V, d) bf16 embedding table = the logits GEMM's A operand
+    B1Plan* b1 = nullptr; // per-CTA weight tiles for the single-sequence persistent kernel
 };
 
 DeviceModel* upload_model(const gradb_model_desc& desc, const float* const* tensors, int n_tensors, int device,

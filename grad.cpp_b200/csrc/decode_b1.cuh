@@ -1,0 +1,56 @@
+// Single-sequence decode step as ONE persistent cooperative kernel (decode_b1.cu).
+#pragma once
+#include "common.cuh"
+
+namespace gradb {
+
+// How one (K x N) projection is cut into per-CTA tiles: N into column tiles of CW
+// columns, K into KS slices of Kt rows. Tile (ct, ks) belongs to CTA ks*col_tiles+ct
+// and is stored contiguously ([Kt][CW], zero padded) so it can be fetched with one
+// bulk copy.
+struct B1Mat {
+    int K, N, CW, KS, Kt, col_tiles, tiles;
+    int tile_elems;  // Kt * CW
+};
+
+struct B1Layer {
+    const void *qkv, *o, *gate, *up, *down;  // packed tiles (fp32 or bf16)
+    const float *bq, *bk, *bv, *bo, *b1, *b2, *n1g, *n1b, *n2g, *n2b;
+};
+
+struct B1Plan {
+    bool ok = false;
+    int G = 0;  // CTAs = SMs
+    int wbytes = 4;
+    B1Mat qkv{}, o{}, up{}, down{};
+    int logit_rows_per_cta = 0, logit_chunk_rows = 0;
+    int attn_splits = 1;
+    B1Layer* layers_dev = nullptr;  // [L]
+    std::vector<void*> owned;       // packed buffers
+};
+
+struct B1Params {
+    int G, d, dff, H, hs, V, L, T, modern, wbytes;
+    B1Mat qkv, o, up, down;
+    int logit_rows_per_cta, logit_chunk_rows, attn_splits;
+    const B1Layer* layers;
+    const float* emb32;  // (V, d) fp32: token lookup
+    const void* emb_w;   // (V, d) in the weight precision: logits
+    const float *pos_emb, *fng, *fnb, *rope_cos, *rope_sin;
+    float *kcache, *vcache;  // [L][1][H][T][hs] of sequence 0
+    size_t layer_cache_stride;
+    // exchange buffers (global, L2 resident)
+    float *q, *attn_part, *opart, *ffn, *dpart, *logits;
+    const int *tok, *logit_tok;
+    int *pos, *hist, *hist_len;
+    int hist_stride, append_hist;
+    unsigned *bar_counter, *bar_base;
+    int* status;
+};
+
+B1Plan* b1_make_plan(const DeviceModel* m);
+void b1_free_plan(B1Plan* p);
+size_t b1_workspace_floats(const DeviceModel* m, const B1Plan* plan);
+void launch_decode_b1(const B1Params& p, cudaStream_t st);
+
+}  // namespace gradb

@@ -2,6 +2,7 @@
 #include <cmath>
 
 #include "common.cuh"
+#include "decode_b1.cuh"
 #include "gemm_tc.cuh"
 
 namespace gradb {
@@ -132,6 +133,7 @@ DeviceModel* upload_model(const gradb_model_desc& desc_in, const float* const* t
             GRADB_CUDA(cudaMemcpy(m->rope_sin, s.data(), s.size() * sizeof(float), cudaMemcpyHostToDevice));
         }
         GRADB_CUDA(cudaDeviceSynchronize());
+        m->b1 = b1_make_plan(m);
         return m;
     } catch (...) {
         free_model(m);
@@ -142,6 +144,7 @@ DeviceModel* upload_model(const gradb_model_desc& desc_in, const float* const* t
 void free_model(DeviceModel* m) {
     if (!m) return;
     cudaSetDevice(m->device);
+    b1_free_plan(m->b1);
     cudaFree(m->blob);
     cudaFree(m->blob16);
     for (LayerWeights& w : m->layers) {

@@ -154,7 +154,47 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
     launch_advance(tok_dev, s->pos, append_history ? s->hist : nullptr, s->hist_len, s->hist_stride, n_seq, st);
 }
 
+// The whole step of a single sequence as one persistent kernel.
+void enqueue_step_b1(Session* s, const int* tok_dev, const int* logit_tok_dev, bool append_history) {
+    const DeviceModel* m = s->m;
+    const B1Plan* plan = m->b1;
+    const bool modern = m->desc.arch == GRADB_ARCH_MODERN;
+    B1Params p{};
+    p.G = plan->G; p.d = s->d; p.dff = s->dff; p.H = s->H; p.hs = s->hs; p.V = s->V; p.L = s->L; p.T = s->T;
+    p.modern = modern; p.wbytes = plan->wbytes;
+    p.qkv = plan->qkv; p.o = plan->o; p.up = plan->up; p.down = plan->down;
+    p.logit_rows_per_cta = plan->logit_rows_per_cta; p.logit_chunk_rows = plan->logit_chunk_rows;
+    p.attn_splits = plan->attn_splits;
+    p.layers = plan->layers_dev;
+    p.emb32 = m->emb;
+    p.emb_w = plan->wbytes == 2 ? (const void*)m->emb16 : (const void*)m->emb;
+    p.pos_emb = modern ? nullptr : m->pos;
+    p.fng = m->fng; p.fnb = m->fnb;
+    p.rope_cos = modern ? m->rope_cos : nullptr;
+    p.rope_sin = modern ? m->rope_sin : nullptr;
+    p.kcache = s->kcache; p.vcache = s->vcache;
+    p.layer_cache_stride = layer_cache_elems(s);
+    float* ws = s->b1_ws;
+    p.q = ws; ws += s->d;
+    p.attn_part = ws; ws += (size_t)s->H * plan->attn_splits * (s->hs + 2);
+    p.opart = ws; ws += (size_t)plan->o.KS * s->d;
+    p.ffn = ws; ws += s->dff;
+    p.dpart = ws;
+    p.logits = s->logits;
+    p.tok = tok_dev; p.logit_tok = logit_tok_dev;
+    p.pos = s->pos; p.hist = s->hist; p.hist_len = s->hist_len;
+    p.hist_stride = s->hist_stride; p.append_hist = append_history ? 1 : 0;
+    p.bar_counter = s->b1_bar; p.bar_base = s->b1_bar + 1;
+    p.status = s->status;
+    Timed t(s, KC_STEP_B1);
+    launch_decode_b1(p, s->stream);
+}
+
 void enqueue_step(Session* s, int n_seq, const int* tok_dev, const int* logit_tok_dev, bool append_history) {
+    if (s->use_b1 && n_seq == 1) {
+        enqueue_step_b1(s, tok_dev, logit_tok_dev, append_history);
+        return;
+    }
     if (s->use_tc && n_seq >= 16) {
         enqueue_step_tc(s, n_seq, tok_dev, logit_tok_dev, append_history);
         return;
@@ -396,6 +436,13 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         dalloc(&s->out_tok, B);
         dalloc(&s->status, 1);
         GRADB_CUDA(cudaMemsetAsync(s->status, 0, sizeof(int), s->stream));
+        const char* nb1 = std::getenv("GRADB_NO_B1");
+        s->use_b1 = s->B == 1 && m->b1 && m->b1->ok && !(nb1 && nb1[0] == '1');
+        if (s->use_b1) {
+            dalloc(&s->b1_ws, b1_workspace_floats(m, m->b1));
+            dalloc(&s->b1_bar, 2);
+            GRADB_CUDA(cudaMemsetAsync(s->b1_bar, 0, 2 * sizeof(unsigned), s->stream));
+        }
         const char* ntc = std::getenv("GRADB_NO_TC");
         s->use_tc = m->tc_ok && s->B >= 16 && !(ntc && ntc[0] == '1');
         if (s->use_tc) {
@@ -448,6 +495,7 @@ void destroy_session(Session* s) {
     cudaFree(s->tok); cudaFree(s->pos); cudaFree(s->hist); cudaFree(s->hist_len);
     cudaFree(s->gen); cudaFree(s->done); cudaFree(s->out_tok); cudaFree(s->tok_matrix);
     cudaFree(s->uniforms); cudaFree(s->probs);
+    cudaFree(s->b1_ws); cudaFree(s->b1_bar);
     cudaFree(s->h16); cudaFree(s->attn16); cudaFree(s->ffn16); cudaFree(s->status);
     if (s->h_stage) cudaFreeHost(s->h_stage);
     if (s->own_stream && s->stream) cudaStreamDestroy(s->stream);
@@ -487,7 +535,7 @@ void session_step(Session* s, const int32_t* tokens, int n_seq, float* logits_ho
     GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
-    if (s->use_tc) check_status(s);
+    if (s->use_tc || s->use_b1) check_status(s);
     GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
     for (int b = 0; b < n_seq; b++) {
         if (tokens[b] >= 0) s->h_pos[b]++;
@@ -507,7 +555,7 @@ void session_prefill(Session* s, const int32_t* tokens, const int32_t* offsets, 
     }
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
-    if (s->use_tc) check_status(s);
+    if (s->use_tc || s->use_b1) check_status(s);
     GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
     for (int b = 0; b < n_seq; b++) s->h_pos[b] += offsets[b + 1] - offsets[b];
 }
@@ -646,7 +694,7 @@ void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets
             launch_select(p, n_seq, s->stream);  // the last ids need no further step
         } else if (graph_ok) {
             GRADB_CUDA(cudaGraphLaunch(s->graph, s->stream));
-            count_launch(4 + 5 * s->L);  // kernels inside the graph
+            count_launch(s->use_b1 && n_seq == 1 ? 2 : 4 + 5 * s->L);  // kernels inside the graph
         } else {
             {
                 Timed t(s, KC_SELECT);
@@ -663,7 +711,7 @@ void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets
     GRADB_CUDA(cudaMemcpyAsync(hist.data(), s->hist, hist.size() * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
-    if (s->use_tc) check_status(s);
+    if (s->use_tc || s->use_b1) check_status(s);
     for (int b = 0; b < n_seq; b++) {
         const int len = offsets[b + 1] - offsets[b];
         const int n = len <= 0 ? 0 : std::min(lens[b], out_stride);
@@ -688,7 +736,7 @@ void session_set_profiling(Session* s, bool on) {
     GRADB_CUDA(cudaSetDevice(s->m->device));
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
-    if (s->use_tc) check_status(s);
+    if (s->use_tc || s->use_b1) check_status(s);
     s->profiling = on;
     for (int i = 0; i < kKernelClasses; i++) {
         s->class_ms[i] = 0.0;

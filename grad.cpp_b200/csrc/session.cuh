@@ -3,6 +3,7 @@
 // to many sequences; TextGen's loops, text_gen.cpp:37-120).
 #pragma once
 #include "common.cuh"
+#include "decode_b1.cuh"
 #include "gemm_tc.cuh"
 #include "select_kernels.cuh"
 #include "step_kernels.cuh"
@@ -10,7 +11,7 @@
 namespace gradb {
 
 enum KernelClass { KC_EMBED = 0, KC_QKV, KC_ATTN, KC_OPROJ, KC_FFN_UP, KC_FFN_DOWN, KC_LOGITS, KC_ADVANCE, KC_SELECT,
-                   kKernelClasses };
+                   KC_STEP_B1, kKernelClasses };
 
 struct Session {
     const DeviceModel* m = nullptr;
@@ -40,6 +41,11 @@ struct Session {
     __nv_bfloat16 *h16 = nullptr, *attn16 = nullptr, *ffn16 = nullptr;
     CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];  // token tiles of 32, 64, 128 rows
     int* status = nullptr;
+
+    // single-sequence persistent kernel: workspace and grid-barrier words
+    bool use_b1 = false;
+    float* b1_ws = nullptr;
+    unsigned* b1_bar = nullptr;  // [0] arrival counter, [1] base of the next launch
 
     // host mirrors / staging (pinned)
     std::vector<int> h_pos;
