@@ -78,6 +78,7 @@ SIGNATURES = {
     "gradb_kernel_class_count": (C.c_int, []),
     "gradb_kernel_class_name": (C.c_char_p, [C.c_int]),
     "gradb_session_profile": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
+    "gradb_session_stage_trace": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.c_int, C.POINTER(C.c_int)]),
     "gradb_kernel_launches": (C.c_uint64, []),
 }
 
@@ -254,6 +255,12 @@ class BatchSession:
         cnt = (C.c_uint64 * n)()
         _check(lib().gradb_session_profile(self._h, ms, cnt))
         return {lib().gradb_kernel_class_name(i).decode(): (ms[i], int(cnt[i])) for i in range(n)}
+
+    def stage_trace(self):
+        buf = (C.c_uint64 * 1024)()
+        n = C.c_int()
+        _check(lib().gradb_session_stage_trace(self._h, buf, 1024, C.byref(n)))
+        return np.array(buf[:n.value], np.uint64)
 
     def last_ms(self):
         v = C.c_float()

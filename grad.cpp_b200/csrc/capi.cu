@@ -282,6 +282,25 @@ gradb_status gradb_session_profile(const gradb_session* session, double* ms_out,
     return GRADB_OK;
 }
 
+gradb_status gradb_session_stage_trace(gradb_session* session, uint64_t* stamps_out, int capacity, int* count_out) {
+    return guarded([&] {
+        if (!session || !stamps_out || !count_out) throw Error(GRADB_ERR_INVALID, "null argument");
+        Session* s = session->impl;
+        *count_out = 0;
+        if (!s->b1_trace) return;
+        GRADB_CUDA(cudaSetDevice(s->m->device));
+        GRADB_CUDA(cudaStreamSynchronize(s->stream));
+        std::vector<unsigned long long> host(1024);
+        GRADB_CUDA(cudaMemcpy(host.data(), s->b1_trace, host.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        int n = 0;
+        while (n < 1024 && n < capacity && host[n] != 0) {
+            stamps_out[n] = host[n];
+            n++;
+        }
+        *count_out = n;
+    });
+}
+
 uint64_t gradb_kernel_launches(void) { return g_kernel_launches.load(); }
 
 }  // extern "C"

@@ -36,6 +36,7 @@ constexpr int kWarpsB1 = kCompute / 32;
 constexpr int kSlots = 4;
 constexpr int kSlotBytes = 48 * 1024;
 constexpr uint32_t kPollLimit = 1u << 22;
+constexpr int kMaxLayersB1 = 32;  // layer tables are staged in shared memory
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -111,8 +112,9 @@ __device__ __forceinline__ void ring_release(Ring& r) {
 __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target, int* status, volatile int* abort_flag) {
     bar_compute();
     if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(counter, 1u);
+        // release: everything this CTA wrote (ordered before by the CTA barrier) is visible to
+        // whoever later observes the count with an acquire load
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
         uint32_t it = 0;
         for (;;) {
             unsigned cur;
@@ -124,7 +126,6 @@ __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target,
                 break;
             }
         }
-        __threadfence();
     }
     bar_compute();
     return *abort_flag == 0;
@@ -192,36 +193,60 @@ __device__ __forceinline__ float block_total(float v, float* sh) {
     return s;
 }
 
-// in_s = norm(x_s) (inference.cpp:30-58)
+// in_s = norm(x_s) (inference.cpp:30-58). gamma/beta are fetched before the reductions so their
+// latency overlaps them.
 __device__ void norm_vec(const float* x_s, float* in_s, const float* gamma, const float* beta, int d, int rms,
                          float* sh) {
+    constexpr int kHold = 4;  // elements per thread kept in registers (d <= 2048); beyond that, loaded late
+    float gv[kHold], bv[kHold];
+#pragma unroll
+    for (int i = 0; i < kHold; i++) {
+        const int k = threadIdx.x + i * kCompute;
+        gv[i] = k < d ? __ldg(gamma + k) : 0.f;
+        bv[i] = (k < d && !rms) ? __ldg(beta + k) : 0.f;
+    }
     float s = 0.f;
     for (int k = threadIdx.x; k < d; k += kCompute) s += rms ? x_s[k] * x_s[k] : x_s[k];
     s = block_total(s, sh);
+    float mean = 0.f, r;
     if (rms) {
-        const float r = 1.0f / sqrtf(s / (float)d + 1e-5f);
-        for (int k = threadIdx.x; k < d; k += kCompute) in_s[k] = __ldg(gamma + k) * x_s[k] * r;
+        r = 1.0f / sqrtf(s / (float)d + 1e-5f);
     } else {
-        const float mean = s / (float)d;
+        mean = s / (float)d;
         float v = 0.f;
         for (int k = threadIdx.x; k < d; k += kCompute) {
             const float dl = x_s[k] - mean;
             v += dl * dl;
         }
         v = block_total(v, sh);
-        const float inv_std = 1.0f / sqrtf(v / (float)d + 1e-5f);
-        for (int k = threadIdx.x; k < d; k += kCompute) {
-            in_s[k] = __ldg(gamma + k) * (x_s[k] - mean) * inv_std + __ldg(beta + k);
-        }
+        r = 1.0f / sqrtf(v / (float)d + 1e-5f);
+    }
+#pragma unroll
+    for (int i = 0; i < kHold; i++) {
+        const int k = threadIdx.x + i * kCompute;
+        if (k < d) in_s[k] = rms ? gv[i] * x_s[k] * r : gv[i] * (x_s[k] - mean) * r + bv[i];
+    }
+    for (int k = threadIdx.x + kHold * kCompute; k < d; k += kCompute) {
+        in_s[k] = rms ? __ldg(gamma + k) * x_s[k] * r : __ldg(gamma + k) * (x_s[k] - mean) * r + __ldg(beta + k);
     }
     bar_compute();
 }
 
 // x_s += bias + sum of KS partial vectors (fixed order)
 __device__ void add_partials(float* x_s, const float* bias, const float* part, int KS, int d) {
+    // All loads of an element are issued before the first add, so they share one trip to L2;
+    // the adds keep the slice order.
+    constexpr int kMaxKS = 16;
     for (int k = threadIdx.x; k < d; k += kCompute) {
-        float v = x_s[k] + (bias ? __ldg(bias + k) : 0.f);
-        for (int s = 0; s < KS; s++) v += __ldcg(part + (size_t)s * d + k);
+        float pv[kMaxKS];
+        const float bv = bias ? __ldg(bias + k) : 0.f;
+#pragma unroll
+        for (int s = 0; s < kMaxKS; s++) pv[s] = s < KS ? __ldcg(part + (size_t)s * d + k) : 0.f;
+        float v = x_s[k] + bv;
+#pragma unroll
+        for (int s = 0; s < kMaxKS; s++) {
+            if (s < KS) v += pv[s];
+        }
         x_s[k] = v;
     }
     bar_compute();
@@ -235,6 +260,7 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
     __shared__ float out_s[64], out2_s[64];
     __shared__ float sh[kWarpsB1];
     __shared__ volatile int abort_flag;
+    __shared__ B1Layer layers_s[kMaxLayersB1];
 
     const int g = blockIdx.x, t = threadIdx.x;
     const int token = p.tok[0];
@@ -248,6 +274,13 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
     float* x_s = reinterpret_cast<float*>(slots + (size_t)kSlots * kSlotBytes);
     float* in_s = x_s + d;  // input vector of the current projection: max(d, largest K slice) floats
 
+    {
+        // per-layer pointer tables: one coalesced copy now instead of a dependent load per use
+        const unsigned long long* src = reinterpret_cast<const unsigned long long*>(p.layers);
+        unsigned long long* dst = reinterpret_cast<unsigned long long*>(layers_s);
+        const int words = p.L * (int)(sizeof(B1Layer) / 8);
+        for (int i = t; i < words; i += kThreadsB1) dst[i] = __ldg(src + i);
+    }
     if (t == 0) {
         for (int s = 0; s < kSlots; s++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&full_bar[s])));
@@ -272,7 +305,7 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
                 }
             };
             for (int l = 0; l < p.L && !abort_flag; l++) {
-                const B1Layer* ly = p.layers + l;
+                const B1Layer* ly = layers_s + l;
                 if (g < p.qkv.tiles) push_tile(ly->qkv, p.qkv);
                 if (g < p.o.tiles) push_tile(ly->o, p.o);
                 if (g < p.up.tiles) {
@@ -295,10 +328,22 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
     // -------------------------------------------------------------------- compute warps
     const int lane = t & 31, w = t >> 5;
     unsigned bar_i = 0;
+    int trace_i = 0;
+    auto stamp = [&]() {
+        if (p.trace && g == 0 && t == 0) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            p.trace[trace_i++] = now;
+        }
+    };
     auto barrier = [&]() {
         bar_i++;
-        return grid_barrier(p.bar_counter, base + bar_i * (unsigned)p.G, p.status, &abort_flag);
+        stamp();  // stage work done
+        const bool okb = grid_barrier(p.bar_counter, base + bar_i * (unsigned)p.G, p.status, &abort_flag);
+        stamp();  // barrier passed
+        return okb;
     };
+    stamp();
 
     // x = E[token] (+ P[pos])  (inference.cpp:159-182)
     for (int k = t; k < d; k += kCompute) {
@@ -313,26 +358,35 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
     bool alive = true;
 
     for (int l = 0; l < p.L && alive; l++) {
-        const B1Layer* ly = p.layers + l;
+        const B1Layer* ly = layers_s + l;
         float* kc = p.kcache + (size_t)l * p.layer_cache_stride;
         float* vc = p.vcache + (size_t)l * p.layer_cache_stride;
 
         // ---- A: (previous FFN output joins the residual) norm1, Q/K/V columns of this CTA
-        if (l > 0) add_partials(x_s, (p.layers + l - 1)->b2, p.dpart, p.down.KS, d);
+        if (l > 0) add_partials(x_s, (layers_s + l - 1)->b2, p.dpart, p.down.KS, d);
         if (g < p.qkv.tiles) {
+            const int CW = p.qkv.CW;
+            // this thread's output pair: fetch its bias and rotation before the heavy part
+            const int n = g * CW + 2 * t;  // column among the 3d outputs
+            const bool mine = t < CW / 2 && n < 3 * d;
+            const int which = mine ? n / d : 0, n_in = mine ? n - which * d : 0;
+            const int h = n_in / hs, c_in = n_in % hs;
+            float b0 = 0.f, b1 = 0.f, cs = 1.f, sn = 0.f;
+            if (mine) {
+                const float* bias = which == 0 ? ly->bq : (which == 1 ? ly->bk : ly->bv);
+                b0 = __ldg(bias + n_in);
+                b1 = __ldg(bias + n_in + 1);
+                if (p.rope_cos && which < 2) {
+                    cs = __ldg(p.rope_cos + (size_t)pos * (hs / 2) + c_in / 2);
+                    sn = __ldg(p.rope_sin + (size_t)pos * (hs / 2) + c_in / 2);
+                }
+            }
             norm_vec(x_s, in_s, ly->n1g, ly->n1b, d, p.modern, sh);
             tile_matvec<WT>(ring, in_s, d, p.qkv.Kt, p.qkv.CW, red_s, out_s);
-            const int CW = p.qkv.CW;
-            if (t < CW / 2) {
-                const int n = g * CW + 2 * t;  // column among the 3d outputs
-                if (n < 3 * d) {
-                    const int which = n / d, n_in = n - which * d;
-                    const float* bias = which == 0 ? ly->bq : (which == 1 ? ly->bk : ly->bv);
-                    float a0 = out_s[2 * t] + __ldg(bias + n_in), a1 = out_s[2 * t + 1] + __ldg(bias + n_in + 1);
-                    const int h = n_in / hs, c_in = n_in % hs;
+            if (mine) {
+                {
+                    float a0 = out_s[2 * t] + b0, a1 = out_s[2 * t + 1] + b1;
                     if (p.rope_cos && which < 2) {  // inference.cpp:101-115
-                        const float cs = __ldg(p.rope_cos + (size_t)pos * (hs / 2) + c_in / 2);
-                        const float sn = __ldg(p.rope_sin + (size_t)pos * (hs / 2) + c_in / 2);
                         const float r0 = a0 * cs - a1 * sn, r1 = a0 * sn + a1 * cs;
                         a0 = r0;
                         a1 = r1;
@@ -358,17 +412,30 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
             const float* V = vc + (size_t)head * p.T * hs;
             const float2 qv = __ldcg(reinterpret_cast<const float2*>(p.q + head * hs) + lane);
             float m_run = -INFINITY, l_run = 0.f, o0 = 0.f, o1 = 0.f;
-            for (int tt = t0 + w; tt < t1; tt += kWarpsB1) {
-                const float2 kv = __ldcg(reinterpret_cast<const float2*>(K + (size_t)tt * hs) + lane);
-                const float2 vv = __ldcg(reinterpret_cast<const float2*>(V + (size_t)tt * hs) + lane);
-                const float sc = warp_sum(qv.x * kv.x + qv.y * kv.y) * scale;
-                const float m_new = fmaxf(m_run, sc);
-                const float corr = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
-                const float pr = expf(sc - m_new);
-                l_run = l_run * corr + pr;
-                o0 = o0 * corr + pr * vv.x;
-                o1 = o1 * corr + pr * vv.y;
-                m_run = m_new;
+            // four positions per trip: their K and V rows are requested together
+            for (int tt = t0 + w; tt < t1; tt += 4 * kWarpsB1) {
+                float2 kv[4], vv[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int tu = tt + u * kWarpsB1;
+                    if (tu < t1) {
+                        kv[u] = __ldcg(reinterpret_cast<const float2*>(K + (size_t)tu * hs) + lane);
+                        vv[u] = __ldcg(reinterpret_cast<const float2*>(V + (size_t)tu * hs) + lane);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    if (tt + u * kWarpsB1 < t1) {
+                        const float sc = warp_sum(qv.x * kv[u].x + qv.y * kv[u].y) * scale;
+                        const float m_new = fmaxf(m_run, sc);
+                        const float corr = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
+                        const float pr = expf(sc - m_new);
+                        l_run = l_run * corr + pr;
+                        o0 = o0 * corr + pr * vv[u].x;
+                        o1 = o1 * corr + pr * vv[u].y;
+                        m_run = m_new;
+                    }
+                }
             }
             // combine the warps in order; red_s rows: [w][0..63] = o, then m and l
             red_s[w * 64 + 2 * lane] = o0;
@@ -407,14 +474,24 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
             for (int k = t; k < rows; k += kCompute) {
                 const int kk = k0 + k, head = kk / hs, dim = kk % hs;
                 const float* part = p.attn_part + (size_t)head * S * (hs + 2);
+                constexpr int kMaxS = 16;  // all loads first: one trip to L2 instead of three
+                float ms[kMaxS], ls[kMaxS], os[kMaxS];
+#pragma unroll
+                for (int s = 0; s < kMaxS; s++) {
+                    const bool in = s < S;
+                    ms[s] = in ? __ldcg(part + s * (hs + 2) + hs) : -INFINITY;
+                    ls[s] = in ? __ldcg(part + s * (hs + 2) + hs + 1) : 0.f;
+                    os[s] = in ? __ldcg(part + s * (hs + 2) + dim) : 0.f;
+                }
                 float M = -INFINITY;
-                for (int s = 0; s < S; s++) M = fmaxf(M, __ldcg(part + s * (hs + 2) + hs));
+#pragma unroll
+                for (int s = 0; s < kMaxS; s++) M = fmaxf(M, ms[s]);
                 float Lsum = 0.f, acc = 0.f;
-                for (int s = 0; s < S; s++) {
-                    const float ms = __ldcg(part + s * (hs + 2) + hs);
-                    const float f = ms == -INFINITY ? 0.f : expf(ms - M);
-                    Lsum += __ldcg(part + s * (hs + 2) + hs + 1) * f;
-                    acc += __ldcg(part + s * (hs + 2) + dim) * f;
+#pragma unroll
+                for (int s = 0; s < kMaxS; s++) {
+                    const float f = ms[s] == -INFINITY ? 0.f : expf(ms[s] - M);
+                    Lsum += ls[s] * f;
+                    acc += os[s] * f;
                 }
                 in_s[k] = acc / Lsum;
             }
@@ -462,7 +539,7 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
     if (alive) {
         // ---- final norm + tied-embedding logits (inference.cpp:251-254)
         if (do_logits) {
-            add_partials(x_s, (p.layers + p.L - 1)->b2, p.dpart, p.down.KS, d);
+            add_partials(x_s, (layers_s + p.L - 1)->b2, p.dpart, p.down.KS, d);
             norm_vec(x_s, in_s, p.fng, p.fnb, d, p.modern, sh);
             const int r0 = g * p.logit_rows_per_cta, r1 = min(p.V, r0 + p.logit_rows_per_cta);
             for (int r = r0; r < r1; r += p.logit_chunk_rows) {
@@ -482,6 +559,7 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
                 ring_release(ring);
             }
         }
+        stamp();
         if (g == 0 && t == 0) {
             p.pos[0] = pos + 1;
             if (p.append_hist) {
@@ -525,6 +603,7 @@ B1Mat plan_matrix(int K, int N, int G, int max_ks) {
             if (col_tiles * KS > G) break;
             const int Kt = (((K + KS - 1) / KS) + 3) / 4 * 4;
             if ((long)(KS - 1) * Kt >= K) continue;  // an empty slice
+            if (KS > 16) continue;                   // consumers hold at most 16 partials
             const long cost = (long)Kt * CW;
             if (best_cost < 0 || cost < best_cost) {
                 best_cost = cost;
@@ -560,7 +639,7 @@ B1Plan* b1_make_plan(const DeviceModel* m) {
     const bool modern = ds.arch == GRADB_ARCH_MODERN;
     plan->G = m->sm_count;
     plan->wbytes = m->precision == GRADB_BF16 ? 2 : 4;
-    if (hs != 64 || d % 4 != 0 || ds.num_heads > plan->G) return plan;  // not supported: the generic kernels run instead
+    if (hs != 64 || d % 4 != 0 || ds.num_heads > plan->G || ds.num_layers > kMaxLayersB1) return plan;  // not supported: the generic kernels run instead
     // Q/K/V and FFN-up have non-linear epilogues, so their tiles span the whole reduction.
     plan->qkv = plan_matrix(d, 3 * d, plan->G, 1);
     plan->o = plan_matrix(d, d, plan->G, 16);
@@ -570,7 +649,7 @@ B1Plan* b1_make_plan(const DeviceModel* m) {
     plan->logit_rows_per_cta = (ds.vocab_size + plan->G - 1) / plan->G;
     plan->logit_chunk_rows = kSlotBytes / (d * plan->wbytes);
     if (plan->logit_chunk_rows < 1) return plan;
-    plan->attn_splits = std::max(1, plan->G / ds.num_heads);
+    plan->attn_splits = std::max(1, std::min(16, plan->G / ds.num_heads));
     if (b1_smem_bytes(m, plan) > 227 * 1024) return plan;
 
     GRADB_CUDA(cudaSetDevice(m->device));

@@ -46,6 +46,7 @@ struct B1Params {
     int hist_stride, append_hist;
     unsigned *bar_counter, *bar_base;
     int* status;
+    unsigned long long* trace;  // optional: %globaltimer stamps of CTA 0 at every stage boundary
 };
 
 B1Plan* b1_make_plan(const DeviceModel* m);

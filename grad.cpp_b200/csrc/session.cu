@@ -186,6 +186,7 @@ void enqueue_step_b1(Session* s, const int* tok_dev, const int* logit_tok_dev, b
     p.hist_stride = s->hist_stride; p.append_hist = append_history ? 1 : 0;
     p.bar_counter = s->b1_bar; p.bar_base = s->b1_bar + 1;
     p.status = s->status;
+    p.trace = s->b1_trace;
     Timed t(s, KC_STEP_B1);
     launch_decode_b1(p, s->stream);
 }
@@ -442,6 +443,11 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
             dalloc(&s->b1_ws, b1_workspace_floats(m, m->b1));
             dalloc(&s->b1_bar, 2);
             GRADB_CUDA(cudaMemsetAsync(s->b1_bar, 0, 2 * sizeof(unsigned), s->stream));
+            const char* tr = std::getenv("GRADB_B1_TRACE");
+            if (tr && tr[0] == '1') {
+                dalloc(&s->b1_trace, 1024);
+                GRADB_CUDA(cudaMemsetAsync(s->b1_trace, 0, 1024 * sizeof(unsigned long long), s->stream));
+            }
         }
         const char* ntc = std::getenv("GRADB_NO_TC");
         s->use_tc = m->tc_ok && s->B >= 16 && !(ntc && ntc[0] == '1');
@@ -495,7 +501,7 @@ void destroy_session(Session* s) {
     cudaFree(s->tok); cudaFree(s->pos); cudaFree(s->hist); cudaFree(s->hist_len);
     cudaFree(s->gen); cudaFree(s->done); cudaFree(s->out_tok); cudaFree(s->tok_matrix);
     cudaFree(s->uniforms); cudaFree(s->probs);
-    cudaFree(s->b1_ws); cudaFree(s->b1_bar);
+    cudaFree(s->b1_ws); cudaFree(s->b1_bar); cudaFree(s->b1_trace);
     cudaFree(s->h16); cudaFree(s->attn16); cudaFree(s->ffn16); cudaFree(s->status);
     if (s->h_stage) cudaFreeHost(s->h_stage);
     if (s->own_stream && s->stream) cudaStreamDestroy(s->stream);

@@ -46,6 +46,7 @@ struct Session {
     bool use_b1 = false;
     float* b1_ws = nullptr;
     unsigned* b1_bar = nullptr;  // [0] arrival counter, [1] base of the next launch
+    unsigned long long* b1_trace = nullptr;  // stage timestamps when GRADB_B1_TRACE=1
 
     // host mirrors / staging (pinned)
     std::vector<int> h_pos;
