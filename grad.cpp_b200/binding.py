@@ -74,6 +74,8 @@ SIGNATURES = {
                                  C.c_int, _i32p, _f32p, _f32p]),
     "gradb_session_last_ms": (C.c_int, [C.c_void_p, _f32p]),
     "gradb_session_cache_row": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]),
+    "gradb_attention_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                       C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "gradb_session_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
     "gradb_kernel_class_count": (C.c_int, []),
     "gradb_kernel_class_name": (C.c_char_p, [C.c_int]),
@@ -114,6 +116,15 @@ def _check(status):
 
 def _p(a, ty):
     return None if a is None else a.ctypes.data_as(ty)
+
+
+def attention_decode(q, kcache, vcache, pos, max_len, splits, out, stream=0, fn="gradb_attention_decode"):
+    """Stand-alone cached attention on torch CUDA tensors (device pointers are passed through).
+    q/out: [n_seq, heads*64] float32; caches: [n_seq, heads, max_len, 64] float32; pos: [n_seq] int32."""
+    n_seq, heads = kcache.shape[0], kcache.shape[1]
+    _check(getattr(lib(), fn)(q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), pos.data_ptr(), n_seq, heads, 64,
+                              max_len, splits, out.data_ptr(), stream))
+    return out
 
 
 def inspect_checkpoint(path) -> ModelDesc:

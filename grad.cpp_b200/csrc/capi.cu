@@ -1,5 +1,6 @@
 // extern "C" surface declared in include/gradb.h. Exceptions stop here and
 // become status codes plus a thread-local message.
+#include <cmath>
 #include <cstring>
 
 #include "session.cuh"
@@ -252,6 +253,45 @@ gradb_status gradb_session_cache_row(gradb_session* session, int seq, int layer,
     return guarded([&] {
         if (!session || !row_host) throw Error(GRADB_ERR_INVALID, "null argument");
         session_cache_row(session->impl, seq, layer, which, pos, row_host);
+    });
+}
+
+gradb_status gradb_attention_decode(const float* q_dev, const float* kcache_dev, const float* vcache_dev,
+                                    const int32_t* pos_dev, int n_seq, int heads, int head_dim, int max_len,
+                                    int splits, float* out_dev, void* stream) {
+    return guarded([&] {
+        if (!q_dev || !kcache_dev || !vcache_dev || !pos_dev || !out_dev) throw Error(GRADB_ERR_INVALID, "null argument");
+        if (n_seq < 1 || heads < 1 || max_len < 1 || splits < 1 || splits > 64) {
+            throw Error(GRADB_ERR_INVALID, "bad attention shape");
+        }
+        if (head_dim != 64) throw Error(GRADB_ERR_INVALID, "the stand-alone attention entry point supports head_dim 64");
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        float* partial = nullptr;
+        int* counters = nullptr;
+        const size_t units = (size_t)n_seq * heads;
+        GRADB_CUDA(cudaMalloc(&partial, units * splits * (head_dim + 2) * sizeof(float)));
+        if (cudaMalloc(&counters, units * sizeof(int)) != cudaSuccess) {
+            cudaFree(partial);
+            throw Error(GRADB_ERR_CUDA, "cudaMalloc failed");
+        }
+        try {
+            GRADB_CUDA(cudaMemsetAsync(counters, 0, units * sizeof(int), st));
+            AttnParams a{};
+            a.q = q_dev; a.kcache = kcache_dev; a.vcache = vcache_dev;
+            a.tok = pos_dev;  // every sequence takes part: positions are never negative
+            a.pos = pos_dev;
+            a.out = out_dev; a.out16 = nullptr; a.partial = partial; a.counters = counters;
+            a.H = heads; a.hs = head_dim; a.T = max_len; a.d = heads * head_dim;
+            a.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+            launch_attention(a, n_seq, splits, st);
+            GRADB_CUDA(cudaStreamSynchronize(st));
+        } catch (...) {
+            cudaFree(partial);
+            cudaFree(counters);
+            throw;
+        }
+        cudaFree(partial);
+        cudaFree(counters);
     });
 }
 

@@ -200,6 +200,19 @@ gradb_status gradb_session_last_ms(const gradb_session* session, float* ms_out);
 gradb_status gradb_session_cache_row(gradb_session* session, int seq, int layer, int which, int pos,
                                      float* row_host);
 
+/* ---- single kernels ------------------------------------------------------ */
+
+/* The cached-attention stage of one decode step on its own (inference.cpp:208-225 with
+ * softmax_row :60-67), for n_seq sequences: out[s, h*64..] = softmax(q_h . K_h[0..pos] / sqrt(64)) V_h.
+ * All pointers are DEVICE memory: q_dev and out_dev are [n_seq][heads*64]; the caches are
+ * [n_seq][heads][max_len][64] (one layer); pos_dev[s] is the index of the newest cached
+ * position of sequence s. The context is cut into `splits` ranges whose partial results are
+ * combined by the last CTA to finish; the scratch for those partials is allocated and freed
+ * inside the call, which therefore synchronises the stream. head_dim must be 64. */
+gradb_status gradb_attention_decode(const float* q_dev, const float* kcache_dev, const float* vcache_dev,
+                                    const int32_t* pos_dev, int n_seq, int heads, int head_dim, int max_len,
+                                    int splits, float* out_dev, void* stream);
+
 /* Built-in device-side tracing (the reference has none for this path; its `grad bench`
  * times whole generations, src/cli/bench.cpp:269-286). While profiling is on, every kernel
  * launch is bracketed by CUDA events on the session's stream (graphs are bypassed) and the
