@@ -75,11 +75,15 @@ def peaks():
 
 def seq_prompt(global_seq: int, vocab: int, n: int = PROMPT_LEN):
     """Per-sequence stream, so a sequence is the same whichever GPU it lands on."""
-    return np.random.default_rng([PROMPT_SEED, global_seq]).integers(0, vocab, n).astype(np.int32)
+    load_package()
+    from grad_cpp_b200 import sharding
+    return sharding.seq_prompt(PROMPT_SEED, global_seq, vocab, n)
 
 
 def seq_draws(global_seq: int, n: int):
-    return np.random.default_rng([PROMPT_SEED + 1, global_seq]).random(n, dtype=np.float32)
+    load_package()
+    from grad_cpp_b200 import sharding
+    return sharding.seq_draws(PROMPT_SEED, global_seq, n)
 
 
 class ClockSampler:
@@ -208,10 +212,9 @@ def run_ours(args):
     clocks.start()
     t0 = time.perf_counter()
     ids, step_ms, prefill_ms = sess.generate(prompts, sp, K + 1, uniforms=draws, timings=True)
-    if world > 1:
-        mine = torch.from_numpy(np.stack([np.pad(s, (0, CONTEXT + 1 - len(s))) for s in ids])).cuda()
-        gathered = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(gathered, mine)
+    from grad_cpp_b200 import sharding
+    all_ids = sharding.gather_ids(sharding.pad_ids(ids, CONTEXT + 1), world, device="cuda")  # one NCCL all_gather
+    assert all_ids.shape[0] == world * B
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
     clk = clocks.stop()
@@ -219,10 +222,7 @@ def run_ours(args):
     launches = g.lib().gradb_kernel_launches() - launches0
 
     dev_s = float(np.sum(step_ms[:K])) / 1e3
-    times = torch.tensor([dev_s, wall], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_s, wall = float(times[0]), float(times[1])
+    dev_s, wall = sharding.max_over_ranks([dev_s, wall], world, device="cuda")
     new_ids = sum(len(s) - PROMPT_LEN for s in ids)
     assert new_ids == B * (K + 1), (new_ids, B, K)
 
