@@ -76,6 +76,9 @@ SIGNATURES = {
     "gradb_session_cache_row": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]),
     "gradb_attention_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                        C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "gradb_attention_decode_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                              C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "gradb_attention_static_capacity": (C.c_int, []),
     "gradb_session_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
     "gradb_kernel_class_count": (C.c_int, []),
     "gradb_kernel_class_name": (C.c_char_p, [C.c_int]),

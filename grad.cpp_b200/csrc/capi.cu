@@ -295,6 +295,27 @@ gradb_status gradb_attention_decode(const float* q_dev, const float* kcache_dev,
     });
 }
 
+gradb_status gradb_attention_decode_static(const float* q_dev, const float* kcache_dev, const float* vcache_dev,
+                                           const int32_t* pos_dev, int n_seq, int heads, int head_dim, int max_len,
+                                           int splits, float* out_dev, void* stream) {
+    return guarded([&] {
+        if (!q_dev || !kcache_dev || !vcache_dev || !pos_dev || !out_dev) throw Error(GRADB_ERR_INVALID, "null argument");
+        if (n_seq < 1 || heads < 1 || max_len < 1 || splits < 1 || splits > 64) {
+            throw Error(GRADB_ERR_INVALID, "bad attention shape");
+        }
+        AttnParams a{};
+        a.q = q_dev; a.kcache = kcache_dev; a.vcache = vcache_dev;
+        a.tok = pos_dev;  // every sequence takes part: positions are never negative
+        a.pos = pos_dev;
+        a.out = out_dev; a.out16 = nullptr;
+        a.H = heads; a.hs = head_dim; a.T = max_len; a.d = heads * head_dim;
+        a.scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+        launch_attention_static(a, n_seq, splits, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int gradb_attention_static_capacity(void) { return static_attention_capacity(); }
+
 gradb_status gradb_session_set_profiling(gradb_session* session, int on) {
     return guarded([&] {
         if (!session) throw Error(GRADB_ERR_INVALID, "null session");

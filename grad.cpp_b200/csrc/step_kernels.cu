@@ -11,6 +11,8 @@
 //   logits       final norm + h @ E^T                                     inference.cpp:251-254
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "step_kernels.cuh"
 
 namespace cg = cooperative_groups;
@@ -670,6 +672,51 @@ void launch_logits(const LogitsParams& p_in, bool bf16, cudaStream_t st) {
         GRADB_MB_CASE(8)
     }
 #undef GRADB_MB_CASE
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention without any allocation: the split partials and arrival tickets live in a fixed
+// device array that every GPU loading this library carries until the process exits.
+constexpr int kStaticAttnUnits = 4096;  // (sequence, head, split) slots
+constexpr int kStaticAttnFloats = kStaticAttnUnits * (64 + 2);
+static __device__ __align__(256) float g_static_attn_scratch[kStaticAttnFloats + kStaticAttnUnits];
+
+int static_attention_capacity() { return kStaticAttnUnits; }
+
+// In host code the array's name is only a handle: the device address has to be asked for,
+// once per device, with that device current.
+static float* static_attn_scratch_address() {
+    static std::mutex mu;
+    static float* cached[64] = {};
+    int dev = 0;
+    GRADB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) throw Error(GRADB_ERR_INVALID, "device index out of range");
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[dev]) {
+        float* ptr = nullptr;
+        GRADB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_attn_scratch));
+        cached[dev] = ptr;
+    }
+    return cached[dev];
+}
+
+void launch_attention_static(const AttnParams& p_in, int B, int splits, cudaStream_t st) {
+    if (p_in.hs != 64) throw Error(GRADB_ERR_INVALID, "the allocation-free attention entry point supports head_dim 64");
+    const long units = (long)B * p_in.H * splits;
+    if (units > kStaticAttnUnits) {
+        throw Error(GRADB_ERR_INVALID, "n_seq * heads * splits = " + std::to_string(units) +
+                                           " exceeds the fixed scratch of " + std::to_string(kStaticAttnUnits) +
+                                           " slots of the allocation-free attention entry point");
+    }
+    float* scratch = static_attn_scratch_address();
+    AttnParams p = p_in;
+    p.partial = scratch;
+    p.counters = reinterpret_cast<int*>(scratch + kStaticAttnFloats);
+    // The array keeps whatever the previous call left; the tickets must start at zero.
+    GRADB_CUDA(cudaMemsetAsync(p.counters, 0, (size_t)B * p.H * sizeof(int), st));
+    attn_decode64_kernel<<<dim3(splits, p.H, B), kAttnWarps * 32, 0, st>>>(p);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }

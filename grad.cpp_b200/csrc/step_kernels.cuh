@@ -54,5 +54,8 @@ void launch_advance(const int* tok, int* pos, int* hist, int* hist_len, int hist
 void launch_gemv(const GemvParams& p, int pro, int epi, bool bf16, int sm_count, cudaStream_t st);
 void launch_logits(const LogitsParams& p, bool bf16, cudaStream_t st);
 void launch_attention(const AttnParams& p, int B, int splits, cudaStream_t st);
+// Same kernel with its scratch in a fixed device array (no allocation); see step_kernels.cu.
+void launch_attention_static(const AttnParams& p, int B, int splits, cudaStream_t st);
+int static_attention_capacity();
 
 }  // namespace gradb

@@ -213,6 +213,28 @@ gradb_status gradb_attention_decode(const float* q_dev, const float* kcache_dev,
                                     const int32_t* pos_dev, int n_seq, int heads, int head_dim, int max_len,
                                     int splits, float* out_dev, void* stream);
 
+/* The same cached-attention kernel for callers that must not allocate. It has no counterpart
+ * in the reference. Two kinds of caller need it: hosts that give a plugin a fixed device-memory
+ * budget up front (a serving process that reserves all of its device memory at start), and
+ * latency-critical loops that cannot afford the allocator: cudaMalloc may block for an unbounded
+ * time and cudaFree synchronises the whole device, stalling every other stream of the process.
+ * The split partials and arrival
+ * tickets live in a fixed array of gradb_attention_static_capacity() = 4096 (sequence, head, split)
+ * slots, about 1.1 MB, that every GPU loading this library holds until the process exits; a call
+ * with n_seq * heads * splits above that is rejected with GRADB_ERR_INVALID and a message naming
+ * the limit. The call issues no cudaMalloc, cudaFree or other allocating routine, does not
+ * synchronise, and returns as soon as the work is queued on `stream`.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *     with that device current); make that first call before starting any stream capture.
+ *   - All calls share the array. It keeps the previous call's contents; the tickets are cleared
+ *     on `stream` at the start of every call. Two calls that overlap on the GPU (different
+ *     streams, or different host threads on one device) race on it: serialise them.
+ * Arguments and results are those of gradb_attention_decode. */
+gradb_status gradb_attention_decode_static(const float* q_dev, const float* kcache_dev, const float* vcache_dev,
+                                           const int32_t* pos_dev, int n_seq, int heads, int head_dim, int max_len,
+                                           int splits, float* out_dev, void* stream);
+int gradb_attention_static_capacity(void);
+
 /* Built-in device-side tracing (the reference has none for this path; its `grad bench`
  * times whole generations, src/cli/bench.cpp:269-286). While profiling is on, every kernel
  * launch is bracketed by CUDA events on the session's stream (graphs are bypassed) and the
