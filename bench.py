@@ -73,11 +73,11 @@ def peaks():
     return 6650.0, 1400.0, "fallback"
 
 
-def seq_prompt(global_seq: int, vocab: int, n: int = PROMPT_LEN):
+def seq_prompt(global_seq: int, vocab: int, n: int | None = None):
     """Per-sequence stream, so a sequence is the same whichever GPU it lands on."""
     load_package()
     from grad_cpp_b200 import sharding
-    return sharding.seq_prompt(PROMPT_SEED, global_seq, vocab, n)
+    return sharding.seq_prompt(PROMPT_SEED, global_seq, vocab, PROMPT_LEN if n is None else n)
 
 
 def seq_draws(global_seq: int, n: int):
@@ -251,7 +251,7 @@ def run_ours(args):
         "clocks": clk,
     }
 
-    if rank == 0:
+    if rank == 0 and not args.main_only:
         # Per-kernel device time over the same K steps, from events around every launch.
         sess.set_profiling(True)
         sess.generate(prompts, sp, K + 1, uniforms=draws)
@@ -457,8 +457,14 @@ def main():
     ap.add_argument("--batch", type=int, default=256, help="sequences per GPU")
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--cpu-tokens", type=int, default=48, help="decode ids per sequence in the CPU sample")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
+                    help="ids per prompt (default 32, the benchmark configuration; longer prompts are for profiling)")
+    ap.add_argument("--main-only", action="store_true",
+                    help="only the timed workload: no per-kernel pass, batch-1 block or CPU baseline (for profilers)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    global PROMPT_LEN
+    PROMPT_LEN = max(1, min(args.prompt_len, CONTEXT - 2))
     if args.impl == "reference":
         run_reference(args)
     else:

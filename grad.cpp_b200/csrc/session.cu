@@ -113,6 +113,7 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
             AttnParams a{};
             a.q = s->q; a.kcache = kc; a.vcache = vc; a.tok = tok_dev; a.pos = s->pos;
             a.out = s->attn; a.out16 = s->attn16; a.partial = s->attn_partial; a.counters = s->attn_counters;
+            a.status = s->status;
             a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = d;
             a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
             launch_attention(a, n_seq, s->attn_splits, st);
@@ -237,6 +238,7 @@ void enqueue_step(Session* s, int n_seq, const int* tok_dev, const int* logit_to
         AttnParams a{};
         a.q = s->q; a.kcache = g.kcache; a.vcache = g.vcache; a.tok = tok_dev; a.pos = s->pos;
         a.out = s->attn; a.out16 = nullptr; a.partial = s->attn_partial; a.counters = s->attn_counters;
+        a.status = s->status;
         a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = s->d;
         a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));  // inference.cpp:184
         {
@@ -541,7 +543,7 @@ void session_step(Session* s, const int32_t* tokens, int n_seq, float* logits_ho
     GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
-    if (s->use_tc || s->use_b1) check_status(s);
+    check_status(s);
     GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
     for (int b = 0; b < n_seq; b++) {
         if (tokens[b] >= 0) s->h_pos[b]++;
@@ -561,7 +563,7 @@ void session_prefill(Session* s, const int32_t* tokens, const int32_t* offsets, 
     }
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
-    if (s->use_tc || s->use_b1) check_status(s);
+    check_status(s);
     GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
     for (int b = 0; b < n_seq; b++) s->h_pos[b] += offsets[b + 1] - offsets[b];
 }
@@ -717,7 +719,7 @@ void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets
     GRADB_CUDA(cudaMemcpyAsync(hist.data(), s->hist, hist.size() * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
-    if (s->use_tc || s->use_b1) check_status(s);
+    check_status(s);
     for (int b = 0; b < n_seq; b++) {
         const int len = offsets[b + 1] - offsets[b];
         const int n = len <= 0 ? 0 : std::min(lens[b], out_stride);
@@ -742,7 +744,7 @@ void session_set_profiling(Session* s, bool on) {
     GRADB_CUDA(cudaSetDevice(s->m->device));
     GRADB_CUDA(cudaStreamSynchronize(s->stream));
     collect_spans(s);
-    if (s->use_tc || s->use_b1) check_status(s);
+    check_status(s);
     s->profiling = on;
     for (int i = 0; i < kKernelClasses; i++) {
         s->class_ms[i] = 0.0;

@@ -518,6 +518,253 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode64_kernel(const At
     if (lane == 0) p.counters[b * p.H + h] = 0;
 }
 
+// ---- pipelined variant -----------------------------------------------------------------
+// Head size 64, persistent: one CTA per SM, four independent warps. The (sequence, head,
+// context split) units are dealt round-robin to the grid's warps; each warp turns its units
+// into one flat sequence of 32-position tiles and keeps two tiles ahead of the arithmetic in a
+// private three-stage shared-memory ring filled by bulk asynchronous copies (one copy for the
+// tile's K rows, one for its V rows: both are contiguous in the head-major cache). So the HBM
+// stream of a warp continues across unit boundaries instead of restarting per (sequence, head).
+// Scores: lane r owns row r of the tile and walks its 64 columns rotated by r, which keeps the
+// 128-bit shared-memory reads conflict free and needs no shuffles. P@V: lane owns two columns.
+constexpr int kPipeStages = 3;
+constexpr int kPipeTileRows = 32;
+constexpr int kPipeStageFloats = 2 * kPipeTileRows * 64;  // K tile then V tile
+constexpr uint32_t kPipeSpin = 1u << 22;
+
+struct AttnCursor {  // position in a warp's flat sequence of tiles
+    int unit;        // current unit index (advances by the number of warps in the grid)
+    int tile, tile_end;
+    int b, h, split, ctx;
+};
+
+__device__ __forceinline__ bool attn_unit_setup(const AttnParams& p, int S, int total_units, AttnCursor& c) {
+    // Fills the cursor for c.unit; returns false when the unit is beyond the end.
+    if (c.unit >= total_units) return false;
+    const int hs_units = p.H * S;
+    c.b = c.unit / hs_units;
+    c.h = (c.unit / S) % p.H;
+    c.split = c.unit % S;
+    if (p.tok[c.b] < 0) {  // sequence sits this step out: no tiles, nothing to finalise
+        c.ctx = 0;
+        c.tile = c.tile_end = 0;
+        return true;
+    }
+    c.ctx = p.pos[c.b] + 1;
+    const int ntiles = (c.ctx + kPipeTileRows - 1) / kPipeTileRows;
+    const int tps = (ntiles + S - 1) / S;
+    c.tile = c.split * tps;
+    c.tile_end = min(ntiles, c.tile + tps);
+    if (c.tile_end < c.tile) c.tile_end = c.tile;
+    return true;
+}
+
+__global__ void __launch_bounds__(kAttnWarps * 32, 1) attn_decode64_pipe_kernel(const AttnParams p, int S,
+                                                                              int total_units) {
+    constexpr int HS = 64;
+    extern __shared__ __align__(128) float pipe_smem[];
+    __shared__ __align__(8) uint64_t full_bar[kAttnWarps][kPipeStages];
+    __shared__ float q_s[kAttnWarps][HS];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int warps_total = gridDim.x * kAttnWarps;
+    const int gw = blockIdx.x * kAttnWarps + w;
+    float* ring = pipe_smem + (size_t)w * kPipeStages * kPipeStageFloats;
+
+    if (lane == 0) {
+        for (int s = 0; s < kPipeStages; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&full_bar[w][s])));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    // issue the copies of the tile the fetch cursor points at, then advance it
+    AttnCursor fc{};
+    fc.unit = gw;
+    bool f_ok = attn_unit_setup(p, S, total_units, fc);
+    int issued = 0;
+    auto fetch_next = [&]() {
+        while (f_ok && fc.tile >= fc.tile_end) {  // skip units without tiles
+            fc.unit += warps_total;
+            f_ok = attn_unit_setup(p, S, total_units, fc);
+        }
+        if (!f_ok) return;
+        const int stage = issued % kPipeStages;
+        const int r0 = fc.tile * kPipeTileRows;
+        const int nrows = min(kPipeTileRows, fc.ctx - r0);
+        if (lane == 0) {
+            const size_t off = (((size_t)fc.b * p.H + fc.h) * p.T + r0) * HS;
+            const uint32_t bytes = (uint32_t)nrows * HS * 4;
+            const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&full_bar[w][stage]);
+            const uint32_t dstk = (uint32_t)__cvta_generic_to_shared(ring + (size_t)stage * kPipeStageFloats);
+            const uint32_t dstv = dstk + kPipeTileRows * HS * 4;
+            // the stage was last read with ordinary loads: order them before the asynchronous writes
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dstk),
+                         "l"(p.kcache + off), "r"(bytes), "r"(bar)
+                         : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dstv),
+                         "l"(p.vcache + off), "r"(bytes), "r"(bar)
+                         : "memory");
+        }
+        issued++;
+        fc.tile++;
+    };
+    fetch_next();
+    fetch_next();
+
+    int consumed = 0;
+    AttnCursor cc{};
+    cc.unit = gw;
+    bool c_ok = attn_unit_setup(p, S, total_units, cc);
+    // q of a unit is fetched one unit early so that its latency hides behind the previous unit's tiles
+    float qa = 0.f, qb = 0.f;
+    if (c_ok && cc.ctx > 0) {
+        qa = p.q[(size_t)cc.b * p.d + cc.h * HS + lane];
+        qb = p.q[(size_t)cc.b * p.d + cc.h * HS + lane + 32];
+    }
+    for (; c_ok;) {
+        AttnCursor nx = cc;
+        nx.unit = cc.unit + warps_total;
+        const bool n_ok = attn_unit_setup(p, S, total_units, nx);
+        float nqa = 0.f, nqb = 0.f;
+        if (n_ok && nx.ctx > 0) {
+            nqa = p.q[(size_t)nx.b * p.d + nx.h * HS + lane];
+            nqb = p.q[(size_t)nx.b * p.d + nx.h * HS + lane + 32];
+        }
+        const AttnCursor cur = cc;
+        const float cqa = qa, cqb = qb;
+        cc = nx;
+        c_ok = n_ok;
+        qa = nqa;
+        qb = nqb;
+        if (cur.ctx == 0) continue;  // inactive sequence
+        __syncwarp();
+        q_s[w][lane] = cqa;
+        q_s[w][lane + 32] = cqb;
+        __syncwarp();
+        float m_run = -INFINITY, l_run = 0.f, o0 = 0.f, o1 = 0.f;
+        for (int t = cur.tile; t < cur.tile_end; t++) {
+            const int stage = consumed % kPipeStages;
+            const uint32_t parity = (consumed / kPipeStages) & 1;
+            {
+                const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&full_bar[w][stage]);
+                uint32_t ok = 0;
+                for (uint32_t it = 0; it < kPipeSpin && !ok; ++it) {
+                    asm volatile(
+                        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                        : "=r"(ok)
+                        : "r"(bar), "r"(parity)
+                        : "memory");
+                }
+                if (!ok) {  // bounded: give up on this launch, the host sees the status word
+                    if (lane == 0 && p.status) atomicExch(p.status, 301);
+                    return;
+                }
+            }
+            const float* Kt = ring + (size_t)stage * kPipeStageFloats;
+            const float* Vt = Kt + kPipeTileRows * HS;
+            const int r0 = t * kPipeTileRows;
+            const int nrows = min(kPipeTileRows, cur.ctx - r0);
+            // scores: lane r <-> row r, columns visited rotated by r (16-byte chunks)
+            float dot = 0.f;
+            if (lane < nrows) {
+                const float4* kr = reinterpret_cast<const float4*>(Kt + lane * HS);
+                const float4* qr = reinterpret_cast<const float4*>(q_s[w]);
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int c = (j + lane) & 15;
+                    const float4 kv = kr[c], qv = qr[c];
+                    d0 += qv.x * kv.x;
+                    d1 += qv.y * kv.y;
+                    d2 += qv.z * kv.z;
+                    d3 += qv.w * kv.w;
+                }
+                dot = (d0 + d1) + (d2 + d3);
+            }
+            const float mine = lane < nrows ? dot * p.scale : -INFINITY;
+            const float m_new = fmaxf(m_run, warp_max(mine));
+            const float corr = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
+            const float pr = lane < nrows ? expf(mine - m_new) : 0.f;
+            l_run = l_run * corr + warp_sum(pr);
+            o0 *= corr;
+            o1 *= corr;
+            m_run = m_new;
+            const float2* vr = reinterpret_cast<const float2*>(Vt) + lane;
+            float e0 = 0.f, e1 = 0.f;  // second accumulator pair: two independent chains
+            if (nrows == kPipeTileRows) {
+#pragma unroll
+                for (int r = 0; r < kPipeTileRows; r += 2) {
+                    const float pa = __shfl_sync(0xffffffffu, pr, r), pb = __shfl_sync(0xffffffffu, pr, r + 1);
+                    const float2 va = vr[r * (HS / 2)], vb = vr[(r + 1) * (HS / 2)];
+                    o0 += pa * va.x;
+                    o1 += pa * va.y;
+                    e0 += pb * vb.x;
+                    e1 += pb * vb.y;
+                }
+            } else {
+                for (int r = 0; r < nrows; r++) {
+                    const float pv = __shfl_sync(0xffffffffu, pr, r);
+                    const float2 vv = vr[r * (HS / 2)];
+                    o0 += pv * vv.x;
+                    o1 += pv * vv.y;
+                }
+            }
+            o0 += e0;
+            o1 += e1;
+            consumed++;
+            __syncwarp();   // the whole warp is done with this stage ...
+            fetch_next();   // ... so the tile two ahead may land in the stage freed one tile ago
+        }
+        // finalise the unit
+        if (S == 1) {
+            const float inv = 1.0f / l_run;
+            *reinterpret_cast<float2*>(p.out + (size_t)cur.b * p.d + cur.h * HS + 2 * lane) = make_float2(o0 * inv, o1 * inv);
+            if (p.out16) {
+                *reinterpret_cast<__nv_bfloat162*>(p.out16 + (size_t)cur.b * p.d + cur.h * HS + 2 * lane) =
+                    __floats2bfloat162_rn(o0 * inv, o1 * inv);
+            }
+            continue;
+        }
+        const int bh = cur.b * p.H + cur.h;
+        float* part = p.partial + ((size_t)bh * S + cur.split) * (HS + 2);
+        part[2 * lane] = o0;
+        part[2 * lane + 1] = o1;
+        if (lane == 0) {
+            part[HS] = m_run;
+            part[HS + 1] = l_run;
+        }
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = atomicAdd(p.counters + bh, 1) == S - 1;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) continue;
+        // the last split to arrive combines all of them, in split order
+        __threadfence();
+        const float* base = p.partial + (size_t)bh * S * (HS + 2);
+        float Mt = -INFINITY;
+        for (int s2 = 0; s2 < S; s2++) Mt = fmaxf(Mt, __ldcg(base + s2 * (HS + 2) + HS));
+        float Lt = 0.f, c0 = 0.f, c1 = 0.f;
+        for (int s2 = 0; s2 < S; s2++) {
+            const float ms = __ldcg(base + s2 * (HS + 2) + HS);
+            const float f = ms == -INFINITY ? 0.f : expf(ms - Mt);
+            Lt += __ldcg(base + s2 * (HS + 2) + HS + 1) * f;
+            c0 += __ldcg(base + s2 * (HS + 2) + 2 * lane) * f;
+            c1 += __ldcg(base + s2 * (HS + 2) + 2 * lane + 1) * f;
+        }
+        const float inv = 1.0f / Lt;
+        *reinterpret_cast<float2*>(p.out + (size_t)cur.b * p.d + cur.h * HS + 2 * lane) = make_float2(c0 * inv, c1 * inv);
+        if (p.out16) {
+            *reinterpret_cast<__nv_bfloat162*>(p.out16 + (size_t)cur.b * p.d + cur.h * HS + 2 * lane) =
+                __floats2bfloat162_rn(c0 * inv, c1 * inv);
+        }
+        if (lane == 0) p.counters[bh] = 0;
+    }
+}
+
 // Any head size: one CTA per (head, sequence), scores kept in shared memory.
 // Mirrors the reference loop structure directly (inference.cpp:208-225).
 __global__ void __launch_bounds__(128) attn_decode_generic_kernel(const AttnParams p) {
@@ -723,7 +970,18 @@ void launch_attention_static(const AttnParams& p_in, int B, int splits, cudaStre
 
 void launch_attention(const AttnParams& p, int B, int splits, cudaStream_t st) {
     if (p.hs == 64) {
-        attn_decode64_kernel<<<dim3(splits, p.H, B), kAttnWarps * 32, 0, st>>>(p);
+        // persistent, pipelined kernel: one CTA per SM (its rings take most of the shared memory)
+        static int sm_count = 0;
+        if (!sm_count) {
+            int dev = 0;
+            GRADB_CUDA(cudaGetDevice(&dev));
+            GRADB_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+        }
+        const int total_units = B * p.H * splits;
+        const int grid = std::max(1, std::min(sm_count, (total_units + kAttnWarps - 1) / kAttnWarps));
+        const size_t bytes = (size_t)kAttnWarps * kPipeStages * kPipeStageFloats * sizeof(float);
+        set_smem(attn_decode64_pipe_kernel, bytes);
+        attn_decode64_pipe_kernel<<<grid, kAttnWarps * 32, bytes, st>>>(p, splits, total_units);
     } else {
         const size_t bytes = (size_t)p.T * sizeof(float);
         set_smem(attn_decode_generic_kernel, bytes);

@@ -44,6 +44,7 @@ struct AttnParams {
     __nv_bfloat16* out16;  // optional bf16 copy of out (operand of the tensor-core projection)
     float* partial;   // [B][H][S][hs+2] split results: o[hs], max, sum
     int* counters;    // [B][H] arrival tickets, zero between launches
+    int* status;      // optional: set non-zero if a bounded wait expires
     int H, hs, T, d;
     float scale;
 };
