@@ -449,6 +449,7 @@ def run_reference(args):
 
 
 def main():
+    global PROMPT_LEN
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=CONTEXT - PROMPT_LEN)
@@ -463,7 +464,6 @@ def main():
                     help="only the timed workload: no per-kernel pass, batch-1 block or CPU baseline (for profilers)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    global PROMPT_LEN
     PROMPT_LEN = max(1, min(args.prompt_len, CONTEXT - 2))
     if args.impl == "reference":
         run_reference(args)
