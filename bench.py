@@ -287,7 +287,8 @@ def run_ours(args):
         line["roofline"] = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                             "frac": achieved / hbm_peak, "peak_source": peak_kind,
                             "algorithmic_bytes_per_launch": alg[dom] / n_dom,
-                            "avg_launch_us": dom_ms * 1e3 / n_dom, "traffic": ncu_traffic(dom)}
+                            "avg_launch_us": dom_ms * 1e3 / n_dom,
+                            "traffic": ncu_traffic(dom, alg[dom] / n_dom)}
         step_bytes = sum(sum(algorithmic_bytes_per_step(dm, B, PROMPT_LEN + i + 1, w_bytes).values()) for i in range(K))
         line["step_roofline"] = {"algorithmic_bytes_per_step_avg": step_bytes / K,
                                  "achieved_gbs": step_bytes / dev_s / 1e9, "frac": step_bytes / dev_s / 1e9 / hbm_peak}
@@ -309,12 +310,16 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def ncu_traffic(kernel_class):
-    """DRAM bytes per launch of a kernel class from a committed ncu capture, if one exists."""
+def ncu_traffic(kernel_class, algorithmic_bytes_per_launch):
+    """DRAM bytes per launch of a kernel class, scaled from a committed ncu capture (traffic grows in
+    proportion to the positions read), or None when no capture of that class is on file."""
     p = ROOT / "profiles" / "ncu_traffic.json"
     if not p.exists():
         return None
-    return json.loads(p.read_text()).get(kernel_class)
+    rec = json.loads(p.read_text()).get(kernel_class)
+    if not rec:
+        return None
+    return rec["traffic_over_algorithmic"] * algorithmic_bytes_per_launch
 
 
 def bench_batch1(g, ck, device, hbm_peak):
