@@ -37,29 +37,22 @@ GRADB_HD IncPair compose(IncPair a, IncPair b) {
 
 // Increments of one term with bit pattern `bits` (a >= 0, finite) when the
 // unit is u = 2^ue, i.e. the running sum has biased exponent ue + 150.
+// Branch free: a = man * 2^(ex-150), so a/u = man >> shift with shift = ue - (ex - 150);
+// a shift above 25 leaves less than a quarter ulp (no effect), a shift of zero or less means
+// a >= 2^23 u, which certainly lifts the sum out of the binade.
 GRADB_HD IncPair term_inc(uint32_t bits, int ue) {
+    const uint32_t exf = (bits >> 23) & 0xffu;
+    const uint32_t man = (bits & 0x7fffffu) | (exf ? 0x800000u : 0u);  // subnormals carry no hidden bit
+    const int ex = exf ? (int)exf : 1;
+    const int shift = ue - (ex - 150);
+    const int sh = shift < 1 ? 1 : (shift > 26 ? 26 : shift);
+    const uint32_t q = man >> sh;
+    const uint32_t rem = man & ((1u << sh) - 1u), half = 1u << (sh - 1);
+    const uint32_t up = rem > half ? 1u : 0u, tie = rem == half ? 1u : 0u;
     IncPair r;
-    r.e = r.o = 0u;
-    if ((bits & 0x7fffffffu) == 0u) return r;
-    int ex = (int)((bits >> 23) & 0xffu);
-    uint32_t man = bits & 0x7fffffu;
-    if (ex == 0) ex = 1; else man |= 0x800000u;  // subnormals carry no hidden bit
-    const int shift = ue - (ex - 150);           // a / u = man * 2^-shift
-    if (shift <= 0) {                            // a >= 2^23 u: certainly leaves the binade
-        r.e = r.o = kBinadeEnd;
-        return r;
-    }
-    if (shift > 25) return r;                    // a < u/4: no effect
-    const uint32_t q = shift >= 25 ? 0u : (man >> shift);
-    const uint32_t rem = man & ((1u << shift) - 1u), half = 1u << (shift - 1);
-    if (rem > half) {
-        r.e = r.o = q + 1u;
-    } else if (rem < half) {
-        r.e = r.o = q;
-    } else {
-        r.e = q + (q & 1u);         // S even: S + q has q's parity
-        r.o = q + ((q + 1u) & 1u);  // S odd
-    }
+    r.e = q + up + (tie & q & 1u);          // S even: S + q has q's parity, a tie rounds to even
+    r.o = q + up + (tie & (q + 1u) & 1u);   // S odd
+    if (shift <= 0) r.e = r.o = kBinadeEnd;
     return r;
 }
 

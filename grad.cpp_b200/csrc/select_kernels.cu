@@ -95,7 +95,7 @@ struct ScanResult {
     int hit;     // first index whose running sum satisfied the predicate, or n
 };
 
-constexpr int kSerialPrefix = 128;   // terms one thread adds natively before the block-wide passes start
+constexpr int kSerialPrefix = 64;   // terms one thread adds natively before the block-wide passes start
 constexpr int kMaxPer = 16;          // terms per thread per pass (register resident)
 constexpr int kMaxRange = kMaxPer * kSelThreads;
 
@@ -329,6 +329,305 @@ __device__ ScanResult seq_scan(int n, Term term, Hit hit, uint32_t* sh) {
     return r;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fast path of the exact sequential sum: one sweep instead of one pass per binade.
+//
+// A cheap double-precision prefix sum predicts, for every 16-term chunk, an interval that is
+// GUARANTEED to contain the sequential fp32 running sum throughout the chunk (sequential
+// summation of n non-negative terms is within (n-1) * 2^-24 of the exact sum, under 2^-10 for
+// n <= 16384; the interval is widened by 2^-9). A chunk whose interval lies inside one binade is
+// "safe": its binade is known in advance and nothing can leave it, so its parity -> increment map
+// can be built immediately. Runs of safe chunks that share a binade are composed by a segmented
+// scan; the few chunks that straddle a power of two are added natively. One thread then walks
+// the resulting short list (tens of items) carrying the exact sum, and finally every thread
+// walks its own chunk from its exact start to test the predicate. Any surprise (a start outside
+// the predicted binade, an unexpected exit) abandons the sweep and the pass-per-binade scan above
+// redoes the work, so exactness never rests on the prediction.
+constexpr int kFastPer = 16;
+constexpr int kFastMax = kFastPer * kSelThreads;
+
+struct SegVal {  // segmented-scan payload: map composed since the segment head, and that head
+    IncPair m;
+    int head;  // index of the head chunk if one lies inside the scanned window, else -1
+};
+__device__ __forceinline__ SegVal seg_combine(const SegVal& a, const SegVal& b) {  // a earlier
+    if (b.head >= 0) return b;
+    SegVal r;
+    r.m = compose(a.m, b.m);
+    r.head = a.head;
+    return r;
+}
+__device__ __forceinline__ SegVal seg_shfl_up(const SegVal& v, int o) {
+    SegVal r;
+    r.m.e = __shfl_up_sync(0xffffffffu, v.m.e, o);
+    r.m.o = __shfl_up_sync(0xffffffffu, v.m.o, o);
+    r.head = __shfl_up_sync(0xffffffffu, v.head, o);
+    return r;
+}
+
+// work: 4096 words of shared scratch (the sort's histogram is dead by the time scans run).
+// Returns false when the sweep had to be abandoned; the caller then runs seq_scan.
+template <typename Term, typename Hit>
+__device__ bool seq_scan_fast(int n, Term term, Hit hit, bool has_predicate, uint32_t* work, ScanResult& out) {
+    __shared__ float f_s0;
+    __shared__ int f_start, f_hit, f_fail, f_upto;
+    __shared__ float f_wd[kSelWarps];
+    __shared__ uint32_t f_we[kSelWarps], f_wo[kSelWarps], f_headbits[kSelWarps];
+    __shared__ int f_wh[kSelWarps];
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    uint32_t* seg_e = work;
+    uint32_t* seg_o = work + kSelThreads;
+    int* seg_head = reinterpret_cast<int*>(work + 2 * kSelThreads);
+    int* info = reinterpret_cast<int*>(work + 3 * kSelThreads);  // binade of a safe chunk, -1 unsafe; later: start sums
+
+    // ---- leading zeros and a short native prefix (the sum doubles every few terms at first)
+    if (tid == 0) {
+        f_start = 0x7fffffff;
+        f_hit = n;
+        f_fail = 0;
+    }
+    __syncthreads();
+    {
+        int first = 0x7fffffff;
+        for (int i = tid; i < n && first == 0x7fffffff; i += kSelThreads) {
+            if (term(i) != 0.0f) first = i;
+        }
+        if (first != 0x7fffffff) atomicMin(&f_start, first);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int i = f_start;
+        float s = 0.0f;
+        int h = n;
+        if (hit(0.0f)) {
+            h = 0;  // the predicate already holds for a zero sum: the very first term triggers it
+            i = n;
+        } else if (i == 0x7fffffff) {
+            i = n;  // all zero
+        } else {
+            const int stop = min(n, i + kSerialPrefix);
+            while (i + 8 <= stop && h == n) {  // loads of a group are issued together
+                float v[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) v[k] = term(i + k);
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    if (h == n) {
+                        s = __fadd_rn(s, v[k]);
+                        if (has_predicate && hit(s)) h = i + k;
+                    }
+                }
+                i = h == n ? i + 8 : h + 1;
+            }
+            while (i < stop && h == n) {
+                s = __fadd_rn(s, term(i));
+                if (has_predicate && hit(s)) h = i;
+                i++;
+            }
+        }
+        f_s0 = s;
+        f_start = i;
+        f_hit = h;
+        f_upto = 0;
+    }
+    __syncthreads();
+    const int start = f_start;
+    const float s0 = f_s0;
+    if (f_hit < n || start >= n) {
+        out.sum = s0;
+        out.hit = f_hit;
+        __syncthreads();
+        return true;
+    }
+    if (n - start > kFastMax) return false;  // uniform
+
+    // ---- chunk terms into registers, double prefix
+    const int beg = min(n, start + tid * kFastPer), end = min(n, beg + kFastPer);
+    // The prediction only has to be within ~1e-4 of the exact sum: pairwise fp32 sums (error a few
+    // 2^-24 per level) are ample, and much cheaper than double precision here.
+    float a[kFastPer];
+#pragma unroll
+    for (int i = 0; i < kFastPer; i++) a[i] = beg + i < end ? term(beg + i) : 0.0f;
+    const float dsum = (((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]))) +
+                       (((a[8] + a[9]) + (a[10] + a[11])) + ((a[12] + a[13]) + (a[14] + a[15])));
+    float incl = dsum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) f_wd[w] = incl;
+    __syncthreads();
+    float wpre;
+    {   // exclusive scan of the 32 warp sums, by every warp
+        float wv = f_wd[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float v = __shfl_up_sync(0xffffffffu, wv, o);
+            if (lane >= o) wv += v;
+        }
+        wpre = __shfl_sync(0xffffffffu, wv, (w + 31) & 31);
+        if (w == 0) wpre = 0.f;
+    }
+    const float P = s0 + (wpre + (incl - dsum));  // predicted sum before this chunk
+
+    // ---- classify: safe <=> the guaranteed interval of the running sum stays in one binade
+    const float lo = P * (1.0f - 1.0f / 512.0f), hi = (P + dsum) * (1.0f + 1.0f / 512.0f);
+    const int elo = (int)(__float_as_uint(lo) >> 23), ehi = (int)(__float_as_uint(hi) >> 23);
+    const bool used = beg < end;
+    const bool safe = used && elo == ehi && elo >= 30 && elo < 254;
+    SegVal sv;
+    sv.m.e = sv.m.o = 0u;
+    if (safe) {
+        const int ue = elo - 150;
+#pragma unroll
+        for (int i = 0; i < kFastPer; i++) sv.m = compose(sv.m, term_inc(__float_as_uint(a[i]), ue));
+    }
+    info[tid] = safe ? elo : -1;
+    __syncthreads();
+    const bool is_head = used && (!safe || tid == 0 || info[tid - 1] != elo);
+    sv.head = is_head ? tid : -1;
+    const uint32_t hb = __ballot_sync(0xffffffffu, is_head);
+    if (lane == 0) f_headbits[w] = hb;
+
+    // ---- segmented inclusive scan of the maps
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const SegVal pv = seg_shfl_up(sv, o);
+        if (lane >= o) sv = seg_combine(pv, sv);
+    }
+    if (lane == 31) {
+        f_we[w] = sv.m.e;
+        f_wo[w] = sv.m.o;
+        f_wh[w] = sv.head;
+    }
+    __syncthreads();
+    {
+        SegVal wv;
+        wv.m.e = f_we[lane];
+        wv.m.o = f_wo[lane];
+        wv.head = f_wh[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const SegVal pv = seg_shfl_up(wv, o);
+            if (lane >= o) wv = seg_combine(pv, wv);
+        }
+        SegVal before;  // everything in earlier warps, cut at the last head
+        before.m.e = __shfl_sync(0xffffffffu, wv.m.e, (w + 31) & 31);
+        before.m.o = __shfl_sync(0xffffffffu, wv.m.o, (w + 31) & 31);
+        before.head = __shfl_sync(0xffffffffu, wv.head, (w + 31) & 31);
+        if (w > 0) sv = seg_combine(before, sv);
+    }
+    seg_e[tid] = sv.m.e;
+    seg_o[tid] = sv.m.o;
+    seg_head[tid] = sv.head;
+    __syncthreads();
+
+    // ---- one thread walks the items (segments and unsafe chunks) with the exact sum
+    const int chunks = (n - start + kFastPer - 1) / kFastPer;
+    if (tid == 0) {
+        float s = s0;
+        int h = n, fail = 0, upto = chunks;
+        int t = 0;
+        while (t < chunks) {
+            // next head after t
+            int nxt = chunks;
+            {
+                const int q = t + 1;
+                int ww = q >> 5;
+                uint32_t bits = ww < kSelWarps ? (f_headbits[ww] & (0xffffffffu << (q & 31))) : 0u;
+                while (ww < kSelWarps) {
+                    if (bits) {
+                        nxt = min(chunks, ww * 32 + __ffs(bits) - 1);
+                        break;
+                    }
+                    ww++;
+                    if (ww < kSelWarps) bits = f_headbits[ww];
+                }
+            }
+            const int e = info[t];
+            if (e < 0) {  // unsafe chunk: native adds
+                const int b0 = start + t * kFastPer, e0 = min(n, b0 + kFastPer);
+                float v[kFastPer];
+#pragma unroll
+                for (int i = 0; i < kFastPer; i++) v[i] = b0 + i < e0 ? term(b0 + i) : 0.0f;  // loads first
+#pragma unroll
+                for (int i = 0; i < kFastPer; i++) {
+                    if (b0 + i < e0 && h == n) {
+                        s = __fadd_rn(s, v[i]);
+                        if (has_predicate && hit(s)) h = b0 + i;
+                    }
+                }
+            } else {  // run of safe chunks t .. nxt-1 in binade e
+                const uint32_t sb = __float_as_uint(s);
+                if ((int)(sb >> 23) != e) {
+                    fail = 1;
+                    break;
+                }
+                info[t] = (int)sb;  // exact start sum of the segment, for the walkers
+                const uint32_t S0 = (sb & 0x7fffffu) | 0x800000u;
+                IncPair m;
+                m.e = seg_e[nxt - 1];
+                m.o = seg_o[nxt - 1];
+                const uint32_t S1 = step_S(S0, m);
+                if (S1 >= kBinadeEnd) {
+                    fail = 1;
+                    break;
+                }
+                s = __uint_as_float(((uint32_t)e << 23) | (S1 & 0x7fffffu));
+            }
+            t = nxt;
+            if (h < n || (has_predicate && hit(s))) {  // the first hit lies at or before this point
+                upto = t;
+                break;
+            }
+        }
+        f_s0 = s;
+        f_hit = h;
+        f_fail = fail;
+        f_upto = upto;
+    }
+    __syncthreads();
+    if (f_fail) return false;  // uniform
+
+    // ---- predicate: every safe chunk before `upto` is walked from its exact start
+    if (has_predicate && safe && tid < f_upto) {
+        const int head = seg_head[tid];
+        const uint32_t sb = (uint32_t)info[head];
+        const uint32_t S0 = (sb & 0x7fffffu) | 0x800000u;
+        IncPair ex;
+        ex.e = ex.o = 0u;
+        if (head != tid) {
+            ex.e = seg_e[tid - 1];
+            ex.o = seg_o[tid - 1];
+        }
+        uint32_t S = step_S(S0, ex);
+        int mine = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kFastPer; i++) {
+            if (mine == 0x7fffffff && beg + i < end) {
+                S = step_S(S, term_inc(__float_as_uint(term(beg + i)), elo - 150));
+                if (hit(__uint_as_float(((uint32_t)elo << 23) | (S & 0x7fffffu)))) mine = beg + i;
+            }
+        }
+        if (mine != 0x7fffffff) atomicMin(&f_hit, mine);
+    }
+    __syncthreads();
+    out.sum = f_s0;
+    out.hit = f_hit;
+    __syncthreads();
+    return true;
+}
+
+// The exact scan: the one-sweep fast path, or the pass-per-binade scan when it declines.
+template <typename Term, typename Hit>
+__device__ ScanResult exact_scan(int n, Term term, Hit hit, bool has_predicate, uint32_t* sh, uint32_t* work) {
+    ScanResult r;
+    if (seq_scan_fast(n, term, hit, has_predicate, work, r)) return r;
+    __syncthreads();
+    return seq_scan(n, term, hit, sh);
+}
+
 // Bitonic sort, descending, of n_pad (power of two) floats in shared memory.
 __device__ void sort_desc(float* a, int n_pad) {
     for (int k = 2; k <= n_pad; k <<= 1) {
@@ -440,6 +739,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
 
     float* x = smem;           // [V]
     float* sorted = smem + V;  // [n_pad]
+    uint32_t* work = reinterpret_cast<uint32_t*>(sorted + p.n_pad);  // 4096 words: sort histogram, then scan scratch
     const float* lg = p.logits + (size_t)b * V;
     for (int i = tid; i < V; i += kSelThreads) x[i] = lg[i];
     __syncthreads();
@@ -551,7 +851,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         // softmax (tensor.cpp:434-448): exp(x - max), sequential sum in index order, times 1/sum
         for (int i = tid; i < V; i += kSelThreads) x[i] = expf_libm(__fsub_rn(x[i], mx));
         __syncthreads();
-        const ScanResult den = seq_scan(V, [&](int i) { return x[i]; }, [](float) { return false; }, scan_sh);
+        const ScanResult den = exact_scan(V, [&](int i) { return x[i]; }, [](float) { return false; }, false, scan_sh, work);
         const float inv_sum = __fdiv_rn(1.0f, den.sum);
         for (int i = tid; i < V; i += kSelThreads) x[i] = __fmul_rn(x[i], inv_sum);
         __syncthreads();
@@ -565,8 +865,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             }
             __syncthreads();
             const float top_p = p.top_p;
-            const ScanResult cut = seq_scan(V, [&](int i) { return sorted[i]; },
-                                            [top_p](float s) { return s >= top_p; }, scan_sh);
+            const ScanResult cut = exact_scan(V, [&](int i) { return sorted[i]; },
+                                              [top_p](float s) { return s >= top_p; }, true, scan_sh, work);
             const int cutoff = cut.hit < V ? cut.hit : 0;  // never reached: index stays 0
             const float cutoff_prob = sorted[cutoff];
             __syncthreads();
@@ -574,7 +874,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
                 if (x[i] < cutoff_prob) x[i] = 0.0f;
             }
             __syncthreads();
-            const ScanResult kept = seq_scan(V, [&](int i) { return x[i]; }, [](float) { return false; }, scan_sh);
+            const ScanResult kept = exact_scan(V, [&](int i) { return x[i]; }, [](float) { return false; }, false, scan_sh, work);
             if (kept.sum > 0.0f) {
                 const float tk = kept.sum;
                 for (int i = tid; i < V; i += kSelThreads) x[i] = __fdiv_rn(x[i], tk);
@@ -586,7 +886,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         }
         // draw (text_gen.cpp:199-208): first index with u <= running sum, else the last id
         const float u = p.uniforms[(size_t)b * p.u_stride + (p.loop_mode ? p.gen[b] : 0)];
-        const ScanResult dr = seq_scan(V, [&](int i) { return x[i]; }, [u](float s) { return u <= s; }, scan_sh);
+        const ScanResult dr = exact_scan(V, [&](int i) { return x[i]; }, [u](float s) { return u <= s; }, true, scan_sh, work);
         pick = dr.hit < V ? dr.hit : V - 1;
     }
 

@@ -114,12 +114,92 @@ static Result emulated(const std::vector<float>& a, int mode, float thr, int T) 
     return {s_sum, s_hit};
 }
 
+// Host emulation of the one-sweep scan (select_kernels.cu::seq_scan_fast): double prefix sum to
+// predict each 16-term chunk's binade, maps of safe chunks composed per run, unsafe chunks added
+// natively, exact sums carried by one walker, predicate tested per chunk from its exact start.
+// Returns false when the sweep declines (the kernel then falls back to the pass-per-binade scan).
+static bool emulated_fast(const std::vector<float>& a, int mode, float thr, Result& out, long* unsafe_chunks) {
+    const int n = (int)a.size(), PER = 16, PREFIX = 128;
+    int i = 0;
+    while (i < n && a[i] == 0.0f) i++;
+    volatile float s = 0.0f;
+    int h = n;
+    if (pred(mode, thr, 0.0f)) { out = {0.0f, 0}; return true; }
+    if (i == n) { out = {0.0f, n}; return true; }
+    {
+        const int stop = std::min(n, i + PREFIX);
+        while (i < stop && h == n) { s = s + a[i]; if (pred(mode, thr, s)) h = i; i++; }
+    }
+    if (h < n || i >= n) { out = {s, h}; return true; }
+    const int start = i;
+    const float s0 = s;
+    const int chunks = (n - start + PER - 1) / PER;
+    if (chunks > 1024) return false;
+    std::vector<int> info(chunks);
+    std::vector<IncPair> cmap(chunks);
+    std::vector<double> dsum(chunks);
+    double P = (double)s0;
+    for (int c = 0; c < chunks; c++) {
+        const int b = start + c * PER, e = std::min(n, b + PER);
+        double d = 0; for (int k = b; k < e; k++) d += (double)a[k];
+        const float lo = (float)(P * (1.0 - 1.0 / 512.0)), hi = (float)((P + d) * (1.0 + 1.0 / 512.0));
+        const int elo = (int)(fbits(lo) >> 23), ehi = (int)(fbits(hi) >> 23);
+        const bool safe = elo == ehi && elo >= 30 && elo < 254;
+        info[c] = safe ? elo : -1;
+        IncPair m = {0u, 0u};
+        if (safe) for (int k = b; k < e; k++) m = compose(m, term_inc(fbits(a[k]), elo - 150));
+        cmap[c] = m;
+        P += d;
+        if (!safe) (*unsafe_chunks)++;
+    }
+    float cur = s0;
+    int c = 0;
+    while (c < chunks && h == n) {
+        if (info[c] < 0) {
+            const int b = start + c * PER, e = std::min(n, b + PER);
+            volatile float v = cur;
+            for (int k = b; k < e && h == n; k++) { v = v + a[k]; if (pred(mode, thr, v)) h = k; }
+            cur = v;
+            c++;
+            continue;
+        }
+        const int e = info[c];
+        int c1 = c;
+        while (c1 + 1 < chunks && info[c1 + 1] == e) c1++;
+        const uint32_t sb = fbits(cur);
+        if ((int)(sb >> 23) != e) return false;
+        const uint32_t S0 = (sb & 0x7fffffu) | 0x800000u;
+        uint32_t S = S0;
+        // walk chunk by chunk (the kernel composes with a segmented scan; composition is checked too)
+        IncPair run = {0u, 0u};
+        for (int cc = c; cc <= c1; cc++) run = compose(run, cmap[cc]);
+        const uint32_t S1 = step_S(S0, run);
+        if (S1 >= kBinadeEnd) return false;
+        const float after = bitsf(((uint32_t)e << 23) | (S1 & 0x7fffffu));
+        if (mode != 0 && pred(mode, thr, after)) {
+            // find the exact index inside the run
+            for (int cc = c; cc <= c1 && h == n; cc++) {
+                const int b = start + cc * PER, ee = std::min(n, b + PER);
+                for (int k = b; k < ee; k++) {
+                    S = step_S(S, term_inc(fbits(a[k]), e - 150));
+                    if (pred(mode, thr, bitsf(((uint32_t)e << 23) | (S & 0x7fffffu)))) { h = k; break; }
+                }
+            }
+            if (h == n) return false;  // cannot happen: the run's end satisfied the predicate
+        }
+        cur = after;
+        c = c1 + 1;
+    }
+    out = {cur, h};
+    return true;
+}
+
 int main(int argc, char** argv) {
     const int cases = argc > 1 ? std::atoi(argv[1]) : 2000;
     std::mt19937 rng(argc > 2 ? std::atoi(argv[2]) : 1);
     std::uniform_real_distribution<float> U(0.0f, 1.0f);
     std::normal_distribution<float> N(0.0f, 1.0f);
-    long checked = 0;
+    long checked = 0, fast_ok = 0, fast_declined = 0, unsafe_chunks = 0;
     for (int c = 0; c < cases; c++) {
         const int kind = c % 8;
         const int n = 1 + (int)(rng() % (kind == 7 ? 20000 : 3000));
@@ -142,6 +222,20 @@ int main(int argc, char** argv) {
         for (int mode = 0; mode < 3; mode++) {
             const float thr = mode == 0 ? 0.f : full.sum * U(rng) * 1.1f;
             const Result want = sequential(a, mode, thr);
+            {
+                Result fast{};
+                if (emulated_fast(a, mode, thr, fast, &unsafe_chunks)) {
+                    fast_ok++;
+                    const bool sum_ok = mode != 0 || fbits(fast.sum) == fbits(want.sum);
+                    if (!sum_ok || fast.hit != want.hit) {
+                        std::fprintf(stderr, "FAST MISMATCH case %d kind %d n %d mode %d: sum %a vs %a, hit %d vs %d\n", c,
+                                     kind, n, mode, fast.sum, want.sum, fast.hit, want.hit);
+                        return 1;
+                    }
+                } else {
+                    fast_declined++;
+                }
+            }
             for (int T : {1, 7, 64, 1024}) {
                 const Result got = emulated(a, mode, thr, T);
                 checked++;
@@ -153,6 +247,7 @@ int main(int argc, char** argv) {
             }
         }
     }
-    std::printf("ok %ld comparisons\n", checked);
+    std::printf("ok %ld comparisons; one-sweep path: %ld exact, %ld declined, %ld unsafe chunks\n", checked, fast_ok,
+                fast_declined, unsafe_chunks);
     return 0;
 }
