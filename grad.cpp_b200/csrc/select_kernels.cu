@@ -367,8 +367,9 @@ __device__ __forceinline__ SegVal seg_shfl_up(const SegVal& v, int o) {
 
 // work: 4096 words of shared scratch (the sort's histogram is dead by the time scans run).
 // Returns false when the sweep had to be abandoned; the caller then runs seq_scan.
-template <typename Term, typename Hit>
-__device__ bool seq_scan_fast(int n, Term term, Hit hit, bool has_predicate, uint32_t* work, ScanResult& out) {
+template <typename Hit>
+__device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predicate, uint32_t* work, ScanResult& out) {
+    auto term = [arr](int i) { return arr[i]; };
     __shared__ float f_s0;
     __shared__ int f_start, f_hit, f_fail, f_upto;
     __shared__ float f_wd[kSelWarps];
@@ -439,15 +440,34 @@ __device__ bool seq_scan_fast(int n, Term term, Hit hit, bool has_predicate, uin
         __syncthreads();
         return true;
     }
-    if (n - start > kFastMax) return false;  // uniform
+    // Chunks are 16-aligned in index space so a thread's terms are four 128-bit shared-memory loads
+    // (a thread-per-chunk scalar pattern would put the whole warp on two banks).
+    const int base0 = start & ~(kFastPer - 1);
+    if (n - base0 > kFastMax) return false;  // uniform
 
-    // ---- chunk terms into registers, double prefix
-    const int beg = min(n, start + tid * kFastPer), end = min(n, beg + kFastPer);
+    // ---- chunk terms into registers, predicted prefix
+    const int beg = base0 + tid * kFastPer, end = min(n, beg + kFastPer);
     // The prediction only has to be within ~1e-4 of the exact sum: pairwise fp32 sums (error a few
     // 2^-24 per level) are ample, and much cheaper than double precision here.
     float a[kFastPer];
+    if ((reinterpret_cast<uintptr_t>(arr) & 15) == 0) {  // uniform
 #pragma unroll
-    for (int i = 0; i < kFastPer; i++) a[i] = beg + i < end ? term(beg + i) : 0.0f;
+        for (int j = 0; j < kFastPer / 4; j++) {
+            // may read past n inside the shared-memory allocation; such lanes are masked below
+            const float4 v = beg < n ? *reinterpret_cast<const float4*>(arr + beg + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            a[4 * j] = v.x;
+            a[4 * j + 1] = v.y;
+            a[4 * j + 2] = v.z;
+            a[4 * j + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kFastPer; i++) a[i] = beg + i < end ? arr[beg + i] : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < kFastPer; i++) {
+        if (beg + i < start || beg + i >= end) a[i] = 0.0f;  // already consumed by the prefix, or past the end
+    }
     const float dsum = (((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]))) +
                        (((a[8] + a[9]) + (a[10] + a[11])) + ((a[12] + a[13]) + (a[14] + a[15])));
     float incl = dsum;
@@ -474,7 +494,7 @@ __device__ bool seq_scan_fast(int n, Term term, Hit hit, bool has_predicate, uin
     // ---- classify: safe <=> the guaranteed interval of the running sum stays in one binade
     const float lo = P * (1.0f - 1.0f / 512.0f), hi = (P + dsum) * (1.0f + 1.0f / 512.0f);
     const int elo = (int)(__float_as_uint(lo) >> 23), ehi = (int)(__float_as_uint(hi) >> 23);
-    const bool used = beg < end;
+    const bool used = beg < end && beg + kFastPer > start;
     const bool safe = used && elo == ehi && elo >= 30 && elo < 254;
     SegVal sv;
     sv.m.e = sv.m.o = 0u;
@@ -524,7 +544,7 @@ __device__ bool seq_scan_fast(int n, Term term, Hit hit, bool has_predicate, uin
     __syncthreads();
 
     // ---- one thread walks the items (segments and unsafe chunks) with the exact sum
-    const int chunks = (n - start + kFastPer - 1) / kFastPer;
+    const int chunks = (n - base0 + kFastPer - 1) / kFastPer;
     if (tid == 0) {
         float s = s0;
         int h = n, fail = 0, upto = chunks;
@@ -547,13 +567,13 @@ __device__ bool seq_scan_fast(int n, Term term, Hit hit, bool has_predicate, uin
             }
             const int e = info[t];
             if (e < 0) {  // unsafe chunk: native adds
-                const int b0 = start + t * kFastPer, e0 = min(n, b0 + kFastPer);
+                const int b0 = base0 + t * kFastPer, e0 = min(n, b0 + kFastPer);
                 float v[kFastPer];
 #pragma unroll
-                for (int i = 0; i < kFastPer; i++) v[i] = b0 + i < e0 ? term(b0 + i) : 0.0f;  // loads first
+                for (int i = 0; i < kFastPer; i++) v[i] = (b0 + i >= start && b0 + i < e0) ? term(b0 + i) : 0.0f;  // loads first
 #pragma unroll
                 for (int i = 0; i < kFastPer; i++) {
-                    if (b0 + i < e0 && h == n) {
+                    if (b0 + i >= start && b0 + i < e0 && h == n) {
                         s = __fadd_rn(s, v[i]);
                         if (has_predicate && hit(s)) h = b0 + i;
                     }
@@ -605,8 +625,8 @@ __device__ bool seq_scan_fast(int n, Term term, Hit hit, bool has_predicate, uin
         int mine = 0x7fffffff;
 #pragma unroll
         for (int i = 0; i < kFastPer; i++) {
-            if (mine == 0x7fffffff && beg + i < end) {
-                S = step_S(S, term_inc(__float_as_uint(term(beg + i)), elo - 150));
+            if (mine == 0x7fffffff && beg + i >= start && beg + i < end) {
+                S = step_S(S, term_inc(__float_as_uint(a[i]), elo - 150));
                 if (hit(__uint_as_float(((uint32_t)elo << 23) | (S & 0x7fffffu)))) mine = beg + i;
             }
         }
@@ -620,12 +640,12 @@ __device__ bool seq_scan_fast(int n, Term term, Hit hit, bool has_predicate, uin
 }
 
 // The exact scan: the one-sweep fast path, or the pass-per-binade scan when it declines.
-template <typename Term, typename Hit>
-__device__ ScanResult exact_scan(int n, Term term, Hit hit, bool has_predicate, uint32_t* sh, uint32_t* work) {
+template <typename Hit>
+__device__ ScanResult exact_scan(int n, const float* arr, Hit hit, bool has_predicate, uint32_t* sh, uint32_t* work) {
     ScanResult r;
-    if (seq_scan_fast(n, term, hit, has_predicate, work, r)) return r;
+    if (seq_scan_fast(n, arr, hit, has_predicate, work, r)) return r;
     __syncthreads();
-    return seq_scan(n, term, hit, sh);
+    return seq_scan(n, [arr](int i) { return arr[i]; }, hit, sh);
 }
 
 // Bitonic sort, descending, of n_pad (power of two) floats in shared memory.
@@ -851,7 +871,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         // softmax (tensor.cpp:434-448): exp(x - max), sequential sum in index order, times 1/sum
         for (int i = tid; i < V; i += kSelThreads) x[i] = expf_libm(__fsub_rn(x[i], mx));
         __syncthreads();
-        const ScanResult den = exact_scan(V, [&](int i) { return x[i]; }, [](float) { return false; }, false, scan_sh, work);
+        const ScanResult den = exact_scan(V, x, [](float) { return false; }, false, scan_sh, work);
         const float inv_sum = __fdiv_rn(1.0f, den.sum);
         for (int i = tid; i < V; i += kSelThreads) x[i] = __fmul_rn(x[i], inv_sum);
         __syncthreads();
@@ -865,8 +885,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             }
             __syncthreads();
             const float top_p = p.top_p;
-            const ScanResult cut = exact_scan(V, [&](int i) { return sorted[i]; },
-                                              [top_p](float s) { return s >= top_p; }, true, scan_sh, work);
+            const ScanResult cut = exact_scan(V, sorted, [top_p](float s) { return s >= top_p; }, true, scan_sh, work);
             const int cutoff = cut.hit < V ? cut.hit : 0;  // never reached: index stays 0
             const float cutoff_prob = sorted[cutoff];
             __syncthreads();
@@ -874,7 +893,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
                 if (x[i] < cutoff_prob) x[i] = 0.0f;
             }
             __syncthreads();
-            const ScanResult kept = exact_scan(V, [&](int i) { return x[i]; }, [](float) { return false; }, false, scan_sh, work);
+            const ScanResult kept = exact_scan(V, x, [](float) { return false; }, false, scan_sh, work);
             if (kept.sum > 0.0f) {
                 const float tk = kept.sum;
                 for (int i = tid; i < V; i += kSelThreads) x[i] = __fdiv_rn(x[i], tk);
@@ -886,7 +905,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         }
         // draw (text_gen.cpp:199-208): first index with u <= running sum, else the last id
         const float u = p.uniforms[(size_t)b * p.u_stride + (p.loop_mode ? p.gen[b] : 0)];
-        const ScanResult dr = exact_scan(V, [&](int i) { return x[i]; }, [u](float s) { return u <= s; }, true, scan_sh, work);
+        const ScanResult dr = exact_scan(V, x, [u](float s) { return u <= s; }, true, scan_sh, work);
         pick = dr.hit < V ? dr.hit : V - 1;
     }
 
