@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int s_tok[TN], s_pos[TN];
+    __shared__ int s_tok[TN], s_pos[TN], s_seq[TN];
 
     constexpr int kABytes = NW * kTileM * kBlockK * 2;
     constexpr int kBBytes = TN * kBlockK * 2;
@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
         const int tk = b < p.B ? p.tok[b] : kSkip;
         s_tok[c] = tk;
         s_pos[c] = tk >= 0 ? p.pos[b] : 0;
+        s_seq[c] = (tk >= 0 && p.row_seq) ? p.row_seq[b] : b;
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) {
@@ -267,7 +268,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
                             if (which == 0) {
                                 p.out_f32[(size_t)b * p.ld_out + n_in] = val;
                             } else {
-                                cache[(((size_t)b * p.H + h) * p.T + posn[jj]) * p.hs + c_in] = val;
+                                cache[(((size_t)s_seq[c0 + j] * p.H + h) * p.T + posn[jj]) * p.hs + c_in] = val;
                             }
                         }
                     } else if (EPI == TC_RESID) {
@@ -420,6 +421,31 @@ void make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
 
 // Largest token tile that still yields enough CTAs to occupy most of the SMs: these GEMMs
 // are short, so CTA count (latency hiding across SMs) matters more than MMA width.
+namespace {
+template <int EPI, int NW, int TN>
+void configure_one() {
+    constexpr size_t bytes = (size_t)kStages * (NW * kTileM * kBlockK * 2 + TN * kBlockK * 2) + 1024;
+    GRADB_CUDA(cudaFuncSetAttribute(gemm_bf16_tc_kernel<EPI, NW, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)bytes));
+}
+template <int EPI, int NW>
+void configure_tiles() {
+    configure_one<EPI, NW, 32>();
+    configure_one<EPI, NW, 64>();
+    configure_one<EPI, NW, 128>();
+}
+}  // namespace
+
+// Opt every GEMM variant into its dynamic shared memory up front (per device), so that no
+// attribute call is needed later, in particular not while a stream is being captured.
+void tc_configure_all() {
+    configure_tiles<TC_QKV, 1>();
+    configure_tiles<TC_RESID, 1>();
+    configure_tiles<TC_GELU, 1>();
+    configure_tiles<TC_SWIGLU, 2>();
+    configure_tiles<TC_LOGITS, 1>();
+}
+
 int tc_token_tile(int n_seq, int n_tiles, int want_ctas) {
     for (int tn : {128, 64, 32}) {
         if (tn > 32 && tn >= 2 * n_seq) continue;  // do not pad a small batch to a wide tile

@@ -14,6 +14,7 @@ struct TcGemmParams {
     int ld_out;
     const float* bias[3];
     const int *tok, *pos;
+    const int* row_seq;  // optional: cache sequence of each row (prompt feed: one row per prompt token); null = row index
     const float *rope_cos, *rope_sin;
     float* out_f32;           // q / residual stream / logits
     __nv_bfloat16* out_bf16;  // FFN activation
@@ -24,6 +25,7 @@ struct TcGemmParams {
 // 2-D bf16 tensor map over a row-major (rows, cols) matrix: boxes of 64 columns x box_rows, 128-byte swizzle.
 void make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 int tc_token_tile(int n_seq, int n_tiles, int want_ctas);
+void tc_configure_all();
 void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int token_tile,
                     int k_splits, cudaStream_t st);
 void launch_norm_bf16(const float* X, const float* gamma, const float* beta, const int* tok, __nv_bfloat16* out, int d,

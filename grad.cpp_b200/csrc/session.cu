@@ -379,6 +379,168 @@ int upload_prompt_matrix(Session* s, const int32_t* tokens, const int32_t* offse
     return steps;
 }
 
+constexpr int kFeedRows = 8192;  // prompt tokens processed at once by the batched feed
+
+void ensure_feed_buffers(Session* s) {
+    Session::Feed& f = s->feed;
+    if (f.cap) return;
+    const size_t R = kFeedRows;
+    dalloc(&f.x, R * s->d);
+    dalloc(&f.q, R * s->d);
+    dalloc(&f.attn, R * s->d);
+    dalloc(&f.h16, R * s->d);
+    dalloc(&f.attn16, R * s->d);
+    dalloc(&f.ffn16, R * s->dff);
+    dalloc(&f.row_tok, R);
+    dalloc(&f.row_pos, R);
+    dalloc(&f.row_seq, R);
+    dalloc(&f.row_last, R);
+    dalloc(&f.seq_count, (size_t)s->B);
+    dalloc(&f.last_tok, (size_t)s->B);
+    for (int i = 0; i < 3; i++) {
+        const uint32_t tn = 32u << i;
+        make_tensor_map_bf16(&f.map_h16[i], f.h16, R, s->d, tn);
+        make_tensor_map_bf16(&f.map_attn16[i], f.attn16, R, s->d, tn);
+        make_tensor_map_bf16(&f.map_ffn16[i], f.ffn16, R, s->dff, tn);
+    }
+    f.cap = (int)R;
+}
+
+// Batched prompt feed on the tensor-core path: every prompt token of a chunk of positions is one
+// row, so each projection runs once per layer over all of them (M = rows) instead of once per
+// position. Row r stands for (sequence row_seq[r], position row_pos[r]); K/V rows go to that
+// sequence's cache slot and attention reads positions 0..row_pos[r] of it, which is the causal
+// prompt attention. Leaves caches, positions, history and last-position logits exactly as the
+// reference's step-by-step feed would (text_gen.cpp:44-46).
+void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_t* offsets, int n_seq) {
+    const DeviceModel* m = s->m;
+    const bool modern = m->desc.arch == GRADB_ARCH_MODERN;
+    cudaStream_t st = s->stream;
+    ensure_feed_buffers(s);
+    Session::Feed& f = s->feed;
+    const int d = s->d, ff = s->dff;
+    int max_len = 0;
+    for (int b = 0; b < n_seq; b++) max_len = std::max(max_len, offsets[b + 1] - offsets[b]);
+    const int width = std::max(1, f.cap / n_seq);  // positions per chunk
+    const int want = m->sm_count * 3 / 4;
+    auto map_idx = [](int tn) { return tn == 32 ? 0 : (tn == 64 ? 1 : 2); };
+
+    // per-sequence logits mask: id of the last prompt token, or skip
+    f.h_rows.resize((size_t)4 * f.cap + 2 * (size_t)s->B);
+    int* h_last = f.h_rows.data() + (size_t)4 * f.cap + s->B;
+    for (int b = 0; b < n_seq; b++) h_last[b] = offsets[b + 1] > offsets[b] ? tokens[offsets[b + 1] - 1] : kSkip;
+    GRADB_CUDA(cudaMemcpyAsync(f.last_tok, h_last, n_seq * sizeof(int), cudaMemcpyHostToDevice, st));
+
+    for (int p0 = 0; p0 < max_len; p0 += width) {
+        const int p1 = std::min(max_len, p0 + width);
+        int* h_tok = f.h_rows.data();
+        int* h_pos = h_tok + f.cap;
+        int* h_seq = h_pos + f.cap;
+        int* h_lastrow = h_seq + f.cap;
+        int* h_cnt = h_lastrow + f.cap;
+        int R = 0;
+        for (int b = 0; b < n_seq; b++) {
+            const int len = offsets[b + 1] - offsets[b];
+            h_cnt[b] = 0;
+            for (int j = p0; j < std::min(p1, len); j++) {
+                h_tok[R] = tokens[offsets[b] + j];
+                h_pos[R] = s->h_pos[b] + j;
+                h_seq[R] = b;
+                h_lastrow[R] = j == len - 1 ? h_tok[R] : kSkip;
+                R++;
+                h_cnt[b]++;
+            }
+        }
+        if (R == 0) continue;
+        GRADB_CUDA(cudaMemcpyAsync(f.row_tok, h_tok, R * sizeof(int), cudaMemcpyHostToDevice, st));
+        GRADB_CUDA(cudaMemcpyAsync(f.row_pos, h_pos, R * sizeof(int), cudaMemcpyHostToDevice, st));
+        GRADB_CUDA(cudaMemcpyAsync(f.row_seq, h_seq, R * sizeof(int), cudaMemcpyHostToDevice, st));
+        GRADB_CUDA(cudaMemcpyAsync(f.row_last, h_lastrow, R * sizeof(int), cudaMemcpyHostToDevice, st));
+        GRADB_CUDA(cudaMemcpyAsync(f.seq_count, h_cnt, n_seq * sizeof(int), cudaMemcpyHostToDevice, st));
+        GRADB_CUDA(cudaStreamSynchronize(st));  // the staging vector is reused by the next chunk
+
+        auto tile_for = [&](int n_features) { return tc_token_tile(R, (n_features + 127) / 128, want); };
+        {
+            Timed t(s, KC_EMBED);
+            launch_embed(m->emb, modern ? nullptr : m->pos, f.row_tok, f.row_pos, f.x, d, R, st);
+        }
+        TcGemmParams base{};
+        base.B = R; base.d = d; base.H = s->H; base.hs = s->hs; base.T = s->T;
+        base.tok = f.row_tok; base.pos = f.row_pos; base.row_seq = f.row_seq; base.status = s->status;
+        for (int l = 0; l < s->L; l++) {
+            const LayerWeights& w = m->layers[l];
+            float* kc = s->kcache + (size_t)l * layer_cache_elems(s);
+            float* vc = s->vcache + (size_t)l * layer_cache_elems(s);
+            {
+                Timed t(s, KC_QKV);
+                launch_norm_bf16(f.x, w.n1g, w.n1b, f.row_tok, f.h16, d, modern, 1e-5f, R, st);
+                TcGemmParams g = base;
+                g.K = d; g.N = 3 * d; g.ld_out = d;
+                g.bias[0] = w.bq; g.bias[1] = w.bk; g.bias[2] = w.bv;
+                g.rope_cos = modern ? m->rope_cos : nullptr;
+                g.rope_sin = modern ? m->rope_sin : nullptr;
+                g.out_f32 = f.q; g.kcache = kc; g.vcache = vc;
+                const int tn = tile_for(3 * d);
+                launch_tc_gemm(TC_QKV, w.map_qkv, f.map_h16[map_idx(tn)], g, tn, 1, st);
+            }
+            {
+                Timed t(s, KC_ATTN);
+                AttnParams a{};
+                a.q = f.q; a.kcache = kc; a.vcache = vc; a.tok = f.row_tok; a.pos = f.row_pos; a.row_seq = f.row_seq;
+                a.out = f.attn; a.out16 = f.attn16; a.partial = nullptr; a.counters = nullptr; a.status = s->status;
+                a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = d;
+                a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
+                launch_attention(a, R, 1, st);
+            }
+            {
+                Timed t(s, KC_OPROJ);
+                TcGemmParams g = base;
+                g.K = d; g.N = d; g.ld_out = d; g.bias[0] = w.bo; g.out_f32 = f.x;
+                const int tn = tile_for(d);
+                launch_tc_gemm(TC_RESID, w.map_o, f.map_attn16[map_idx(tn)], g, tn, 1, st);
+            }
+            {
+                Timed t(s, KC_FFN_UP);
+                launch_norm_bf16(f.x, w.n2g, w.n2b, f.row_tok, f.h16, d, modern, 1e-5f, R, st);
+                TcGemmParams g = base;
+                g.K = d; g.N = ff; g.ld_out = ff; g.out_bf16 = f.ffn16;
+                g.bias[0] = modern ? nullptr : w.b1;
+                const int tn = tile_for(ff);
+                launch_tc_gemm(modern ? TC_SWIGLU : TC_GELU, w.map_up, f.map_h16[map_idx(tn)], g, tn, 1, st);
+            }
+            {
+                Timed t(s, KC_FFN_DOWN);
+                TcGemmParams g = base;
+                g.K = ff; g.N = d; g.ld_out = d; g.bias[0] = modern ? nullptr : w.b2; g.out_f32 = f.x;
+                const int tn = tile_for(d);
+                launch_tc_gemm(TC_RESID, w.map_down, f.map_ffn16[map_idx(tn)], g, tn, 1, st);
+            }
+        }
+        launch_gather_last_rows(f.x, f.row_last, f.row_seq, s->x, d, R, st);
+        launch_feed_bookkeeping(f.row_tok, f.row_pos, f.row_seq, f.seq_count, s->pos, s->hist_len, s->hist, s->hist_stride,
+                                R, n_seq, st);
+        for (int b = 0; b < n_seq; b++) s->h_pos[b] += h_cnt[b];
+    }
+    for (int b = 0; b < n_seq; b++) s->h_pos[b] -= offsets[b + 1] - offsets[b];  // callers add the lengths themselves
+
+    // last-position logits: final norm + tied-embedding GEMM over the per-sequence rows
+    {
+        Timed t(s, KC_LOGITS);
+        launch_norm_bf16(s->x, m->fng, m->fnb, f.last_tok, s->h16, d, modern, 1e-5f, n_seq, st);
+        TcGemmParams g{};
+        g.B = n_seq; g.d = d; g.H = s->H; g.hs = s->hs; g.T = s->T;
+        g.tok = f.last_tok; g.pos = s->pos; g.status = s->status;
+        g.K = d; g.N = s->V; g.ld_out = s->V; g.out_f32 = s->logits;
+        const int tn = tc_token_tile(n_seq, (s->V + 127) / 128, want);
+        launch_tc_gemm(TC_LOGITS, m->map_emb, s->map_h16[map_idx(tn)], g, tn, 1, st);
+    }
+}
+
+bool use_batched_feed(const Session* s, int n_seq) {
+    const char* off = std::getenv("GRADB_NO_BATCHED_FEED");
+    return s->use_tc && n_seq >= 16 && s->hs == 64 && !(off && off[0] == '1');
+}
+
 void enqueue_prompt_feed(Session* s, int steps, int n_seq) {
     for (int t = 0; t < steps; t++) {
         const int* row = s->tok_matrix + (size_t)t * 2 * n_seq;
@@ -416,8 +578,10 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         }
         const char* ng = std::getenv("GRADB_NO_GRAPH");
         s->use_graph = !(ng && ng[0] == '1');
-        // Enough attention CTAs to cover the SMs about twice, at most 16 splits of the context.
-        const int want = (2 * m->sm_count + s->B * s->H - 1) / (s->B * s->H);
+        // The attention kernel deals (sequence, head, context split) units to 4 warps per SM; about four
+        // units per warp keep the tail short. More splits only when sequences x heads alone are too few.
+        const int want_units = 16 * m->sm_count;
+        const int want = (want_units + s->B * s->H - 1) / (s->B * s->H);
         s->attn_splits = std::max(1, std::min({want, 16, (s->T + 31) / 32}));
         const size_t B = s->B;
         dalloc(&s->x, B * s->d);
@@ -453,7 +617,10 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         }
         const char* ntc = std::getenv("GRADB_NO_TC");
         s->use_tc = m->tc_ok && s->B >= 16 && !(ntc && ntc[0] == '1');
+        if (s->hs == 64) attention_configure();
+        configure_select(s->V);
         if (s->use_tc) {
+            tc_configure_all();
             // rows padded to a whole 128-row tile so a TMA box never starts outside the buffer
             const size_t rows = (size_t)((s->B + 127) / 128) * 128;
             dalloc(&s->h16, rows * s->d);
@@ -504,6 +671,9 @@ void destroy_session(Session* s) {
     cudaFree(s->gen); cudaFree(s->done); cudaFree(s->out_tok); cudaFree(s->tok_matrix);
     cudaFree(s->uniforms); cudaFree(s->probs);
     cudaFree(s->b1_ws); cudaFree(s->b1_bar); cudaFree(s->b1_trace);
+    cudaFree(s->feed.x); cudaFree(s->feed.q); cudaFree(s->feed.attn); cudaFree(s->feed.h16); cudaFree(s->feed.attn16);
+    cudaFree(s->feed.ffn16); cudaFree(s->feed.row_tok); cudaFree(s->feed.row_pos); cudaFree(s->feed.row_seq);
+    cudaFree(s->feed.row_last); cudaFree(s->feed.seq_count); cudaFree(s->feed.last_tok);
     cudaFree(s->h16); cudaFree(s->attn16); cudaFree(s->ffn16); cudaFree(s->status);
     if (s->h_stage) cudaFreeHost(s->h_stage);
     if (s->own_stream && s->stream) cudaStreamDestroy(s->stream);
@@ -555,7 +725,8 @@ void session_prefill(Session* s, const int32_t* tokens, const int32_t* offsets, 
     GRADB_CUDA(cudaSetDevice(s->m->device));
     const int steps = upload_prompt_matrix(s, tokens, offsets, n_seq);
     GRADB_CUDA(cudaEventRecord(s->ev_begin, s->stream));
-    enqueue_prompt_feed(s, steps, n_seq);
+    if (use_batched_feed(s, n_seq)) enqueue_prompt_feed_batched(s, tokens, offsets, n_seq);
+    else enqueue_prompt_feed(s, steps, n_seq);
     GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
     if (logits_host) {
         GRADB_CUDA(cudaMemcpyAsync(logits_host, s->logits, (size_t)n_seq * s->V * sizeof(float),
@@ -645,7 +816,8 @@ void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets
     }
 
     GRADB_CUDA(cudaEventRecord(s->ev_begin, s->stream));
-    enqueue_prompt_feed(s, steps, n_seq);
+    if (use_batched_feed(s, n_seq)) enqueue_prompt_feed_batched(s, prompts, offsets, n_seq);
+    else enqueue_prompt_feed(s, steps, n_seq);
     GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
 
     SelectParams p = make_select(s, sp);

@@ -42,6 +42,17 @@ struct Session {
     CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];  // token tiles of 32, 64, 128 rows
     int* status = nullptr;
 
+    // batched prompt feed (one row per prompt token, all positions of a chunk at once)
+    struct Feed {
+        int cap = 0;  // rows per chunk
+        float *x = nullptr, *q = nullptr, *attn = nullptr;
+        __nv_bfloat16 *h16 = nullptr, *attn16 = nullptr, *ffn16 = nullptr;
+        int *row_tok = nullptr, *row_pos = nullptr, *row_seq = nullptr, *row_last = nullptr, *seq_count = nullptr,
+            *last_tok = nullptr;
+        CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];
+        std::vector<int> h_rows;  // host staging: 4 * cap + 2 * B ints
+    } feed;
+
     // single-sequence persistent kernel: workspace and grid-barrier words
     bool use_b1 = false;
     float* b1_ws = nullptr;

@@ -101,6 +101,36 @@ __global__ void advance_kernel(const int* __restrict__ tok, int* __restrict__ po
     }
 }
 
+// Prompt feed with one row per prompt token: copy each sequence's last row into the per-sequence
+// residual buffer (the logits are only needed there).
+__global__ void gather_last_rows_kernel(const float* __restrict__ rows, const int* __restrict__ row_last,
+                                        const int* __restrict__ row_seq, float* __restrict__ x_seq, int d) {
+    const int r = blockIdx.x;
+    if (row_last[r] < 0) return;
+    const float4* src = reinterpret_cast<const float4*>(rows + (size_t)r * d);
+    float4* dst = reinterpret_cast<float4*>(x_seq + (size_t)row_seq[r] * d);
+    for (int j = threadIdx.x; j < d / 4; j += blockDim.x) dst[j] = src[j];
+}
+
+// Prompt feed bookkeeping, rows: the fed ids join their sequence's history.
+__global__ void feed_history_kernel(const int* __restrict__ row_tok, const int* __restrict__ row_pos,
+                                    const int* __restrict__ row_seq, const int* __restrict__ pos,
+                                    const int* __restrict__ hist_len, int* __restrict__ hist, int hist_stride, int R) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    const int s = row_seq[r];
+    const int idx = hist_len[s] + (row_pos[r] - pos[s]);
+    if (idx >= 0 && idx < hist_stride) hist[(size_t)s * hist_stride + idx] = row_tok[r];
+}
+// Prompt feed bookkeeping, sequences: positions and history lengths move on by the ids fed.
+__global__ void feed_advance_kernel(const int* __restrict__ seq_count, int* __restrict__ pos, int* __restrict__ hist_len,
+                                    int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    pos[b] += seq_count[b];
+    hist_len[b] += seq_count[b];
+}
+
 // ------------------------------------------------------------- fused gemv
 
 // Shared-memory layout (floats): xs[MB][Kc] | xfull[K] (norm prologue only) | red[kWarps][NW][MB][128]
@@ -536,6 +566,7 @@ struct AttnCursor {  // position in a warp's flat sequence of tiles
     int unit;        // current unit index (advances by the number of warps in the grid)
     int tile, tile_end;
     int b, h, split, ctx;
+    int seq;  // cache sequence of row b
 };
 
 __device__ __forceinline__ bool attn_unit_setup(const AttnParams& p, int S, int total_units, AttnCursor& c) {
@@ -545,12 +576,14 @@ __device__ __forceinline__ bool attn_unit_setup(const AttnParams& p, int S, int 
     c.b = c.unit / hs_units;
     c.h = (c.unit / S) % p.H;
     c.split = c.unit % S;
+    c.seq = c.b;
     if (p.tok[c.b] < 0) {  // sequence sits this step out: no tiles, nothing to finalise
         c.ctx = 0;
         c.tile = c.tile_end = 0;
         return true;
     }
     c.ctx = p.pos[c.b] + 1;
+    if (p.row_seq) c.seq = p.row_seq[c.b];
     const int ntiles = (c.ctx + kPipeTileRows - 1) / kPipeTileRows;
     const int tps = (ntiles + S - 1) / S;
     c.tile = c.split * tps;
@@ -593,7 +626,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) attn_decode64_pipe_kernel(
         const int r0 = fc.tile * kPipeTileRows;
         const int nrows = min(kPipeTileRows, fc.ctx - r0);
         if (lane == 0) {
-            const size_t off = (((size_t)fc.b * p.H + fc.h) * p.T + r0) * HS;
+            const size_t off = (((size_t)fc.seq * p.H + fc.h) * p.T + r0) * HS;
             const uint32_t bytes = (uint32_t)nrows * HS * 4;
             const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&full_bar[w][stage]);
             const uint32_t dstk = (uint32_t)__cvta_generic_to_shared(ring + (size_t)stage * kPipeStageFloats);
@@ -860,6 +893,21 @@ int pick_mb(int B) { return B >= 8 ? 8 : (B >= 4 ? 4 : (B >= 2 ? 2 : 1)); }
 
 }  // namespace
 
+void launch_gather_last_rows(const float* rows, const int* row_last, const int* row_seq, float* x_seq, int d, int R,
+                             cudaStream_t st) {
+    gather_last_rows_kernel<<<R, 128, 0, st>>>(rows, row_last, row_seq, x_seq, d);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+void launch_feed_bookkeeping(const int* row_tok, const int* row_pos, const int* row_seq, const int* seq_count, int* pos,
+                             int* hist_len, int* hist, int hist_stride, int R, int B, cudaStream_t st) {
+    feed_history_kernel<<<(R + 255) / 256, 256, 0, st>>>(row_tok, row_pos, row_seq, pos, hist_len, hist, hist_stride, R);
+    feed_advance_kernel<<<(B + 255) / 256, 256, 0, st>>>(seq_count, pos, hist_len, B);
+    count_launch(2);
+    GRADB_CUDA(cudaGetLastError());
+}
+
 void launch_embed(const float* E, const float* P, const int* tok, const int* pos, float* x, int d, int B,
                   cudaStream_t st) {
     embed_kernel<<<B, 128, 0, st>>>(E, P, tok, pos, x, d);
@@ -966,6 +1014,12 @@ void launch_attention_static(const AttnParams& p_in, int B, int splits, cudaStre
     attn_decode64_kernel<<<dim3(splits, p.H, B), kAttnWarps * 32, 0, st>>>(p);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
+}
+
+// Opt the pipelined attention kernel into its shared memory up front (per device).
+void attention_configure() {
+    const size_t bytes = (size_t)kAttnWarps * kPipeStages * kPipeStageFloats * sizeof(float);
+    GRADB_CUDA(cudaFuncSetAttribute(attn_decode64_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
 }
 
 void launch_attention(const AttnParams& p, int B, int splits, cudaStream_t st) {

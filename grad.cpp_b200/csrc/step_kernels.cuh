@@ -40,6 +40,7 @@ struct AttnParams {
     const float* q;  // [B][d]
     const float *kcache, *vcache;
     const int *tok, *pos;
+    const int* row_seq;  // optional: cache sequence of each row (prompt feed); null = row index
     float* out;       // [B][d]
     __nv_bfloat16* out16;  // optional bf16 copy of out (operand of the tensor-core projection)
     float* partial;   // [B][H][S][hs+2] split results: o[hs], max, sum
@@ -49,12 +50,17 @@ struct AttnParams {
     float scale;
 };
 
+void launch_gather_last_rows(const float* rows, const int* row_last, const int* row_seq, float* x_seq, int d, int R,
+                             cudaStream_t st);
+void launch_feed_bookkeeping(const int* row_tok, const int* row_pos, const int* row_seq, const int* seq_count, int* pos,
+                             int* hist_len, int* hist, int hist_stride, int R, int B, cudaStream_t st);
 void launch_embed(const float* E, const float* P, const int* tok, const int* pos, float* x, int d, int B,
                   cudaStream_t st);
 void launch_advance(const int* tok, int* pos, int* hist, int* hist_len, int hist_stride, int B, cudaStream_t st);
 void launch_gemv(const GemvParams& p, int pro, int epi, bool bf16, int sm_count, cudaStream_t st);
 void launch_logits(const LogitsParams& p, bool bf16, cudaStream_t st);
 void launch_attention(const AttnParams& p, int B, int splits, cudaStream_t st);
+void attention_configure();
 // Same kernel with its scratch in a fixed device array (no allocation); see step_kernels.cu.
 void launch_attention_static(const AttnParams& p, int B, int splits, cudaStream_t st);
 int static_attention_capacity();
