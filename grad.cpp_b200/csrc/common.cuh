@@ -33,6 +33,32 @@ extern std::atomic<uint64_t> g_kernel_launches;
 extern thread_local bool g_capturing;
 inline void count_launch(uint64_t n = 1) { g_kernel_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// Programmatic dependent launch: a kernel launched with this attribute may start while its
+// predecessor on the stream is still running; it must execute pdl_wait() before touching anything
+// the predecessor produces (or still reads). Predecessors call pdl_trigger() as early as they can.
+// Set by the session code around the launches that may overlap (g_pdl is per host thread).
+extern thread_local bool g_pdl;
+
+#if defined(__CUDACC__)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl ? 1 : 0;
+    GRADB_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+#endif
+
 // Sequences whose current token id is negative take no part in a step.
 constexpr int kSkip = -1;
 // Width of the repetition-penalty window (text_gen.cpp:22).

@@ -27,7 +27,13 @@ namespace gradb {
 
 namespace {
 
-constexpr int kStages = 4;
+// Ring depth: four stages (fewer only if a stage is very large). Deeper rings were measured slower here:
+// they push every variant to one CTA per SM and lengthen the prologue of kernels that run for a few microseconds.
+constexpr int stages_for(int nw, int tn) {
+    const int stage = nw * 128 * 64 * 2 + tn * 64 * 2;
+    const int n = (200 * 1024) / stage;
+    return n > 4 ? 4 : (n < 2 ? 2 : n);
+}
 constexpr int kBlockK = 64;  // bf16 elements = one 128-byte swizzle row
 constexpr int kTileM = 128;  // features per MMA
 constexpr uint32_t kSpinLimit = 1u << 20;
@@ -119,6 +125,7 @@ template <int EPI, int NW, int TN>
 __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            const __grid_constant__ CUtensorMap map_b,
                                                            const TcGemmParams p) {
+    constexpr int kStages = stages_for(NW, TN);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
     __shared__ uint32_t tmem_base_slot;
@@ -138,13 +145,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
     const int k_beg = kz * k_per, k_end = min(k_iters_total, k_beg + k_per);
     const int n_iters = max(0, k_end - k_beg);
 
-    for (int c = threadIdx.x; c < TN; c += blockDim.x) {
-        const int b = blockIdx.y * TN + c;
-        const int tk = b < p.B ? p.tok[b] : kSkip;
-        s_tok[c] = tk;
-        s_pos[c] = tk >= 0 ? p.pos[b] : 0;
-        s_seq[c] = (tk >= 0 && p.row_seq) ? p.row_seq[b] : b;
-    }
+    pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) {
             mbar_init(&full_bar[s], 1);
@@ -166,9 +167,36 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
     const uint32_t tmem_base = tmem_base_slot;
     bool ok = true;
 
+    // The weight tiles do not depend on earlier kernels: start their stream before waiting for the
+    // predecessor (programmatic dependent launch); activations, positions and ids come after.
+    const int pre = min(n_iters, kStages);
+    if (threadIdx.x == 0) {
+        for (int it = 0; it < pre; it++) {
+            uint8_t* st = smem + (size_t)it * kStageBytes;
+            mbar_expect_tx(&full_bar[it], kStageBytes);
+            const int kx = (k_beg + it) * kBlockK;
+#pragma unroll
+            for (int w = 0; w < NW; w++) {
+                tma_load_2d(st + w * (kTileM * kBlockK * 2), &map_a, kx, (tile_n * NW + w) * kTileM, &full_bar[it]);
+            }
+        }
+    }
+    pdl_wait();
+    for (int c = threadIdx.x; c < TN; c += blockDim.x) {
+        const int b = blockIdx.y * TN + c;
+        const int tk = b < p.B ? p.tok[b] : kSkip;
+        s_tok[c] = tk;
+        s_pos[c] = tk >= 0 ? p.pos[b] : 0;
+        s_seq[c] = (tk >= 0 && p.row_seq) ? p.row_seq[b] : b;
+    }
+    __syncthreads();
+
     if (warp == 0 && lane == 0) {
         // ---- TMA producer
-        for (int it = 0; it < n_iters && ok; it++) {
+        for (int it = 0; it < pre; it++) {
+            tma_load_2d(smem + (size_t)it * kStageBytes + kABytes, &map_b, (k_beg + it) * kBlockK, tile_b * TN, &full_bar[it]);
+        }
+        for (int it = pre; it < n_iters && ok; it++) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1;
             ok = mbar_wait(&empty_bar[s], ph ^ 1, p.status, 101);
@@ -305,10 +333,13 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
 }
 
 // fp32 rows -> normalised bf16 rows (LayerNorm or RMSNorm), the tensor-core GEMMs' B operand.
+// One 256-thread CTA per row (a warp-per-row variant with fewer CTAs measured slower).
 __global__ void __launch_bounds__(256) norm_bf16_kernel(const float* __restrict__ X, const float* __restrict__ gamma,
                                                         const float* __restrict__ beta, const int* __restrict__ tok,
                                                         __nv_bfloat16* __restrict__ out, int d, int rms, float eps) {
     __shared__ float sh[8];
+    pdl_trigger();
+    pdl_wait();
     const int b = blockIdx.x;
     if (tok[b] < 0) return;
     const float* xr = X + (size_t)b * d;
@@ -384,12 +415,12 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 
 template <int EPI, int NW, int TN>
 void launch_t(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, dim3 grid, cudaStream_t st) {
-    constexpr size_t bytes = (size_t)kStages * (NW * kTileM * kBlockK * 2 + TN * kBlockK * 2) + 1024;
+    constexpr size_t bytes = (size_t)stages_for(NW, TN) * (NW * kTileM * kBlockK * 2 + TN * kBlockK * 2) + 1024;
     auto kernel = gemm_bf16_tc_kernel<EPI, NW, TN>;
     if (!g_capturing) {
         GRADB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
-    kernel<<<grid, 128, bytes, st>>>(a, b, p);
+    launch_kernel(kernel, grid, dim3(128), bytes, st, a, b, p);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }
@@ -424,7 +455,7 @@ void make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
 namespace {
 template <int EPI, int NW, int TN>
 void configure_one() {
-    constexpr size_t bytes = (size_t)kStages * (NW * kTileM * kBlockK * 2 + TN * kBlockK * 2) + 1024;
+    constexpr size_t bytes = (size_t)stages_for(NW, TN) * (NW * kTileM * kBlockK * 2 + TN * kBlockK * 2) + 1024;
     GRADB_CUDA(cudaFuncSetAttribute(gemm_bf16_tc_kernel<EPI, NW, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     (int)bytes));
 }
@@ -470,7 +501,7 @@ void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b,
 
 void launch_norm_bf16(const float* X, const float* gamma, const float* beta, const int* tok, __nv_bfloat16* out, int d,
                       int rms, float eps, int B, cudaStream_t st) {
-    norm_bf16_kernel<<<B, 256, 0, st>>>(X, gamma, beta, tok, out, d, rms, eps);
+    launch_kernel(norm_bf16_kernel, dim3(B), dim3(256), 0, st, X, gamma, beta, tok, out, d, rms, eps);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }

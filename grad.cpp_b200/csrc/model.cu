@@ -9,6 +9,7 @@ namespace gradb {
 
 std::atomic<uint64_t> g_kernel_launches{0};
 thread_local bool g_capturing = false;
+thread_local bool g_pdl = false;
 
 namespace {
 __global__ void to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {

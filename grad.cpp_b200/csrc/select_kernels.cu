@@ -755,6 +755,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     __shared__ int s_pick;
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int V = p.V;
+    pdl_trigger();
+    pdl_wait();
     if (p.loop_mode && p.done[b]) return;
 
     float* x = smem;           // [V]
@@ -949,7 +951,7 @@ void launch_select(const SelectParams& p_in, int B, cudaStream_t st) {
     if (bytes > 48 * 1024 && !g_capturing) {
         GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
-    select_kernel<<<B, kSelThreads, bytes, st>>>(p);
+    launch_kernel(select_kernel, dim3(B), dim3(kSelThreads), bytes, st, p);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }

@@ -71,6 +71,13 @@ void collect_spans(Session* s) {
 // only needs them at each sequence's last position).
 // Tensor-core variant of a step: every projection is a TMA-fed tcgen05 GEMM over all
 // sequences; norms produce the bf16 operand, attention stays the streaming kernel.
+// Scope in which launches carry the programmatic-dependent-launch attribute.
+struct PdlScope {
+    bool prev;
+    explicit PdlScope(bool on) : prev(g_pdl) { g_pdl = on; }
+    ~PdlScope() { g_pdl = prev; }
+};
+
 void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit_tok_dev, bool append_history) {
     const DeviceModel* m = s->m;
     const bool modern = m->desc.arch == GRADB_ARCH_MODERN;
@@ -89,6 +96,9 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
         Timed t(s, KC_EMBED);
         launch_embed(m->emb, modern ? nullptr : m->pos, tok_dev, s->pos, s->x, d, n_seq, st);
     }
+    // Every kernel of the step after the first may begin (its set-up, and for the GEMMs the weight
+    // stream) while its predecessor drains; each waits for the predecessor before touching its data.
+    PdlScope pdl(s->use_pdl && !s->profiling);
     TcGemmParams base{};
     base.B = n_seq; base.d = d; base.H = s->H; base.hs = s->hs; base.T = s->T;
     base.tok = tok_dev; base.pos = s->pos; base.status = s->status;
@@ -614,6 +624,8 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
                 GRADB_CUDA(cudaMemsetAsync(s->b1_trace, 0, 1024 * sizeof(unsigned long long), s->stream));
             }
         }
+        const char* npdl = std::getenv("GRADB_NO_PDL");
+        s->use_pdl = !(npdl && npdl[0] == '1');
         const char* ntc = std::getenv("GRADB_NO_TC");
         s->use_tc = m->tc_ok && s->B >= 16 && !(ntc && ntc[0] == '1');
         if (s->hs == 64) attention_configure();

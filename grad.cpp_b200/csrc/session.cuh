@@ -38,6 +38,7 @@ struct Session {
 
     // tensor-core path: bf16 activations (GEMM B operands), their TMA descriptors, device status word
     bool use_tc = false;
+    bool use_pdl = true;  // programmatic dependent launch between the kernels of a tensor-core step
     __nv_bfloat16 *h16 = nullptr, *attn16 = nullptr, *ffn16 = nullptr;
     CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];  // token tiles of 32, 64, 128 rows
     int* status = nullptr;

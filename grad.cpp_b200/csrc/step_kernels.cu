@@ -70,6 +70,8 @@ __device__ __forceinline__ float4 load_w4(const __nv_bfloat16* p) {
 
 __global__ void embed_kernel(const float* __restrict__ E, const float* __restrict__ P, const int* __restrict__ tok,
                              const int* __restrict__ pos, float* __restrict__ x, int d) {
+    pdl_trigger();
+    pdl_wait();
     const int b = blockIdx.x;
     const int t = tok[b];
     if (t < 0) return;
@@ -91,6 +93,8 @@ __global__ void embed_kernel(const float* __restrict__ E, const float* __restric
 // repetition penalty reads.
 __global__ void advance_kernel(const int* __restrict__ tok, int* __restrict__ pos, int* __restrict__ hist,
                                int* __restrict__ hist_len, int hist_stride, int B) {
+    pdl_trigger();
+    pdl_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B || tok[b] < 0) return;
     pos[b] += 1;
@@ -610,6 +614,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) attn_decode64_pipe_kernel(
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
+    pdl_trigger();
+    pdl_wait();  // q, positions and the newest K/V rows come from the kernels before this one
 
     // issue the copies of the tile the fetch cursor points at, then advance it
     AttnCursor fc{};
@@ -910,13 +916,13 @@ void launch_feed_bookkeeping(const int* row_tok, const int* row_pos, const int* 
 
 void launch_embed(const float* E, const float* P, const int* tok, const int* pos, float* x, int d, int B,
                   cudaStream_t st) {
-    embed_kernel<<<B, 128, 0, st>>>(E, P, tok, pos, x, d);
+    launch_kernel(embed_kernel, dim3(B), dim3(128), 0, st, E, P, tok, pos, x, d);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }
 
 void launch_advance(const int* tok, int* pos, int* hist, int* hist_len, int hist_stride, int B, cudaStream_t st) {
-    advance_kernel<<<(B + 127) / 128, 128, 0, st>>>(tok, pos, hist, hist_len, hist_stride, B);
+    launch_kernel(advance_kernel, dim3((B + 127) / 128), dim3(128), 0, st, tok, pos, hist, hist_len, hist_stride, B);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }
@@ -1035,7 +1041,7 @@ void launch_attention(const AttnParams& p, int B, int splits, cudaStream_t st) {
         const int grid = std::max(1, std::min(sm_count, (total_units + kAttnWarps - 1) / kAttnWarps));
         const size_t bytes = (size_t)kAttnWarps * kPipeStages * kPipeStageFloats * sizeof(float);
         set_smem(attn_decode64_pipe_kernel, bytes);
-        attn_decode64_pipe_kernel<<<grid, kAttnWarps * 32, bytes, st>>>(p, splits, total_units);
+        launch_kernel(attn_decode64_pipe_kernel, dim3(grid), dim3(kAttnWarps * 32), bytes, st, p, splits, total_units);
     } else {
         const size_t bytes = (size_t)p.T * sizeof(float);
         set_smem(attn_decode_generic_kernel, bytes);
