@@ -592,6 +592,9 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         // (measured: at 32 sequences x 12 heads and context ~1100, one split per unit beats seven).
         const int want = (2 * m->sm_count + s->B * s->H - 1) / (s->B * s->H);
         s->attn_splits = std::max(1, std::min({want, 16, (s->T + 31) / 32}));
+        if (const char* sp = std::getenv("GRADB_ATTN_SPLITS")) {
+            s->attn_splits = std::max(1, std::min({std::atoi(sp), 16, (s->T + 31) / 32}));
+        }
         const size_t B = s->B;
         dalloc(&s->x, B * s->d);
         dalloc(&s->q, B * s->d);

@@ -561,7 +561,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode64_kernel(const At
 // stream of a warp continues across unit boundaries instead of restarting per (sequence, head).
 // Scores: lane r owns row r of the tile and walks its 64 columns rotated by r, which keeps the
 // 128-bit shared-memory reads conflict free and needs no shuffles. P@V: lane owns two columns.
-constexpr int kPipeStages = 3;
+constexpr int kPipeWarps = 7;   // independent warps per CTA: as many 2-stage rings as shared memory holds
+constexpr int kPipeStages = 2;  // per warp: one tile being consumed, one in flight
 constexpr int kPipeTileRows = 32;
 constexpr int kPipeStageFloats = 2 * kPipeTileRows * 64;  // K tile then V tile
 constexpr uint32_t kPipeSpin = 1u << 22;
@@ -596,15 +597,15 @@ __device__ __forceinline__ bool attn_unit_setup(const AttnParams& p, int S, int 
     return true;
 }
 
-__global__ void __launch_bounds__(kAttnWarps * 32, 1) attn_decode64_pipe_kernel(const AttnParams p, int S,
+__global__ void __launch_bounds__(kPipeWarps * 32, 1) attn_decode64_pipe_kernel(const AttnParams p, int S,
                                                                               int total_units) {
     constexpr int HS = 64;
     extern __shared__ __align__(128) float pipe_smem[];
-    __shared__ __align__(8) uint64_t full_bar[kAttnWarps][kPipeStages];
-    __shared__ float q_s[kAttnWarps][HS];
+    __shared__ __align__(8) uint64_t full_bar[kPipeWarps][kPipeStages];
+    __shared__ float q_s[kPipeWarps][HS];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int warps_total = gridDim.x * kAttnWarps;
-    const int gw = blockIdx.x * kAttnWarps + w;
+    const int warps_total = gridDim.x * kPipeWarps;
+    const int gw = blockIdx.x * kPipeWarps + w;
     float* ring = pipe_smem + (size_t)w * kPipeStages * kPipeStageFloats;
 
     if (lane == 0) {
@@ -650,8 +651,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) attn_decode64_pipe_kernel(
         issued++;
         fc.tile++;
     };
-    fetch_next();
-    fetch_next();
+    for (int i = 0; i < kPipeStages; i++) fetch_next();  // fill the ring
 
     int consumed = 0;
     AttnCursor cc{};
@@ -755,7 +755,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) attn_decode64_pipe_kernel(
             o1 += e1;
             consumed++;
             __syncwarp();   // the whole warp is done with this stage ...
-            fetch_next();   // ... so the tile two ahead may land in the stage freed one tile ago
+            fetch_next();   // ... so the next tile of the sequence may land in it
         }
         // finalise the unit
         if (S == 1) {
@@ -1024,7 +1024,7 @@ void launch_attention_static(const AttnParams& p_in, int B, int splits, cudaStre
 
 // Opt the pipelined attention kernel into its shared memory up front (per device).
 void attention_configure() {
-    const size_t bytes = (size_t)kAttnWarps * kPipeStages * kPipeStageFloats * sizeof(float);
+    const size_t bytes = (size_t)kPipeWarps * kPipeStages * kPipeStageFloats * sizeof(float);
     GRADB_CUDA(cudaFuncSetAttribute(attn_decode64_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
 }
 
@@ -1038,10 +1038,10 @@ void launch_attention(const AttnParams& p, int B, int splits, cudaStream_t st) {
             GRADB_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
         }
         const int total_units = B * p.H * splits;
-        const int grid = std::max(1, std::min(sm_count, (total_units + kAttnWarps - 1) / kAttnWarps));
-        const size_t bytes = (size_t)kAttnWarps * kPipeStages * kPipeStageFloats * sizeof(float);
+        const int grid = std::max(1, std::min(sm_count, (total_units + kPipeWarps - 1) / kPipeWarps));
+        const size_t bytes = (size_t)kPipeWarps * kPipeStages * kPipeStageFloats * sizeof(float);
         set_smem(attn_decode64_pipe_kernel, bytes);
-        launch_kernel(attn_decode64_pipe_kernel, dim3(grid), dim3(kAttnWarps * 32), bytes, st, p, splits, total_units);
+        launch_kernel(attn_decode64_pipe_kernel, dim3(grid), dim3(kPipeWarps * 32), bytes, st, p, splits, total_units);
     } else {
         const size_t bytes = (size_t)p.T * sizeof(float);
         set_smem(attn_decode_generic_kernel, bytes);
