@@ -603,3 +603,46 @@ int GRO(generate)(const gro_model* m, const int* prompt, int n_prompt, int max_t
     GRO(session_free)(s);
     return total;
 }
+
+/* trainer.cpp:319-340 over variable.cpp:465-497 (log_softmax) and :533-556 (nll_loss). */
+int GRO(mean_loss)(const gro_model* m, const int* inputs, const int* targets, int n_windows, int seq_len,
+                   int batch_windows, double* mean_out, float* batch_loss_out, float* row_logp_out) {
+    const int V = m->vocab;
+    float* logits = (float*)malloc((size_t)V * sizeof(float));
+    gro_session* s = GRO(session_new)(m);
+    double weighted = 0.0;
+    size_t rows = 0;
+    int rc = 0, batch_index = 0;
+    for (int w0 = 0; w0 < n_windows && rc == 0; w0 += batch_windows, batch_index++) {
+        const int nb = batch_windows < n_windows - w0 ? batch_windows : n_windows - w0;
+        float total = 0.0f; /* nll_loss keeps an fp32 running total */
+        for (int b = 0; b < nb && rc == 0; b++) {
+            GRO(session_reset)(s);
+            for (int t = 0; t < seq_len && rc == 0; t++) {
+                const size_t at = ((size_t)w0 + (size_t)b) * (size_t)seq_len + (size_t)t;
+                rc = GRO(session_step)(s, inputs[at], logits);
+                if (rc) break;
+                real mx = logits[0];
+                for (int j = 1; j < V; j++) mx = logits[j] > mx ? (real)logits[j] : mx;
+                real sum = 0;
+                for (int j = 0; j < V; j++) sum += exp_r((real)logits[j] - mx);
+                const real log_sum = (sizeof(real) == 4 ? (real)logf((float)sum) : (real)log((double)sum));
+                const int tg = targets[at];
+                float logp = 0.0f;
+                if (tg >= 0 && tg < V) {
+                    logp = (float)(((real)logits[tg] - mx) - log_sum);
+                    total -= logp;
+                }
+                if (row_logp_out) row_logp_out[at] = logp;
+            }
+        }
+        total /= (float)((size_t)nb * (size_t)seq_len);
+        if (batch_loss_out) batch_loss_out[batch_index] = total;
+        weighted += (double)total * (double)nb;
+        rows += (size_t)nb;
+    }
+    *mean_out = rows ? weighted / (double)rows : -1.0;
+    free(logits);
+    GRO(session_free)(s);
+    return rc;
+}

@@ -76,6 +76,19 @@ int GRO(generate)(const gro_model* m, const int* prompt, int n_prompt, int max_t
                   float temperature, float repetition_penalty, int top_k, float top_p,
                   const float* draws, int* out, int cap);
 
+/* Teacher-forced scoring the way `grad eval` computes it. Each window of seq_len ids is fed
+ * through a fresh session; row (window, position) is scored with log_softmax of that
+ * position's logits at targets[row] (max-subtract, exp, sum, log: src/transformer/variable.cpp:465-497;
+ * an id outside [0, vocab) contributes nothing: variable.cpp:547-552). A batch is batch_windows
+ * consecutive windows; its loss is the sequential fp32 sum of -logp over its rows divided by the
+ * row count (variable.cpp:544-553), and the result is the window-weighted mean of the batch losses
+ * in double (src/training/trainer.cpp:319-340). The reference runs its full-sequence forward
+ * and a SIMD exp here; this restatement uses the step path (which the reference's own parity test
+ * ties to that forward) and libm, so agreement is to rounding, not bitwise.
+ * batch_loss_out, row_logp_out: optional. Returns 0, or the session_step code. */
+int GRO(mean_loss)(const gro_model* m, const int* inputs, const int* targets, int n_windows, int seq_len,
+                   int batch_windows, double* mean_out, float* batch_loss_out, float* row_logp_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,6 +43,22 @@ def ref_available() -> bool:
     return (HERE / "_ref" / "libgradref.so").exists()
 
 
+def _mean_loss(fn, m, inputs, targets, batch_windows):
+    inp = np.ascontiguousarray(inputs, np.int32)
+    tgt = np.ascontiguousarray(targets, np.int32)
+    n, S = inp.shape
+    assert tgt.shape == inp.shape
+    nb = (n + batch_windows - 1) // batch_windows
+    mean = C.c_double(0)
+    batch = np.zeros(max(nb, 1), np.float32)
+    logp = np.zeros((n, S), np.float32)
+    rc = fn(m, _ptr(inp, _i32p), _ptr(tgt, _i32p), n, S, batch_windows, C.byref(mean), _ptr(batch, _f32p),
+            _ptr(logp, _f32p))
+    if rc:
+        raise RuntimeError(f"mean_loss failed rc={rc}")
+    return float(mean.value), batch[:nb].copy(), logp
+
+
 class Port:
     """The restated algorithm. ``double=True`` selects the double-precision witness."""
 
@@ -69,6 +85,8 @@ class Port:
         f("session_cache_row").argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _f32p]
         f("generate").argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,
                                   C.c_int, C.c_float, _f32p, _i32p, C.c_int]
+        f("mean_loss").argtypes = [C.c_void_p, _i32p, _i32p, C.c_int, C.c_int, C.c_int,
+                                   C.POINTER(C.c_double), _f32p, _f32p]
         L.gro_apply_penalty.argtypes = [_f32p, C.c_int, _i32p, C.c_int, C.c_float]
         L.gro_argmax.argtypes = [_f32p, C.c_int]
         L.gro_sample.argtypes = [_f32p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float, _f32p]
@@ -135,6 +153,10 @@ class Port:
             raise RuntimeError(f"oracle generate failed rc={-n}")
         return out[:n].copy()
 
+    def mean_loss(self, m, inputs, targets, batch_windows=8):
+        """Teacher-forced scoring: (mean loss, per-batch losses, per-row target log-probabilities)."""
+        return _mean_loss(self._f("mean_loss"), m, inputs, targets, batch_windows)
+
     # -- selection stage ---------------------------------------------------
     def apply_penalty(self, logits, tokens, penalty):
         lg = np.array(logits, np.float32, copy=True)
@@ -183,6 +205,8 @@ class Ref:
         L.gradref_generate_stream.argtypes = gs
         L.gradref_sample_from_logits.argtypes = [C.c_void_p, _f32p, C.c_int, C.c_float, C.c_int,
                                                  C.c_float, _f32p]
+        L.gradref_mean_loss.argtypes = [C.c_void_p, _i32p, _i32p, C.c_int, C.c_int, C.c_int,
+                                        C.POINTER(C.c_double), _f32p, _f32p]
 
     def load(self, path):
         # The reference prints a success line to stdout from load(); keep it off ours.
@@ -248,6 +272,10 @@ class Ref:
                _ptr(out, _i32p), cap, _ptr(draws, _f32p))
         n_gen = n if stream else n - len(prompt)
         return out[:n].copy(), draws[:n_gen].copy()
+
+    def mean_loss(self, m, inputs, targets, batch_windows=8):
+        """The reference's full-sequence forward + cross_entropy, batched as `grad eval` does."""
+        return _mean_loss(self.L.gradref_mean_loss, m, inputs, targets, batch_windows)
 
     def sample_from_logits(self, m, logits, temperature, top_k, top_p):
         lg = np.ascontiguousarray(logits, np.float32)

@@ -245,3 +245,56 @@ int gradref_sample_from_logits(void* m, const float* logits, int vocab, float te
 }
 
 }  // extern "C"
+
+// Teacher-forced scoring through the reference's own full-sequence forward and loss operators
+// (GPTModel::forward, Variable::log_softmax, Variable::cross_entropy), batched and averaged the
+// way `grad eval` does it (src/training/trainer.cpp:319-340 mean_loss with the batches
+// src/data/dataloader.cpp:31-66 assembles). inputs/targets: n_windows x seq_len ids.
+// batch_loss_out (optional): one fp32 loss per batch; row_logp_out (optional): the log-probability
+// of each row's target, n_windows x seq_len. Returns 0, or 1 with gradref_last_error() set.
+extern "C" int gradref_mean_loss(void* m, const int* inputs, const int* targets, int n_windows,
+                                 int seq_len, int batch_windows, double* mean_out,
+                                 float* batch_loss_out, float* row_logp_out) {
+    try {
+        grad::GPTModel& g = static_cast<RefModel*>(m)->model;
+        grad::NoGradGuard no_grad;
+        const size_t S = static_cast<size_t>(seq_len);
+        const size_t V = static_cast<size_t>(g.getVocabSize());
+        double weighted = 0.0;
+        size_t rows = 0;
+        int batch_index = 0;
+        for (int w0 = 0; w0 < n_windows; w0 += batch_windows, batch_index++) {
+            const size_t nb = static_cast<size_t>(std::min(batch_windows, n_windows - w0));
+            grad::Tensor in(nb, S, 1), tg(nb, S, 1);
+            for (size_t b = 0; b < nb; b++) {
+                for (size_t s = 0; s < S; s++) {
+                    const size_t at = (static_cast<size_t>(w0) + b) * S + s;
+                    in.setValue(b, s, 0, static_cast<float>(inputs[at]));
+                    tg.setValue(b, s, 0, static_cast<float>(targets[at]));
+                }
+            }
+            auto in_v = grad::Variable::create(in, false);
+            auto tg_v = grad::Variable::create(tg, false);
+            auto logits = g.forward(in_v, false);
+            auto loss = logits->cross_entropy(tg_v);
+            const float batch_loss = loss->getData().getValue(0, 0);
+            if (batch_loss_out) batch_loss_out[batch_index] = batch_loss;
+            if (row_logp_out) {
+                auto logp = logits->log_softmax();
+                const float* lp = logp->getData().raw();
+                for (size_t r = 0; r < nb * S; r++) {
+                    const int t = targets[static_cast<size_t>(w0) * S + r];
+                    row_logp_out[static_cast<size_t>(w0) * S + r] =
+                        (t >= 0 && static_cast<size_t>(t) < V) ? lp[r * V + static_cast<size_t>(t)] : 0.0f;
+                }
+            }
+            weighted += static_cast<double>(batch_loss) * static_cast<double>(nb);
+            rows += nb;
+        }
+        *mean_out = rows > 0 ? weighted / static_cast<double>(rows) : -1.0;
+        return 0;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return 1;
+    }
+}
