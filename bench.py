@@ -292,6 +292,7 @@ def run_ours(args):
         step_bytes = sum(sum(algorithmic_bytes_per_step(dm, B, PROMPT_LEN + i + 1, w_bytes).values()) for i in range(K))
         line["step_roofline"] = {"algorithmic_bytes_per_step_avg": step_bytes / K,
                                  "achieved_gbs": step_bytes / dev_s / 1e9, "frac": step_bytes / dev_s / 1e9 / hbm_peak}
+        line["eval"] = bench_scoring(sess, dm, B, tensor_peak, peak_kind)
         if world == 1:
             line["batch1"] = bench_batch1(g, ck, local, hbm_peak)
             line["cpu_baseline"] = cpu_reference(K_sample=args.cpu_tokens, n_seq=None, timed_only=True)
@@ -320,6 +321,34 @@ def ncu_traffic(kernel_class, algorithmic_bytes_per_launch):
     if not rec:
         return None
     return rec["traffic_over_algorithmic"] * algorithmic_bytes_per_launch
+
+
+def bench_scoring(sess, dm, B, tensor_peak, peak_kind):
+    """Teacher-forced scoring (`grad eval`'s shape: windows of 256 ids, losses over batches of 8) of B windows
+    on the benchmark session: ids scored per second, device time and wall time with host buffers."""
+    S = CONTEXT
+    stream = np.random.default_rng(PROMPT_SEED + 7).integers(0, dm.vocab, B * S + 1).astype(np.int32)
+    inp = np.stack([stream[i * S:i * S + S] for i in range(B)])
+    tgt = np.stack([stream[i * S + 1:i * S + S + 1] for i in range(B)])
+    sess.mean_loss(inp[:32], tgt[:32], 8)  # warm-up: allocates the all-row logits buffer
+    dev, wall = [], []
+    mean = 0.0
+    for _ in range(3):
+        t0 = time.perf_counter()
+        mean, _ = sess.mean_loss(inp, tgt, 8)
+        wall.append(time.perf_counter() - t0)
+        dev.append(sess.last_score_ms / 1e3)
+    ids = B * S
+    d, L, V, dff = dm.d_model, dm.layers, dm.vocab, dm.d_ff
+    macs = L * (4 * d * d + 3 * d * dff) + V * d                      # projections + logits, per id
+    attn = L * 2 * d * (S + 1) / 2                                    # QK and PV over the causal prefix, mean per id
+    flops = 2.0 * (macs + attn) * ids
+    dsec = statistics.median(dev)
+    return {"workload": f"{B} windows x {S} ids, batches of 8, bf16 tensor-core feed + all-position logits + "
+                        "log-softmax/NLL on the device",
+            "ids_per_s": ids / dsec, "device_ms": dsec * 1e3, "e2e_ids_per_s": ids / statistics.median(wall),
+            "mean_loss": mean, "tflops": flops / dsec / 1e12, "tensor_peak_tflops": tensor_peak,
+            "tensor_frac": flops / dsec / 1e12 / tensor_peak if tensor_peak else None, "peak_source": peak_kind}
 
 
 def bench_batch1(g, ck, device, hbm_peak):

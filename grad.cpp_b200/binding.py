@@ -72,6 +72,9 @@ SIGNATURES = {
     "gradb_select_from_logits": (C.c_int, [C.c_void_p, C.POINTER(Sampling), _f32p, _f32p, C.c_int, _i32p, _f32p]),
     "gradb_generate": (C.c_int, [C.c_void_p, _i32p, _i32p, C.c_int, C.POINTER(Sampling), C.c_int, _f32p, _i32p,
                                  C.c_int, _i32p, _f32p, _f32p]),
+    "gradb_score": (C.c_int, [C.c_void_p, _i32p, _i32p, C.c_int, C.c_int, _f32p, _f32p]),
+    "gradb_mean_loss": (C.c_int, [C.c_void_p, _i32p, _i32p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double), _f32p,
+                                  _f32p]),
     "gradb_session_last_ms": (C.c_int, [C.c_void_p, _f32p]),
     "gradb_session_cache_row": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _f32p]),
     "gradb_attention_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
@@ -224,6 +227,36 @@ class BatchSession:
         out = np.empty((len(prompts), self.vocab), np.float32) if want_logits else None
         _check(lib().gradb_prefill(self._h, _p(flat, _i32p), _p(offs, _i32p), len(prompts), _p(out, _f32p)))
         return out
+
+    def score(self, inputs, targets):
+        """Teacher-forced scoring: (n_windows, seq_len) log-probabilities of the targets
+        (0 where a target is outside the vocabulary). Device time in ``last_score_ms``."""
+        inp = np.ascontiguousarray(inputs, np.int32)
+        tgt = np.ascontiguousarray(targets, np.int32)
+        if inp.ndim != 2 or tgt.shape != inp.shape:
+            raise ValueError("inputs and targets must be (n_windows, seq_len) arrays of the same shape")
+        out = np.empty(inp.shape, np.float32)
+        ms = C.c_float(0)
+        _check(lib().gradb_score(self._h, _p(inp, _i32p), _p(tgt, _i32p), inp.shape[0], inp.shape[1],
+                                 _p(out, _f32p), C.cast(C.byref(ms), _f32p)))
+        self.last_score_ms = float(ms.value)
+        return out
+
+    def mean_loss(self, inputs, targets, batch_windows=8):
+        """training::mean_loss over in-memory windows: (mean loss, per-batch losses)."""
+        inp = np.ascontiguousarray(inputs, np.int32)
+        tgt = np.ascontiguousarray(targets, np.int32)
+        if inp.ndim != 2 or tgt.shape != inp.shape:
+            raise ValueError("inputs and targets must be (n_windows, seq_len) arrays of the same shape")
+        n, S = inp.shape
+        nb = (n + batch_windows - 1) // max(batch_windows, 1)
+        batch = np.zeros(max(nb, 1), np.float32)
+        mean = C.c_double(0)
+        ms = C.c_float(0)
+        _check(lib().gradb_mean_loss(self._h, _p(inp, _i32p), _p(tgt, _i32p), n, S, batch_windows, C.byref(mean),
+                                     _p(batch, _f32p), C.cast(C.byref(ms), _f32p)))
+        self.last_score_ms = float(ms.value)
+        return float(mean.value), batch[:nb].copy()
 
     def select(self, sampling: Sampling, uniforms=None, n_seq=None, logits=None, want_probs=False):
         n = n_seq if n_seq is not None else (len(logits) if logits is not None else self.max_batch)

@@ -212,6 +212,48 @@ gradb_status gradb_select(gradb_session* session, const gradb_sampling* params, 
     });
 }
 
+gradb_status gradb_score(gradb_session* session, const int32_t* inputs_host, const int32_t* targets_host, int n_windows,
+                         int seq_len, float* row_logp_host, float* ms_out) {
+    return guarded([&] {
+        if (!session || !inputs_host || !targets_host || !row_logp_host) throw Error(GRADB_ERR_INVALID, "null argument");
+        const float ms = session_score(session->impl, inputs_host, targets_host, n_windows, seq_len, row_logp_host);
+        if (ms_out) *ms_out = ms;
+    });
+}
+
+gradb_status gradb_mean_loss(gradb_session* session, const int32_t* inputs_host, const int32_t* targets_host,
+                             int n_windows, int seq_len, int batch_windows, double* mean_loss_out,
+                             float* batch_loss_host, float* ms_out) {
+    return guarded([&] {
+        if (!session || !mean_loss_out) throw Error(GRADB_ERR_INVALID, "null argument");
+        if (batch_windows < 1) throw Error(GRADB_ERR_INVALID, "batch_windows must be positive");
+        if (n_windows <= 0) {
+            *mean_loss_out = -1.0;  // no batches: trainer.cpp:339
+            if (ms_out) *ms_out = 0.f;
+            return;
+        }
+        if (!inputs_host || !targets_host) throw Error(GRADB_ERR_INVALID, "null argument");
+        std::vector<float> logp((size_t)n_windows * seq_len);
+        const float ms = session_score(session->impl, inputs_host, targets_host, n_windows, seq_len, logp.data());
+        double weighted = 0.0;
+        size_t windows = 0;
+        int batch = 0;
+        for (int w0 = 0; w0 < n_windows; w0 += batch_windows, batch++) {
+            const size_t nb = (size_t)std::min(batch_windows, n_windows - w0);
+            const size_t rows = nb * (size_t)seq_len;
+            const float* lp = logp.data() + (size_t)w0 * seq_len;
+            float total = 0.0f;
+            for (size_t r = 0; r < rows; r++) total -= lp[r];  // rows outside the vocabulary hold 0
+            total /= static_cast<float>(rows);
+            if (batch_loss_host) batch_loss_host[batch] = total;
+            weighted += static_cast<double>(total) * static_cast<double>(nb);
+            windows += nb;
+        }
+        *mean_loss_out = weighted / static_cast<double>(windows);
+        if (ms_out) *ms_out = ms;
+    });
+}
+
 gradb_status gradb_session_set_history(gradb_session* session, int seq, const int32_t* ids_host, int n) {
     return guarded([&] {
         if (!session || (!ids_host && n > 0)) throw Error(GRADB_ERR_INVALID, "null argument");
@@ -327,7 +369,8 @@ int gradb_kernel_class_count(void) { return kKernelClasses; }
 
 const char* gradb_kernel_class_name(int cls) {
     static const char* const names[kKernelClasses] = {"embed",    "norm_qkv_rope", "attn_decode", "attn_out_proj", "norm_ffn_up",
-                                                      "ffn_down", "norm_logits",   "advance",     "select",        "decode_step_b1"};
+                                                      "ffn_down", "norm_logits",   "advance",     "select",        "decode_step_b1",
+                                                      "score_logp"};
     return cls >= 0 && cls < kKernelClasses ? names[cls] : "";
 }
 

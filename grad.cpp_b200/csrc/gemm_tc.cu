@@ -29,9 +29,11 @@ namespace {
 
 // Ring depth: four stages (fewer only if a stage is very large). Deeper rings were measured slower here:
 // they push every variant to one CTA per SM and lengthen the prologue of kernels that run for a few microseconds.
+// The widest token tile only occurs with many CTAs per SM's worth of rows (prompt feed, scoring); its ring is
+// sized for two CTAs per SM so that one CTA's epilogue runs under the other's main loop.
 constexpr int stages_for(int nw, int tn) {
     const int stage = nw * 128 * 64 * 2 + tn * 64 * 2;
-    const int n = (200 * 1024) / stage;
+    const int n = ((tn >= 128 ? 100 : 200) * 1024) / stage;
     return n > 4 ? 4 : (n < 2 ? 2 : n);
 }
 constexpr int kBlockK = 64;  // bf16 elements = one 128-byte swizzle row

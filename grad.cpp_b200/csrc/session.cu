@@ -416,13 +416,25 @@ void ensure_feed_buffers(Session* s) {
     f.cap = (int)R;
 }
 
+void ensure_score_buffers(Session* s) {
+    ensure_feed_buffers(s);
+    Session::Feed& f = s->feed;
+    if (f.score_logits) return;
+    dalloc(&f.score_logits, (size_t)f.cap * s->V);
+    dalloc(&f.row_tgt, (size_t)f.cap);
+    dalloc(&f.row_dst, (size_t)f.cap);
+}
+
 // Batched prompt feed on the tensor-core path: every prompt token of a chunk of positions is one
 // row, so each projection runs once per layer over all of them (M = rows) instead of once per
 // position. Row r stands for (sequence row_seq[r], position row_pos[r]); K/V rows go to that
 // sequence's cache slot and attention reads positions 0..row_pos[r] of it, which is the causal
 // prompt attention. Leaves caches, positions, history and last-position logits exactly as the
 // reference's step-by-step feed would (text_gen.cpp:44-46).
-void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_t* offsets, int n_seq) {
+// With `score_targets` (one id per prompt token, laid out like `tokens`), every row's logits are
+// also formed and the log-probability of its target is written to score_out[offsets[b] + j].
+void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_t* offsets, int n_seq,
+                                 const int32_t* score_targets = nullptr, float* score_out = nullptr) {
     const DeviceModel* m = s->m;
     const bool modern = m->desc.arch == GRADB_ARCH_MODERN;
     cudaStream_t st = s->stream;
@@ -437,6 +449,10 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
 
     // per-sequence logits mask: id of the last prompt token, or skip
     f.h_rows.resize((size_t)4 * f.cap + 2 * (size_t)s->B);
+    if (score_targets) {
+        ensure_score_buffers(s);
+        f.h_score.resize((size_t)2 * f.cap);
+    }
     int* h_last = f.h_rows.data() + (size_t)4 * f.cap + s->B;
     for (int b = 0; b < n_seq; b++) h_last[b] = offsets[b + 1] > offsets[b] ? tokens[offsets[b + 1] - 1] : kSkip;
     GRADB_CUDA(cudaMemcpyAsync(f.last_tok, h_last, n_seq * sizeof(int), cudaMemcpyHostToDevice, st));
@@ -457,6 +473,10 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
                 h_pos[R] = s->h_pos[b] + j;
                 h_seq[R] = b;
                 h_lastrow[R] = j == len - 1 ? h_tok[R] : kSkip;
+                if (score_targets) {
+                    f.h_score[R] = score_targets[offsets[b] + j];
+                    f.h_score[(size_t)f.cap + R] = offsets[b] + j;
+                }
                 R++;
                 h_cnt[b]++;
             }
@@ -467,6 +487,11 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
         GRADB_CUDA(cudaMemcpyAsync(f.row_seq, h_seq, R * sizeof(int), cudaMemcpyHostToDevice, st));
         GRADB_CUDA(cudaMemcpyAsync(f.row_last, h_lastrow, R * sizeof(int), cudaMemcpyHostToDevice, st));
         GRADB_CUDA(cudaMemcpyAsync(f.seq_count, h_cnt, n_seq * sizeof(int), cudaMemcpyHostToDevice, st));
+        if (score_targets) {
+            GRADB_CUDA(cudaMemcpyAsync(f.row_tgt, f.h_score.data(), R * sizeof(int), cudaMemcpyHostToDevice, st));
+            GRADB_CUDA(cudaMemcpyAsync(f.row_dst, f.h_score.data() + f.cap, R * sizeof(int), cudaMemcpyHostToDevice,
+                                       st));
+        }
         GRADB_CUDA(cudaStreamSynchronize(st));  // the staging vector is reused by the next chunk
 
         auto tile_for = [&](int n_features) { return tc_token_tile(R, (n_features + 127) / 128, want); };
@@ -526,12 +551,21 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
                 launch_tc_gemm(TC_RESID, w.map_down, f.map_ffn16[map_idx(tn)], g, tn, 1, st);
             }
         }
+        if (score_targets) {
+            // every row's logits (final norm + tied-embedding GEMM), then the target's log-probability
+            Timed t(s, KC_SCORE);
+            launch_norm_bf16(f.x, m->fng, m->fnb, f.row_tok, f.h16, d, modern, 1e-5f, R, st);
+            TcGemmParams g = base;
+            g.K = d; g.N = s->V; g.ld_out = s->V; g.out_f32 = f.score_logits;
+            const int tn = tile_for(s->V);
+            launch_tc_gemm(TC_LOGITS, m->map_emb, f.map_h16[map_idx(tn)], g, tn, 1, st);
+            launch_row_logp(f.score_logits, (size_t)s->V, s->V, f.row_tgt, f.row_dst, 0, 0, score_out, R, st);
+        }
         launch_gather_last_rows(f.x, f.row_last, f.row_seq, s->x, d, R, st);
         launch_feed_bookkeeping(f.row_tok, f.row_pos, f.row_seq, f.seq_count, s->pos, s->hist_len, s->hist, s->hist_stride,
                                 R, n_seq, st);
-        for (int b = 0; b < n_seq; b++) s->h_pos[b] += h_cnt[b];
     }
-    for (int b = 0; b < n_seq; b++) s->h_pos[b] -= offsets[b + 1] - offsets[b];  // callers add the lengths themselves
+    // the host mirror of the positions is advanced by the callers
 
     // last-position logits: final norm + tied-embedding GEMM over the per-sequence rows
     {
@@ -546,10 +580,14 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
     }
 }
 
-bool use_batched_feed(const Session* s, int n_seq) {
+bool batched_feed_available(const Session* s) {
     const char* off = std::getenv("GRADB_NO_BATCHED_FEED");
-    return s->use_tc && n_seq >= 16 && s->hs == 64 && !(off && off[0] == '1');
+    return s->use_tc && s->hs == 64 && !(off && off[0] == '1');
 }
+
+// Generation keeps a small group of sequences on one family of kernels for the prompt and the
+// decode steps; scoring has no decode steps and batches whenever the session can.
+bool use_batched_feed(const Session* s, int n_seq) { return batched_feed_available(s) && n_seq >= 16; }
 
 void enqueue_prompt_feed(Session* s, int steps, int n_seq) {
     for (int t = 0; t < steps; t++) {
@@ -688,6 +726,8 @@ void destroy_session(Session* s) {
     cudaFree(s->feed.x); cudaFree(s->feed.q); cudaFree(s->feed.attn); cudaFree(s->feed.h16); cudaFree(s->feed.attn16);
     cudaFree(s->feed.ffn16); cudaFree(s->feed.row_tok); cudaFree(s->feed.row_pos); cudaFree(s->feed.row_seq);
     cudaFree(s->feed.row_last); cudaFree(s->feed.seq_count); cudaFree(s->feed.last_tok);
+    cudaFree(s->feed.score_logits); cudaFree(s->feed.row_tgt); cudaFree(s->feed.row_dst);
+    cudaFree(s->score_out); cudaFree(s->score_tgt);
     cudaFree(s->h16); cudaFree(s->attn16); cudaFree(s->ffn16); cudaFree(s->status);
     if (s->h_stage) cudaFreeHost(s->h_stage);
     if (s->own_stream && s->stream) cudaStreamDestroy(s->stream);
@@ -751,6 +791,82 @@ void session_prefill(Session* s, const int32_t* tokens, const int32_t* offsets, 
     check_status(s);
     GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
     for (int b = 0; b < n_seq; b++) s->h_pos[b] += offsets[b + 1] - offsets[b];
+}
+
+float session_score(Session* s, const int32_t* inputs, const int32_t* targets, int n_windows, int seq_len,
+                    float* row_logp_host) {
+    if (n_windows < 1) throw Error(GRADB_ERR_INVALID, "n_windows must be positive");
+    if (seq_len < 1) throw Error(GRADB_ERR_INVALID, "seq_len must be positive");
+    if (seq_len > s->T) throw Error(GRADB_ERR_CONTEXT_FULL, "InferenceSession: context exceeds max_len");
+    for (size_t i = 0; i < (size_t)n_windows * seq_len; i++) {
+        if (inputs[i] < 0 || inputs[i] >= s->V) {
+            throw Error(GRADB_ERR_BAD_TOKEN, "InferenceSession: token id out of vocab range");
+        }
+    }
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    cudaStream_t st = s->stream;
+    if (!s->score_out) {
+        dalloc(&s->score_out, (size_t)s->B * s->T);
+        dalloc(&s->score_tgt, (size_t)s->B * s->T);
+    }
+    const bool batched = batched_feed_available(s);
+    if (batched) ensure_score_buffers(s);
+    float total_ms = 0.f;
+    std::vector<int> offsets, host;
+    for (int w0 = 0; w0 < n_windows; w0 += s->B) {
+        const int n = std::min(s->B, n_windows - w0);
+        const int32_t* in = inputs + (size_t)w0 * seq_len;
+        const int32_t* tg = targets + (size_t)w0 * seq_len;
+        reset_session(s);
+        if (batched) {
+            offsets.resize(n + 1);
+            for (int b = 0; b <= n; b++) offsets[b] = b * seq_len;
+            GRADB_CUDA(cudaEventRecord(s->ev_begin, st));
+            enqueue_prompt_feed_batched(s, in, offsets.data(), n, tg, s->score_out);
+        } else {
+            // position by position through the step kernels, logits for every sequence at every position
+            const size_t need = (size_t)seq_len * 2 * n;
+            if (need > s->tok_matrix_cap) {
+                cudaFree(s->tok_matrix);
+                s->tok_matrix = nullptr;
+                dalloc(&s->tok_matrix, need);
+                s->tok_matrix_cap = need;
+            }
+            host.resize(need + (size_t)seq_len * n);
+            int* h_tgt = host.data() + need;
+            for (int t = 0; t < seq_len; t++) {
+                for (int b = 0; b < n; b++) {
+                    const int id = in[(size_t)b * seq_len + t];
+                    host[(size_t)t * 2 * n + b] = id;
+                    host[(size_t)t * 2 * n + n + b] = id;
+                    h_tgt[(size_t)t * n + b] = tg[(size_t)b * seq_len + t];
+                }
+            }
+            GRADB_CUDA(cudaMemcpyAsync(s->tok_matrix, host.data(), need * sizeof(int), cudaMemcpyHostToDevice, st));
+            GRADB_CUDA(cudaMemcpyAsync(s->score_tgt, h_tgt, (size_t)seq_len * n * sizeof(int),
+                                       cudaMemcpyHostToDevice, st));
+            GRADB_CUDA(cudaEventRecord(s->ev_begin, st));
+            for (int t = 0; t < seq_len; t++) {
+                const int* row = s->tok_matrix + (size_t)t * 2 * n;
+                enqueue_step(s, n, row, row + n, true);
+                Timed tm(s, KC_SCORE);
+                launch_row_logp(s->logits, (size_t)s->V, s->V, s->score_tgt + (size_t)t * n, nullptr, seq_len, t,
+                                s->score_out, n, st);
+            }
+        }
+        GRADB_CUDA(cudaEventRecord(s->ev_end, st));
+        GRADB_CUDA(cudaMemcpyAsync(row_logp_host + (size_t)w0 * seq_len, s->score_out,
+                                   (size_t)n * seq_len * sizeof(float), cudaMemcpyDeviceToHost, st));
+        GRADB_CUDA(cudaStreamSynchronize(st));
+        collect_spans(s);
+        check_status(s);
+        float ms = 0.f;
+        GRADB_CUDA(cudaEventElapsedTime(&ms, s->ev_begin, s->ev_end));
+        total_ms += ms;
+        for (int b = 0; b < n; b++) s->h_pos[b] += seq_len;
+    }
+    s->last_ms = total_ms;
+    return total_ms;
 }
 
 void session_set_history(Session* s, int seq, const int32_t* ids, int n) {

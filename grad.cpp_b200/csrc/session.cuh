@@ -11,7 +11,7 @@
 namespace gradb {
 
 enum KernelClass { KC_EMBED = 0, KC_QKV, KC_ATTN, KC_OPROJ, KC_FFN_UP, KC_FFN_DOWN, KC_LOGITS, KC_ADVANCE, KC_SELECT,
-                   KC_STEP_B1, kKernelClasses };
+                   KC_STEP_B1, KC_SCORE, kKernelClasses };
 
 struct Session {
     const DeviceModel* m = nullptr;
@@ -52,7 +52,13 @@ struct Session {
             *last_tok = nullptr;
         CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];
         std::vector<int> h_rows;  // host staging: 4 * cap + 2 * B ints
+        // teacher-forced scoring: all-row logits of a chunk, per-row target and destination
+        float* score_logits = nullptr;
+        int *row_tgt = nullptr, *row_dst = nullptr;
+        std::vector<int> h_score;  // host staging: 2 * cap ints
     } feed;
+    float* score_out = nullptr;  // [B * T] target log-probabilities of the windows being scored
+    int* score_tgt = nullptr;    // [T][B] targets, position by position (step-by-step scoring)
 
     // single-sequence persistent kernel: workspace and grid-barrier words
     bool use_b1 = false;
@@ -93,6 +99,11 @@ void session_set_history(Session* s, int seq, const int32_t* ids, int n);
 void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets, int n_seq,
                       const gradb_sampling& sp, int max_new, const float* uniforms, int32_t* out_ids,
                       int out_stride, int32_t* out_len, float* step_ms, float* prefill_ms);
+// Teacher-forced scoring of n_windows windows of seq_len ids (any n_windows; scored max_batch at a
+// time from position 0): row_logp_host[w * seq_len + t] = log-probability of targets[w][t] after
+// inputs[w][0..t]. Returns the device time in ms.
+float session_score(Session* s, const int32_t* inputs, const int32_t* targets, int n_windows, int seq_len,
+                    float* row_logp_host);
 void session_set_profiling(Session* s, bool on);
 void session_cache_row(Session* s, int seq, int layer, int which, int pos, float* row_host);
 

@@ -1051,4 +1051,78 @@ void launch_attention(const AttnParams& p, int B, int splits, cudaStream_t st) {
     GRADB_CUDA(cudaGetLastError());
 }
 
+// ---------------------------------------------------------------------------------------------
+// Teacher-forced scoring: one CTA per row, one pass over the row's logits. Every thread keeps a
+// running (max, sum of exp(x - max)) over its slice; the pairs are merged by shuffles.
+namespace {
+constexpr int kLogpThreads = 256;
+
+__device__ __forceinline__ void lse_push(float& m, float& s, float x) {
+    if (x > m) {
+        s = s * expf(m - x) + 1.0f;
+        m = x;
+    } else {
+        s += expf(x - m);
+    }
+}
+__device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2) {
+    const float M = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * expf(m - M)) + (m2 == -INFINITY ? 0.f : s2 * expf(m2 - M));
+    m = M;
+}
+
+__global__ void __launch_bounds__(kLogpThreads) row_logp_kernel(const float* __restrict__ logits, size_t ld, int V,
+                                                                 const int* __restrict__ tgt,
+                                                                 const int* __restrict__ dst, int dst_mul, int dst_add,
+                                                                 float* __restrict__ out) {
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* x = logits + (size_t)r * ld;
+    float m = -INFINITY, s = 0.f;
+    if ((ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        const int n4 = V >> 2;
+        for (int i = threadIdx.x; i < n4; i += kLogpThreads) {
+            const float4 v = __ldg(x4 + i);
+            lse_push(m, s, v.x);
+            lse_push(m, s, v.y);
+            lse_push(m, s, v.z);
+            lse_push(m, s, v.w);
+        }
+        for (int i = (n4 << 2) + threadIdx.x; i < V; i += kLogpThreads) lse_push(m, s, x[i]);
+    } else {
+        for (int i = threadIdx.x; i < V; i += kLogpThreads) lse_push(m, s, x[i]);
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+        const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+        lse_merge(m, s, m2, s2);
+    }
+    __shared__ float sm[kLogpThreads / 32], ss[kLogpThreads / 32];
+    if ((threadIdx.x & 31) == 0) {
+        sm[threadIdx.x >> 5] = m;
+        ss[threadIdx.x >> 5] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        m = sm[0];
+        s = ss[0];
+        for (int w = 1; w < kLogpThreads / 32; w++) lse_merge(m, s, sm[w], ss[w]);
+        const int t = tgt[r];
+        float lp = 0.f;
+        if (t >= 0 && t < V) lp = (x[t] - m) - logf(s);
+        out[dst ? dst[r] : r * dst_mul + dst_add] = lp;
+    }
+}
+}  // namespace
+
+void launch_row_logp(const float* logits, size_t ld, int V, const int* tgt, const int* dst, int dst_mul, int dst_add,
+                     float* out, int rows, cudaStream_t st) {
+    if (rows <= 0) return;
+    launch_kernel(row_logp_kernel, dim3(rows), dim3(kLogpThreads), 0, st, logits, ld, V, tgt, dst, dst_mul, dst_add,
+                  out);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
 }  // namespace gradb

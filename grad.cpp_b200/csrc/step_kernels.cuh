@@ -56,6 +56,11 @@ void launch_feed_bookkeeping(const int* row_tok, const int* row_pos, const int* 
                              int* hist_len, int* hist, int hist_stride, int R, int B, cudaStream_t st);
 void launch_embed(const float* E, const float* P, const int* tok, const int* pos, float* x, int d, int B,
                   cudaStream_t st);
+// Log-probability of each row's target id under log_softmax of the row's logits
+// (src/transformer/variable.cpp:465-497 and :547-552): (x[t] - max) - log(sum exp(x - max)),
+// 0 for a target outside [0, V). Row r is written to out[dst ? dst[r] : r * dst_mul + dst_add].
+void launch_row_logp(const float* logits, size_t ld, int V, const int* tgt, const int* dst, int dst_mul, int dst_add,
+                     float* out, int rows, cudaStream_t st);
 void launch_advance(const int* tok, int* pos, int* hist, int* hist_len, int hist_stride, int B, cudaStream_t st);
 void launch_gemv(const GemvParams& p, int pro, int epi, bool bf16, int sm_count, cudaStream_t st);
 void launch_logits(const LogitsParams& p, bool bf16, cudaStream_t st);

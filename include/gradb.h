@@ -189,6 +189,27 @@ gradb_status gradb_generate(gradb_session* session, const int32_t* prompts_host,
                             const float* uniforms_host, int32_t* out_ids_host, int out_stride,
                             int32_t* out_len_host, float* step_ms_host, float* prefill_ms_host);
 
+/* Teacher-forced scoring, the device half of `grad eval` (src/cli/eval.cpp:77-133): n_windows
+ * windows of seq_len ids each are fed from position 0 (max_batch windows at a time; the session
+ * is reset first and left holding the last group) and every position's logits are reduced on the
+ * device to the log-probability of that position's target,
+ *   row_logp_host[w*seq_len + t] = log_softmax(logits after inputs[w][0..t])[targets[w][t]]
+ * (src/transformer/variable.cpp:465-497), 0 where the target is outside [0, vocab)
+ * (variable.cpp:547-552). Logits never leave the GPU. inputs must be valid ids (BAD_TOKEN),
+ * seq_len <= capacity (CONTEXT_FULL). ms_out (optional): device time. */
+gradb_status gradb_score(gradb_session* session, const int32_t* inputs_host, const int32_t* targets_host,
+                         int n_windows, int seq_len, float* row_logp_host, float* ms_out);
+
+/* training::mean_loss (src/training/trainer.cpp:319-340) over windows held in memory: windows are
+ * taken batch_windows at a time (the reference's eval uses 8, eval.cpp:77); a batch's loss is the
+ * fp32 running total of -logp over its rows, in row order, divided by the row count
+ * (Variable::nll_loss, variable.cpp:544-553); the result is the window-weighted mean of the batch
+ * losses accumulated in double, or -1 with no windows. batch_loss_host (optional):
+ * ceil(n_windows / batch_windows) floats. */
+gradb_status gradb_mean_loss(gradb_session* session, const int32_t* inputs_host, const int32_t* targets_host,
+                             int n_windows, int seq_len, int batch_windows, double* mean_loss_out,
+                             float* batch_loss_host, float* ms_out);
+
 /* Device time of the most recent launches, for benchmarks: milliseconds between
  * the start and end events the session records around gradb_step / gradb_prefill /
  * gradb_generate's decode loop. */

@@ -6,12 +6,14 @@
 //   grad::GPTModel::load / save        include/grad/transformer/gpt_model.h:83-86
 //   grad::InferenceSession             include/grad/transformer/inference.h:16-29
 //   grad::TextGen                      include/grad/transformer/text_gen.h:12-38
+//   grad::training::mean_loss          src/training/trainer.cpp:319-340 (what `grad eval` reports)
 // Status codes come back as the reference's exception types and messages
 // (src/transformer/inference.cpp:151-156, src/transformer/gpt_model.cpp:385-387, 521-524).
 //
 // Header-only; link against libgradb.so.
 #pragma once
 
+#include <algorithm>
 #include <functional>
 #include <random>
 #include <span>
@@ -198,5 +200,66 @@ private:
     gradb_session* session_ = nullptr;
     const TokenDecoder* decoder_;
 };
+
+// Scoring windows over an id stream held in memory: window i covers ids [i*stride, i*stride + seq_length],
+// its targets are its inputs shifted by one, and there are (count - seq_length - 1) / stride + 1 of them,
+// as the reference's token-file dataset cuts them (src/data/token_file.cpp:149-176). `grad eval` uses
+// stride = seq_length (src/cli/eval.cpp:78-79).
+class TokenWindows {
+public:
+    TokenWindows(std::span<const int> stream, int seq_length, int stride)
+        : stream_(stream), seq_(seq_length), stride_(stride) {
+        if (stride < 1) throw std::invalid_argument("stride must be >= 1");
+        if (seq_length < 1) throw std::invalid_argument("seq_length must be >= 1");
+        if (stream.size() < static_cast<size_t>(seq_length) + 1) {
+            throw std::runtime_error("Not enough tokens for even one sequence");
+        }
+    }
+    [[nodiscard]] size_t size() const {
+        return (stream_.size() - static_cast<size_t>(seq_) - 1) / static_cast<size_t>(stride_) + 1;
+    }
+    [[nodiscard]] int seq_length() const { return seq_; }
+    [[nodiscard]] const int* window(size_t index) const { return stream_.data() + index * static_cast<size_t>(stride_); }
+
+private:
+    std::span<const int> stream_;
+    int seq_, stride_;
+};
+
+namespace training {
+
+// Mean loss over the first max_batches batches of batch_size windows (all of them when max_batches <= 0),
+// in window order: what grad::training::mean_loss returns for an unshuffled loader
+// (src/training/trainer.cpp:319-340; batches as src/data/dataloader.cpp:31-66 assembles them, the
+// last one ragged). -1 when there is nothing to score. Windows are scored resident_windows at a time.
+inline double mean_loss(const GPTModel& model, const TokenWindows& windows, int max_batches = 0, int batch_size = 8,
+                        int resident_windows = 64) {
+    size_t n = windows.size();
+    if (max_batches > 0) n = std::min(n, static_cast<size_t>(max_batches) * static_cast<size_t>(batch_size));
+    if (n == 0) return -1.0;
+    const size_t S = static_cast<size_t>(windows.seq_length());
+    if (windows.seq_length() > model.getMaxLen()) {
+        throw std::runtime_error("seq length exceeds the model's context (" + std::to_string(model.getMaxLen()) + ")");
+    }
+    std::vector<int32_t> in(n * S), tg(n * S);
+    for (size_t w = 0; w < n; w++) {
+        const int* ids = windows.window(w);
+        for (size_t t = 0; t < S; t++) {
+            in[w * S + t] = ids[t];
+            tg[w * S + t] = ids[t + 1];
+        }
+    }
+    gradb_session* session = nullptr;
+    const int resident = static_cast<int>(std::min<size_t>(n, static_cast<size_t>(std::max(1, resident_windows))));
+    detail::check(gradb_session_create(model.handle(), resident, 0, nullptr, &session));
+    double mean = -1.0;
+    const gradb_status st = gradb_mean_loss(session, in.data(), tg.data(), static_cast<int>(n), windows.seq_length(),
+                                            batch_size, &mean, nullptr, nullptr);
+    gradb_session_free(session);
+    detail::check(st);
+    return mean;
+}
+
+}  // namespace training
 
 }  // namespace gradb

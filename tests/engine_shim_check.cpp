@@ -51,5 +51,12 @@ int main(int argc, char** argv) {
     const int n = gen.generate_stream(prompt, [&](const std::string& s) { streamed += (int)s.size(); }, 0.9f, 5);
     std::printf("stream %d %d\n", n, streamed);
     std::printf("empty '%s'\n", gen.generate_greedy({}, 5).c_str());
+    // `grad eval`: windows of 5 ids with stride 5 over a 23-id stream -> 4 windows, batches of 3 (last one ragged)
+    std::vector<int> stream;
+    for (int i = 0; i < 23; i++) stream.push_back((i * 7 + 3) % model.getVocabSize());
+    const gradb::TokenWindows windows(stream, 5, 5);
+    std::printf("windows %zu\n", windows.size());
+    std::printf("mean_loss %.9g\n", gradb::training::mean_loss(model, windows, 0, 3));
+    std::printf("mean_loss_first %.9g\n", gradb::training::mean_loss(model, windows, 1, 3));
     return 0;
 }

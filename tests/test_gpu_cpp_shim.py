@@ -39,4 +39,15 @@ def test_cpp_classes_match_oracle(golden_ckpt, port, tmp_path):
     assert len(sample) == 12 and sample[:4] == [3, 11, 7, 0]
     assert "stream 5 5" in text
     assert "empty ''" in text
+    # training::mean_loss over in-memory windows against the restatement (fp32 rounding apart)
+    stream = np.array([(i * 7 + 3) % dm.vocab for i in range(23)], np.int32)
+    inp = np.stack([stream[i * 5:i * 5 + 5] for i in range(4)])
+    tgt = np.stack([stream[i * 5 + 1:i * 5 + 6] for i in range(4)])
+    assert "windows 4" in text
+    want_all, _, _ = port.mean_loss(om, inp, tgt, 3)
+    want_first, _, _ = port.mean_loss(om, inp[:3], tgt[:3], 3)
+    got_all = float(re.search(r"mean_loss (\S+)", text).group(1))
+    got_first = float(re.search(r"mean_loss_first (\S+)", text).group(1))
+    assert abs(got_all - want_all) < 2e-5 * want_all
+    assert abs(got_first - want_first) < 2e-5 * want_first
     port.free(om)

@@ -1,0 +1,128 @@
+"""GPU: teacher-forced scoring (the device half of `grad eval`) through the C ABI, against values
+the reference itself produced (tests/golden/score_golden.npz) and against the CPU restatement.
+
+fp32 mode bars: every target log-probability within 2e-4 absolute, batch losses and the mean
+within 2e-5 relative (the same bars the restatement meets against the reference). bf16 mode is
+not a bit-exact mode; its error is bounded against the fp32 restatement."""
+import numpy as np
+import pytest
+
+from conftest import GOLDEN_MODELS, ROOT
+
+pytestmark = pytest.mark.gpu
+ROW_TOL = 2e-4
+LOSS_TOL = 2e-5
+
+
+@pytest.fixture(scope="module")
+def G(pkg):
+    import grad_cpp_b200 as g
+    g.lib()
+    return g
+
+
+@pytest.fixture(scope="module")
+def score_golden():
+    return np.load(ROOT / "tests" / "golden" / "score_golden.npz")
+
+
+# max_batch 1 scores through the single-sequence persistent kernel, 2 and 64 through the batched
+# streaming kernels; 2 also makes the windows span several resident groups.
+@pytest.mark.parametrize("max_batch", [1, 2, 64])
+@pytest.mark.parametrize("name", list(GOLDEN_MODELS))
+def test_fp32_scores_match_reference_fixture(name, max_batch, G, golden_ckpt, score_golden):
+    dm, path = golden_ckpt(name)
+    g = score_golden
+    inp, tgt = g[f"{name}/inputs"], g[f"{name}/targets"]
+    bw = int(g[f"{name}/batch_windows"][0])
+    m = G.GPTModel.load(path, 0, G.FP32)
+    s = G.BatchSession(m, max_batch)
+    logp = s.score(inp, tgt)
+    np.testing.assert_allclose(logp, g[f"{name}/row_logp"], rtol=0, atol=ROW_TOL)
+    mean, batch = s.mean_loss(inp, tgt, bw)
+    np.testing.assert_allclose(batch, g[f"{name}/batch_loss"], rtol=LOSS_TOL)
+    assert abs(mean - float(g[f"{name}/mean"][0])) <= LOSS_TOL * abs(mean)
+    # the session is left holding the last group, positioned after its window
+    assert s.position(0) == inp.shape[1]
+    s.close()
+    m.close()
+
+
+def test_scoring_errors_and_empty_input(G, golden_ckpt):
+    dm, path = golden_ckpt("tiny_gpt2")
+    m = G.GPTModel.load(path, 0, G.FP32)
+    s = G.BatchSession(m, 4)
+    ok = np.zeros((2, dm.max_len), np.int32)
+    s.score(ok, ok)
+    with pytest.raises(RuntimeError, match="InferenceSession: context exceeds max_len"):
+        s.score(np.zeros((2, dm.max_len + 1), np.int32), np.zeros((2, dm.max_len + 1), np.int32))
+    bad = ok.copy()
+    bad[1, 2] = dm.vocab
+    with pytest.raises(IndexError, match="InferenceSession: token id out of vocab range"):
+        s.score(bad, ok)
+    mean, batch = s.mean_loss(np.zeros((0, 4), np.int32), np.zeros((0, 4), np.int32), 8)
+    assert mean == -1.0 and len(batch) == 0   # no batches: trainer.cpp:339
+    s.close()
+    m.close()
+
+
+@pytest.mark.parametrize("name,n_windows", [("hs64_modern", 20), ("hs64_gpt2", 40), ("odd_modern", 17)])
+def test_bf16_batched_scoring_tracks_fp32_oracle(name, n_windows, G, golden_ckpt, port, monkeypatch):
+    """>= 16 windows in bf16 mode: all windows' positions go through the tensor-core GEMMs at once
+    and every row's logits are formed by one GEMM over the tied embedding."""
+    dm, path = golden_ckpt(name)
+    S = dm.max_len - 3
+    stream = np.random.default_rng(31).integers(0, dm.vocab, n_windows * S + 1).astype(np.int32)
+    inp = np.stack([stream[i * S:i * S + S] for i in range(n_windows)])
+    tgt = np.stack([stream[i * S + 1:i * S + S + 1] for i in range(n_windows)])
+    tgt[2, 1] = -1
+    m16 = G.GPTModel.load(path, 0, G.BF16)
+    s = G.BatchSession(m16, n_windows)
+    got = s.score(inp, tgt)
+    assert got[2, 1] == 0.0
+    om = port.load(path)
+    _, _, want = port.mean_loss(om, inp[:6], tgt[:6], 8)
+    port.free(om)
+    err = float(np.abs(got[:6] - want).max())
+    assert err < 6e-2, err
+    # the same windows position by position through the bf16 step kernels
+    monkeypatch.setenv("GRADB_NO_BATCHED_FEED", "1")
+    s2 = G.BatchSession(m16, n_windows)
+    stepwise = s2.score(inp, tgt)
+    assert float(np.abs(got - stepwise).max()) < 6e-2
+    mean_a, _ = s.mean_loss(inp, tgt, 8)
+    mean_b, _ = s2.mean_loss(inp, tgt, 8)
+    assert abs(mean_a - mean_b) < 2e-3 * mean_b
+    s.close(); s2.close(); m16.close()
+
+
+def test_eval_shape_windows_of_256_on_the_69m_model(G, ck, port, tmp_path):
+    """`grad eval`'s shape: windows of 256 ids in batches of 8 (src/cli/eval.cpp:77,142) on the 69.0M
+    modern block. The oracle scores the start of one window; the rest is checked through properties:
+    with N(0, 0.02) tied embeddings over unit-RMS hidden rows the logits are near N(0, d * 0.02^2) and
+    independent of the target, so every batch loss sits near ln(vocab) + d * 0.02^2 / 2; and the bf16
+    and fp32 modes agree."""
+    dm = ck.PRESETS["modern"]
+    path = str(ck.write_synthetic(tmp_path / "modern.bin", dm, 1004))
+    n, S = 40, 256
+    stream = np.random.default_rng(2011).integers(0, dm.vocab, n * S + 1).astype(np.int32)
+    inp = np.stack([stream[i * S:i * S + S] for i in range(n)])
+    tgt = np.stack([stream[i * S + 1:i * S + S + 1] for i in range(n)])
+    m16 = G.GPTModel.load(path, 0, G.BF16)
+    s16 = G.BatchSession(m16, 32, 256)
+    lp16 = s16.score(inp, tgt)
+    ms = s16.last_score_ms
+    mean16, batch16 = s16.mean_loss(inp, tgt, 8)
+    s16.close(); m16.close()
+    assert len(batch16) == 5
+    assert np.all(np.abs(batch16 - (np.log(dm.vocab) + dm.d_model * 0.02 ** 2 / 2)) < 0.03)
+    m32 = G.GPTModel.load(path, 0, G.FP32)
+    s32 = G.BatchSession(m32, 8, 256)
+    lp32 = s32.score(inp[:8], tgt[:8])
+    s32.close(); m32.close()
+    assert float(np.abs(lp16[:8] - lp32).max()) < 2e-2
+    om = port.load(path)
+    _, _, want = port.mean_loss(om, inp[:1, :12], tgt[:1, :12], 8)
+    port.free(om)
+    np.testing.assert_allclose(lp32[0, :12], want[0], rtol=0, atol=ROW_TOL)
+    print(f"scored {n * S} ids in {ms:.2f} ms ({n * S / ms * 1e3:.0f} ids/s), mean loss {mean16:.4f}")

@@ -54,6 +54,36 @@ def test_tensor_core_path_tracks_fp32_oracle(name, n_seq, G, golden_ckpt, port):
     m16.close()
 
 
+def test_batched_prompt_feed_over_several_chunks(G, golden_ckpt, port):
+    """300 prompts of 30-40 ids are more rows than one pass of the batched prompt feed holds, so the
+    feed runs in several position ranges; later ranges must land at their own cache positions."""
+    dm, path = golden_ckpt("hs64_modern")
+    n_seq = 300
+    rng = np.random.default_rng(23)
+    lens = rng.integers(30, dm.max_len, n_seq)
+    prompts = [rng.integers(0, dm.vocab, int(n)).astype(np.int32) for n in lens]
+    m16 = G.GPTModel.load(path, 0, G.BF16)
+    s = G.BatchSession(m16, n_seq)
+    got = s.prefill(prompts)
+    om = port.load(path)
+    for i in (0, 1, 149, 298, 299):
+        want = port.logits_for(om, prompts[i])[-1]
+        assert rel_err(got[i], want) < 4e-2, (i, rel_err(got[i], want))
+        assert s.position(i) == len(prompts[i])
+        osess = port.session(om)
+        for t in prompts[i]:
+            port.step(osess, int(t), dm.vocab)
+        for pos in (0, 26, 27, len(prompts[i]) - 1):
+            for which in (0, 1):
+                gotr = s.cache_row(i, dm.layers - 1, which, pos)
+                wantr = port.cache_row(osess, dm.layers - 1, which, pos, dm.d_model)
+                assert np.abs(gotr - wantr).max() < 3e-2 * max(np.abs(wantr).max(), 1e-6), (i, pos, which)
+        port.session_free(osess)
+    port.free(om)
+    s.close()
+    m16.close()
+
+
 def test_tensor_core_and_streaming_bf16_paths_agree(G, golden_ckpt, monkeypatch):
     dm, path = golden_ckpt("hs64_modern")
     rng = np.random.default_rng(22)
