@@ -13,7 +13,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libgradb.so"
-SOURCES = ["checkpoint.cpp", "model.cu", "step_kernels.cu", "select_kernels.cu", "gemm_tc.cu", "decode_b1.cu", "session.cu", "capi.cu"]
+SOURCES = ["checkpoint.cpp", "model.cu", "step_kernels.cu", "attn_prefill.cu", "select_kernels.cu", "gemm_tc.cu", "decode_b1.cu", "session.cu", "capi.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "--expt-extended-lambda"]
 

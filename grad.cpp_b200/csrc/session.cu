@@ -1,5 +1,7 @@
 #include "session.cuh"
 
+#include "attn_prefill.cuh"
+
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
@@ -407,6 +409,8 @@ void ensure_feed_buffers(Session* s) {
     dalloc(&f.row_last, R);
     dalloc(&f.seq_count, (size_t)s->B);
     dalloc(&f.last_tok, (size_t)s->B);
+    dalloc(&f.tiles, R);
+    prefill_attention_configure();
     for (int i = 0; i < 3; i++) {
         const uint32_t tn = 32u << i;
         make_tensor_map_bf16(&f.map_h16[i], f.h16, R, s->d, tn);
@@ -446,6 +450,8 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
     const int width = std::max(1, f.cap / n_seq);  // positions per chunk
     const int want = m->sm_count * 3 / 4;
     auto map_idx = [](int tn) { return tn == 32 ? 0 : (tn == 64 ? 1 : 2); };
+    const char* no_tiled = std::getenv("GRADB_NO_TILED_ATTN");
+    const bool tiled_ok = !(no_tiled && no_tiled[0] == '1');
 
     // per-sequence logits mask: id of the last prompt token, or skip
     f.h_rows.resize((size_t)4 * f.cap + 2 * (size_t)s->B);
@@ -465,9 +471,13 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
         int* h_lastrow = h_seq + f.cap;
         int* h_cnt = h_lastrow + f.cap;
         int R = 0;
+        f.h_tiles.clear();
         for (int b = 0; b < n_seq; b++) {
             const int len = offsets[b + 1] - offsets[b];
             h_cnt[b] = 0;
+            for (int j = p0; j < std::min(p1, len); j += 64) {
+                f.h_tiles.push_back(make_int4(b, R + (j - p0), s->h_pos[b] + j, std::min(64, std::min(p1, len) - j)));
+            }
             for (int j = p0; j < std::min(p1, len); j++) {
                 h_tok[R] = tokens[offsets[b] + j];
                 h_pos[R] = s->h_pos[b] + j;
@@ -487,6 +497,15 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
         GRADB_CUDA(cudaMemcpyAsync(f.row_seq, h_seq, R * sizeof(int), cudaMemcpyHostToDevice, st));
         GRADB_CUDA(cudaMemcpyAsync(f.row_last, h_lastrow, R * sizeof(int), cudaMemcpyHostToDevice, st));
         GRADB_CUDA(cudaMemcpyAsync(f.seq_count, h_cnt, n_seq * sizeof(int), cudaMemcpyHostToDevice, st));
+        // Query-tiled attention when the rows form runs of consecutive positions; single positions per
+        // sequence stream their prefix through the decode kernel instead. Longest prefixes first.
+        const bool tiled = tiled_ok && (size_t)R >= 8 * f.h_tiles.size();
+        if (tiled) {
+            std::sort(f.h_tiles.begin(), f.h_tiles.end(),
+                      [](const int4& a, const int4& b) { return a.z + a.w > b.z + b.w; });
+            GRADB_CUDA(cudaMemcpyAsync(f.tiles, f.h_tiles.data(), f.h_tiles.size() * sizeof(int4),
+                                       cudaMemcpyHostToDevice, st));
+        }
         if (score_targets) {
             GRADB_CUDA(cudaMemcpyAsync(f.row_tgt, f.h_score.data(), R * sizeof(int), cudaMemcpyHostToDevice, st));
             GRADB_CUDA(cudaMemcpyAsync(f.row_dst, f.h_score.data() + f.cap, R * sizeof(int), cudaMemcpyHostToDevice,
@@ -520,12 +539,21 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
             }
             {
                 Timed t(s, KC_ATTN);
-                AttnParams a{};
-                a.q = f.q; a.kcache = kc; a.vcache = vc; a.tok = f.row_tok; a.pos = f.row_pos; a.row_seq = f.row_seq;
-                a.out = f.attn; a.out16 = f.attn16; a.partial = nullptr; a.counters = nullptr; a.status = s->status;
-                a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = d;
-                a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
-                launch_attention(a, R, 1, st);
+                if (tiled) {
+                    PrefillAttnParams a{};
+                    a.q = f.q; a.kcache = kc; a.vcache = vc; a.out = nullptr; a.out16 = f.attn16;
+                    a.tiles = f.tiles; a.n_tiles = (int)f.h_tiles.size();
+                    a.H = s->H; a.T = s->T; a.d = d;
+                    a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
+                    launch_prefill_attention(a, st);
+                } else {
+                    AttnParams a{};
+                    a.q = f.q; a.kcache = kc; a.vcache = vc; a.tok = f.row_tok; a.pos = f.row_pos; a.row_seq = f.row_seq;
+                    a.out = f.attn; a.out16 = f.attn16; a.partial = nullptr; a.counters = nullptr; a.status = s->status;
+                    a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = d;
+                    a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
+                    launch_attention(a, R, 1, st);
+                }
             }
             {
                 Timed t(s, KC_OPROJ);
@@ -726,7 +754,7 @@ void destroy_session(Session* s) {
     cudaFree(s->feed.x); cudaFree(s->feed.q); cudaFree(s->feed.attn); cudaFree(s->feed.h16); cudaFree(s->feed.attn16);
     cudaFree(s->feed.ffn16); cudaFree(s->feed.row_tok); cudaFree(s->feed.row_pos); cudaFree(s->feed.row_seq);
     cudaFree(s->feed.row_last); cudaFree(s->feed.seq_count); cudaFree(s->feed.last_tok);
-    cudaFree(s->feed.score_logits); cudaFree(s->feed.row_tgt); cudaFree(s->feed.row_dst);
+    cudaFree(s->feed.tiles); cudaFree(s->feed.score_logits); cudaFree(s->feed.row_tgt); cudaFree(s->feed.row_dst);
     cudaFree(s->score_out); cudaFree(s->score_tgt);
     cudaFree(s->h16); cudaFree(s->attn16); cudaFree(s->ffn16); cudaFree(s->status);
     if (s->h_stage) cudaFreeHost(s->h_stage);

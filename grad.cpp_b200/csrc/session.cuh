@@ -53,6 +53,8 @@ struct Session {
         CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];
         std::vector<int> h_rows;  // host staging: 4 * cap + 2 * B ints
         // teacher-forced scoring: all-row logits of a chunk, per-row target and destination
+        int4* tiles = nullptr;  // query tiles of the current chunk (prompt attention)
+        std::vector<int4> h_tiles;
         float* score_logits = nullptr;
         int *row_tgt = nullptr, *row_dst = nullptr;
         std::vector<int> h_score;  // host staging: 2 * cap ints

@@ -84,6 +84,25 @@ def test_batched_prompt_feed_over_several_chunks(G, golden_ckpt, port):
     m16.close()
 
 
+@pytest.mark.parametrize("name,n_seq", [("hs64_modern", 40), ("odd_modern", 350), ("hs64_gpt2", 16)])
+def test_tiled_prompt_attention_matches_per_position_attention(name, n_seq, G, golden_ckpt, monkeypatch):
+    """The prompt feed's query-tiled attention (TF32 tensor-core products over tiles of 64 positions) against
+    the same feed with every position streaming its prefix through the decode attention kernel (fp32)."""
+    dm, path = golden_ckpt(name)
+    rng = np.random.default_rng(24)
+    lens = rng.integers(1, dm.max_len + 1, n_seq)
+    lens[0], lens[1] = dm.max_len, 1
+    prompts = [rng.integers(0, dm.vocab, int(n)).astype(np.int32) for n in lens]
+    m16 = G.GPTModel.load(path, 0, G.BF16)
+    a_s = G.BatchSession(m16, n_seq)
+    a = a_s.prefill(prompts)
+    monkeypatch.setenv("GRADB_NO_TILED_ATTN", "1")
+    b_s = G.BatchSession(m16, n_seq)
+    b = b_s.prefill(prompts)
+    assert rel_err(a, b) < 1e-2, rel_err(a, b)
+    a_s.close(); b_s.close(); m16.close()
+
+
 def test_tensor_core_and_streaming_bf16_paths_agree(G, golden_ckpt, monkeypatch):
     dm, path = golden_ckpt("hs64_modern")
     rng = np.random.default_rng(22)
