@@ -207,6 +207,11 @@ class Ref:
                                                  C.c_float, _f32p]
         L.gradref_mean_loss.argtypes = [C.c_void_p, _i32p, _i32p, C.c_int, C.c_int, C.c_int,
                                         C.POINTER(C.c_double), _f32p, _f32p]
+        L.gradref_tokenfile_write.argtypes = [C.c_char_p, _i32p, C.c_ulonglong, C.c_int]
+        L.gradref_dataset_open.argtypes = [C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_ulonglong)]
+        L.gradref_loader_windows.restype = C.c_longlong
+        L.gradref_loader_windows.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint, C.c_int,
+                                             _i32p, _i32p, C.c_longlong]
 
     def load(self, path):
         # The reference prints a success line to stdout from load(); keep it off ours.
@@ -276,6 +281,29 @@ class Ref:
     def mean_loss(self, m, inputs, targets, batch_windows=8):
         """The reference's full-sequence forward + cross_entropy, batched as `grad eval` does."""
         return _mean_loss(self.L.gradref_mean_loss, m, inputs, targets, batch_windows)
+
+    # -- token files and batch assembly (src/data) -------------------------
+    def tokenfile_write(self, path, ids, vocab):
+        a = np.ascontiguousarray(ids, np.int32)
+        if self.L.gradref_tokenfile_write(str(path).encode(), _ptr(a, _i32p), len(a), vocab):
+            raise RuntimeError(self.L.gradref_last_error().decode())
+
+    def dataset_open(self, path, seq_length, stride):
+        """(windows, vocab, token count) as MappedTokenDataset reports them; raises with its message."""
+        info = (C.c_ulonglong * 3)()
+        if self.L.gradref_dataset_open(str(path).encode(), seq_length, stride, info):
+            raise RuntimeError(self.L.gradref_last_error().decode())
+        return int(info[0]), int(info[1]), int(info[2])
+
+    def loader_windows(self, path, seq_length, stride, batch_size, shuffle, seed, max_batches, cap=1 << 16):
+        inp = np.zeros((cap, seq_length), np.int32)
+        tgt = np.zeros((cap, seq_length), np.int32)
+        n = self.L.gradref_loader_windows(str(path).encode(), seq_length, stride, batch_size, int(shuffle), seed,
+                                          max_batches, _ptr(inp, _i32p), _ptr(tgt, _i32p), cap)
+        if n < 0:
+            raise RuntimeError(self.L.gradref_last_error().decode())
+        assert n <= cap
+        return inp[:n].copy(), tgt[:n].copy()
 
     def sample_from_logits(self, m, logits, temperature, top_k, top_p):
         lg = np.ascontiguousarray(logits, np.float32)

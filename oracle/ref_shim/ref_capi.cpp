@@ -35,6 +35,8 @@
 #include <string_view>
 #include <vector>
 
+#include "grad/data/dataloader.h"
+#include "grad/data/token_file.h"
 #include "grad/transformer/gpt_model.h"
 #include "grad/transformer/inference.h"
 #include "grad/tokenizer/tokenizer.h"
@@ -296,5 +298,61 @@ extern "C" int gradref_mean_loss(void* m, const int* inputs, const int* targets,
     } catch (const std::exception& e) {
         g_error = e.what();
         return 1;
+    }
+}
+
+// Token files and batch assembly exactly as `grad eval` uses them: tokenfile::write
+// (src/data/token_file.cpp:33-70), MappedTokenDataset (:83-176) and DataLoader (src/data/dataloader.cpp).
+extern "C" int gradref_tokenfile_write(const char* path, const int* ids, unsigned long long count, int vocab) {
+    try {
+        grad::tokenfile::write(path, ids, static_cast<size_t>(count), vocab);
+        return 0;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return 1;
+    }
+}
+
+// Opens a token file as the reference does and reports {windows, vocab, token count}; on failure
+// returns 1 and leaves the reference's message in gradref_last_error().
+extern "C" int gradref_dataset_open(const char* path, int seq_length, int stride, unsigned long long* info) {
+    try {
+        grad::MappedTokenDataset ds(path, seq_length, stride);
+        info[0] = ds.size();
+        info[1] = static_cast<unsigned long long>(ds.vocabSize());
+        info[2] = ds.tokenCount();
+        return 0;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return 1;
+    }
+}
+
+// The windows a DataLoader hands out, batch after batch, for the first max_batches batches
+// (all when <= 0). inputs/targets: up to cap_windows x seq_length ids. Returns the window count,
+// or -1 with gradref_last_error() set.
+extern "C" long long gradref_loader_windows(const char* path, int seq_length, int stride, int batch_size,
+                                            int shuffle, unsigned seed, int max_batches, int* inputs,
+                                            int* targets, long long cap_windows) {
+    try {
+        auto ds = std::make_shared<grad::MappedTokenDataset>(path, seq_length, stride);
+        grad::DataLoader loader(ds, batch_size, shuffle != 0, seed);
+        long long n = 0;
+        for (int batches = 0; loader.has_next(); batches++) {
+            if (max_batches > 0 && batches >= max_batches) break;
+            grad::Batch batch = loader.next_batch();
+            const size_t nb = batch.input.getBatchSize();
+            for (size_t b = 0; b < nb; b++, n++) {
+                if (n >= cap_windows) continue;
+                for (int s = 0; s < seq_length; s++) {
+                    inputs[n * seq_length + s] = static_cast<int>(batch.input.getValue(b, s, 0));
+                    targets[n * seq_length + s] = static_cast<int>(batch.target.getValue(b, s, 0));
+                }
+            }
+        }
+        return n;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return -1;
     }
 }

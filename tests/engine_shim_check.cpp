@@ -1,7 +1,7 @@
 // Exercises the C++ drop-in classes (include/gradb/engine.hpp) the way the reference's
 // own parity test drives its classes (tests/integration/sanity_tests.cpp:293-333):
 // load a checkpoint, step a fixed sequence, check errors and a greedy rollout.
-// Usage: engine_shim_check <checkpoint> ; prints ids and a few logits for the Python side to compare.
+// Usage: engine_shim_check <checkpoint> [<token file>] ; prints ids and a few logits for the Python side to compare.
 #include <cstdio>
 #include <string>
 #include <vector>
@@ -51,12 +51,43 @@ int main(int argc, char** argv) {
     const int n = gen.generate_stream(prompt, [&](const std::string& s) { streamed += (int)s.size(); }, 0.9f, 5);
     std::printf("stream %d %d\n", n, streamed);
     std::printf("empty '%s'\n", gen.generate_greedy({}, 5).c_str());
-    // `grad eval`: windows of 5 ids with stride 5 over a 23-id stream -> 4 windows, batches of 3 (last one ragged)
-    std::vector<int> stream;
-    for (int i = 0; i < 23; i++) stream.push_back((i * 7 + 3) % model.getVocabSize());
-    const gradb::TokenWindows windows(stream, 5, 5);
-    std::printf("windows %zu\n", windows.size());
-    std::printf("mean_loss %.9g\n", gradb::training::mean_loss(model, windows, 0, 3));
-    std::printf("mean_loss_first %.9g\n", gradb::training::mean_loss(model, windows, 1, 3));
+    // `grad eval` (src/cli/eval.cpp:77-133): token file -> windows of 5 ids, stride 5 -> batches of 3
+    if (argc >= 3) {
+        const std::string tokens = argv[2];
+        auto val = std::make_shared<gradb::MappedTokenDataset>(tokens, 5, 5);
+        std::printf("dataset %zu %d %zu\n", val->size(), val->vocabSize(), val->tokenCount());
+        gradb::DataLoader all(val, 3, /*shuffle=*/false, 20260921u);
+        std::printf("batches %zu\n", all.num_batches());
+        std::printf("mean_loss_all %.9g\n", gradb::training::mean_loss(model, all, 0));
+        gradb::DataLoader capped(val, 3, /*shuffle=*/true, 20260921u);
+        gradb::Batch first = capped.next_batch();
+        std::printf("shuffled");
+        for (int32_t id : first.input) std::printf(" %d", id);
+        std::printf("\n");
+        capped.reset();
+        gradb::DataLoader capped2(val, 3, /*shuffle=*/true, 20260921u);
+        std::printf("mean_loss_capped %.9g\n", gradb::training::mean_loss(model, capped2, 2));
+        // a copy written by this side must be byte-identical to the reference's file
+        std::vector<int> ids;
+        for (size_t i = 0; i < val->size(); i++) {
+            auto [in, tg] = val->get_item(i);
+            ids.insert(ids.end(), in.begin(), in.end());
+        }
+        gradb::tokenfile::write(tokens + ".copy", ids, val->vocabSize());
+        try {
+            gradb::MappedTokenDataset bad(std::string(argv[1]), 5, 5);
+            std::printf("FAIL checkpoint accepted as token file\n");
+            return 1;
+        } catch (const std::runtime_error& e) {
+            std::printf("bad magic: %s\n", e.what());
+        }
+        try {
+            gradb::MappedTokenDataset huge(tokens, 100000, 5);
+            std::printf("FAIL oversized window accepted\n");
+            return 1;
+        } catch (const std::runtime_error& e) {
+            std::printf("too short: %s\n", e.what());
+        }
+    }
     return 0;
 }

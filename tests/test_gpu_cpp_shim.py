@@ -17,7 +17,9 @@ def test_cpp_classes_match_oracle(golden_ckpt, port, tmp_path):
     libdir = ROOT / "grad.cpp_b200"
     subprocess.run(["g++", "-std=c++20", "-O1", str(ROOT / "tests" / "engine_shim_check.cpp"), "-o", str(exe),
                     f"-L{libdir}", "-lgradb", f"-Wl,-rpath,{libdir}"], check=True)
-    out = subprocess.run([str(exe), path], capture_output=True, text=True, timeout=120)
+    tokens = tmp_path / "tokens.bin"
+    tokens.write_bytes((ROOT / "tests" / "golden" / "ref_tokens.bin").read_bytes())
+    out = subprocess.run([str(exe), path, str(tokens)], capture_output=True, text=True, timeout=120)
     assert out.returncode == 0, out.stdout + out.stderr
     text = out.stdout
     assert f"missing: Could not open checkpoint for reading: {path}.missing" in text
@@ -39,15 +41,18 @@ def test_cpp_classes_match_oracle(golden_ckpt, port, tmp_path):
     assert len(sample) == 12 and sample[:4] == [3, 11, 7, 0]
     assert "stream 5 5" in text
     assert "empty ''" in text
-    # training::mean_loss over in-memory windows against the restatement (fp32 rounding apart)
-    stream = np.array([(i * 7 + 3) % dm.vocab for i in range(23)], np.int32)
-    inp = np.stack([stream[i * 5:i * 5 + 5] for i in range(4)])
-    tgt = np.stack([stream[i * 5 + 1:i * 5 + 6] for i in range(4)])
-    assert "windows 4" in text
-    want_all, _, _ = port.mean_loss(om, inp, tgt, 3)
-    want_first, _, _ = port.mean_loss(om, inp[:3], tgt[:3], 3)
-    got_all = float(re.search(r"mean_loss (\S+)", text).group(1))
-    got_first = float(re.search(r"mean_loss_first (\S+)", text).group(1))
-    assert abs(got_all - want_all) < 2e-5 * want_all
-    assert abs(got_first - want_first) < 2e-5 * want_first
+    # `grad eval` through the C++ classes: token file -> loaders -> training::mean_loss, against the loss the
+    # reference computes over the same loaders (tests/golden/tokenfile_golden.npz)
+    tg = np.load(ROOT / "tests" / "golden" / "tokenfile_golden.npz")
+    assert "dataset 40 23 203" in text and "batches 14" in text
+    got_all = float(re.search(r"mean_loss_all (\S+)", text).group(1))
+    got_capped = float(re.search(r"mean_loss_capped (\S+)", text).group(1))
+    assert abs(got_all - float(tg["tiny_modern/seq/mean"][0])) < 2e-5 * got_all
+    assert abs(got_capped - float(tg["tiny_modern/capped/mean"][0])) < 2e-5 * got_capped
+    shuffled = [int(x) for x in re.search(r"shuffled((?: \d+)+)", text).group(1).split()]
+    assert shuffled == list(tg["capped/inputs"][:3].reshape(-1))
+    assert (tmp_path / "tokens.bin.copy").read_bytes()[:16] == (ROOT / "tests/golden/ref_tokens.bin").read_bytes()[:8] \
+        + (200).to_bytes(8, "little")
+    assert f"bad magic: Not a token file (bad magic): {path}" in text
+    assert "too short: Not enough tokens for even one sequence: " in text
     port.free(om)

@@ -126,3 +126,28 @@ def test_eval_shape_windows_of_256_on_the_69m_model(G, ck, port, tmp_path):
     port.free(om)
     np.testing.assert_allclose(lp32[0, :12], want[0], rtol=0, atol=ROW_TOL)
     print(f"scored {n * S} ids in {ms:.2f} ms ({n * S / ms * 1e3:.0f} ids/s), mean loss {mean16:.4f}")
+
+
+@pytest.mark.parametrize("name", ["tiny_gpt2", "tiny_modern"])
+def test_eval_over_a_token_file_matches_reference(name, G, golden_ckpt):
+    """`grad eval` end to end: the reference's token file -> windows -> device scoring -> the loss the
+    reference reports for the same loader (sequential, ragged last batch, and its shuffled picks)."""
+    from grad_cpp_b200 import tokenfile
+    tg = np.load(ROOT / "tests" / "golden" / "tokenfile_golden.npz")
+    dm, path = golden_ckpt(name)
+    m = G.GPTModel.load(path, 0, G.FP32)
+    s = G.BatchSession(m, 16)
+    for tag in ("seq", "ragged"):
+        seq, batch = int(tg[f"{tag}/params"][0]), int(tg[f"{tag}/params"][1])
+        ds = tokenfile.MappedTokenDataset(ROOT / "tests" / "golden" / "ref_tokens.bin", seq, seq)
+        inp, tgt = ds.windows()
+        mean, _ = s.mean_loss(inp, tgt, batch)
+        want = float(tg[f"{name}/{tag}/mean"][0])
+        assert abs(mean - want) <= LOSS_TOL * want, (tag, mean, want)
+    for tag in ("capped", "train"):
+        batch = int(tg[f"{tag}/params"][1])
+        mean, _ = s.mean_loss(tg[f"{tag}/inputs"], tg[f"{tag}/targets"], batch)
+        want = float(tg[f"{name}/{tag}/mean"][0])
+        assert abs(mean - want) <= LOSS_TOL * want, (tag, mean, want)
+    s.close()
+    m.close()
