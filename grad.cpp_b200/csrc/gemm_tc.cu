@@ -21,6 +21,9 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "gemm_tc.cuh"
 
 namespace gradb {
@@ -122,6 +125,105 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
 
+// Epilogue of one output tile, run by the four warps that own the TMEM lane quarters: thread t
+// (0..127, t / 32 = the warp's lane quarter) owns feature tile_n * 128 + t; lane_addr is the
+// accumulator's TMEM address with the quarter's lane offset applied. nz = number of K splits.
+template <int EPI, int NW, int TN>
+__device__ __forceinline__ void tc_epilogue(const TcGemmParams& p, uint32_t lane_addr, int t, int tile_n, int tile_b,
+                                            int kz, int nz, const int* s_tok, const int* s_pos, const long long* s_off,
+                                            int c_begin = 0, int c_end = TN) {
+    const int n = tile_n * kTileM + t;  // feature index inside one matrix (for NW=2: same n in gate and up)
+    const bool n_ok = n < p.N;
+    int which = 0, n_in = n;
+    float bias = 0.f;
+    if (EPI == TC_QKV) {
+        which = n / p.d;
+        n_in = n - which * p.d;
+        if (n_ok) bias = p.bias[which][n_in];
+    } else if (EPI == TC_RESID || EPI == TC_GELU) {
+        if (n_ok && p.bias[0] && kz == 0) bias = p.bias[0][n];
+    }
+    const int h = n_in / p.hs, c_in = n_in % p.hs, half = p.hs / 2;
+    const bool rope = EPI == TC_QKV && p.rope_cos != nullptr && which < 2;
+    // Per-thread base pointers; the per-token part of every address is staged in shared memory (s_off:
+    // element offset of the token's cache row for head 0) or is a multiple of the row pitch.
+    const float* cos_t = p.rope_cos + c_in / 2;
+    const float* sin_t = p.rope_sin + c_in / 2;
+    float* kv_t = (which == 1 ? p.kcache : p.vcache) + (size_t)h * p.T * p.hs + c_in;
+    float* out_t = p.out_f32 + (EPI == TC_QKV ? n_in : n);
+    __nv_bfloat16* out16_t = p.out_bf16 + n;
+    for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+        float v[32], v2[32];
+        tmem_ld32(lane_addr + c0, v);
+        if (NW == 2) tmem_ld32(lane_addr + TN + c0, v2);
+        // kGroup tokens at a time, in three passes so that independent work is adjacent: every load the
+        // group needs (all in flight together), then the arithmetic of all its tokens (one warp per
+        // scheduler runs this code, so latency is only hidden by instruction-level parallelism), then the stores.
+        constexpr int kGroup = TN >= 128 ? 16 : 8;
+#pragma unroll
+        for (int j0 = 0; j0 < 32; j0 += kGroup) {
+            float aux0[kGroup], aux1[kGroup], res[kGroup];
+            int posn[kGroup];
+            bool live[kGroup];
+#pragma unroll
+            for (int jj = 0; jj < kGroup; jj++) {
+                const int c = c0 + j0 + jj;
+                live[jj] = s_tok[c] >= 0;  // warp-uniform; rows past the batch were staged as skipped
+                posn[jj] = s_pos[c];
+                aux0[jj] = aux1[jj] = 0.f;
+                if (rope) {
+                    aux0[jj] = __ldg(cos_t + posn[jj] * half);
+                    aux1[jj] = __ldg(sin_t + posn[jj] * half);
+                }
+                if (EPI == TC_RESID && nz == 1 && live[jj] && n_ok) {
+                    aux0[jj] = out_t[(size_t)(tile_b * TN + c) * p.ld_out];
+                }
+            }
+#pragma unroll
+            for (int jj = 0; jj < kGroup; jj++) {
+                const int j = j0 + jj;
+                float val = v[j] + bias;
+                if (EPI == TC_QKV) {
+                    if (rope) {
+                        // pairs (2j, 2j+1) inside a head sit in neighbouring lanes (inference.cpp:101-115)
+                        const float other = __shfl_xor_sync(0xffffffffu, val, 1);
+                        val = (c_in & 1) ? (other * aux1[jj] + val * aux0[jj]) : (val * aux0[jj] - other * aux1[jj]);
+                    }
+                } else if (EPI == TC_RESID) {
+                    if (nz == 1) val += aux0[jj];
+                } else if (EPI == TC_GELU) {
+                    const float u = 0.79788456f * (val + 0.044715f * val * val * val);
+                    val = 0.5f * val * (1.0f + tanhf(u));
+                } else if (EPI == TC_SWIGLU) {
+                    const float gte = v[j];
+                    val = v2[j] * (gte / (1.0f + __expf(-gte)));
+                } else {
+                    val = v[j];
+                }
+                res[jj] = val;
+            }
+#pragma unroll
+            for (int jj = 0; jj < kGroup; jj++) {
+                if (!(live[jj] && n_ok)) continue;
+                const int c = c0 + j0 + jj;
+                const int b = tile_b * TN + c;
+                if (EPI == TC_QKV) {
+                    if (which == 0) out_t[(size_t)b * p.ld_out] = res[jj];
+                    else kv_t[s_off[c]] = res[jj];
+                } else if (EPI == TC_RESID) {
+                    float* y = out_t + (size_t)b * p.ld_out;
+                    if (nz == 1) *y = res[jj];
+                    else atomicAdd(y, res[jj]);
+                } else if (EPI == TC_GELU || EPI == TC_SWIGLU) {
+                    out16_t[(size_t)b * p.ld_out] = __float2bfloat16_rn(res[jj]);
+                } else {  // TC_LOGITS
+                    out_t[(size_t)b * p.ld_out] = res[jj];
+                }
+            }
+        }
+    }
+}
+
 // Shared memory: [stage][A tiles (NW x 16 KB) | B tile (TN x 128 B)], 1024-byte aligned.
 template <int EPI, int NW, int TN>
 __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -131,7 +233,8 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int s_tok[TN], s_pos[TN], s_seq[TN];
+    __shared__ int s_tok[TN], s_pos[TN];
+    __shared__ long long s_off[TN];
 
     constexpr int kABytes = NW * kTileM * kBlockK * 2;
     constexpr int kBBytes = TN * kBlockK * 2;
@@ -187,9 +290,11 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
     for (int c = threadIdx.x; c < TN; c += blockDim.x) {
         const int b = blockIdx.y * TN + c;
         const int tk = b < p.B ? p.tok[b] : kSkip;
+        const int ps = tk >= 0 ? p.pos[b] : 0;
+        const int sq = (tk >= 0 && p.row_seq) ? p.row_seq[b] : b;
         s_tok[c] = tk;
-        s_pos[c] = tk >= 0 ? p.pos[b] : 0;
-        s_seq[c] = (tk >= 0 && p.row_seq) ? p.row_seq[b] : b;
+        s_pos[c] = ps;
+        s_off[c] = (((long long)sq * p.H) * p.T + ps) * p.hs;
     }
     __syncthreads();
 
@@ -242,92 +347,179 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
     if (n_iters > 0) ok = mbar_wait(&accum_bar, 0, p.status, 103);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok && n_iters > 0) {
-        const int t = threadIdx.x;
-        const int n = tile_n * kTileM + t;  // feature index inside one matrix (for NW=2: same n in gate and up)
-        const bool n_ok = n < p.N;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        int which = 0, n_in = n;
-        float bias = 0.f;
-        if (EPI == TC_QKV) {
-            which = n / p.d;
-            n_in = n - which * p.d;
-            if (n_ok) bias = p.bias[which][n_in];
-        } else if (EPI == TC_RESID || EPI == TC_GELU) {
-            if (n_ok && p.bias[0] && kz == 0) bias = p.bias[0][n];
-        }
-        const int h = n_in / p.hs, c_in = n_in % p.hs, half = p.hs / 2;
-        const bool rope = EPI == TC_QKV && p.rope_cos != nullptr && which < 2;
-        float* cache = which == 1 ? p.kcache : p.vcache;
-        for (int c0 = 0; c0 < TN; c0 += 32) {
-            float v[32], v2[32];
-            tmem_ld32(lane_addr + c0, v);
-            if (NW == 2) tmem_ld32(lane_addr + TN + c0, v2);
-            // Eight tokens at a time: first every load the group needs (so they are all in
-            // flight together), then the arithmetic and the stores.
-#pragma unroll
-            for (int j0 = 0; j0 < 32; j0 += 8) {
-                float aux0[8], aux1[8];
-                int posn[8];
-                bool live[8];
-#pragma unroll
-                for (int jj = 0; jj < 8; jj++) {
-                    const int c = c0 + j0 + jj;
-                    live[jj] = s_tok[c] >= 0;  // warp-uniform; rows past the batch were staged as skipped
-                    posn[jj] = s_pos[c];
-                    aux0[jj] = aux1[jj] = 0.f;
-                    if (rope) {
-                        aux0[jj] = __ldg(p.rope_cos + (size_t)posn[jj] * half + c_in / 2);
-                        aux1[jj] = __ldg(p.rope_sin + (size_t)posn[jj] * half + c_in / 2);
-                    }
-                    if (EPI == TC_RESID && gridDim.z == 1 && live[jj] && n_ok) {
-                        aux0[jj] = p.out_f32[(size_t)(tile_b * TN + c) * p.ld_out + n];
-                    }
-                }
-#pragma unroll
-                for (int jj = 0; jj < 8; jj++) {
-                    const int j = j0 + jj;
-                    const int b = tile_b * TN + c0 + j;
-                    float val = v[j] + bias;
-                    if (EPI == TC_QKV) {
-                        if (rope) {
-                            // pairs (2j, 2j+1) inside a head sit in neighbouring lanes (inference.cpp:101-115)
-                            const float other = __shfl_xor_sync(0xffffffffu, val, 1);
-                            val = (c_in & 1) ? (other * aux1[jj] + val * aux0[jj]) : (val * aux0[jj] - other * aux1[jj]);
-                        }
-                        if (live[jj] && n_ok) {
-                            if (which == 0) {
-                                p.out_f32[(size_t)b * p.ld_out + n_in] = val;
-                            } else {
-                                cache[(((size_t)s_seq[c0 + j] * p.H + h) * p.T + posn[jj]) * p.hs + c_in] = val;
-                            }
-                        }
-                    } else if (EPI == TC_RESID) {
-                        if (live[jj] && n_ok) {
-                            float* y = p.out_f32 + (size_t)b * p.ld_out + n;
-                            if (gridDim.z == 1) *y = aux0[jj] + val;
-                            else atomicAdd(y, val);
-                        }
-                    } else if (EPI == TC_GELU) {
-                        if (live[jj] && n_ok) {
-                            const float u = 0.79788456f * (val + 0.044715f * val * val * val);
-                            p.out_bf16[(size_t)b * p.ld_out + n] = __float2bfloat16_rn(0.5f * val * (1.0f + tanhf(u)));
-                        }
-                    } else if (EPI == TC_SWIGLU) {
-                        if (live[jj] && n_ok) {
-                            const float gte = v[j];
-                            const float sg = gte / (1.0f + __expf(-gte));
-                            p.out_bf16[(size_t)b * p.ld_out + n] = __float2bfloat16_rn(v2[j] * sg);
-                        }
-                    } else {  // TC_LOGITS
-                        if (live[jj] && n_ok) p.out_f32[(size_t)b * p.ld_out + n] = v[j];
-                    }
-                }
-            }
-        }
+        tc_epilogue<EPI, NW, TN>(p, tmem_base + ((uint32_t)(warp * 32) << 16), threadIdx.x, tile_n, tile_b, kz,
+                                 (int)gridDim.z, s_tok, s_pos, s_off);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same GEMM for many rows (prompt feed, scoring): persistent, one CTA per SM, warp-specialised.
+// With thousands of 128x128 output tiles the one-tile-per-CTA kernel above spends most of each CTA's
+// life in its prologue, in the TMA round trips of a short ring and in an epilogue that nothing
+// overlaps (tensor pipe 11-26 % busy). Here
+//   warp 0 (one lane)  streams A and B tiles through a deep ring, running ahead across tile boundaries,
+//   warp 1 (one lane)  issues the MMAs into one of TWO accumulators in TMEM,
+//   warps 2-9          drain the other accumulator (the shared epilogue; two warps per TMEM lane quarter,
+//                      half of the token columns each), so the epilogue of tile i runs under the main
+//                      loop of tile i+1. The epilogue is arithmetic- and latency-bound, hence eight warps.
+// Tiles are dealt round-robin, feature tile fastest, so CTAs working at the same time share a token tile in L2.
+constexpr int kWideTN = 128;
+constexpr int wide_stages(int nw) { return nw == 1 ? 6 : 4; }  // 192 KB of ring either way
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int EPI, int NW>
+__global__ void __launch_bounds__(320) gemm_bf16_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                const __grid_constant__ CUtensorMap map_b,
+                                                                const TcGemmParams p, int tiles_n, int total_tiles) {
+    constexpr int TN = kWideTN;
+    constexpr int kStages = wide_stages(NW);
+    constexpr int kABytes = NW * kTileM * kBlockK * 2;
+    constexpr int kBBytes = TN * kBlockK * 2;
+    constexpr int kStageBytes = kABytes + kBBytes;
+    constexpr int kAccCols = NW * TN;          // one accumulator
+    constexpr int kTmemCols = 2 * kAccCols;    // two of them: 256 or 512 columns
+    static_assert(kTmemCols <= 512, "two accumulators must fit TMEM");
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int s_tok[2][TN], s_pos[2][TN];
+    __shared__ long long s_off[2][TN];
+    __shared__ volatile int s_fail;  // set when a bounded wait of an epilogue thread expires
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_iters = p.K / kBlockK;
+
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        s_fail = 0;
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"((uint32_t)kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int tile_n = tile % tiles_n, tile_b = tile / tiles_n;
+                for (int k = 0; k < k_iters; k++, it++) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    ok = mbar_wait(&empty_bar[s], ph ^ 1, p.status, 111);
+                    if (!ok) break;
+                    uint8_t* st = smem + (size_t)s * kStageBytes;
+                    mbar_expect_tx(&full_bar[s], kStageBytes);
+#pragma unroll
+                    for (int w = 0; w < NW; w++) {
+                        tma_load_2d(st + w * (kTileM * kBlockK * 2), &map_a, k * kBlockK, (tile_n * NW + w) * kTileM,
+                                    &full_bar[s]);
+                    }
+                    tma_load_2d(st + kABytes, &map_b, k * kBlockK, tile_b * TN, &full_bar[s]);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer
+            constexpr uint32_t idesc = umma_idesc_bf16(kTileM, TN);
+            bool ok = true;
+            int it = 0, lt = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, lt++) {
+                const int buf = lt & 1;
+                ok = mbar_wait(&acc_empty[buf], ((lt >> 1) & 1) ^ 1, p.status, 112);  // drained two tiles ago
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem_base + (uint32_t)(buf * kAccCols);
+                for (int k = 0; k < k_iters; k++, it++) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    ok = mbar_wait(&full_bar[s], ph, p.status, 113);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    uint8_t* st = smem + (size_t)s * kStageBytes;
+                    const uint64_t bdesc = umma_desc_sw128(st + kABytes);
+#pragma unroll
+                    for (int w = 0; w < NW; w++) {
+                        const uint64_t adesc = umma_desc_sw128(st + w * (kTileM * kBlockK * 2));
+#pragma unroll
+                        for (int kk = 0; kk < kBlockK / 16; kk++) {
+                            umma_bf16(acc + w * TN, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(&empty_bar[s]);
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---- eight epilogue warps: TMEM lane quarter = warp index modulo 4, two warps per quarter, each
+        // taking half of the tile's token columns
+        const int q = warp & 3;
+        const int t = q * 32 + lane;
+        const int hf = (warp - 2) >> 2;
+        const int e = (warp - 2) * 32 + lane;  // the first 128 stage one token of the tile each
+        int lt = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, lt++) {
+            const int tile_n = tile % tiles_n, tile_b = tile / tiles_n;
+            const int buf = lt & 1;
+            if (e < TN) {
+                const int b = tile_b * TN + e;
+                const int tk = b < p.B ? p.tok[b] : kSkip;
+                const int ps = tk >= 0 ? p.pos[b] : 0;
+                const int sq = (tk >= 0 && p.row_seq) ? p.row_seq[b] : b;
+                s_tok[buf][e] = tk;
+                s_pos[buf][e] = ps;
+                s_off[buf][e] = (((long long)sq * p.H) * p.T + ps) * p.hs;
+            }
+            if (!mbar_wait(&acc_full[buf], (lt >> 1) & 1, p.status, 114)) s_fail = 1;
+            // The epilogue warps only: publishes the staged ids and makes the give-up decision common,
+            // so that no warp is left waiting at this barrier.
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (s_fail) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            tc_epilogue<EPI, NW, TN>(p, tmem_base + (uint32_t)(buf * kAccCols) + ((uint32_t)(q * 32) << 16), t, tile_n,
+                                     tile_b, 0, 1, s_tok[buf], s_pos[buf], s_off[buf], hf * (TN / 2), (hf + 1) * (TN / 2));
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
                      : "memory");
@@ -487,9 +679,47 @@ int tc_token_tile(int n_seq, int n_tiles, int want_ctas) {
     return 32;
 }
 
+namespace {
+template <int EPI, int NW>
+void launch_wide(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, int tiles_n, int tiles_b, int sm_count,
+                 cudaStream_t st) {
+    constexpr size_t bytes = (size_t)wide_stages(NW) * (NW * kTileM * kBlockK * 2 + kWideTN * kBlockK * 2) + 1024;
+    auto kernel = gemm_bf16_tc_wide_kernel<EPI, NW>;
+    if (!g_capturing) {
+        GRADB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    }
+    const int total = tiles_n * tiles_b;
+    launch_kernel(kernel, dim3(std::min(total, sm_count)), dim3(320), bytes, st, a, b, p, tiles_n, total);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+}  // namespace
+
 void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int token_tile,
                     int k_splits, cudaStream_t st) {
     const int n_tiles = (p.N + kTileM - 1) / kTileM;
+    if (token_tile == kWideTN && k_splits == 1) {
+        // Many tiles per SM: the persistent kernel (the one-tile-per-CTA kernel is for the short decode GEMMs).
+        static int sm_count = 0;
+        if (!sm_count) {
+            int dev = 0;
+            GRADB_CUDA(cudaGetDevice(&dev));
+            GRADB_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+        }
+        const char* off = std::getenv("GRADB_NO_WIDE_GEMM");
+        const bool wide_off = off && off[0] == '1';
+        const int tiles_b = (p.B + kWideTN - 1) / kWideTN;
+        if (!wide_off && n_tiles * tiles_b >= 2 * sm_count) {
+            switch (epi) {
+                case TC_QKV: launch_wide<TC_QKV, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
+                case TC_RESID: launch_wide<TC_RESID, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
+                case TC_GELU: launch_wide<TC_GELU, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
+                case TC_SWIGLU: launch_wide<TC_SWIGLU, 2>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
+                case TC_LOGITS: launch_wide<TC_LOGITS, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
+                default: break;
+            }
+        }
+    }
     const dim3 grid(n_tiles, (p.B + token_tile - 1) / token_tile, k_splits);
     switch (epi) {
         case TC_QKV: launch_tn<TC_QKV, 1>(map_a, map_b, p, token_tile, grid, st); break;

@@ -96,7 +96,7 @@ def test_bf16_batched_scoring_tracks_fp32_oracle(name, n_windows, G, golden_ckpt
     s.close(); s2.close(); m16.close()
 
 
-def test_eval_shape_windows_of_256_on_the_69m_model(G, ck, port, tmp_path):
+def test_eval_shape_windows_of_256_on_the_69m_model(G, ck, port, tmp_path, monkeypatch):
     """`grad eval`'s shape: windows of 256 ids in batches of 8 (src/cli/eval.cpp:77,142) on the 69.0M
     modern block. The oracle scores the start of one window; the rest is checked through properties:
     with N(0, 0.02) tied embeddings over unit-RMS hidden rows the logits are near N(0, d * 0.02^2) and
@@ -125,6 +125,13 @@ def test_eval_shape_windows_of_256_on_the_69m_model(G, ck, port, tmp_path):
     _, _, want = port.mean_loss(om, inp[:1, :12], tgt[:1, :12], 8)
     port.free(om)
     np.testing.assert_allclose(lp32[0, :12], want[0], rtol=0, atol=ROW_TOL)
+    # the persistent many-tile GEMM kernel against the one-tile-per-CTA kernel on the same rows
+    monkeypatch.setenv("GRADB_NO_WIDE_GEMM", "1")
+    m16 = G.GPTModel.load(path, 0, G.BF16)
+    s16 = G.BatchSession(m16, 32, 256)
+    lp16_narrow = s16.score(inp, tgt)
+    s16.close(); m16.close()
+    assert float(np.abs(lp16 - lp16_narrow).max()) < 1e-5
     print(f"scored {n * S} ids in {ms:.2f} ms ({n * S / ms * 1e3:.0f} ids/s), mean loss {mean16:.4f}")
 
 
