@@ -40,6 +40,9 @@ constexpr int stages_for(int nw, int tn) {
     return n > 4 ? 4 : (n < 2 ? 2 : n);
 }
 constexpr int kBlockK = 64;  // bf16 elements = one 128-byte swizzle row
+// Warps per TMEM lane quarter in the one-tile-per-CTA kernel's epilogue: the epilogue is a latency chain, so the
+// short decode tiles spread their token columns over four warps per quarter (16 warps), the widest tile over two.
+constexpr int epi_warps_for(int tn) { return tn <= 64 ? 4 : 2; }
 constexpr int kTileM = 128;  // features per MMA
 constexpr uint32_t kSpinLimit = 1u << 20;
 
@@ -124,11 +127,39 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r[8];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
+}
+template <int CW>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[CW]) {
+    if constexpr (CW == 32) tmem_ld32(taddr, v);
+    else if constexpr (CW == 16) tmem_ld16(taddr, v);
+    else tmem_ld8(taddr, v);
+}
 
 // Epilogue of one output tile, run by the four warps that own the TMEM lane quarters: thread t
 // (0..127, t / 32 = the warp's lane quarter) owns feature tile_n * 128 + t; lane_addr is the
 // accumulator's TMEM address with the quarter's lane offset applied. nz = number of K splits.
-template <int EPI, int NW, int TN>
+template <int EPI, int NW, int TN, int CW = 32>
 __device__ __forceinline__ void tc_epilogue(const TcGemmParams& p, uint32_t lane_addr, int t, int tile_n, int tile_b,
                                             int kz, int nz, const int* s_tok, const int* s_pos, const long long* s_off,
                                             int c_begin = 0, int c_end = TN) {
@@ -152,16 +183,16 @@ __device__ __forceinline__ void tc_epilogue(const TcGemmParams& p, uint32_t lane
     float* kv_t = (which == 1 ? p.kcache : p.vcache) + (size_t)h * p.T * p.hs + c_in;
     float* out_t = p.out_f32 + (EPI == TC_QKV ? n_in : n);
     __nv_bfloat16* out16_t = p.out_bf16 + n;
-    for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-        float v[32], v2[32];
-        tmem_ld32(lane_addr + c0, v);
-        if (NW == 2) tmem_ld32(lane_addr + TN + c0, v2);
+    for (int c0 = c_begin; c0 < c_end; c0 += CW) {
+        float v[CW], v2[CW];
+        tmem_ld<CW>(lane_addr + c0, v);
+        if (NW == 2) tmem_ld<CW>(lane_addr + TN + c0, v2);
         // kGroup tokens at a time, in three passes so that independent work is adjacent: every load the
         // group needs (all in flight together), then the arithmetic of all its tokens (one warp per
         // scheduler runs this code, so latency is only hidden by instruction-level parallelism), then the stores.
         constexpr int kGroup = TN >= 128 ? 16 : 8;
 #pragma unroll
-        for (int j0 = 0; j0 < 32; j0 += kGroup) {
+        for (int j0 = 0; j0 < CW; j0 += kGroup) {
             float aux0[kGroup], aux1[kGroup], res[kGroup];
             int posn[kGroup];
             bool live[kGroup];
@@ -226,7 +257,7 @@ __device__ __forceinline__ void tc_epilogue(const TcGemmParams& p, uint32_t lane
 
 // Shared memory: [stage][A tiles (NW x 16 KB) | B tile (TN x 128 B)], 1024-byte aligned.
 template <int EPI, int NW, int TN>
-__global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            const __grid_constant__ CUtensorMap map_b,
                                                            const TcGemmParams p) {
     constexpr int kStages = stages_for(NW, TN);
@@ -287,6 +318,13 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
         }
     }
     pdl_wait();
+    // Activations first: their tiles are what the first MMA waits for; the ids and positions staged
+    // below are only read by the epilogue.
+    if (threadIdx.x == 0) {
+        for (int it = 0; it < pre; it++) {
+            tma_load_2d(smem + (size_t)it * kStageBytes + kABytes, &map_b, (k_beg + it) * kBlockK, tile_b * TN, &full_bar[it]);
+        }
+    }
     for (int c = threadIdx.x; c < TN; c += blockDim.x) {
         const int b = blockIdx.y * TN + c;
         const int tk = b < p.B ? p.tok[b] : kSkip;
@@ -299,10 +337,7 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
     __syncthreads();
 
     if (warp == 0 && lane == 0) {
-        // ---- TMA producer
-        for (int it = 0; it < pre; it++) {
-            tma_load_2d(smem + (size_t)it * kStageBytes + kABytes, &map_b, (k_beg + it) * kBlockK, tile_b * TN, &full_bar[it]);
-        }
+        // ---- TMA producer (the first `pre` stages were requested above)
         for (int it = pre; it < n_iters && ok; it++) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1;
@@ -347,8 +382,14 @@ __global__ void __launch_bounds__(128) gemm_bf16_tc_kernel(const __grid_constant
     if (n_iters > 0) ok = mbar_wait(&accum_bar, 0, p.status, 103);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok && n_iters > 0) {
-        tc_epilogue<EPI, NW, TN>(p, tmem_base + ((uint32_t)(warp * 32) << 16), threadIdx.x, tile_n, tile_b, kz,
-                                 (int)gridDim.z, s_tok, s_pos, s_off);
+        // TMEM lane quarter = warp modulo 4; the quarter's warps split the token columns between them
+        // (one warp per scheduler would leave every latency of this code exposed)
+        constexpr int kEW = epi_warps_for(TN);
+        constexpr int kCols = TN / kEW;  // token columns per warp
+        const int q = warp & 3, part = warp >> 2;
+        tc_epilogue<EPI, NW, TN, (kCols >= 32 ? 32 : kCols)>(p, tmem_base + ((uint32_t)(q * 32) << 16), q * 32 + lane,
+                                                             tile_n, tile_b, kz, (int)gridDim.z, s_tok, s_pos, s_off,
+                                                             part * kCols, (part + 1) * kCols);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -614,7 +655,7 @@ void launch_t(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p,
     if (!g_capturing) {
         GRADB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
-    launch_kernel(kernel, grid, dim3(128), bytes, st, a, b, p);
+    launch_kernel(kernel, grid, dim3(128 * epi_warps_for(TN)), bytes, st, a, b, p);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }
