@@ -42,7 +42,7 @@ constexpr int stages_for(int nw, int tn) {
 constexpr int kBlockK = 64;  // bf16 elements = one 128-byte swizzle row
 // Warps per TMEM lane quarter in the one-tile-per-CTA kernel's epilogue: the epilogue is a latency chain, so the
 // short decode tiles spread their token columns over four warps per quarter (16 warps), the widest tile over two.
-constexpr int epi_warps_for(int tn) { return tn <= 64 ? 4 : 2; }
+constexpr int epi_warps_for(int tn) { return tn <= 64 ? 4 : 2; }  // eight per quarter measured slower
 constexpr int kTileM = 128;  // features per MMA
 constexpr uint32_t kSpinLimit = 1u << 20;
 
@@ -713,6 +713,10 @@ void tc_configure_all() {
 }
 
 int tc_token_tile(int n_seq, int n_tiles, int want_ctas) {
+    if (const char* force = std::getenv("GRADB_TC_TILE")) {  // diagnostic: 32, 64 or 128
+        const int tn = std::atoi(force);
+        if (tn == 32 || tn == 64 || tn == 128) return tn;
+    }
     for (int tn : {128, 64, 32}) {
         if (tn > 32 && tn >= 2 * n_seq) continue;  // do not pad a small batch to a wide tile
         if (n_tiles * ((n_seq + tn - 1) / tn) >= want_ctas || tn == 32) return tn;
