@@ -38,11 +38,11 @@ def gather_ids(local_table, world: int, device=None):
     import torch
     import torch.distributed as dist
 
+    if world == 1:
+        return np.ascontiguousarray(local_table)  # nothing to exchange
     t = torch.from_numpy(np.ascontiguousarray(local_table))
     if device is not None:
         t = t.to(device)
-    if world == 1:
-        return t.cpu().numpy()
     parts = [torch.empty_like(t) for _ in range(world)]
     dist.all_gather(parts, t)
     return torch.cat(parts).cpu().numpy()
