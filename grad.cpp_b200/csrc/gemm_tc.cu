@@ -412,7 +412,98 @@ __global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(c
 //                      loop of tile i+1. The epilogue is arithmetic- and latency-bound, hence eight warps.
 // Tiles are dealt round-robin, feature tile fastest, so CTAs working at the same time share a token tile in L2.
 constexpr int kWideTN = 128;
-constexpr int wide_stages(int nw) { return nw == 1 ? 6 : 4; }  // 192 KB of ring either way
+constexpr int wide_stages(int nw) { return nw == 1 ? 4 : 3; }  // 128 or 144 KB of ring
+constexpr int kWideStageTileBytes = kWideTN * kTileM * 4;      // + one fp32 output tile staged for the row-wise epilogue
+
+// Epilogue pass A of the persistent kernel: accumulator (TMEM, one lane per feature) -> fp32 tile in shared
+// memory laid out [token][feature], with the per-feature work done on the way (bias, GELU, SwiGLU).
+// Thread t = feature, columns [c_begin, c_end). Consecutive lanes write consecutive words: no bank conflicts.
+template <int EPI, int NW>
+__device__ __forceinline__ void wide_epilogue_stage(const TcGemmParams& p, uint32_t lane_addr, int t, int tile_n,
+                                                    float* stg, int c_begin, int c_end) {
+    constexpr int TN = kWideTN;
+    const int n = tile_n * kTileM + t;
+    const bool n_ok = n < p.N;
+    float bias = 0.f;
+    if (EPI == TC_QKV) {
+        const int which = n / p.d;
+        if (n_ok) bias = p.bias[which][n - which * p.d];
+    } else if (EPI == TC_RESID || EPI == TC_GELU) {
+        if (n_ok && p.bias[0]) bias = p.bias[0][n];
+    }
+    for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+        float v[32], v2[32];
+        tmem_ld32(lane_addr + c0, v);
+        if (NW == 2) tmem_ld32(lane_addr + TN + c0, v2);
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            float val = v[j] + bias;
+            if (EPI == TC_GELU) {
+                const float u = 0.79788456f * (val + 0.044715f * val * val * val);
+                val = 0.5f * val * (1.0f + tanhf(u));
+            } else if (EPI == TC_SWIGLU) {
+                const float gte = v[j];
+                val = v2[j] * (gte / (1.0f + __expf(-gte)));
+            }
+            stg[(c0 + j) * kTileM + t] = val;
+        }
+    }
+}
+
+// Epilogue pass B: the staged tile, one token row per warp at a time, four consecutive features per lane:
+// everything that depends on the token (RoPE angle, cache row, residual row) is fetched once per row and the
+// stores are 128-bit and row-contiguous. `we` = epilogue warp 0..7.
+template <int EPI>
+__device__ __forceinline__ void wide_epilogue_rows(const TcGemmParams& p, const float* stg, int we, int lane, int tile_n,
+                                                   int tile_b, const int* s_tok, const int* s_pos,
+                                                   const long long* s_off) {
+    constexpr int TN = kWideTN;
+    const int f = tile_n * kTileM + 4 * lane;  // first of this lane's four features
+    if (f >= p.N) return;                      // N is a multiple of 4 on this path
+    int which = 0, n_in = f;
+    if (EPI == TC_QKV) {
+        which = f / p.d;  // a 128-feature tile lies inside one of Q, K, V (d is a multiple of 128 on this path)
+        n_in = f - which * p.d;
+    }
+    const int h = n_in / p.hs, c_in = n_in % p.hs;
+    const bool rope = EPI == TC_QKV && p.rope_cos != nullptr && which < 2;
+    const int half = p.hs / 2;
+    float* kv_t = (which == 1 ? p.kcache : p.vcache) + (size_t)h * p.T * p.hs + c_in;
+#pragma unroll 8
+    for (int c = we; c < TN; c += 8) {
+        if (s_tok[c] < 0) continue;  // warp-uniform
+        float4 x = *reinterpret_cast<const float4*>(stg + c * kTileM + 4 * lane);
+        const size_t row = (size_t)(tile_b * TN + c) * p.ld_out;
+        if (EPI == TC_QKV) {
+            if (rope) {
+                // pairs (2j, 2j+1) of a head rotate by the angle of index j (inference.cpp:101-115)
+                const int pos = s_pos[c];
+                const float2 cs = __ldg(reinterpret_cast<const float2*>(p.rope_cos + (size_t)pos * half + c_in / 2));
+                const float2 sn = __ldg(reinterpret_cast<const float2*>(p.rope_sin + (size_t)pos * half + c_in / 2));
+                const float a0 = x.x, b0 = x.y, a1 = x.z, b1 = x.w;
+                x.x = a0 * cs.x - b0 * sn.x;
+                x.y = a0 * sn.x + b0 * cs.x;
+                x.z = a1 * cs.y - b1 * sn.y;
+                x.w = a1 * sn.y + b1 * cs.y;
+            }
+            if (which == 0) *reinterpret_cast<float4*>(p.out_f32 + row + n_in) = x;
+            else *reinterpret_cast<float4*>(kv_t + s_off[c]) = x;
+        } else if (EPI == TC_RESID) {
+            float4* y = reinterpret_cast<float4*>(p.out_f32 + row + f);
+            const float4 r = *y;
+            x.x += r.x; x.y += r.y; x.z += r.z; x.w += r.w;
+            *y = x;
+        } else if (EPI == TC_GELU || EPI == TC_SWIGLU) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(p.out_bf16 + row + f) = pk;
+        } else {  // TC_LOGITS
+            *reinterpret_cast<float4*>(p.out_f32 + row + f) = x;
+        }
+    }
+}
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -438,6 +529,7 @@ __global__ void __launch_bounds__(320) gemm_bf16_tc_wide_kernel(const __grid_con
     __shared__ volatile int s_fail;  // set when a bounded wait of an epilogue thread expires
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* stg = reinterpret_cast<float*>(smem + (size_t)kStages * kStageBytes);  // [TN][128] fp32 output tile
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_iters = p.K / kBlockK;
 
@@ -551,11 +643,15 @@ __global__ void __launch_bounds__(320) gemm_bf16_tc_wide_kernel(const __grid_con
             asm volatile("bar.sync 1, 256;" ::: "memory");
             if (s_fail) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            tc_epilogue<EPI, NW, TN>(p, tmem_base + (uint32_t)(buf * kAccCols) + ((uint32_t)(q * 32) << 16), t, tile_n,
-                                     tile_b, 0, 1, s_tok[buf], s_pos[buf], s_off[buf], hf * (TN / 2), (hf + 1) * (TN / 2));
+            wide_epilogue_stage<EPI, NW>(p, tmem_base + (uint32_t)(buf * kAccCols) + ((uint32_t)(q * 32) << 16), t, tile_n,
+                                         stg, hf * (TN / 2), (hf + 1) * (TN / 2));
+            // the accumulator is drained: hand it back before the row pass
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // staged tile complete
+            wide_epilogue_rows<EPI>(p, stg, warp - 2, lane, tile_n, tile_b, s_tok[buf], s_pos[buf], s_off[buf]);
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // staged tile free again
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -728,7 +824,8 @@ namespace {
 template <int EPI, int NW>
 void launch_wide(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, int tiles_n, int tiles_b, int sm_count,
                  cudaStream_t st) {
-    constexpr size_t bytes = (size_t)wide_stages(NW) * (NW * kTileM * kBlockK * 2 + kWideTN * kBlockK * 2) + 1024;
+    constexpr size_t bytes =
+        (size_t)wide_stages(NW) * (NW * kTileM * kBlockK * 2 + kWideTN * kBlockK * 2) + kWideStageTileBytes + 1024;
     auto kernel = gemm_bf16_tc_wide_kernel<EPI, NW>;
     if (!g_capturing) {
         GRADB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
@@ -754,7 +851,9 @@ void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b,
         const char* off = std::getenv("GRADB_NO_WIDE_GEMM");
         const bool wide_off = off && off[0] == '1';
         const int tiles_b = (p.B + kWideTN - 1) / kWideTN;
-        if (!wide_off && n_tiles * tiles_b >= 2 * sm_count) {
+        // the row-wise epilogue works on four features per lane and on tiles that lie inside one of Q, K, V
+        const bool shape_ok = p.N % 4 == 0 && p.ld_out % 4 == 0 && (epi != TC_QKV || (p.d % kTileM == 0 && p.hs % 4 == 0));
+        if (!wide_off && shape_ok && n_tiles * tiles_b >= 2 * sm_count) {
             switch (epi) {
                 case TC_QKV: launch_wide<TC_QKV, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
                 case TC_RESID: launch_wide<TC_RESID, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
