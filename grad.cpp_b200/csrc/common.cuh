@@ -77,6 +77,11 @@ struct LayerWeights {
     // downT: [d][dff].
     __nv_bfloat16 *qkvT = nullptr, *oT = nullptr, *upT = nullptr, *downT = nullptr;
     CUtensorMap map_qkv, map_o, map_up, map_down;
+    // Tensor-core path (FP32 mode): the same transposed matrices as fp32 TF32 hi/lo pairs, [2][rows][in];
+    // the maps cover both halves (the lo half starts `rows` rows down).
+    float *qkvS = nullptr, *oS = nullptr, *upS = nullptr, *downS = nullptr;
+    CUtensorMap map_qkvS, map_oS, map_upS, map_downS;
+    int up_rows = 0;  // rows of one half of upS / upT
 };
 
 struct B1Plan;
@@ -90,12 +95,15 @@ struct DeviceModel {
     __nv_bfloat16* blob16 = nullptr; // bf16 copies of the matrices (BF16 mode)
     const float *emb = nullptr, *pos = nullptr, *fng = nullptr, *fnb = nullptr;
     const __nv_bfloat16* emb16 = nullptr;
+    float* embS = nullptr;  // FP32 mode: embedding table as a TF32 hi/lo pair [2][V][d] (logits GEMM)
     std::vector<LayerWeights> layers;
     float* rope_cos = nullptr;  // [max_len][hs/2], host-computed with the reference's expressions
     float* rope_sin = nullptr;
     int sm_count = 148;
     bool tc_ok = false;   // shapes fit the tensor-core kernels (BF16 mode, d and d_ff multiples of 64)
     CUtensorMap map_emb;  // (V, d) bf16 embedding table = the logits GEMM's A operand
+    bool tc32_ok = false;  // FP32 mode: TF32 hi/lo operands built (d and d_ff multiples of 64)
+    CUtensorMap map_embS;  // (2V, d) fp32 hi/lo embedding table
     B1Plan* b1 = nullptr; // per-CTA weight tiles for the single-sequence persistent kernel
 };
 

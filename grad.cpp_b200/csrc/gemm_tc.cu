@@ -34,8 +34,8 @@ namespace {
 // they push every variant to one CTA per SM and lengthen the prologue of kernels that run for a few microseconds.
 // The widest token tile only occurs with many CTAs per SM's worth of rows (prompt feed, scoring); its ring is
 // sized for two CTAs per SM so that one CTA's epilogue runs under the other's main loop.
-constexpr int stages_for(int nw, int tn) {
-    const int stage = nw * 128 * 64 * 2 + tn * 64 * 2;
+constexpr int stages_for(int nw, int tn, int kind = 0) {
+    const int stage = (nw * 128 * 128 + tn * 128) * (kind == 1 ? 2 : 1);  // 128-byte rows; hi and lo halves in fp32 mode
     const int n = ((tn >= 128 ? 100 : 200) * 1024) / stage;
     return n > 4 ? 4 : (n < 2 ? 2 : n);
 }
@@ -108,6 +108,27 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
         "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
         : "memory");
 }
+// kind::tf32: fp32 bit patterns in shared memory, the low 13 mantissa bits ignored; K = 8 per instruction.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// TF32-rounded value and TF32-rounded remainder: hi + lo carries 21 or more mantissa bits of x.
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+    uint32_t h, l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    hi = __uint_as_float(h);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(x - hi));
+    lo = __uint_as_float(l);
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
@@ -159,7 +180,7 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[CW]) {
 // Epilogue of one output tile, run by the four warps that own the TMEM lane quarters: thread t
 // (0..127, t / 32 = the warp's lane quarter) owns feature tile_n * 128 + t; lane_addr is the
 // accumulator's TMEM address with the quarter's lane offset applied. nz = number of K splits.
-template <int EPI, int NW, int TN, int CW = 32>
+template <int EPI, int NW, int TN, int CW = 32, int KIND = 0>
 __device__ __forceinline__ void tc_epilogue(const TcGemmParams& p, uint32_t lane_addr, int t, int tile_n, int tile_b,
                                             int kz, int nz, const int* s_tok, const int* s_pos, const long long* s_off,
                                             int c_begin = 0, int c_end = TN) {
@@ -246,7 +267,15 @@ __device__ __forceinline__ void tc_epilogue(const TcGemmParams& p, uint32_t lane
                     if (nz == 1) *y = res[jj];
                     else atomicAdd(y, res[jj]);
                 } else if (EPI == TC_GELU || EPI == TC_SWIGLU) {
-                    out16_t[(size_t)b * p.ld_out] = __float2bfloat16_rn(res[jj]);
+                    if (KIND == 1) {
+                        float hi, lo;
+                        split_tf32(res[jj], hi, lo);
+                        float* y = p.out_split + (size_t)b * p.ld_out + n;
+                        y[0] = hi;
+                        y[p.out_lo_elems] = lo;
+                    } else {
+                        out16_t[(size_t)b * p.ld_out] = __float2bfloat16_rn(res[jj]);
+                    }
                 } else {  // TC_LOGITS
                     out_t[(size_t)b * p.ld_out] = res[jj];
                 }
@@ -256,19 +285,24 @@ __device__ __forceinline__ void tc_epilogue(const TcGemmParams& p, uint32_t lane
 }
 
 // Shared memory: [stage][A tiles (NW x 16 KB) | B tile (TN x 128 B)], 1024-byte aligned.
-template <int EPI, int NW, int TN>
+// KIND 1 (fp32 mode): each operand tile comes as a TF32 hi tile and a lo tile (two TMA boxes), K blocks are 32
+// elements (still one 128-byte swizzle row) and every product is three MMAs: lo*hi + hi*lo + hi*hi.
+template <int EPI, int NW, int TN, int KIND = 0>
 __global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            const __grid_constant__ CUtensorMap map_b,
                                                            const TcGemmParams p) {
-    constexpr int kStages = stages_for(NW, TN);
+    constexpr int kStages = stages_for(NW, TN, KIND);
+    constexpr int kParts = KIND == 1 ? 2 : 1;
+    constexpr int kBlockK = KIND == 1 ? 32 : 64;  // elements per 128-byte row (shadows the bf16 constant)
+    constexpr int kATile = kTileM * 128, kBTile = TN * 128;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int s_tok[TN], s_pos[TN];
     __shared__ long long s_off[TN];
 
-    constexpr int kABytes = NW * kTileM * kBlockK * 2;
-    constexpr int kBBytes = TN * kBlockK * 2;
+    constexpr int kABytes = NW * kParts * kATile;
+    constexpr int kBBytes = kParts * kBTile;
     constexpr int kStageBytes = kABytes + kBBytes;
     constexpr int kTmemCols = NW * TN < 32 ? 32 : NW * TN;
     static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two");
@@ -313,7 +347,11 @@ __global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(c
             const int kx = (k_beg + it) * kBlockK;
 #pragma unroll
             for (int w = 0; w < NW; w++) {
-                tma_load_2d(st + w * (kTileM * kBlockK * 2), &map_a, kx, (tile_n * NW + w) * kTileM, &full_bar[it]);
+#pragma unroll
+                for (int part = 0; part < kParts; part++) {
+                    tma_load_2d(st + (w * kParts + part) * kATile, &map_a, kx,
+                                (tile_n * NW + w) * kTileM + part * p.a_lo_rows, &full_bar[it]);
+                }
             }
         }
     }
@@ -322,7 +360,11 @@ __global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(c
     // below are only read by the epilogue.
     if (threadIdx.x == 0) {
         for (int it = 0; it < pre; it++) {
-            tma_load_2d(smem + (size_t)it * kStageBytes + kABytes, &map_b, (k_beg + it) * kBlockK, tile_b * TN, &full_bar[it]);
+#pragma unroll
+            for (int part = 0; part < kParts; part++) {
+                tma_load_2d(smem + (size_t)it * kStageBytes + kABytes + part * kBTile, &map_b, (k_beg + it) * kBlockK,
+                            tile_b * TN + part * p.b_lo_rows, &full_bar[it]);
+            }
         }
     }
     for (int c = threadIdx.x; c < TN; c += blockDim.x) {
@@ -348,13 +390,20 @@ __global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(c
             const int kx = (k_beg + it) * kBlockK;
 #pragma unroll
             for (int w = 0; w < NW; w++) {
-                tma_load_2d(st + w * (kTileM * kBlockK * 2), &map_a, kx, (tile_n * NW + w) * kTileM, &full_bar[s]);
+#pragma unroll
+                for (int part = 0; part < kParts; part++) {
+                    tma_load_2d(st + (w * kParts + part) * kATile, &map_a, kx,
+                                (tile_n * NW + w) * kTileM + part * p.a_lo_rows, &full_bar[s]);
+                }
             }
-            tma_load_2d(st + kABytes, &map_b, kx, tile_b * TN, &full_bar[s]);
+#pragma unroll
+            for (int part = 0; part < kParts; part++) {
+                tma_load_2d(st + kABytes + part * kBTile, &map_b, kx, tile_b * TN + part * p.b_lo_rows, &full_bar[s]);
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer
-        constexpr uint32_t idesc = umma_idesc_bf16(kTileM, TN);
+        constexpr uint32_t idesc = KIND == 1 ? umma_idesc_tf32(kTileM, TN) : umma_idesc_bf16(kTileM, TN);
         for (int it = 0; it < n_iters && ok; it++) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1;
@@ -365,11 +414,23 @@ __global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(c
             const uint64_t bdesc = umma_desc_sw128(st + kABytes);
 #pragma unroll
             for (int w = 0; w < NW; w++) {
-                const uint64_t adesc = umma_desc_sw128(st + w * (kTileM * kBlockK * 2));
+                const uint64_t adesc = umma_desc_sw128(st + w * kParts * kATile);
+                if constexpr (KIND == 0) {
 #pragma unroll
-                for (int k = 0; k < kBlockK / 16; k++) {
-                    // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in the address field
-                    umma_bf16(tmem_base + w * TN, adesc + 2 * k, bdesc + 2 * k, idesc, (it | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < 4; k++) {
+                        // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in the address field
+                        umma_bf16(tmem_base + w * TN, adesc + 2 * k, bdesc + 2 * k, idesc, (it | k) != 0 ? 1u : 0u);
+                    }
+                } else {
+                    const uint64_t adesc_lo = umma_desc_sw128(st + (w * kParts + 1) * kATile);
+                    const uint64_t bdesc_lo = umma_desc_sw128(st + kABytes + kBTile);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        // 8 tf32 = 32 bytes along K; small cross terms first, then the main product
+                        umma_tf32(tmem_base + w * TN, adesc_lo + 2 * k, bdesc + 2 * k, idesc, (it | k) != 0 ? 1u : 0u);
+                        umma_tf32(tmem_base + w * TN, adesc + 2 * k, bdesc_lo + 2 * k, idesc, 1u);
+                        umma_tf32(tmem_base + w * TN, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
+                    }
                 }
             }
             umma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
@@ -387,7 +448,7 @@ __global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(c
         constexpr int kEW = epi_warps_for(TN);
         constexpr int kCols = TN / kEW;  // token columns per warp
         const int q = warp & 3, part = warp >> 2;
-        tc_epilogue<EPI, NW, TN, (kCols >= 32 ? 32 : kCols)>(p, tmem_base + ((uint32_t)(q * 32) << 16), q * 32 + lane,
+        tc_epilogue<EPI, NW, TN, (kCols >= 32 ? 32 : kCols), KIND>(p, tmem_base + ((uint32_t)(q * 32) << 16), q * 32 + lane,
                                                              tile_n, tile_b, kz, (int)gridDim.z, s_tok, s_pos, s_off,
                                                              part * kCols, (part + 1) * kCols);
     }
@@ -665,10 +726,23 @@ __global__ void __launch_bounds__(320) gemm_bf16_tc_wide_kernel(const __grid_con
 
 // fp32 rows -> normalised bf16 rows (LayerNorm or RMSNorm), the tensor-core GEMMs' B operand.
 // One 256-thread CTA per row (a warp-per-row variant with fewer CTAs measured slower).
-__global__ void __launch_bounds__(256) norm_bf16_kernel(const float* __restrict__ X, const float* __restrict__ gamma,
+// SPLIT: the fp32-mode operand instead, every value as a TF32 hi/lo pair (out32[i] and out32[lo_elems + i]).
+template <bool SPLIT>
+__global__ void __launch_bounds__(256) norm_rows_kernel(const float* __restrict__ X, const float* __restrict__ gamma,
                                                         const float* __restrict__ beta, const int* __restrict__ tok,
-                                                        __nv_bfloat16* __restrict__ out, int d, int rms, float eps) {
+                                                        __nv_bfloat16* __restrict__ out, float* __restrict__ out32,
+                                                        size_t lo_elems, int d, int rms, float eps) {
     __shared__ float sh[8];
+    auto put = [&](size_t i, float v) {
+        if (SPLIT) {
+            float hi, lo;
+            split_tf32(v, hi, lo);
+            out32[i] = hi;
+            out32[lo_elems + i] = lo;
+        } else {
+            out[i] = __float2bfloat16_rn(v);
+        }
+    };
     pdl_trigger();
     pdl_wait();
     const int b = blockIdx.x;
@@ -694,7 +768,7 @@ __global__ void __launch_bounds__(256) norm_bf16_kernel(const float* __restrict_
     s = block_sum(s);
     if (rms) {
         const float r = 1.0f / sqrtf(s / (float)d + eps);
-        for (int k = threadIdx.x; k < d; k += 256) out[(size_t)b * d + k] = __float2bfloat16_rn(gamma[k] * xr[k] * r);
+        for (int k = threadIdx.x; k < d; k += 256) put((size_t)b * d + k, gamma[k] * xr[k] * r);
     } else {
         const float mean = s / (float)d;
         float v2 = 0.f;
@@ -705,7 +779,7 @@ __global__ void __launch_bounds__(256) norm_bf16_kernel(const float* __restrict_
         v2 = block_sum(v2);
         const float inv_std = 1.0f / sqrtf(v2 / (float)d + eps);
         for (int k = threadIdx.x; k < d; k += 256) {
-            out[(size_t)b * d + k] = __float2bfloat16_rn(gamma[k] * (xr[k] - mean) * inv_std + beta[k]);
+            put((size_t)b * d + k, gamma[k] * (xr[k] - mean) * inv_std + beta[k]);
         }
     }
 }
@@ -744,10 +818,14 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     return fn;
 }
 
-template <int EPI, int NW, int TN>
+constexpr size_t tc_smem_bytes(int nw, int tn, int kind) {
+    return (size_t)stages_for(nw, tn, kind) * (nw * 128 * 128 + tn * 128) * (kind == 1 ? 2 : 1) + 1024;
+}
+
+template <int EPI, int NW, int TN, int KIND>
 void launch_t(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, dim3 grid, cudaStream_t st) {
-    constexpr size_t bytes = (size_t)stages_for(NW, TN) * (NW * kTileM * kBlockK * 2 + TN * kBlockK * 2) + 1024;
-    auto kernel = gemm_bf16_tc_kernel<EPI, NW, TN>;
+    constexpr size_t bytes = tc_smem_bytes(NW, TN, KIND);
+    auto kernel = gemm_bf16_tc_kernel<EPI, NW, TN, KIND>;
     if (!g_capturing) {
         GRADB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
@@ -757,11 +835,21 @@ void launch_t(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p,
 }
 
 template <int EPI, int NW>
-void launch_tn(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, int tn, dim3 grid, cudaStream_t st) {
+void launch_tn(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, int tn, dim3 grid, cudaStream_t st,
+               int kind) {
+    if (kind == 1) {
+        switch (tn) {
+            case 32: launch_t<EPI, NW, 32, 1>(a, b, p, grid, st); break;
+            case 64: launch_t<EPI, NW, 64, 1>(a, b, p, grid, st); break;
+            case 128: launch_t<EPI, NW, 128, 1>(a, b, p, grid, st); break;
+            default: throw Error(GRADB_ERR_INVALID, "unsupported token tile");
+        }
+        return;
+    }
     switch (tn) {
-        case 32: launch_t<EPI, NW, 32>(a, b, p, grid, st); break;
-        case 64: launch_t<EPI, NW, 64>(a, b, p, grid, st); break;
-        case 128: launch_t<EPI, NW, 128>(a, b, p, grid, st); break;
+        case 32: launch_t<EPI, NW, 32, 0>(a, b, p, grid, st); break;
+        case 64: launch_t<EPI, NW, 64, 0>(a, b, p, grid, st); break;
+        case 128: launch_t<EPI, NW, 128, 0>(a, b, p, grid, st); break;
         default: throw Error(GRADB_ERR_INVALID, "unsupported token tile");
     }
 }
@@ -781,14 +869,28 @@ void make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
     if (r != CUDA_SUCCESS) throw Error(GRADB_ERR_CUDA, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
 }
 
+void make_tensor_map_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    auto fn = encode_fn();
+    if (!fn) throw Error(GRADB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 4};
+    const cuuint32_t box[2] = {32, box_rows};  // 32 floats = one 128-byte swizzle row
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw Error(GRADB_ERR_CUDA, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
+}
+
 // Largest token tile that still yields enough CTAs to occupy most of the SMs: these GEMMs
 // are short, so CTA count (latency hiding across SMs) matters more than MMA width.
 namespace {
 template <int EPI, int NW, int TN>
 void configure_one() {
-    constexpr size_t bytes = (size_t)stages_for(NW, TN) * (NW * kTileM * kBlockK * 2 + TN * kBlockK * 2) + 1024;
-    GRADB_CUDA(cudaFuncSetAttribute(gemm_bf16_tc_kernel<EPI, NW, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)bytes));
+    GRADB_CUDA(cudaFuncSetAttribute(gemm_bf16_tc_kernel<EPI, NW, TN, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)tc_smem_bytes(NW, TN, 0)));
+    GRADB_CUDA(cudaFuncSetAttribute(gemm_bf16_tc_kernel<EPI, NW, TN, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)tc_smem_bytes(NW, TN, 1)));
 }
 template <int EPI, int NW>
 void configure_tiles() {
@@ -838,9 +940,9 @@ void launch_wide(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams&
 }  // namespace
 
 void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int token_tile,
-                    int k_splits, cudaStream_t st) {
+                    int k_splits, cudaStream_t st, int kind) {
     const int n_tiles = (p.N + kTileM - 1) / kTileM;
-    if (token_tile == kWideTN && k_splits == 1) {
+    if (token_tile == kWideTN && k_splits == 1 && kind == 0) {
         // Many tiles per SM: the persistent kernel (the one-tile-per-CTA kernel is for the short decode GEMMs).
         static int sm_count = 0;
         if (!sm_count) {
@@ -866,18 +968,77 @@ void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b,
     }
     const dim3 grid(n_tiles, (p.B + token_tile - 1) / token_tile, k_splits);
     switch (epi) {
-        case TC_QKV: launch_tn<TC_QKV, 1>(map_a, map_b, p, token_tile, grid, st); break;
-        case TC_RESID: launch_tn<TC_RESID, 1>(map_a, map_b, p, token_tile, grid, st); break;
-        case TC_GELU: launch_tn<TC_GELU, 1>(map_a, map_b, p, token_tile, grid, st); break;
-        case TC_SWIGLU: launch_tn<TC_SWIGLU, 2>(map_a, map_b, p, token_tile, grid, st); break;
-        case TC_LOGITS: launch_tn<TC_LOGITS, 1>(map_a, map_b, p, token_tile, grid, st); break;
+        case TC_QKV: launch_tn<TC_QKV, 1>(map_a, map_b, p, token_tile, grid, st, kind); break;
+        case TC_RESID: launch_tn<TC_RESID, 1>(map_a, map_b, p, token_tile, grid, st, kind); break;
+        case TC_GELU: launch_tn<TC_GELU, 1>(map_a, map_b, p, token_tile, grid, st, kind); break;
+        case TC_SWIGLU: launch_tn<TC_SWIGLU, 2>(map_a, map_b, p, token_tile, grid, st, kind); break;
+        case TC_LOGITS: launch_tn<TC_LOGITS, 1>(map_a, map_b, p, token_tile, grid, st, kind); break;
         default: throw Error(GRADB_ERR_INVALID, "unknown epilogue");
     }
 }
 
 void launch_norm_bf16(const float* X, const float* gamma, const float* beta, const int* tok, __nv_bfloat16* out, int d,
                       int rms, float eps, int B, cudaStream_t st) {
-    launch_kernel(norm_bf16_kernel, dim3(B), dim3(256), 0, st, X, gamma, beta, tok, out, d, rms, eps);
+    launch_kernel(norm_rows_kernel<false>, dim3(B), dim3(256), 0, st, X, gamma, beta, tok, out, (float*)nullptr, (size_t)0, d,
+                  rms, eps);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+void launch_norm_split(const float* X, const float* gamma, const float* beta, const int* tok, float* out, size_t lo_elems,
+                       int d, int rms, float eps, int B, cudaStream_t st) {
+    launch_kernel(norm_rows_kernel<true>, dim3(B), dim3(256), 0, st, X, gamma, beta, tok, (__nv_bfloat16*)nullptr, out,
+                  lo_elems, d, rms, eps);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+namespace {
+__global__ void split_tf32_kernel(const float* __restrict__ in, float* __restrict__ out, size_t lo_elems, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float hi, lo;
+    split_tf32(in[i], hi, lo);
+    out[i] = hi;
+    out[lo_elems + i] = lo;
+}
+
+// W (K, N) fp32 row-major -> W^T (rows, K) fp32 as a TF32 hi/lo pair, same row mapping as transpose_bf16_kernel.
+__global__ void transpose_split_kernel(const float* __restrict__ W, float* __restrict__ out, size_t lo_elems, int K, int N,
+                                       int row_offset, int interleave_tiles) {
+    __shared__ float tile[32][33];
+    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int k = k0 + i, n = n0 + threadIdx.x;
+        tile[i][threadIdx.x] = (k < K && n < N) ? W[(size_t)k * N + n] : 0.f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int n = n0 + i, k = k0 + threadIdx.x;
+        if (n < N && k < K) {
+            const size_t row = interleave_tiles ? (size_t)(n / 128) * 256 + row_offset + (n % 128) : (size_t)row_offset + n;
+            float hi, lo;
+            split_tf32(tile[threadIdx.x][i], hi, lo);
+            out[row * K + k] = hi;
+            out[lo_elems + row * K + k] = lo;
+        }
+    }
+}
+}  // namespace
+
+void launch_split_tf32(const float* in, float* out, size_t lo_elems, size_t n, cudaStream_t st) {
+    if (!n) return;
+    launch_kernel(split_tf32_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, in, out, lo_elems, n);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+void launch_transpose_split(const float* W, float* out, size_t lo_elems, int K, int N, int row_offset, bool interleave,
+                            cudaStream_t st) {
+    const dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
+    transpose_split_kernel<<<grid, block, 0, st>>>(W, out, lo_elems, K, N, row_offset, interleave ? 1 : 0);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }

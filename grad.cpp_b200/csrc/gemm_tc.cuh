@@ -20,14 +20,31 @@ struct TcGemmParams {
     __nv_bfloat16* out_bf16;  // FFN activation
     float *kcache, *vcache;
     int* status;  // set non-zero by a kernel whose bounded wait expired
+    // fp32 mode (3xTF32): every operand is stored as two fp32 matrices, the TF32-rounded value and the
+    // TF32-rounded remainder, stacked in one allocation; *_lo_rows is the row distance between the two
+    // halves inside the operand's tensor map. The FFN activation is written the same way.
+    int a_lo_rows = 0, b_lo_rows = 0;
+    float* out_split = nullptr;  // FFN activation: [2][rows][ld_out]
+    size_t out_lo_elems = 0;
 };
 
 // 2-D bf16 tensor map over a row-major (rows, cols) matrix: boxes of 64 columns x box_rows, 128-byte swizzle.
 void make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 int tc_token_tile(int n_seq, int n_tiles, int want_ctas);
 void tc_configure_all();
+// kind 0: bf16 operands; kind 1: fp32 operands as TF32 hi/lo pairs, three MMAs per product (fp32-grade result).
 void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int token_tile,
-                    int k_splits, cudaStream_t st);
+                    int k_splits, cudaStream_t st, int kind = 0);
+// 2-D fp32 tensor map over a row-major (rows, cols) matrix: boxes of 32 columns x box_rows, 128-byte swizzle.
+void make_tensor_map_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+// Normalised rows as TF32 hi/lo pairs: out[0][row][d] and out[1][row][d], the halves lo_elems apart.
+void launch_norm_split(const float* X, const float* gamma, const float* beta, const int* tok, float* out, size_t lo_elems,
+                       int d, int rms, float eps, int B, cudaStream_t st);
+// in[n] -> out[n] (TF32-rounded) and out[lo_elems + n] (TF32-rounded remainder)
+void launch_split_tf32(const float* in, float* out, size_t lo_elems, size_t n, cudaStream_t st);
+// W (K, N) fp32 -> W^T as hi/lo pair [2][rows_total][K], same row mapping as launch_transpose_bf16.
+void launch_transpose_split(const float* W, float* out, size_t lo_elems, int K, int N, int row_offset, bool interleave,
+                            cudaStream_t st);
 void launch_norm_bf16(const float* X, const float* gamma, const float* beta, const int* tok, __nv_bfloat16* out, int d,
                       int rms, float eps, int B, cudaStream_t st);
 void launch_transpose_bf16(const float* W, __nv_bfloat16* out, int K, int N, int row_offset, bool interleave,

@@ -116,6 +116,41 @@ DeviceModel* upload_model(const gradb_model_desc& desc_in, const float* const* t
             }
             make_tensor_map_bf16(&m->map_emb, m->emb16, desc.vocab_size, d, 128);
         }
+        m->tc32_ok = precision == GRADB_FP32 && d % 64 == 0 && desc.d_ff % 64 == 0;
+        if (m->tc32_ok) {
+            // fp32 mode on the tensor cores: every weight as a TF32 hi/lo pair, transposed like the bf16 copies
+            const int f = desc.d_ff;
+            for (int l = 0; l < desc.num_layers; l++) {
+                LayerWeights& w = m->layers[l];
+                const size_t up_rows = modern ? (size_t)((f + 127) / 128) * 256 : (size_t)f;
+                w.up_rows = (int)up_rows;
+                GRADB_CUDA(cudaMalloc(&w.qkvS, (size_t)2 * 3 * d * d * 4));
+                GRADB_CUDA(cudaMalloc(&w.oS, (size_t)2 * d * d * 4));
+                GRADB_CUDA(cudaMalloc(&w.upS, 2 * up_rows * d * 4));
+                GRADB_CUDA(cudaMalloc(&w.downS, (size_t)2 * d * f * 4));
+                GRADB_CUDA(cudaMemset(w.upS, 0, 2 * up_rows * d * 4));
+                const size_t lo_qkv = (size_t)3 * d * d, lo_o = (size_t)d * d, lo_up = up_rows * d, lo_down = (size_t)d * f;
+                launch_transpose_split(w.wq, w.qkvS, lo_qkv, d, d, 0, false, nullptr);
+                launch_transpose_split(w.wk, w.qkvS, lo_qkv, d, d, d, false, nullptr);
+                launch_transpose_split(w.wv, w.qkvS, lo_qkv, d, d, 2 * d, false, nullptr);
+                launch_transpose_split(w.wo, w.oS, lo_o, d, d, 0, false, nullptr);
+                if (modern) {
+                    launch_transpose_split(w.gate, w.upS, lo_up, d, f, 0, true, nullptr);
+                    launch_transpose_split(w.w1, w.upS, lo_up, d, f, 128, true, nullptr);
+                } else {
+                    launch_transpose_split(w.w1, w.upS, lo_up, d, f, 0, false, nullptr);
+                }
+                launch_transpose_split(w.w2, w.downS, lo_down, f, d, 0, false, nullptr);
+                make_tensor_map_f32(&w.map_qkvS, w.qkvS, (uint64_t)2 * 3 * d, d, 128);
+                make_tensor_map_f32(&w.map_oS, w.oS, (uint64_t)2 * d, d, 128);
+                make_tensor_map_f32(&w.map_upS, w.upS, 2 * up_rows, d, 128);
+                make_tensor_map_f32(&w.map_downS, w.downS, (uint64_t)2 * d, f, 128);
+            }
+            const size_t emb_elems = (size_t)desc.vocab_size * d;
+            GRADB_CUDA(cudaMalloc(&m->embS, 2 * emb_elems * 4));
+            launch_split_tf32(m->emb, m->embS, emb_elems, emb_elems, nullptr);
+            make_tensor_map_f32(&m->map_embS, m->embS, (uint64_t)2 * desc.vocab_size, d, 128);
+        }
         if (modern) {
             // RoPE angles, computed with the reference's own float expressions
             // (inference.cpp:169-175) on the host so that cos/sin bits are libm's.
@@ -148,7 +183,9 @@ void free_model(DeviceModel* m) {
     b1_free_plan(m->b1);
     cudaFree(m->blob);
     cudaFree(m->blob16);
+    cudaFree(m->embS);
     for (LayerWeights& w : m->layers) {
+        cudaFree(w.qkvS); cudaFree(w.oS); cudaFree(w.upS); cudaFree(w.downS);
         cudaFree(w.qkvT);
         cudaFree(w.oT);
         cudaFree(w.upT);

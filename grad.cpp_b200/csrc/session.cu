@@ -101,67 +101,81 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
     // Every kernel of the step after the first may begin (its set-up, and for the GEMMs the weight
     // stream) while its predecessor drains; each waits for the predecessor before touching its data.
     PdlScope pdl(s->use_pdl && !s->profiling);
+    // fp32 sessions run the same kernels on TF32 hi/lo operand pairs (three MMAs per product)
+    const bool s32 = s->use_tc32;
+    const int kind = s32 ? 1 : 0;
+    const size_t lo_d = (size_t)s->split_rows * d, lo_f = (size_t)s->split_rows * f;
+    auto norm_rows = [&](const float* g, const float* b, const int* tk) {
+        if (s32) launch_norm_split(s->x, g, b, tk, s->hS, lo_d, d, modern, 1e-5f, n_seq, st);
+        else launch_norm_bf16(s->x, g, b, tk, s->h16, d, modern, 1e-5f, n_seq, st);
+    };
     TcGemmParams base{};
     base.B = n_seq; base.d = d; base.H = s->H; base.hs = s->hs; base.T = s->T;
     base.tok = tok_dev; base.pos = s->pos; base.status = s->status;
+    base.b_lo_rows = s->split_rows;
     for (int l = 0; l < s->L; l++) {
         const LayerWeights& w = m->layers[l];
         float* kc = s->kcache + (size_t)l * layer_cache_elems(s);
         float* vc = s->vcache + (size_t)l * layer_cache_elems(s);
         {
             Timed t(s, KC_QKV);
-            launch_norm_bf16(s->x, w.n1g, w.n1b, tok_dev, s->h16, d, modern, 1e-5f, n_seq, st);
+            norm_rows(w.n1g, w.n1b, tok_dev);
             TcGemmParams g = base;
-            g.K = d; g.N = 3 * d; g.ld_out = d;
+            g.K = d; g.N = 3 * d; g.ld_out = d; g.a_lo_rows = 3 * d;
             g.bias[0] = w.bq; g.bias[1] = w.bk; g.bias[2] = w.bv;
             g.rope_cos = modern ? m->rope_cos : nullptr;
             g.rope_sin = modern ? m->rope_sin : nullptr;
             g.out_f32 = s->q; g.kcache = kc; g.vcache = vc;
             const int tn = tile_for(3 * d);
-            launch_tc_gemm(TC_QKV, w.map_qkv, s->map_h16[map_idx(tn)], g, tn, 1, st);
+            launch_tc_gemm(TC_QKV, s32 ? w.map_qkvS : w.map_qkv, s->map_h16[map_idx(tn)], g, tn, 1, st, kind);
         }
         {
             Timed t(s, KC_ATTN);
             AttnParams a{};
             a.q = s->q; a.kcache = kc; a.vcache = vc; a.tok = tok_dev; a.pos = s->pos;
-            a.out = s->attn; a.out16 = s->attn16; a.partial = s->attn_partial; a.counters = s->attn_counters;
+            a.out = s->attn; a.out16 = s32 ? nullptr : s->attn16; a.partial = s->attn_partial; a.counters = s->attn_counters;
             a.status = s->status;
             a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = d;
             a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
             launch_attention(a, n_seq, s->attn_splits, st);
+            if (s32) launch_split_tf32(s->attn, s->attnS, lo_d, (size_t)n_seq * d, st);
         }
         {
             Timed t(s, KC_OPROJ);
             TcGemmParams g = base;
-            g.K = d; g.N = d; g.ld_out = d; g.bias[0] = w.bo; g.out_f32 = s->x;
+            g.K = d; g.N = d; g.ld_out = d; g.bias[0] = w.bo; g.out_f32 = s->x; g.a_lo_rows = d;
             const int tn = tile_for(d);
-            launch_tc_gemm(TC_RESID, w.map_o, s->map_attn16[map_idx(tn)], g, tn, splits(d, tn, d / 64), st);
+            launch_tc_gemm(TC_RESID, s32 ? w.map_oS : w.map_o, s->map_attn16[map_idx(tn)], g, tn,
+                           splits(d, tn, d / (s32 ? 32 : 64)), st, kind);
         }
         {
             Timed t(s, KC_FFN_UP);
-            launch_norm_bf16(s->x, w.n2g, w.n2b, tok_dev, s->h16, d, modern, 1e-5f, n_seq, st);
+            norm_rows(w.n2g, w.n2b, tok_dev);
             TcGemmParams g = base;
-            g.K = d; g.N = f; g.ld_out = f; g.out_bf16 = s->ffn16;
+            g.K = d; g.N = f; g.ld_out = f; g.out_bf16 = s->ffn16; g.out_split = s->ffnS; g.out_lo_elems = lo_f;
+            g.a_lo_rows = w.up_rows;
             g.bias[0] = modern ? nullptr : w.b1;
             const int tn = tile_for(f);
-            launch_tc_gemm(modern ? TC_SWIGLU : TC_GELU, w.map_up, s->map_h16[map_idx(tn)], g, tn, 1, st);
+            launch_tc_gemm(modern ? TC_SWIGLU : TC_GELU, s32 ? w.map_upS : w.map_up, s->map_h16[map_idx(tn)], g, tn, 1, st,
+                           kind);
         }
         {
             Timed t(s, KC_FFN_DOWN);
             TcGemmParams g = base;
-            g.K = f; g.N = d; g.ld_out = d; g.bias[0] = modern ? nullptr : w.b2; g.out_f32 = s->x;
+            g.K = f; g.N = d; g.ld_out = d; g.bias[0] = modern ? nullptr : w.b2; g.out_f32 = s->x; g.a_lo_rows = d;
             const int tn = tile_for(d);
-            launch_tc_gemm(TC_RESID, w.map_down, s->map_ffn16[map_idx(tn)], g, tn, splits(d, tn, f / 64), st);
+            launch_tc_gemm(TC_RESID, s32 ? w.map_downS : w.map_down, s->map_ffn16[map_idx(tn)], g, tn,
+                           splits(d, tn, f / (s32 ? 32 : 64)), st, kind);
         }
     }
     {
         Timed t(s, KC_LOGITS);
-        launch_norm_bf16(s->x, m->fng, m->fnb, logit_tok_dev, s->h16, d, modern, 1e-5f, n_seq, st);
+        norm_rows(m->fng, m->fnb, logit_tok_dev);
         TcGemmParams g = base;
         g.tok = logit_tok_dev;
-        g.K = d; g.N = s->V; g.ld_out = s->V; g.out_f32 = s->logits;
+        g.K = d; g.N = s->V; g.ld_out = s->V; g.out_f32 = s->logits; g.a_lo_rows = s->V;
         const int tn = tile_for(s->V);
-        launch_tc_gemm(TC_LOGITS, m->map_emb, s->map_h16[map_idx(tn)], g, tn, 1, st);
+        launch_tc_gemm(TC_LOGITS, s32 ? m->map_embS : m->map_emb, s->map_h16[map_idx(tn)], g, tn, 1, st, kind);
     }
     Timed t(s, KC_ADVANCE);
     launch_advance(tok_dev, s->pos, append_history ? s->hist : nullptr, s->hist_len, s->hist_stride, n_seq, st);
@@ -209,7 +223,7 @@ void enqueue_step(Session* s, int n_seq, const int* tok_dev, const int* logit_to
         enqueue_step_b1(s, tok_dev, logit_tok_dev, append_history);
         return;
     }
-    if (s->use_tc && n_seq >= 16) {
+    if ((s->use_tc || s->use_tc32) && n_seq >= 16) {
         enqueue_step_tc(s, n_seq, tok_dev, logit_tok_dev, append_history);
         return;
     }
@@ -699,6 +713,25 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         s->use_tc = m->tc_ok && s->B >= 16 && !(ntc && ntc[0] == '1');
         if (s->hs == 64) attention_configure();
         configure_select(s->V);
+        const char* ntc32 = std::getenv("GRADB_NO_TC32");
+        s->use_tc32 = m->tc32_ok && s->B >= 16 && !(ntc && ntc[0] == '1') && !(ntc32 && ntc32[0] == '1');
+        if (s->use_tc32) {
+            tc_configure_all();
+            const size_t rows = (size_t)((s->B + 127) / 128) * 128;
+            s->split_rows = (int)rows;
+            dalloc(&s->hS, 2 * rows * s->d);
+            dalloc(&s->attnS, 2 * rows * s->d);
+            dalloc(&s->ffnS, 2 * rows * s->dff);
+            GRADB_CUDA(cudaMemsetAsync(s->hS, 0, 2 * rows * s->d * 4, s->stream));
+            GRADB_CUDA(cudaMemsetAsync(s->attnS, 0, 2 * rows * s->d * 4, s->stream));
+            GRADB_CUDA(cudaMemsetAsync(s->ffnS, 0, 2 * rows * s->dff * 4, s->stream));
+            for (int i = 0; i < 3; i++) {
+                const uint32_t tn = 32u << i;
+                make_tensor_map_f32(&s->map_h16[i], s->hS, 2 * rows, s->d, tn);
+                make_tensor_map_f32(&s->map_attn16[i], s->attnS, 2 * rows, s->d, tn);
+                make_tensor_map_f32(&s->map_ffn16[i], s->ffnS, 2 * rows, s->dff, tn);
+            }
+        }
         if (s->use_tc) {
             tc_configure_all();
             // rows padded to a whole 128-row tile so a TMA box never starts outside the buffer
@@ -757,6 +790,7 @@ void destroy_session(Session* s) {
     cudaFree(s->feed.tiles); cudaFree(s->feed.score_logits); cudaFree(s->feed.row_tgt); cudaFree(s->feed.row_dst);
     cudaFree(s->score_out); cudaFree(s->score_tgt);
     cudaFree(s->h16); cudaFree(s->attn16); cudaFree(s->ffn16); cudaFree(s->status);
+    cudaFree(s->hS); cudaFree(s->attnS); cudaFree(s->ffnS);
     if (s->h_stage) cudaFreeHost(s->h_stage);
     if (s->own_stream && s->stream) cudaStreamDestroy(s->stream);
     delete s;

@@ -41,6 +41,11 @@ struct Session {
     bool use_pdl = true;  // programmatic dependent launch between the kernels of a tensor-core step
     __nv_bfloat16 *h16 = nullptr, *attn16 = nullptr, *ffn16 = nullptr;
     CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];  // token tiles of 32, 64, 128 rows
+    // fp32 mode on the tensor cores: the same operands as TF32 hi/lo pairs [2][rows][width]; the maps of h16 /
+    // attn16 / ffn16 above then describe these buffers.
+    bool use_tc32 = false;
+    float *hS = nullptr, *attnS = nullptr, *ffnS = nullptr;
+    int split_rows = 0;  // rows of one half
     int* status = nullptr;
 
     // batched prompt feed (one row per prompt token, all positions of a chunk at once)

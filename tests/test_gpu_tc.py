@@ -144,3 +144,39 @@ def test_benchmark_shape_greedy_agreement_with_fp32(G, ck, tmp_path):
     print(f"bf16 vs fp32: logits max-abs/max {err:.3e}, mean KL {kl:.3e}, first-id agreement {first:.3f}, "
           f"16-id greedy agreement {agree:.3f}")
     assert err < 5e-2 and kl < 1e-3 and first > 0.9
+
+
+@pytest.mark.parametrize("name,n_seq", [("hs64_modern", 20), ("hs64_gpt2", 40), ("odd_modern", 17)])
+def test_fp32_mode_on_tensor_cores_keeps_fp32_parity(name, n_seq, G, golden_ckpt, port, monkeypatch):
+    """fp32 sessions with >= 16 sequences run the projections as three TF32 MMAs per product (hi/lo operand
+    pairs, fp32 accumulation). Bars are those of fp32 mode: logits within 1e-4 of the oracle (max-abs over
+    max-abs), identical greedy ids, K/V rows within 1e-5."""
+    dm, path = golden_ckpt(name)
+    rng = np.random.default_rng(25)
+    lens = rng.integers(1, dm.max_len // 2, n_seq)
+    prompts = [rng.integers(0, dm.vocab, int(n)).astype(np.int32) for n in lens]
+    m = G.GPTModel.load(path, 0, G.FP32)
+    s = G.BatchSession(m, n_seq)
+    got = s.prefill(prompts)
+    om = port.load(path)
+    worst = max(rel_err(got[i], port.logits_for(om, prompts[i])[-1]) for i in range(n_seq))
+    assert worst < 1e-4, worst
+    osess = port.session(om)
+    for t in prompts[2]:
+        port.step(osess, int(t), dm.vocab)
+    for which in (0, 1):
+        gotr = s.cache_row(2, dm.layers - 1, which, len(prompts[2]) - 1)
+        wantr = port.cache_row(osess, dm.layers - 1, which, len(prompts[2]) - 1, dm.d_model)
+        assert np.abs(gotr - wantr).max() < 1e-5 * max(np.abs(wantr).max(), 1.0)
+    port.session_free(osess)
+    sp = G.Sampling(1, 1.0, 1.2, 0, 1.0)
+    n_new = dm.max_len // 2
+    ids = s.generate(prompts, sp, n_new)
+    for i in (0, n_seq // 2, n_seq - 1):
+        assert list(ids[i]) == list(port.generate(om, prompts[i], n_new, greedy=True, penalty=1.2)), i
+    # and against the streaming fp32 kernels on the same session shape
+    monkeypatch.setenv("GRADB_NO_TC32", "1")
+    s2 = G.BatchSession(m, n_seq)
+    assert rel_err(got, s2.prefill(prompts)) < 2e-5
+    port.free(om)
+    s.close(); s2.close(); m.close()
