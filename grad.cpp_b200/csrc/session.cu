@@ -414,9 +414,15 @@ void ensure_feed_buffers(Session* s) {
     dalloc(&f.x, R * s->d);
     dalloc(&f.q, R * s->d);
     dalloc(&f.attn, R * s->d);
-    dalloc(&f.h16, R * s->d);
-    dalloc(&f.attn16, R * s->d);
-    dalloc(&f.ffn16, R * s->dff);
+    if (s->use_tc32) {
+        dalloc(&f.hS, 2 * R * s->d);
+        dalloc(&f.attnS, 2 * R * s->d);
+        dalloc(&f.ffnS, 2 * R * s->dff);
+    } else {
+        dalloc(&f.h16, R * s->d);
+        dalloc(&f.attn16, R * s->d);
+        dalloc(&f.ffn16, R * s->dff);
+    }
     dalloc(&f.row_tok, R);
     dalloc(&f.row_pos, R);
     dalloc(&f.row_seq, R);
@@ -427,9 +433,15 @@ void ensure_feed_buffers(Session* s) {
     prefill_attention_configure();
     for (int i = 0; i < 3; i++) {
         const uint32_t tn = 32u << i;
-        make_tensor_map_bf16(&f.map_h16[i], f.h16, R, s->d, tn);
-        make_tensor_map_bf16(&f.map_attn16[i], f.attn16, R, s->d, tn);
-        make_tensor_map_bf16(&f.map_ffn16[i], f.ffn16, R, s->dff, tn);
+        if (s->use_tc32) {
+            make_tensor_map_f32(&f.map_h16[i], f.hS, 2 * R, s->d, tn);
+            make_tensor_map_f32(&f.map_attn16[i], f.attnS, 2 * R, s->d, tn);
+            make_tensor_map_f32(&f.map_ffn16[i], f.ffnS, 2 * R, s->dff, tn);
+        } else {
+            make_tensor_map_bf16(&f.map_h16[i], f.h16, R, s->d, tn);
+            make_tensor_map_bf16(&f.map_attn16[i], f.attn16, R, s->d, tn);
+            make_tensor_map_bf16(&f.map_ffn16[i], f.ffn16, R, s->dff, tn);
+        }
     }
     f.cap = (int)R;
 }
@@ -465,7 +477,16 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
     const int want = m->sm_count * 3 / 4;
     auto map_idx = [](int tn) { return tn == 32 ? 0 : (tn == 64 ? 1 : 2); };
     const char* no_tiled = std::getenv("GRADB_NO_TILED_ATTN");
-    const bool tiled_ok = !(no_tiled && no_tiled[0] == '1');
+    // fp32 sessions: TF32 hi/lo operands (three MMAs per product) and the fp32 per-position attention kernel;
+    // the query-tiled attention kernel rounds its operands to TF32 and is for the bf16 mode only.
+    const bool s32 = s->use_tc32;
+    const int kind = s32 ? 1 : 0;
+    const bool tiled_ok = !s32 && !(no_tiled && no_tiled[0] == '1');
+    const size_t lo_d = (size_t)f.cap * d, lo_f = (size_t)f.cap * ff;
+    auto norm_rows = [&](const float* x, const float* g, const float* b, const int* tk, int rows) {
+        if (s32) launch_norm_split(x, g, b, tk, f.hS, lo_d, d, modern, 1e-5f, rows, st);
+        else launch_norm_bf16(x, g, b, tk, f.h16, d, modern, 1e-5f, rows, st);
+    };
 
     // per-sequence logits mask: id of the last prompt token, or skip
     f.h_rows.resize((size_t)4 * f.cap + 2 * (size_t)s->B);
@@ -535,21 +556,22 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
         TcGemmParams base{};
         base.B = R; base.d = d; base.H = s->H; base.hs = s->hs; base.T = s->T;
         base.tok = f.row_tok; base.pos = f.row_pos; base.row_seq = f.row_seq; base.status = s->status;
+        base.b_lo_rows = f.cap;
         for (int l = 0; l < s->L; l++) {
             const LayerWeights& w = m->layers[l];
             float* kc = s->kcache + (size_t)l * layer_cache_elems(s);
             float* vc = s->vcache + (size_t)l * layer_cache_elems(s);
             {
                 Timed t(s, KC_QKV);
-                launch_norm_bf16(f.x, w.n1g, w.n1b, f.row_tok, f.h16, d, modern, 1e-5f, R, st);
+                norm_rows(f.x, w.n1g, w.n1b, f.row_tok, R);
                 TcGemmParams g = base;
-                g.K = d; g.N = 3 * d; g.ld_out = d;
+                g.K = d; g.N = 3 * d; g.ld_out = d; g.a_lo_rows = 3 * d;
                 g.bias[0] = w.bq; g.bias[1] = w.bk; g.bias[2] = w.bv;
                 g.rope_cos = modern ? m->rope_cos : nullptr;
                 g.rope_sin = modern ? m->rope_sin : nullptr;
                 g.out_f32 = f.q; g.kcache = kc; g.vcache = vc;
                 const int tn = tile_for(3 * d);
-                launch_tc_gemm(TC_QKV, w.map_qkv, f.map_h16[map_idx(tn)], g, tn, 1, st);
+                launch_tc_gemm(TC_QKV, s32 ? w.map_qkvS : w.map_qkv, f.map_h16[map_idx(tn)], g, tn, 1, st, kind);
             }
             {
                 Timed t(s, KC_ATTN);
@@ -563,44 +585,48 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
                 } else {
                     AttnParams a{};
                     a.q = f.q; a.kcache = kc; a.vcache = vc; a.tok = f.row_tok; a.pos = f.row_pos; a.row_seq = f.row_seq;
-                    a.out = f.attn; a.out16 = f.attn16; a.partial = nullptr; a.counters = nullptr; a.status = s->status;
+                    a.out = f.attn; a.out16 = s32 ? nullptr : f.attn16; a.partial = nullptr; a.counters = nullptr;
+                    a.status = s->status;
                     a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = d;
                     a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
                     launch_attention(a, R, 1, st);
+                    if (s32) launch_split_tf32(f.attn, f.attnS, lo_d, (size_t)R * d, st);
                 }
             }
             {
                 Timed t(s, KC_OPROJ);
                 TcGemmParams g = base;
-                g.K = d; g.N = d; g.ld_out = d; g.bias[0] = w.bo; g.out_f32 = f.x;
+                g.K = d; g.N = d; g.ld_out = d; g.bias[0] = w.bo; g.out_f32 = f.x; g.a_lo_rows = d;
                 const int tn = tile_for(d);
-                launch_tc_gemm(TC_RESID, w.map_o, f.map_attn16[map_idx(tn)], g, tn, 1, st);
+                launch_tc_gemm(TC_RESID, s32 ? w.map_oS : w.map_o, f.map_attn16[map_idx(tn)], g, tn, 1, st, kind);
             }
             {
                 Timed t(s, KC_FFN_UP);
-                launch_norm_bf16(f.x, w.n2g, w.n2b, f.row_tok, f.h16, d, modern, 1e-5f, R, st);
+                norm_rows(f.x, w.n2g, w.n2b, f.row_tok, R);
                 TcGemmParams g = base;
-                g.K = d; g.N = ff; g.ld_out = ff; g.out_bf16 = f.ffn16;
+                g.K = d; g.N = ff; g.ld_out = ff; g.out_bf16 = f.ffn16; g.out_split = f.ffnS; g.out_lo_elems = lo_f;
+                g.a_lo_rows = w.up_rows;
                 g.bias[0] = modern ? nullptr : w.b1;
                 const int tn = tile_for(ff);
-                launch_tc_gemm(modern ? TC_SWIGLU : TC_GELU, w.map_up, f.map_h16[map_idx(tn)], g, tn, 1, st);
+                launch_tc_gemm(modern ? TC_SWIGLU : TC_GELU, s32 ? w.map_upS : w.map_up, f.map_h16[map_idx(tn)], g, tn, 1,
+                               st, kind);
             }
             {
                 Timed t(s, KC_FFN_DOWN);
                 TcGemmParams g = base;
-                g.K = ff; g.N = d; g.ld_out = d; g.bias[0] = modern ? nullptr : w.b2; g.out_f32 = f.x;
+                g.K = ff; g.N = d; g.ld_out = d; g.bias[0] = modern ? nullptr : w.b2; g.out_f32 = f.x; g.a_lo_rows = d;
                 const int tn = tile_for(d);
-                launch_tc_gemm(TC_RESID, w.map_down, f.map_ffn16[map_idx(tn)], g, tn, 1, st);
+                launch_tc_gemm(TC_RESID, s32 ? w.map_downS : w.map_down, f.map_ffn16[map_idx(tn)], g, tn, 1, st, kind);
             }
         }
         if (score_targets) {
             // every row's logits (final norm + tied-embedding GEMM), then the target's log-probability
             Timed t(s, KC_SCORE);
-            launch_norm_bf16(f.x, m->fng, m->fnb, f.row_tok, f.h16, d, modern, 1e-5f, R, st);
+            norm_rows(f.x, m->fng, m->fnb, f.row_tok, R);
             TcGemmParams g = base;
-            g.K = d; g.N = s->V; g.ld_out = s->V; g.out_f32 = f.score_logits;
+            g.K = d; g.N = s->V; g.ld_out = s->V; g.out_f32 = f.score_logits; g.a_lo_rows = s->V;
             const int tn = tile_for(s->V);
-            launch_tc_gemm(TC_LOGITS, m->map_emb, f.map_h16[map_idx(tn)], g, tn, 1, st);
+            launch_tc_gemm(TC_LOGITS, s32 ? m->map_embS : m->map_emb, f.map_h16[map_idx(tn)], g, tn, 1, st, kind);
             launch_row_logp(f.score_logits, (size_t)s->V, s->V, f.row_tgt, f.row_dst, 0, 0, score_out, R, st);
         }
         launch_gather_last_rows(f.x, f.row_last, f.row_seq, s->x, d, R, st);
@@ -612,19 +638,21 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
     // last-position logits: final norm + tied-embedding GEMM over the per-sequence rows
     {
         Timed t(s, KC_LOGITS);
-        launch_norm_bf16(s->x, m->fng, m->fnb, f.last_tok, s->h16, d, modern, 1e-5f, n_seq, st);
+        if (s32) launch_norm_split(s->x, m->fng, m->fnb, f.last_tok, s->hS, (size_t)s->split_rows * d, d, modern, 1e-5f, n_seq, st);
+        else launch_norm_bf16(s->x, m->fng, m->fnb, f.last_tok, s->h16, d, modern, 1e-5f, n_seq, st);
         TcGemmParams g{};
         g.B = n_seq; g.d = d; g.H = s->H; g.hs = s->hs; g.T = s->T;
         g.tok = f.last_tok; g.pos = s->pos; g.status = s->status;
         g.K = d; g.N = s->V; g.ld_out = s->V; g.out_f32 = s->logits;
+        g.a_lo_rows = s->V; g.b_lo_rows = s->split_rows;
         const int tn = tc_token_tile(n_seq, (s->V + 127) / 128, want);
-        launch_tc_gemm(TC_LOGITS, m->map_emb, s->map_h16[map_idx(tn)], g, tn, 1, st);
+        launch_tc_gemm(TC_LOGITS, s32 ? m->map_embS : m->map_emb, s->map_h16[map_idx(tn)], g, tn, 1, st, kind);
     }
 }
 
 bool batched_feed_available(const Session* s) {
     const char* off = std::getenv("GRADB_NO_BATCHED_FEED");
-    return s->use_tc && s->hs == 64 && !(off && off[0] == '1');
+    return (s->use_tc || s->use_tc32) && s->hs == 64 && !(off && off[0] == '1');
 }
 
 // Generation keeps a small group of sequences on one family of kernels for the prompt and the
@@ -784,6 +812,7 @@ void destroy_session(Session* s) {
     cudaFree(s->gen); cudaFree(s->done); cudaFree(s->out_tok); cudaFree(s->tok_matrix);
     cudaFree(s->uniforms); cudaFree(s->probs);
     cudaFree(s->b1_ws); cudaFree(s->b1_bar); cudaFree(s->b1_trace);
+    cudaFree(s->feed.hS); cudaFree(s->feed.attnS); cudaFree(s->feed.ffnS);
     cudaFree(s->feed.x); cudaFree(s->feed.q); cudaFree(s->feed.attn); cudaFree(s->feed.h16); cudaFree(s->feed.attn16);
     cudaFree(s->feed.ffn16); cudaFree(s->feed.row_tok); cudaFree(s->feed.row_pos); cudaFree(s->feed.row_seq);
     cudaFree(s->feed.row_last); cudaFree(s->feed.seq_count); cudaFree(s->feed.last_tok);

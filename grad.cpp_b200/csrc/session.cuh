@@ -53,6 +53,7 @@ struct Session {
         int cap = 0;  // rows per chunk
         float *x = nullptr, *q = nullptr, *attn = nullptr;
         __nv_bfloat16 *h16 = nullptr, *attn16 = nullptr, *ffn16 = nullptr;
+        float *hS = nullptr, *attnS = nullptr, *ffnS = nullptr;  // fp32 sessions: TF32 hi/lo pairs [2][cap][width]
         int *row_tok = nullptr, *row_pos = nullptr, *row_seq = nullptr, *row_last = nullptr, *seq_count = nullptr,
             *last_tok = nullptr;
         CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];
