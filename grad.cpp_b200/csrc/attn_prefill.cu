@@ -6,8 +6,10 @@
 // Same arithmetic as the reference's cached attention (src/transformer/inference.cpp:208-225 with
 // softmax_row :60-67): s[t] = q . K[t] / sqrt(64) over t <= position, softmax, out = sum s[t] V[t],
 // evaluated flash-style (running maximum and sum, rescaled accumulator). Products run on the tensor
-// cores in TF32 with fp32 accumulation (mma.sync m16n8k8), which is within the error budget of the
-// bf16-weight mode this kernel serves; the fp32 mode never takes this path.
+// cores in TF32 with fp32 accumulation (mma.sync m16n8k8). The plain variant (one MMA per product) is within
+// the error budget of the bf16-weight mode; the X3 variant, used by fp32 sessions, splits every operand into a
+// TF32-rounded value and its TF32-rounded remainder and issues three MMAs per product (lo*hi + hi*lo + hi*hi),
+// which carries fp32-grade accuracy through both products.
 //
 // One CTA = one (query tile, head): 4 warps x 16 queries. K and V tiles of 64 positions are
 // contiguous in the head-major cache and are staged in shared memory by cp.async, double buffered,
@@ -60,6 +62,12 @@ __device__ __forceinline__ void load_tiles(float* stage, const float* kbase, con
     }
 }
 
+__device__ __forceinline__ void split2(float x, uint32_t& hi, uint32_t& lo) {
+    hi = to_tf32(x);
+    lo = to_tf32(x - __uint_as_float(hi));
+}
+
+template <bool X3>
 __global__ void __launch_bounds__(128) attn_prefill64_kernel(const PrefillAttnParams p) {
     extern __shared__ __align__(16) float smem[];
     pdl_wait();
@@ -78,17 +86,26 @@ __global__ void __launch_bounds__(128) attn_prefill64_kernel(const PrefillAttnPa
 
     // This warp's 16 queries as A fragments (rows g and g+8 of the warp's block), scaled, in TF32.
     const int q_lo = warp * 16 + g, q_hi = q_lo + 8;
-    uint32_t qa[8][4];
+    uint32_t qa[8][4], ql[X3 ? 8 : 1][4];
     {
         const float* qr_lo = p.q + (size_t)(row0 + q_lo) * p.d + h * 64;
         const float* qr_hi = p.q + (size_t)(row0 + q_hi) * p.d + h * 64;
         const bool ok_lo = q_lo < nq, ok_hi = q_hi < nq;
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
-            qa[ks][0] = to_tf32(ok_lo ? qr_lo[ks * 8 + t] * p.scale : 0.f);
-            qa[ks][1] = to_tf32(ok_hi ? qr_hi[ks * 8 + t] * p.scale : 0.f);
-            qa[ks][2] = to_tf32(ok_lo ? qr_lo[ks * 8 + t + 4] * p.scale : 0.f);
-            qa[ks][3] = to_tf32(ok_hi ? qr_hi[ks * 8 + t + 4] * p.scale : 0.f);
+            const float q0 = ok_lo ? qr_lo[ks * 8 + t] * p.scale : 0.f, q1 = ok_hi ? qr_hi[ks * 8 + t] * p.scale : 0.f;
+            const float q2 = ok_lo ? qr_lo[ks * 8 + t + 4] * p.scale : 0.f, q3 = ok_hi ? qr_hi[ks * 8 + t + 4] * p.scale : 0.f;
+            if constexpr (X3) {
+                split2(q0, qa[ks][0], ql[ks][0]);
+                split2(q1, qa[ks][1], ql[ks][1]);
+                split2(q2, qa[ks][2], ql[ks][2]);
+                split2(q3, qa[ks][3], ql[ks][3]);
+            } else {
+                qa[ks][0] = to_tf32(q0);
+                qa[ks][1] = to_tf32(q1);
+                qa[ks][2] = to_tf32(q2);
+                qa[ks][3] = to_tf32(q3);
+            }
         }
     }
     const int qpos_lo = pos0 + q_lo, qpos_hi = pos0 + q_hi;
@@ -121,7 +138,16 @@ __global__ void __launch_bounds__(128) attn_prefill64_kernel(const PrefillAttnPa
 #pragma unroll
                 for (int nt = 0; nt < 8; nt++) {
                     const float* kr = Ks + (nt * 8 + g) * kLd + ks * 8 + t;
-                    mma_tf32(s[nt], qa[ks], __float_as_uint(kr[0]), __float_as_uint(kr[4]));
+                    if constexpr (X3) {
+                        uint32_t h0, l0, h1, l1;
+                        split2(kr[0], h0, l0);
+                        split2(kr[4], h1, l1);
+                        mma_tf32(s[nt], ql[ks], h0, h1);
+                        mma_tf32(s[nt], qa[ks], l0, l1);
+                        mma_tf32(s[nt], qa[ks], h0, h1);
+                    } else {
+                        mma_tf32(s[nt], qa[ks], __float_as_uint(kr[0]), __float_as_uint(kr[4]));
+                    }
                 }
             }
             // causal mask: position k0 + nt*8 + 2t (+1) against the query's own position
@@ -169,11 +195,31 @@ __global__ void __launch_bounds__(128) attn_prefill64_kernel(const PrefillAttnPa
             // an A fragment its k index t stands for key 2t and t+4 for key 2t+1, so V rows are fetched to match.
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {
-                const uint32_t pa[4] = {to_tf32(s[ks][0]), to_tf32(s[ks][2]), to_tf32(s[ks][1]), to_tf32(s[ks][3])};
+                uint32_t pa[4], pl[4];
+                if constexpr (X3) {
+                    split2(s[ks][0], pa[0], pl[0]);
+                    split2(s[ks][2], pa[1], pl[1]);
+                    split2(s[ks][1], pa[2], pl[2]);
+                    split2(s[ks][3], pa[3], pl[3]);
+                } else {
+                    pa[0] = to_tf32(s[ks][0]);
+                    pa[1] = to_tf32(s[ks][2]);
+                    pa[2] = to_tf32(s[ks][1]);
+                    pa[3] = to_tf32(s[ks][3]);
+                }
                 const float* v0 = Vs + (ks * 8 + 2 * t) * kLd + g;
 #pragma unroll
                 for (int nt = 0; nt < 8; nt++) {
-                    mma_tf32(o[nt], pa, __float_as_uint(v0[nt * 8]), __float_as_uint(v0[kLd + nt * 8]));
+                    if constexpr (X3) {
+                        uint32_t h0, l0, h1, l1;
+                        split2(v0[nt * 8], h0, l0);
+                        split2(v0[kLd + nt * 8], h1, l1);
+                        mma_tf32(o[nt], pl, h0, h1);
+                        mma_tf32(o[nt], pa, l0, l1);
+                        mma_tf32(o[nt], pa, h0, h1);
+                    } else {
+                        mma_tf32(o[nt], pa, __float_as_uint(v0[nt * 8]), __float_as_uint(v0[kLd + nt * 8]));
+                    }
                 }
             }
         }
@@ -208,13 +254,19 @@ __global__ void __launch_bounds__(128) attn_prefill64_kernel(const PrefillAttnPa
 size_t prefill_attention_smem_bytes() { return (size_t)kStages * kStageFloats * sizeof(float); }
 
 void prefill_attention_configure() {
-    GRADB_CUDA(cudaFuncSetAttribute(attn_prefill64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    GRADB_CUDA(cudaFuncSetAttribute(attn_prefill64_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)prefill_attention_smem_bytes()));
+    GRADB_CUDA(cudaFuncSetAttribute(attn_prefill64_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     (int)prefill_attention_smem_bytes()));
 }
 
-void launch_prefill_attention(const PrefillAttnParams& p, cudaStream_t st) {
+void launch_prefill_attention(const PrefillAttnParams& p, cudaStream_t st, bool fp32_grade) {
     if (p.n_tiles <= 0) return;
-    launch_kernel(attn_prefill64_kernel, dim3(p.n_tiles, p.H), dim3(128), prefill_attention_smem_bytes(), st, p);
+    if (fp32_grade) {
+        launch_kernel(attn_prefill64_kernel<true>, dim3(p.n_tiles, p.H), dim3(128), prefill_attention_smem_bytes(), st, p);
+    } else {
+        launch_kernel(attn_prefill64_kernel<false>, dim3(p.n_tiles, p.H), dim3(128), prefill_attention_smem_bytes(), st, p);
+    }
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }

@@ -21,6 +21,7 @@ struct PrefillAttnParams {
 };
 
 void prefill_attention_configure();
-void launch_prefill_attention(const PrefillAttnParams& p, cudaStream_t st);
+// fp32_grade: three TF32 MMAs per product on hi/lo operand pairs (fp32 sessions) instead of one.
+void launch_prefill_attention(const PrefillAttnParams& p, cudaStream_t st, bool fp32_grade = false);
 
 }  // namespace gradb

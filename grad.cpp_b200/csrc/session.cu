@@ -477,11 +477,10 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
     const int want = m->sm_count * 3 / 4;
     auto map_idx = [](int tn) { return tn == 32 ? 0 : (tn == 64 ? 1 : 2); };
     const char* no_tiled = std::getenv("GRADB_NO_TILED_ATTN");
-    // fp32 sessions: TF32 hi/lo operands (three MMAs per product) and the fp32 per-position attention kernel;
-    // the query-tiled attention kernel rounds its operands to TF32 and is for the bf16 mode only.
+    // fp32 sessions: TF32 hi/lo operands, three MMAs per product, in the GEMMs and in the tiled attention
     const bool s32 = s->use_tc32;
     const int kind = s32 ? 1 : 0;
-    const bool tiled_ok = !s32 && !(no_tiled && no_tiled[0] == '1');
+    const bool tiled_ok = !(no_tiled && no_tiled[0] == '1');
     const size_t lo_d = (size_t)f.cap * d, lo_f = (size_t)f.cap * ff;
     auto norm_rows = [&](const float* x, const float* g, const float* b, const int* tk, int rows) {
         if (s32) launch_norm_split(x, g, b, tk, f.hS, lo_d, d, modern, 1e-5f, rows, st);
@@ -577,11 +576,12 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
                 Timed t(s, KC_ATTN);
                 if (tiled) {
                     PrefillAttnParams a{};
-                    a.q = f.q; a.kcache = kc; a.vcache = vc; a.out = nullptr; a.out16 = f.attn16;
+                    a.q = f.q; a.kcache = kc; a.vcache = vc; a.out = s32 ? f.attn : nullptr; a.out16 = s32 ? nullptr : f.attn16;
                     a.tiles = f.tiles; a.n_tiles = (int)f.h_tiles.size();
                     a.H = s->H; a.T = s->T; a.d = d;
                     a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
-                    launch_prefill_attention(a, st);
+                    launch_prefill_attention(a, st, s32);
+                    if (s32) launch_split_tf32(f.attn, f.attnS, lo_d, (size_t)R * d, st);
                 } else {
                     AttnParams a{};
                     a.q = f.q; a.kcache = kc; a.vcache = vc; a.tok = f.row_tok; a.pos = f.row_pos; a.row_seq = f.row_seq;
