@@ -180,3 +180,32 @@ def test_fp32_mode_on_tensor_cores_keeps_fp32_parity(name, n_seq, G, golden_ckpt
     assert rel_err(got, s2.prefill(prompts)) < 2e-5
     port.free(om)
     s.close(); s2.close(); m.close()
+
+
+def test_many_row_gemm_kernel_on_the_gpt2_block(G, ck, port, tmp_path, monkeypatch):
+    """`medium` (GPT-2 block: LayerNorm, biases, GELU 3072, learned positions), 64 prompts of 64 ids in bf16
+    mode: 4096 rows per projection put the prompt feed on the persistent many-tile GEMM kernel. Checked against
+    the one-tile-per-CTA kernel on the same rows and, for one sequence, against the fp32 oracle."""
+    dm = ck.PRESETS["medium"]
+    path = str(ck.write_synthetic(tmp_path / "medium.bin", dm, 1003))
+    rng = np.random.default_rng(26)
+    prompts = [rng.integers(0, dm.vocab, 64).astype(np.int32) for _ in range(64)]
+    m16 = G.GPTModel.load(path, 0, G.BF16)
+    a_s = G.BatchSession(m16, 64, 128)
+    a = a_s.prefill(prompts)
+    rows_a = [a_s.cache_row(5, dm.layers - 1, which, 63) for which in (0, 1)]
+    monkeypatch.setenv("GRADB_NO_WIDE_GEMM", "1")
+    b_s = G.BatchSession(m16, 64, 128)
+    b = b_s.prefill(prompts)
+    rows_b = [b_s.cache_row(5, dm.layers - 1, which, 63) for which in (0, 1)]
+    assert rel_err(a, b) < 1e-2, rel_err(a, b)
+    for x, y in zip(rows_a, rows_b):
+        assert np.abs(x - y).max() < 1e-2 * max(np.abs(y).max(), 1e-6)
+    om = port.load(path)
+    want = port.logits_for(om, prompts[5][:24])[-1]
+    port.free(om)
+    c_s = G.BatchSession(m16, 64, 128)
+    monkeypatch.delenv("GRADB_NO_WIDE_GEMM")
+    c = c_s.prefill([p[:24] for p in prompts])
+    assert rel_err(c[5], want) < 4e-2, rel_err(c[5], want)
+    a_s.close(); b_s.close(); c_s.close(); m16.close()
