@@ -137,8 +137,10 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
             a.status = s->status;
             a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = d;
             a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
+            const bool split_inside = s32 && s->hs == 64;  // the pipelined kernel writes the hi/lo operand itself
+            if (split_inside) { a.out_split = s->attnS; a.out_lo_elems = lo_d; }
             launch_attention(a, n_seq, s->attn_splits, st);
-            if (s32) launch_split_tf32(s->attn, s->attnS, lo_d, (size_t)n_seq * d, st);
+            if (s32 && !split_inside) launch_split_tf32(s->attn, s->attnS, lo_d, (size_t)n_seq * d, st);
         }
         {
             Timed t(s, KC_OPROJ);

@@ -597,6 +597,22 @@ __device__ __forceinline__ bool attn_unit_setup(const AttnParams& p, int S, int 
     return true;
 }
 
+// x as a TF32-rounded value and its TF32-rounded remainder (the fp32 sessions' tensor-core operand format)
+__device__ __forceinline__ void split_tf32_pair(float x, float& hi, float& lo) {
+    uint32_t h, l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    hi = __uint_as_float(h);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(x - hi));
+    lo = __uint_as_float(l);
+}
+__device__ __forceinline__ void store_split2(float* out, size_t lo_elems, size_t at, float a, float b) {
+    float ah, al, bh, bl;
+    split_tf32_pair(a, ah, al);
+    split_tf32_pair(b, bh, bl);
+    *reinterpret_cast<float2*>(out + at) = make_float2(ah, bh);
+    *reinterpret_cast<float2*>(out + lo_elems + at) = make_float2(al, bl);
+}
+
 __global__ void __launch_bounds__(kPipeWarps * 32, 1) attn_decode64_pipe_kernel(const AttnParams p, int S,
                                                                               int total_units) {
     constexpr int HS = 64;
@@ -765,6 +781,9 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 1) attn_decode64_pipe_kernel(
                 *reinterpret_cast<__nv_bfloat162*>(p.out16 + (size_t)cur.b * p.d + cur.h * HS + 2 * lane) =
                     __floats2bfloat162_rn(o0 * inv, o1 * inv);
             }
+            if (p.out_split) {
+                store_split2(p.out_split, p.out_lo_elems, (size_t)cur.b * p.d + cur.h * HS + 2 * lane, o0 * inv, o1 * inv);
+            }
             continue;
         }
         const int bh = cur.b * p.H + cur.h;
@@ -799,6 +818,9 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 1) attn_decode64_pipe_kernel(
         if (p.out16) {
             *reinterpret_cast<__nv_bfloat162*>(p.out16 + (size_t)cur.b * p.d + cur.h * HS + 2 * lane) =
                 __floats2bfloat162_rn(c0 * inv, c1 * inv);
+        }
+        if (p.out_split) {
+            store_split2(p.out_split, p.out_lo_elems, (size_t)cur.b * p.d + cur.h * HS + 2 * lane, c0 * inv, c1 * inv);
         }
         if (lane == 0) p.counters[bh] = 0;
     }

@@ -43,6 +43,10 @@ struct AttnParams {
     const int* row_seq;  // optional: cache sequence of each row (prompt feed); null = row index
     float* out;       // [B][d]
     __nv_bfloat16* out16;  // optional bf16 copy of out (operand of the tensor-core projection)
+    // optional TF32 hi/lo copy of out (fp32 sessions' tensor-core operand), halves out_lo_elems apart; written by
+    // the pipelined head-size-64 kernel only
+    float* out_split = nullptr;
+    size_t out_lo_elems = 0;
     float* partial;   // [B][H][S][hs+2] split results: o[hs], max, sum
     int* counters;    // [B][H] arrival tickets, zero between launches
     int* status;      // optional: set non-zero if a bounded wait expires
