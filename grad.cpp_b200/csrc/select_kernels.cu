@@ -43,7 +43,9 @@ __constant__ uint64_t c_exp2_tab[32] = {
     0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull};
 
 // expf with the bits of the host C library's, for finite x <= ~88.
-__device__ __forceinline__ float expf_libm(float x) {
+// `tab` = c_exp2_tab copied to shared memory: lanes index it with unrelated values, which the constant cache
+// would serve one distinct address at a time.
+__device__ __forceinline__ float expf_libm(float x, const uint64_t* tab) {
     if (x < -0x1.9fe368p6f) return 0.0f;     // underflows to zero (also -inf, -1e10 - max)
     // The one input in [-104, 0] where glibc 2.39's FMA-contracted build rounds the other way.
     if (__float_as_uint(x) == 0xc27c65d9u) return 0x1.f45326p-92f;
@@ -60,7 +62,7 @@ __device__ __forceinline__ float expf_libm(float x) {
     const uint64_t ki = (uint64_t)__double_as_longlong(kd);
     kd = __dsub_rn(kd, Shift);
     const double r = __dsub_rn(z, kd);
-    const uint64_t t = c_exp2_tab[ki & 31] + (ki << 47);
+    const uint64_t t = tab[ki & 31] + (ki << 47);
     const double s = __longlong_as_double((long long)t);
     z = __dadd_rn(__dmul_rn(C0, r), C1);
     const double r2 = __dmul_rn(r, r);
@@ -375,6 +377,7 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
     __shared__ float f_wd[kSelWarps];
     __shared__ uint32_t f_we[kSelWarps], f_wo[kSelWarps], f_headbits[kSelWarps];
     __shared__ int f_wh[kSelWarps];
+    __shared__ int f_items[kSelThreads + 1], f_nitems;  // first chunk of every item (segment or unsafe chunk), in order
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     uint32_t* seg_e = work;
     uint32_t* seg_o = work + kSelThreads;
@@ -543,29 +546,43 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
     seg_head[tid] = sv.head;
     __syncthreads();
 
-    // ---- one thread walks the items (segments and unsafe chunks) with the exact sum
+    // ---- the items (segments and unsafe chunks) in order: warp 0 turns the head bits into a list, so that the
+    // serial walk below does no searching and can request the next item's data ahead of its arithmetic
     const int chunks = (n - base0 + kFastPer - 1) / kFastPer;
+    if (w == 0) {
+        uint32_t bits = f_headbits[lane];
+        const int cnt = __popc(bits);
+        int pre = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, pre, o);
+            if (lane >= o) pre += v;
+        }
+        const int total = __shfl_sync(0xffffffffu, pre, 31);
+        int at = pre - cnt;
+        while (bits) {
+            f_items[at++] = lane * 32 + __ffs(bits) - 1;
+            bits &= bits - 1;
+        }
+        if (lane == 0) {
+            f_items[total] = chunks;
+            f_nitems = total;
+        }
+    }
+    __syncthreads();
+
+    // ---- one thread walks the items with the exact sum
     if (tid == 0) {
         float s = s0;
         int h = n, fail = 0, upto = chunks;
-        int t = 0;
-        while (t < chunks) {
-            // next head after t
-            int nxt = chunks;
-            {
-                const int q = t + 1;
-                int ww = q >> 5;
-                uint32_t bits = ww < kSelWarps ? (f_headbits[ww] & (0xffffffffu << (q & 31))) : 0u;
-                while (ww < kSelWarps) {
-                    if (bits) {
-                        nxt = min(chunks, ww * 32 + __ffs(bits) - 1);
-                        break;
-                    }
-                    ww++;
-                    if (ww < kSelWarps) bits = f_headbits[ww];
-                }
-            }
-            const int e = info[t];
+        const int nitems = f_nitems;
+        int t = f_items[0];
+        int e = nitems > 0 ? info[t] : 0;
+        for (int k = 0; k < nitems; k++) {
+            const int nxt = f_items[k + 1];
+            // independent of the running sum: issued before the arithmetic of this item
+            const int e_next = nxt < chunks ? info[nxt] : 0;
+            const uint32_t me = seg_e[nxt - 1], mo = seg_o[nxt - 1];
             if (e < 0) {  // unsafe chunk: native adds
                 const int b0 = base0 + t * kFastPer, e0 = min(n, b0 + kFastPer);
                 float v[kFastPer];
@@ -587,8 +604,8 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
                 info[t] = (int)sb;  // exact start sum of the segment, for the walkers
                 const uint32_t S0 = (sb & 0x7fffffu) | 0x800000u;
                 IncPair m;
-                m.e = seg_e[nxt - 1];
-                m.o = seg_o[nxt - 1];
+                m.e = me;
+                m.o = mo;
                 const uint32_t S1 = step_S(S0, m);
                 if (S1 >= kBinadeEnd) {
                     fail = 1;
@@ -597,6 +614,7 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
                 s = __uint_as_float(((uint32_t)e << 23) | (S1 & 0x7fffffu));
             }
             t = nxt;
+            e = e_next;
             if (h < n || (has_predicate && hit(s))) {  // the first hit lies at or before this point
                 upto = t;
                 break;
@@ -753,7 +771,9 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     __shared__ float red_v[kSelWarps], red_lo[kSelWarps];
     __shared__ int red_i[kSelWarps];
     __shared__ int s_pick;
+    __shared__ uint64_t s_exp_tab[32];
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    if (tid < 32) s_exp_tab[tid] = c_exp2_tab[tid];  // published to all threads by the barriers below
     const int V = p.V;
     pdl_trigger();
     pdl_wait();
@@ -871,7 +891,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         }
         __syncthreads();
         // softmax (tensor.cpp:434-448): exp(x - max), sequential sum in index order, times 1/sum
-        for (int i = tid; i < V; i += kSelThreads) x[i] = expf_libm(__fsub_rn(x[i], mx));
+        for (int i = tid; i < V; i += kSelThreads) x[i] = expf_libm(__fsub_rn(x[i], mx), s_exp_tab);
         __syncthreads();
         const ScanResult den = exact_scan(V, x, [](float) { return false; }, false, scan_sh, work);
         const float inv_sum = __fdiv_rn(1.0f, den.sum);
@@ -883,7 +903,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
             for (int i = tid; i < V; i += kSelThreads) {
                 float v = sorted[i];
                 if (use_k && v < kth) v = -1e10f;
-                sorted[i] = __fmul_rn(expf_libm(__fsub_rn(v, mx)), inv_sum);
+                sorted[i] = __fmul_rn(expf_libm(__fsub_rn(v, mx), s_exp_tab), inv_sum);
             }
             __syncthreads();
             const float top_p = p.top_p;
