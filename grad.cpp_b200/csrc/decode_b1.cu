@@ -21,7 +21,9 @@
 //
 // Stages per layer: A norm1+QKV(+RoPE, cache write) | B attention over the cache,
 // split along the context | C output projection | D residual+norm2+FFN up (GELU or
-// SwiGLU) | E FFN down; then final norm + tied-embedding logits.
+// SwiGLU) and, in the same stage, the FFN down product of this CTA's hidden units with
+// their rows of the down matrix, added into a fixed-point accumulator that every CTA
+// reads in the next stage A; then final norm + tied-embedding logits.
 #include <cooperative_groups.h>
 
 #include "decode_b1.cuh"
@@ -37,6 +39,9 @@ constexpr int kSlots = 4;
 constexpr int kSlotBytes = 48 * 1024;
 constexpr uint32_t kPollLimit = 1u << 22;
 constexpr int kMaxLayersB1 = 32;  // layer tables are staged in shared memory
+// Elements of the fixed-point FFN accumulator sit one per 128-byte line: every CTA adds to every element at
+// about the same time, and same-line atomics queue up in one L2 slice.
+constexpr int kAccStride = 16;  // in 64-bit words
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -138,6 +143,9 @@ __device__ __forceinline__ float4 ld_tile4(const __nv_bfloat16* p) {
     const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
     return make_float4(a.x, a.y, b.x, b.y);
 }
+
+__device__ __forceinline__ float ld_tile1(const float* p) { return *p; }
+__device__ __forceinline__ float ld_tile1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 
 // out_s[0..CW) = in_s[0..rows) @ tile, the tile arriving through the ring in chunks of
 // whole rows. All compute threads call this together.
@@ -252,12 +260,24 @@ __device__ void add_partials(float* x_s, const float* bias, const float* part, i
     bar_compute();
 }
 
+// x_s += bias + the fixed-point accumulator (units of 2^-32), read past L1: other CTAs' adds land in L2
+__device__ void add_fixed(float* x_s, const float* bias, const long long* acc, int d) {
+    for (int k = threadIdx.x; k < d; k += kCompute) {
+        const float bv = bias ? __ldg(bias + k) : 0.f;
+        const long long q = __ldcg(acc + (size_t)k * kAccStride);
+        float v = x_s[k] + bv;
+        v += (float)((double)q * 2.3283064365386963e-10);
+        x_s[k] = v;
+    }
+    bar_compute();
+}
+
 template <typename WT>
 __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kSlots], empty_bar[kSlots];
     __shared__ float red_s[kWarpsB1 * 64];
-    __shared__ float out_s[64], out2_s[64];
+    __shared__ float out_s[64], out2_s[64], hid_s[64];
     __shared__ float sh[kWarpsB1];
     __shared__ volatile int abort_flag;
     __shared__ B1Layer layers_s[kMaxLayersB1];
@@ -312,7 +332,15 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
                     if (p.modern) push_tile(ly->gate, p.up);
                     push_tile(ly->up, p.up);
                 }
-                if (g < p.down.tiles) push_tile(ly->down, p.down);
+                if (g < p.up.tiles) {  // rows [g*CW, g*CW + CW) of the down matrix, whole rows per chunk
+                    const int row0 = g * p.up.CW, nrows = min(p.up.CW, p.dff - row0);
+                    const int chunk_rows = kSlotBytes / (p.d * (int)wb);
+                    const uint8_t* src = static_cast<const uint8_t*>(ly->down) + (size_t)row0 * p.d * wb;
+                    for (int r = 0; r < nrows && !abort_flag; r += chunk_rows) {
+                        const int n = min(chunk_rows, nrows - r);
+                        ring_push(ring, src + (size_t)r * p.d * wb, (uint32_t)n * p.d * wb);
+                    }
+                }
             }
             if (do_logits) {
                 const int r0 = g * p.logit_rows_per_cta, r1 = min(p.V, r0 + p.logit_rows_per_cta);
@@ -363,7 +391,7 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
         float* vc = p.vcache + (size_t)l * p.layer_cache_stride;
 
         // ---- A: (previous FFN output joins the residual) norm1, Q/K/V columns of this CTA
-        if (l > 0) add_partials(x_s, (layers_s + l - 1)->b2, p.dpart, p.down.KS, d);
+        if (l > 0) add_fixed(x_s, (layers_s + l - 1)->b2, p.ffn_acc + (size_t)((l - 1) & 1) * d * kAccStride, d);
         if (g < p.qkv.tiles) {
             const int CW = p.qkv.CW;
             // this thread's output pair: fetch its bias and rotation before the heavy part
@@ -403,6 +431,11 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
         if (!(alive = barrier())) break;
 
         // ---- B: attention of (head, context split) g over the cached positions (inference.cpp:208-225)
+        // This layer's FFN accumulator is cleared here: its previous contents (layer l-2) were consumed
+        // before the barrier just passed, and the first add comes two barriers from now.
+        for (int k = g * kCompute + t; k < d; k += p.G * kCompute) {
+            p.ffn_acc[((size_t)(l & 1) * d + k) * kAccStride] = 0;
+        }
         if (g < p.H * S) {
             const int head = g / S, split = g % S;
             const int ctx = pos + 1;
@@ -509,29 +542,54 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
             if (p.modern) {  // silu(gate) * up (inference.cpp:232-239)
                 tile_matvec<WT>(ring, in_s, d, p.up.Kt, CW, red_s, out2_s);
                 tile_matvec<WT>(ring, in_s, d, p.up.Kt, CW, red_s, out_s);
-                if (t < CW && g * CW + t < p.dff) {
+                if (t < CW) {
                     const float gt = out2_s[t];
-                    p.ffn[g * CW + t] = out_s[t] * (gt / (1.0f + expf(-gt)));
+                    hid_s[t] = g * CW + t < p.dff ? out_s[t] * (gt / (1.0f + expf(-gt))) : 0.f;
                 }
             } else {  // gelu(h @ W1 + b1) (inference.cpp:69-80, 242-244)
                 tile_matvec<WT>(ring, in_s, d, p.up.Kt, CW, red_s, out_s);
-                if (t < CW && g * CW + t < p.dff) {
-                    const float v = out_s[t] + __ldg(ly->b1 + g * CW + t);
-                    const float u = 0.79788456f * (v + 0.044715f * v * v * v);
-                    p.ffn[g * CW + t] = 0.5f * v * (1.0f + tanhf(u));
+                if (t < CW) {
+                    float hv = 0.f;
+                    if (g * CW + t < p.dff) {
+                        const float v = out_s[t] + __ldg(ly->b1 + g * CW + t);
+                        const float u = 0.79788456f * (v + 0.044715f * v * v * v);
+                        hv = 0.5f * v * (1.0f + tanhf(u));
+                    }
+                    hid_s[t] = hv;
                 }
             }
-        }
-        if (!(alive = barrier())) break;
-
-        // ---- E: FFN down tile
-        if (g < p.down.tiles) {
-            const int ct = g % p.down.col_tiles, ks = g / p.down.col_tiles;
-            const int k0 = ks * p.down.Kt, rows = min(p.down.Kt, p.dff - k0);
-            for (int k = t; k < rows; k += kCompute) in_s[k] = __ldcg(p.ffn + k0 + k);
             bar_compute();
-            tile_matvec<WT>(ring, in_s, rows, p.down.Kt, p.down.CW, red_s, out_s);
-            if (t < p.down.CW && ct * p.down.CW + t < d) p.dpart[(size_t)ks * d + ct * p.down.CW + t] = out_s[t];
+            // FFN down (inference.cpp:240-247), this CTA's share: its hidden units times their rows of the down
+            // matrix, every thread a few output columns; the partial vector joins the accumulator by integer adds.
+            {
+                const int row0 = g * CW, nrows = min(CW, p.dff - row0);
+                const int chunk_rows = kSlotBytes / (d * (int)sizeof(WT));
+                constexpr int kColsPerThread = 4;  // d <= 4 * kCompute
+                float y[kColsPerThread] = {0.f, 0.f, 0.f, 0.f};
+                for (int r = 0; r < nrows; r += chunk_rows) {
+                    const int n = min(chunk_rows, nrows - r);
+                    const WT* rows = reinterpret_cast<const WT*>(ring_acquire(ring));
+#pragma unroll
+                    for (int c = 0; c < kColsPerThread; c++) {
+                        const int col = t + c * kCompute;
+                        if (col < d) {
+                            float a = y[c];
+                            for (int i = 0; i < n; i++) a += hid_s[r + i] * ld_tile1(rows + (size_t)i * d + col);
+                            y[c] = a;
+                        }
+                    }
+                    ring_release(ring);
+                }
+                long long* acc = p.ffn_acc + (size_t)(l & 1) * d * kAccStride;
+#pragma unroll
+                for (int c = 0; c < kColsPerThread; c++) {
+                    const int col = t + c * kCompute;
+                    if (col < d) {
+                        const long long q = __double2ll_rn((double)y[c] * 4294967296.0);
+                        asm volatile("red.global.add.u64 [%0], %1;" ::"l"(acc + (size_t)col * kAccStride), "l"(q) : "memory");
+                    }
+                }
+            }
         }
         if (!(alive = barrier())) break;
     }
@@ -539,7 +597,7 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
     if (alive) {
         // ---- final norm + tied-embedding logits (inference.cpp:251-254)
         if (do_logits) {
-            add_partials(x_s, (layers_s + p.L - 1)->b2, p.dpart, p.down.KS, d);
+            add_fixed(x_s, (layers_s + p.L - 1)->b2, p.ffn_acc + (size_t)((p.L - 1) & 1) * d * kAccStride, d);
             norm_vec(x_s, in_s, p.fng, p.fnb, d, p.modern, sh);
             const int r0 = g * p.logit_rows_per_cta, r1 = min(p.V, r0 + p.logit_rows_per_cta);
             for (int r = r0; r < r1; r += p.logit_chunk_rows) {
@@ -626,7 +684,7 @@ void* pack_matrix(const float* s0, const float* s1, const float* s2, int n_singl
 }
 
 size_t b1_smem_bytes(const DeviceModel* m, const B1Plan* plan) {
-    const int in_len = std::max({m->desc.d_model, plan->o.Kt, plan->down.Kt});
+    const int in_len = std::max(m->desc.d_model, plan->o.Kt);
     return (size_t)kSlots * kSlotBytes + 128 + sizeof(float) * ((size_t)m->desc.d_model + in_len + 8);
 }
 
@@ -639,13 +697,13 @@ B1Plan* b1_make_plan(const DeviceModel* m) {
     const bool modern = ds.arch == GRADB_ARCH_MODERN;
     plan->G = m->sm_count;
     plan->wbytes = m->precision == GRADB_BF16 ? 2 : 4;
-    if (hs != 64 || d % 4 != 0 || ds.num_heads > plan->G || ds.num_layers > kMaxLayersB1) return plan;  // not supported: the generic kernels run instead
+    if (hs != 64 || d % 8 != 0 || d > 4 * kCompute || ds.num_heads > plan->G || ds.num_layers > kMaxLayersB1) return plan;  // not supported: the generic kernels run instead
     // Q/K/V and FFN-up have non-linear epilogues, so their tiles span the whole reduction.
     plan->qkv = plan_matrix(d, 3 * d, plan->G, 1);
     plan->o = plan_matrix(d, d, plan->G, 16);
     plan->up = plan_matrix(d, f, plan->G, 1);
-    plan->down = plan_matrix(f, d, plan->G, 16);
-    if (!plan->qkv.tiles || !plan->o.tiles || !plan->up.tiles || !plan->down.tiles) return plan;
+    if (!plan->qkv.tiles || !plan->o.tiles || !plan->up.tiles) return plan;
+    if (plan->up.CW > 64 || kSlotBytes / (d * plan->wbytes) < 1) return plan;
     plan->logit_rows_per_cta = (ds.vocab_size + plan->G - 1) / plan->G;
     plan->logit_chunk_rows = kSlotBytes / (d * plan->wbytes);
     if (plan->logit_chunk_rows < 1) return plan;
@@ -667,7 +725,7 @@ B1Plan* b1_make_plan(const DeviceModel* m) {
         b.o = pack(w.wo, nullptr, nullptr, d, plan->o);
         b.gate = modern ? pack(w.gate, nullptr, nullptr, f, plan->up) : nullptr;
         b.up = pack(w.w1, nullptr, nullptr, f, plan->up);
-        b.down = pack(w.w2, nullptr, nullptr, d, plan->down);
+        b.down = plan->wbytes == 2 ? (const void*)w.w216 : (const void*)w.w2;  // read by rows, no repacking
         b.bq = w.bq; b.bk = w.bk; b.bv = w.bv; b.bo = w.bo;
         b.b1 = w.b1; b.b2 = w.b2;
         b.n1g = w.n1g; b.n1b = w.n1b; b.n2g = w.n2g; b.n2b = w.n2b;
@@ -702,11 +760,11 @@ size_t b1_workspace_floats(const DeviceModel* m, const B1Plan* plan) {
     const int d = m->desc.d_model, hs = d / m->desc.num_heads;
     return (size_t)d                                                      // q
            + (size_t)m->desc.num_heads * plan->attn_splits * (hs + 2)     // attention partials
-           + (size_t)plan->o.KS * d + m->desc.d_ff + (size_t)plan->down.KS * d + 64;
+           + (size_t)plan->o.KS * d + 4 * (size_t)d * kAccStride + 64;  // + two fixed-point accumulators, one line per element
 }
 
 void launch_decode_b1(const B1Params& p, cudaStream_t st) {
-    const int in_len = std::max({p.d, p.o.Kt, p.down.Kt});
+    const int in_len = std::max(p.d, p.o.Kt);
     const size_t smem = (size_t)kSlots * kSlotBytes + 128 + sizeof(float) * ((size_t)p.d + in_len + 8);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(p.G);

@@ -14,7 +14,8 @@ struct B1Mat {
 };
 
 struct B1Layer {
-    const void *qkv, *o, *gate, *up, *down;  // packed tiles (fp32 or bf16)
+    const void *qkv, *o, *gate, *up;  // packed tiles (fp32 or bf16)
+    const void* down;               // FFN down matrix in checkpoint layout [d_ff][d] (fp32 or bf16): read by rows
     const float *bq, *bk, *bv, *bo, *b1, *b2, *n1g, *n1b, *n2g, *n2b;
 };
 
@@ -40,7 +41,10 @@ struct B1Params {
     float *kcache, *vcache;  // [L][1][H][T][hs] of sequence 0
     size_t layer_cache_stride;
     // exchange buffers (global, L2 resident)
-    float *q, *attn_part, *opart, *ffn, *dpart, *logits;
+    float *q, *attn_part, *opart, *logits;
+    // FFN output of the layer, accumulated by every CTA in 2^-32 fixed point (integer adds commute, so the
+    // result does not depend on arrival order); two buffers of d, alternating by layer
+    long long* ffn_acc;
     const int *tok, *logit_tok;
     int *pos, *hist, *hist_len;
     int hist_stride, append_hist;

@@ -207,8 +207,8 @@ void enqueue_step_b1(Session* s, const int* tok_dev, const int* logit_tok_dev, b
     p.q = ws; ws += s->d;
     p.attn_part = ws; ws += (size_t)s->H * plan->attn_splits * (s->hs + 2);
     p.opart = ws; ws += (size_t)plan->o.KS * s->d;
-    p.ffn = ws; ws += s->dff;
-    p.dpart = ws;
+    ws = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(ws) + 15) & ~uintptr_t(15));
+    p.ffn_acc = reinterpret_cast<long long*>(ws);
     p.logits = s->logits;
     p.tok = tok_dev; p.logit_tok = logit_tok_dev;
     p.pos = s->pos; p.hist = s->hist; p.hist_len = s->hist_len;
