@@ -520,7 +520,8 @@ __device__ __forceinline__ void wide_epilogue_rows(const TcGemmParams& p, const 
                                                    const long long* s_off) {
     constexpr int TN = kWideTN;
     const int f = tile_n * kTileM + 4 * lane;  // first of this lane's four features
-    if (f >= p.N) return;                      // N is a multiple of 4 on this path
+    const bool f_in = f < p.N;                 // N is a multiple of 4 on this path
+    if (EPI != TC_LSE && !f_in) return;        // (the log-sum-exp pass keeps every lane for its shuffles)
     int which = 0, n_in = f;
     if (EPI == TC_QKV) {
         which = f / p.d;  // a 128-feature tile lies inside one of Q, K, V (d is a multiple of 128 on this path)
@@ -534,6 +535,7 @@ __device__ __forceinline__ void wide_epilogue_rows(const TcGemmParams& p, const 
     for (int c = we; c < TN; c += 8) {
         if (s_tok[c] < 0) continue;  // warp-uniform
         float4 x = *reinterpret_cast<const float4*>(stg + c * kTileM + 4 * lane);
+        if (EPI == TC_LSE && !f_in) x = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
         const size_t row = (size_t)(tile_b * TN + c) * p.ld_out;
         if (EPI == TC_QKV) {
             if (rope) {
@@ -560,6 +562,18 @@ __device__ __forceinline__ void wide_epilogue_rows(const TcGemmParams& p, const 
             pk.x = *reinterpret_cast<const uint32_t*>(&lo);
             pk.y = *reinterpret_cast<const uint32_t*>(&hi);
             *reinterpret_cast<uint2*>(p.out_bf16 + row + f) = pk;
+        } else if (EPI == TC_LSE) {
+            // this tile's share of the row's log-sum-exp, and the target's logit if it lives here
+            float m = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            float sum = (expf(x.x - m) + expf(x.y - m)) + (expf(x.z - m) + expf(x.w - m));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const size_t r = (size_t)(tile_b * TN + c);
+            if (lane == 0) *reinterpret_cast<float2*>(p.out_f32 + r * p.ld_out + 2 * tile_n) = make_float2(m, sum);
+            const int tg = s_pos[c] - f;  // `pos` carries the target id on this path
+            if (tg >= 0 && tg < 4) p.lse_tgt[r] = tg == 0 ? x.x : (tg == 1 ? x.y : (tg == 2 ? x.z : x.w));
         } else {  // TC_LOGITS
             *reinterpret_cast<float4*>(p.out_f32 + row + f) = x;
         }
@@ -939,6 +953,17 @@ void launch_wide(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams&
 }
 }  // namespace
 
+bool tc_many_rows(const TcGemmParams& p, int token_tile) {
+    if (token_tile != kWideTN) return false;
+    int dev = 0, sm_count = 0;
+    GRADB_CUDA(cudaGetDevice(&dev));
+    GRADB_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+    const char* off = std::getenv("GRADB_NO_WIDE_GEMM");
+    if (off && off[0] == '1') return false;
+    const int n_tiles = (p.N + kTileM - 1) / kTileM, tiles_b = (p.B + kWideTN - 1) / kWideTN;
+    return p.N % 4 == 0 && n_tiles * tiles_b >= 2 * sm_count;
+}
+
 void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int token_tile,
                     int k_splits, cudaStream_t st, int kind) {
     const int n_tiles = (p.N + kTileM - 1) / kTileM;
@@ -954,7 +979,8 @@ void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b,
         const bool wide_off = off && off[0] == '1';
         const int tiles_b = (p.B + kWideTN - 1) / kWideTN;
         // the row-wise epilogue works on four features per lane and on tiles that lie inside one of Q, K, V
-        const bool shape_ok = p.N % 4 == 0 && p.ld_out % 4 == 0 && (epi != TC_QKV || (p.d % kTileM == 0 && p.hs % 4 == 0));
+        const bool shape_ok = p.N % 4 == 0 && (p.ld_out % 4 == 0 || epi == TC_LSE) &&
+                              (epi != TC_QKV || (p.d % kTileM == 0 && p.hs % 4 == 0));
         if (!wide_off && shape_ok && n_tiles * tiles_b >= 2 * sm_count) {
             switch (epi) {
                 case TC_QKV: launch_wide<TC_QKV, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
@@ -962,6 +988,7 @@ void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b,
                 case TC_GELU: launch_wide<TC_GELU, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
                 case TC_SWIGLU: launch_wide<TC_SWIGLU, 2>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
                 case TC_LOGITS: launch_wide<TC_LOGITS, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
+                case TC_LSE: launch_wide<TC_LSE, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
                 default: break;
             }
         }
@@ -973,7 +1000,7 @@ void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b,
         case TC_GELU: launch_tn<TC_GELU, 1>(map_a, map_b, p, token_tile, grid, st, kind); break;
         case TC_SWIGLU: launch_tn<TC_SWIGLU, 2>(map_a, map_b, p, token_tile, grid, st, kind); break;
         case TC_LOGITS: launch_tn<TC_LOGITS, 1>(map_a, map_b, p, token_tile, grid, st, kind); break;
-        default: throw Error(GRADB_ERR_INVALID, "unknown epilogue");
+        default: throw Error(GRADB_ERR_INVALID, "this epilogue has no one-tile-per-CTA kernel");
     }
 }
 

@@ -6,7 +6,9 @@
 
 namespace gradb {
 
-enum { TC_QKV = 0, TC_RESID = 1, TC_GELU = 2, TC_SWIGLU = 3, TC_LOGITS = 4 };
+// TC_LSE (many-row kernel only): logits are not written; every 128-feature tile leaves, per token, its maximum and
+// sum of exp(x - max), plus the logit of the token's target id if the tile holds it (scoring).
+enum { TC_QKV = 0, TC_RESID = 1, TC_GELU = 2, TC_SWIGLU = 3, TC_LOGITS = 4, TC_LSE = 5 };
 
 struct TcGemmParams {
     int K, N, B;  // reduction length, output features (of one matrix), rows (sequences)
@@ -26,6 +28,9 @@ struct TcGemmParams {
     int a_lo_rows = 0, b_lo_rows = 0;
     float* out_split = nullptr;  // FFN activation: [2][rows][ld_out]
     size_t out_lo_elems = 0;
+    // TC_LSE: per (row, feature tile) pairs (max, sum of exp) in out_f32 [rows][ld_out = 2 * tiles]; `pos` carries the
+    // rows' target ids; lse_tgt[row] receives the target's logit.
+    float* lse_tgt = nullptr;
 };
 
 // 2-D bf16 tensor map over a row-major (rows, cols) matrix: boxes of 64 columns x box_rows, 128-byte swizzle.
@@ -35,6 +40,8 @@ void tc_configure_all();
 // kind 0: bf16 operands; kind 1: fp32 operands as TF32 hi/lo pairs, three MMAs per product (fp32-grade result).
 void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int token_tile,
                     int k_splits, cudaStream_t st, int kind = 0);
+// True when launch_tc_gemm would run the many-row persistent kernel for this shape (needed by TC_LSE callers).
+bool tc_many_rows(const TcGemmParams& p, int token_tile);
 // 2-D fp32 tensor map over a row-major (rows, cols) matrix: boxes of 32 columns x box_rows, 128-byte swizzle.
 void make_tensor_map_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 // Normalised rows as TF32 hi/lo pairs: out[0][row][d] and out[1][row][d], the halves lo_elems apart.

@@ -451,10 +451,11 @@ void ensure_feed_buffers(Session* s) {
 void ensure_score_buffers(Session* s) {
     ensure_feed_buffers(s);
     Session::Feed& f = s->feed;
-    if (f.score_logits) return;
-    dalloc(&f.score_logits, (size_t)f.cap * s->V);
+    if (f.row_tgt) return;
     dalloc(&f.row_tgt, (size_t)f.cap);
     dalloc(&f.row_dst, (size_t)f.cap);
+    dalloc(&f.lse_part, (size_t)f.cap * 2 * ((s->V + 127) / 128));
+    dalloc(&f.lse_tgt, (size_t)f.cap);
 }
 
 // Batched prompt feed on the tensor-core path: every prompt token of a chunk of positions is one
@@ -626,10 +627,21 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
             Timed t(s, KC_SCORE);
             norm_rows(f.x, m->fng, m->fnb, f.row_tok, R);
             TcGemmParams g = base;
-            g.K = d; g.N = s->V; g.ld_out = s->V; g.out_f32 = f.score_logits; g.a_lo_rows = s->V;
+            g.K = d; g.N = s->V; g.a_lo_rows = s->V;
             const int tn = tile_for(s->V);
-            launch_tc_gemm(TC_LOGITS, s32 ? m->map_embS : m->map_emb, f.map_h16[map_idx(tn)], g, tn, 1, st, kind);
-            launch_row_logp(f.score_logits, (size_t)s->V, s->V, f.row_tgt, f.row_dst, 0, 0, score_out, R, st);
+            if (!s32 && tc_many_rows(g, tn)) {
+                // logits never reach memory: every feature tile leaves (max, sum of exp) per row and the target's logit
+                const int tiles = (s->V + 127) / 128;
+                g.pos = f.row_tgt;  // this epilogue reads the rows' target ids where the others read positions
+                g.out_f32 = f.lse_part; g.ld_out = 2 * tiles; g.lse_tgt = f.lse_tgt;
+                launch_tc_gemm(TC_LSE, m->map_emb, f.map_h16[map_idx(tn)], g, tn, 1, st, 0);
+                launch_lse_combine(f.lse_part, tiles, f.lse_tgt, f.row_tgt, s->V, f.row_dst, score_out, R, st);
+            } else {
+                if (!f.score_logits) dalloc(&f.score_logits, (size_t)f.cap * s->V);
+                g.ld_out = s->V; g.out_f32 = f.score_logits;
+                launch_tc_gemm(TC_LOGITS, s32 ? m->map_embS : m->map_emb, f.map_h16[map_idx(tn)], g, tn, 1, st, kind);
+                launch_row_logp(f.score_logits, (size_t)s->V, s->V, f.row_tgt, f.row_dst, 0, 0, score_out, R, st);
+            }
         }
         launch_gather_last_rows(f.x, f.row_last, f.row_seq, s->x, d, R, st);
         launch_feed_bookkeeping(f.row_tok, f.row_pos, f.row_seq, f.seq_count, s->pos, s->hist_len, s->hist, s->hist_stride,
@@ -818,7 +830,7 @@ void destroy_session(Session* s) {
     cudaFree(s->feed.x); cudaFree(s->feed.q); cudaFree(s->feed.attn); cudaFree(s->feed.h16); cudaFree(s->feed.attn16);
     cudaFree(s->feed.ffn16); cudaFree(s->feed.row_tok); cudaFree(s->feed.row_pos); cudaFree(s->feed.row_seq);
     cudaFree(s->feed.row_last); cudaFree(s->feed.seq_count); cudaFree(s->feed.last_tok);
-    cudaFree(s->feed.tiles); cudaFree(s->feed.score_logits); cudaFree(s->feed.row_tgt); cudaFree(s->feed.row_dst);
+    cudaFree(s->feed.tiles); cudaFree(s->feed.score_logits); cudaFree(s->feed.lse_part); cudaFree(s->feed.lse_tgt); cudaFree(s->feed.row_tgt); cudaFree(s->feed.row_dst);
     cudaFree(s->score_out); cudaFree(s->score_tgt);
     cudaFree(s->h16); cudaFree(s->attn16); cudaFree(s->ffn16); cudaFree(s->status);
     cudaFree(s->hS); cudaFree(s->attnS); cudaFree(s->ffnS);

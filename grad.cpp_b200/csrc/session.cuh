@@ -62,6 +62,7 @@ struct Session {
         int4* tiles = nullptr;  // query tiles of the current chunk (prompt attention)
         std::vector<int4> h_tiles;
         float* score_logits = nullptr;
+        float *lse_part = nullptr, *lse_tgt = nullptr;  // fused scoring: per-tile (max, sum) pairs, target logits
         int *row_tgt = nullptr, *row_dst = nullptr;
         std::vector<int> h_score;  // host staging: 2 * cap ints
     } feed;

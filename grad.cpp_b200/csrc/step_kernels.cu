@@ -1147,4 +1147,39 @@ void launch_row_logp(const float* logits, size_t ld, int V, const int* tgt, cons
     GRADB_CUDA(cudaGetLastError());
 }
 
+namespace {
+__global__ void __launch_bounds__(256) lse_combine_kernel(const float* __restrict__ part, int tiles,
+                                                          const float* __restrict__ tgt_logit,
+                                                          const int* __restrict__ tgt, int V,
+                                                          const int* __restrict__ dst, float* __restrict__ out, int rows) {
+    pdl_wait();
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    const float2* pr = reinterpret_cast<const float2*>(part) + (size_t)r * tiles;
+    float m = -INFINITY, s = 0.f;
+    for (int t = lane; t < tiles; t += 32) {
+        const float2 v = pr[t];
+        lse_merge(m, s, v.x, v.y);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+        const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+        lse_merge(m, s, m2, s2);
+    }
+    if (lane == 0) {
+        const int t = tgt[r];
+        out[dst[r]] = (t >= 0 && t < V) ? (tgt_logit[r] - m) - logf(s) : 0.f;
+    }
+}
+}  // namespace
+
+void launch_lse_combine(const float* part, int tiles, const float* tgt_logit, const int* tgt, int V, const int* dst,
+                        float* out, int rows, cudaStream_t st) {
+    if (rows <= 0) return;
+    launch_kernel(lse_combine_kernel, dim3((rows + 7) / 8), dim3(256), 0, st, part, tiles, tgt_logit, tgt, V, dst, out, rows);
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
 }  // namespace gradb

@@ -65,6 +65,11 @@ void launch_embed(const float* E, const float* P, const int* tok, const int* pos
 // 0 for a target outside [0, V). Row r is written to out[dst ? dst[r] : r * dst_mul + dst_add].
 void launch_row_logp(const float* logits, size_t ld, int V, const int* tgt, const int* dst, int dst_mul, int dst_add,
                      float* out, int rows, cudaStream_t st);
+// Scoring from per-tile log-sum-exp pairs: part[r][t] = (max, sum of exp(x - max)) over feature tile t of row r,
+// tgt_logit[r] = the logit of the row's target. out[dst[r]] = (tgt_logit - M) - log(sum_t s_t exp(m_t - M)), or 0
+// for a target outside [0, V).
+void launch_lse_combine(const float* part, int tiles, const float* tgt_logit, const int* tgt, int V, const int* dst,
+                        float* out, int rows, cudaStream_t st);
 void launch_advance(const int* tok, int* pos, int* hist, int* hist_len, int hist_stride, int B, cudaStream_t st);
 void launch_gemv(const GemvParams& p, int pro, int epi, bool bf16, int sm_count, cudaStream_t st);
 void launch_logits(const LogitsParams& p, bool bf16, cudaStream_t st);
