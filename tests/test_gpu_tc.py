@@ -209,3 +209,29 @@ def test_many_row_gemm_kernel_on_the_gpt2_block(G, ck, port, tmp_path, monkeypat
     c = c_s.prefill([p[:24] for p in prompts])
     assert rel_err(c[5], want) < 4e-2, rel_err(c[5], want)
     a_s.close(); b_s.close(); c_s.close(); m16.close()
+
+
+@pytest.mark.parametrize("arch", [0, 1])
+def test_tensor_core_paths_with_head_size_32(arch, G, ck, port, tmp_path):
+    """d_model 128 with 4 heads: the projections take the tensor-core kernels (bf16, and fp32 as TF32 pairs) while
+    attention runs on the generic kernel and prompts are fed position by position (the batched feed and the
+    pipelined attention kernel are for head size 64)."""
+    dm = ck.ModelDims(301, 128, 2, 4, 40, arch)
+    path = str(ck.write_synthetic(tmp_path / "hs32.bin", dm, 107, 0.08, True))
+    rng = np.random.default_rng(27)
+    n_seq = 20
+    prompts = [rng.integers(0, dm.vocab, int(n)).astype(np.int32) for n in rng.integers(1, 18, n_seq)]
+    om = port.load(path)
+    want = [port.logits_for(om, p)[-1] for p in prompts]
+    for prec, tol in ((G.FP32, 1e-4), (G.BF16, 4e-2)):
+        m = G.GPTModel.load(path, 0, prec)
+        s = G.BatchSession(m, n_seq)
+        got = s.prefill(prompts)
+        worst = max(rel_err(got[i], want[i]) for i in range(n_seq))
+        assert worst < tol, (prec, worst)
+        if prec == G.FP32:
+            ids = s.generate(prompts, G.Sampling(1, 1.0, 1.0, 0, 1.0), 12)
+            for i in (0, 7, 19):
+                assert list(ids[i]) == list(port.generate(om, prompts[i], 12, greedy=True, penalty=1.0)), i
+        s.close(); m.close()
+    port.free(om)
