@@ -500,8 +500,27 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
     for (int b = 0; b < n_seq; b++) h_last[b] = offsets[b + 1] > offsets[b] ? tokens[offsets[b + 1] - 1] : kSkip;
     GRADB_CUDA(cudaMemcpyAsync(f.last_tok, h_last, n_seq * sizeof(int), cudaMemcpyHostToDevice, st));
 
-    for (int p0 = 0; p0 < max_len; p0 += width) {
-        const int p1 = std::min(max_len, p0 + width);
+    // Passes of at most f.cap rows. Whole sequences per pass when every prompt fits one (long runs of positions
+    // make full 64-query attention tiles and share K/V tiles best); otherwise position ranges over all sequences.
+    struct Pass { int b0, b1, p0, p1; };
+    std::vector<Pass> passes;
+    if (max_len <= f.cap) {
+        int b0 = 0, rows = 0;
+        for (int b = 0; b < n_seq; b++) {
+            const int len = offsets[b + 1] - offsets[b];
+            if (rows + len > f.cap) {
+                passes.push_back({b0, b, 0, max_len});
+                b0 = b;
+                rows = 0;
+            }
+            rows += len;
+        }
+        passes.push_back({b0, n_seq, 0, max_len});
+    } else {
+        for (int p0 = 0; p0 < max_len; p0 += width) passes.push_back({0, n_seq, p0, std::min(max_len, p0 + width)});
+    }
+    for (const Pass& pass : passes) {
+        const int p0 = pass.p0, p1 = pass.p1;
         int* h_tok = f.h_rows.data();
         int* h_pos = h_tok + f.cap;
         int* h_seq = h_pos + f.cap;
@@ -509,9 +528,9 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
         int* h_cnt = h_lastrow + f.cap;
         int R = 0;
         f.h_tiles.clear();
-        for (int b = 0; b < n_seq; b++) {
+        for (int b = 0; b < n_seq; b++) h_cnt[b] = 0;
+        for (int b = pass.b0; b < pass.b1; b++) {
             const int len = offsets[b + 1] - offsets[b];
-            h_cnt[b] = 0;
             for (int j = p0; j < std::min(p1, len); j += 64) {
                 f.h_tiles.push_back(make_int4(b, R + (j - p0), s->h_pos[b] + j, std::min(64, std::min(p1, len) - j)));
             }
