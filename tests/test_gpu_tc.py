@@ -235,3 +235,27 @@ def test_tensor_core_paths_with_head_size_32(arch, G, ck, port, tmp_path):
                 assert list(ids[i]) == list(port.generate(om, prompts[i], 12, greedy=True, penalty=1.0)), i
         s.close(); m.close()
     port.free(om)
+
+
+@pytest.mark.parametrize("precision", ["fp32", "bf16"])
+def test_batched_generation_with_empty_full_and_ragged_prompts(precision, G, golden_ckpt, port):
+    """Edge cases of the batched prompt feed inside generate: an empty prompt (nothing is generated, text_gen.cpp:40),
+    a one-id prompt, a prompt that fills the context (one id is still emitted, text_gen.cpp:61-63), and a stop when the
+    context fills mid-way. fp32 sequences must equal the oracle's; bf16 sequences must have the oracle's lengths."""
+    dm, path = golden_ckpt("hs64_modern")
+    rng = np.random.default_rng(28)
+    lens = [0, 1, dm.max_len, dm.max_len - 3, 7] + [int(x) for x in rng.integers(1, dm.max_len, 19)]
+    prompts = [rng.integers(0, dm.vocab, n).astype(np.int32) for n in lens]
+    n_new = 9
+    m = G.GPTModel.load(path, 0, G.FP32 if precision == "fp32" else G.BF16)
+    s = G.BatchSession(m, len(prompts))
+    ids = s.generate(prompts, G.Sampling(1, 1.0, 1.2, 0, 1.0), n_new)
+    om = port.load(path)
+    for i, p in enumerate(prompts):
+        want = port.generate(om, p, n_new, greedy=True, penalty=1.2) if len(p) else np.zeros(0, np.int32)
+        assert len(ids[i]) == len(want), (i, len(p), len(ids[i]), len(want))
+        assert list(ids[i][:len(p)]) == list(p)
+        if precision == "fp32":
+            assert list(ids[i]) == list(want), i
+    port.free(om)
+    s.close(); m.close()
