@@ -89,6 +89,12 @@ def test_medium_config_batch_of_ragged_prompts(G, ckpts, port):
     for i in (0, 17, 63):
         want = port.generate(om, prompts[i], 24, greedy=True, penalty=1.0)
         assert np.array_equal(outs[i], want), i
+    # the same model, one sequence: the persistent single-sequence kernel with 32 hidden units per CTA
+    # (d_ff 3072 over 148 SMs), i.e. two ring slots of FFN-down rows per CTA
+    s1 = G.BatchSession(m, 1, 256)
+    out1 = s1.generate([prompts[17]], G.Sampling(1, 1.0, 1.0, 0, 1.0), 24)[0]
+    assert np.array_equal(out1, port.generate(om, prompts[17], 24, greedy=True, penalty=1.0))
+    s1.close()
     port.free(om)
     s.close()
     m.close()
