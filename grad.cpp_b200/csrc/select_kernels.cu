@@ -966,7 +966,7 @@ void launch_select(const SelectParams& p_in, int B, cudaStream_t st) {
     SelectParams p = p_in;
     const size_t bytes = select_smem_bytes(p.V, &p.n_pad);
     if (bytes > 200 * 1024) {
-        throw Error(GRADB_ERR_INVALID, "vocabulary too large for the on-device selection stage (limit ~24k ids)");
+        throw Error(GRADB_ERR_INVALID, "vocabulary too large for the on-device sampled selection stage (limit 16384 ids)");
     }
     if (bytes > 48 * 1024 && !g_capturing) {
         GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
