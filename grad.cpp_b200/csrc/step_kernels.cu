@@ -639,6 +639,10 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 1) attn_decode64_pipe_kernel(
     fc.unit = gw;
     bool f_ok = attn_unit_setup(p, S, total_units, fc);
     int issued = 0;
+    // The cache is read once per step and is far larger than L2: mark its lines first to go, so that the weights the
+    // projections re-read every step are what stays.
+    uint64_t stream_policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(stream_policy));
     auto fetch_next = [&]() {
         while (f_ok && fc.tile >= fc.tile_end) {  // skip units without tiles
             fc.unit += warps_total;
@@ -657,12 +661,14 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 1) attn_decode64_pipe_kernel(
             // the stage was last read with ordinary loads: order them before the asynchronous writes
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dstk),
-                         "l"(p.kcache + off), "r"(bytes), "r"(bar)
-                         : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dstv),
-                         "l"(p.vcache + off), "r"(bytes), "r"(bar)
-                         : "memory");
+            asm volatile(
+                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dstk),
+                "l"(p.kcache + off), "r"(bytes), "r"(bar), "l"(stream_policy)
+                : "memory");
+            asm volatile(
+                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dstv),
+                "l"(p.vcache + off), "r"(bytes), "r"(bar), "l"(stream_policy)
+                : "memory");
         }
         issued++;
         fc.tile++;
