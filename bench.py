@@ -144,16 +144,19 @@ def weight_elems(dm):
     return per_layer, V * d + 2 * d
 
 
-def algorithmic_bytes_per_step(dm, batch, ctx, w_bytes):
+def algorithmic_bytes_per_step(dm, batch, ctx, w_bytes, ctx_sum=None):
     """Bytes one decode step must move, per kernel class: weights streamed once per launch
-    (w_bytes per element), fp32 activations in and out, and the K/V rows of every cached position."""
+    (w_bytes per element), fp32 activations in and out, and the K/V rows of every cached position
+    (ctx positions for each of `batch` sequences, or ctx_sum positions in all when contexts differ)."""
     d, f, L, V = dm.d_model, dm.d_ff, dm.layers, dm.vocab
+    if ctx_sum is None:
+        ctx_sum = batch * ctx
     per_layer, logits_w = weight_elems(dm)
     act = 4
     out = {
         "embed": batch * d * act * 2,
         "norm_qkv_rope": L * (per_layer["norm_qkv_rope"] * w_bytes + batch * d * act * 4),
-        "attn_decode": L * (batch * 2 * ctx * d * 4 + batch * d * act * 2),
+        "attn_decode": L * (2 * ctx_sum * d * 4 + batch * d * act * 2),
         "attn_out_proj": L * (per_layer["attn_out_proj"] * w_bytes + batch * d * act * 3),
         "norm_ffn_up": L * (per_layer["norm_ffn_up"] * w_bytes + batch * (d + f) * act),
         "ffn_down": L * (per_layer["ffn_down"] * w_bytes + batch * (f + 2 * d) * act),
@@ -166,12 +169,31 @@ def algorithmic_bytes_per_step(dm, batch, ctx, w_bytes):
 
 # ----------------------------------------------------------------------------- our arm
 
+HBM_CLASSES = ("norm_qkv_rope", "attn_decode", "attn_out_proj", "norm_ffn_up", "ffn_down", "norm_logits")
+KERNEL_NAMES = {"norm_qkv_rope": "norm_rows_kernel + gemm_bf16_tc_kernel<TC_QKV>", "attn_decode": "attn_decode64_pipe_kernel",
+                "attn_out_proj": "gemm_bf16_tc_kernel<TC_RESID>", "norm_ffn_up": "norm_rows_kernel + gemm_bf16_tc_kernel<TC_SWIGLU>",
+                "ffn_down": "gemm_bf16_tc_kernel<TC_RESID>", "norm_logits": "norm_rows_kernel + gemm_bf16_tc_kernel<TC_LOGITS>",
+                "select": "select_kernel", "decode_step_b1": "decode_b1_kernel"}
+
+
+def pick_steps(K, full):
+    """K decode steps spread evenly over the `full` steps of the complete decode (all of them when K >= full)."""
+    if K >= full:
+        return list(range(full))
+    if K == 1:
+        return [full // 2]
+    idx = sorted({int(round(x)) for x in np.linspace(0, full - 1, K)})
+    assert len(idx) == K
+    return idx
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
     g = load_package()
     from grad_cpp_b200 import checkpoint as ck
+    from grad_cpp_b200 import sharding
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -184,8 +206,10 @@ def run_ours(args):
     g.lib()
 
     dm = ck.PRESETS["modern"]
-    B, K, W = args.batch, args.steps, args.warmup
-    K = min(K, CONTEXT - PROMPT_LEN)
+    B, W = args.batch, args.warmup
+    FULL = CONTEXT - PROMPT_LEN            # decode steps of the complete run (context 32 -> 256)
+    K = max(1, min(args.steps, FULL))
+    timed = pick_steps(K, FULL)
     precision = g.BF16 if args.precision == "bf16" else g.FP32
     tmp = tempfile.mkdtemp(prefix="gradb_bench_")
     path = str(ck.write_synthetic(Path(tmp) / f"modern_{rank}.bin", dm, WEIGHT_SEED))
@@ -194,6 +218,7 @@ def run_ours(args):
     sess = g.BatchSession(model, B, CONTEXT, stream=stream.cuda_stream)
     prompts = [seq_prompt(rank * B + i, dm.vocab) for i in range(B)]
     sp = g.Sampling(0, SAMPLER["temperature"], SAMPLER["penalty"], SAMPLER["top_k"], SAMPLER["top_p"])
+    draws = np.stack([seq_draws(rank * B + i, FULL + 1) for i in range(B)])
 
     def barrier():
         torch.cuda.synchronize()
@@ -201,105 +226,142 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # warm-up: W decode steps (builds the step graph, warms caches and clocks)
-    draws_w = np.stack([seq_draws(rank * B + i, W + 1) for i in range(B)])
-    sess.generate(prompts, sp, W + 1, uniforms=draws_w)
-
-    draws = np.stack([seq_draws(rank * B + i, K + 1) for i in range(B)])
-    from grad_cpp_b200 import sharding
-    if world > 1:  # the id gather's first use (communicator set-up, allocator warm-up) stays out of the timed region
+    # Warm-up: one complete generation (all FULL >= W decode steps; captures the step graph with the timed
+    # call's parameters, warms caches and clocks), and the id gather's first use.
+    _, warm_ms, _ = sess.generate(prompts, sp, FULL + 1, uniforms=draws, timings=True)
+    if world > 1:
         sharding.gather_ids(np.zeros((B, CONTEXT + 1), np.int32), world, device="cuda")
+    est_s = float(np.sum(warm_ms[:FULL])) / 1e3
+    reps = int(min(16, max(5, np.ceil(1.0 / max(est_s, 1e-3)))))
+    if args.reps:
+        reps = args.reps
+
     launches0 = g.lib().gradb_kernel_launches()
     clocks = ClockSampler(local)
     barrier()
     clocks.start()
-    t0 = time.perf_counter()
-    ids, step_ms, prefill_ms = sess.generate(prompts, sp, K + 1, uniforms=draws, timings=True)
-    all_ids = sharding.gather_ids(sharding.pad_ids(ids, CONTEXT + 1), world, device="cuda")  # one NCCL all_gather
-    assert all_ids.shape[0] == world * B
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
+    rep_dev, rep_wall, rep_full, ids, step_ms, prefill_ms = [], [], [], None, None, 0.0
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        ids, step_ms, prefill_ms = sess.generate(prompts, sp, FULL + 1, uniforms=draws, timings=True)
+        all_ids = sharding.gather_ids(sharding.pad_ids(ids, CONTEXT + 1), world, device="cuda")  # one NCCL all_gather
+        torch.cuda.synchronize()
+        rep_wall.append(time.perf_counter() - t0)
+        rep_dev.append(float(np.sum(step_ms[timed])) / 1e3)
+        rep_full.append(float(np.sum(step_ms[:FULL])) / 1e3)
+        assert all_ids.shape[0] == world * B
     clk = clocks.stop()
     barrier()
     launches = g.lib().gradb_kernel_launches() - launches0
-
-    dev_s = float(np.sum(step_ms[:K])) / 1e3
-    dev_s, wall = sharding.max_over_ranks([dev_s, wall], world, device="cuda")
     new_ids = sum(len(s) - PROMPT_LEN for s in ids)
-    assert new_ids == B * (K + 1), (new_ids, B, K)
+    assert new_ids == B * (FULL + 1), (new_ids, B, FULL)
+
+    med = lambda v: float(statistics.median(v))
+    stats = sharding.max_over_ranks([med(rep_dev), med(rep_wall), med(rep_full), min(rep_dev), max(rep_dev),
+                                     float(np.median(step_ms[timed]))], world, device="cuda")
+    dev_s, wall, full_s, dev_min, dev_max, p50 = stats
 
     hbm_peak, tensor_peak, peak_kind = peaks()
     w_bytes = 2 if precision == g.BF16 else 4
+    spread = (f"the {K} timed steps are spread evenly over the complete decode (contexts "
+              f"{PROMPT_LEN + timed[0] + 1}..{PROMPT_LEN + timed[-1] + 1})" if K < FULL
+              else "every step of the complete decode is timed")
     line = {
         "metric": "decode tokens/s", "value": world * B * K / dev_s, "unit": "tokens/s", "n_gpus": world,
         "steps": K, "warmup": W, "ms_per_step": dev_s / K * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None,
-        "dtype": "bf16 weights, f32 accumulate, f32 KV cache" if precision == g.BF16 else "f32",
+        "dtype": ("bf16 (weights and GEMM activation operands bf16, f32 accumulate; f32 residual stream, attention "
+                  "and KV cache)") if precision == g.BF16 else "f32 (projections as three TF32 products per term)",
         "data": "synthetic",
         "config": {"workload": f"modern d768 L8 H12 SwiGLU2048 V16000 (69.0M), {B} sequences/GPU, "
                                f"prompt {PROMPT_LEN} ids via batched prompt feed, sampled decode context "
-                               f"{PROMPT_LEN}->{PROMPT_LEN + K} (T 0.8, top-p 0.9)",
-                   "batch_per_gpu": B, "prompt_len": PROMPT_LEN, "context_end": PROMPT_LEN + K,
+                               f"{PROMPT_LEN}->{CONTEXT} (T 0.8, top-p 0.9); each repetition runs the complete "
+                               f"{FULL}-step decode and {spread}; median of {reps} repetitions",
+                   "batch_per_gpu": B, "prompt_len": PROMPT_LEN, "context_end": CONTEXT,
+                   "timed_step_contexts": [PROMPT_LEN + timed[0] + 1, PROMPT_LEN + timed[-1] + 1],
+                   "repetitions": reps, "warmup_steps_run": FULL,
                    "parallelism": f"sequence-sharded replicas x{world}",
                    "l2": "working set (weights + KV of 256 sequences, >1.5 GB) exceeds L2; no flush needed"},
-        "p50_ms_per_step": float(np.median(step_ms[:K])),
+        "p50_ms_per_step": p50,
+        "ms_per_step_min_max": [dev_min / K * 1e3, dev_max / K * 1e3],
+        "full_decode": {"steps": FULL, "ms_per_step": full_s / FULL * 1e3, "tokens_per_s": world * B * FULL / full_s,
+                        "device_s_timed_per_rank": sum(rep_full)},
         "prefill_ms": prefill_ms,
-        "e2e": {"value": world * B * (K + 1) / wall, "unit": "tokens/s",
-                "h2d_bytes_per_step": (B * PROMPT_LEN * 4 + B * (K + 1) * 4) / (K + 1),
-                "d2h_bytes_per_step": (B * (CONTEXT + 2) * 4 + B * 4) / (K + 1),
-                "wall_s": wall, "includes": "prompt upload, prompt feed, decode, id download"
-                                            + (", NCCL all_gather of ids" if world > 1 else "")},
+        "e2e": {"value": world * B * (FULL + 1) / wall, "unit": "tokens/s",
+                "h2d_bytes_per_step": (B * PROMPT_LEN * 4 + B * (FULL + 1) * 4) / (FULL + 1),
+                "d2h_bytes_per_step": (B * (CONTEXT + 2) * 4 + B * 4) / (FULL + 1),
+                "wall_s": wall, "new_ids_per_call": world * B * (FULL + 1),
+                "includes": "per call of the public generate: prompt upload, prompt feed, complete decode, id "
+                            "download" + (", NCCL all_gather of ids" if world > 1 else "") + "; median of the "
+                            "repetitions"},
         "gpu_launches": int(launches),
         "clocks": clk,
     }
 
     if rank == 0 and not args.main_only:
-        # Per-kernel device time over the same K steps, from events around every launch.
+        # Per-kernel device time over the complete decode, from events around every launch.
         sess.set_profiling(True)
-        sess.generate(prompts, sp, K + 1, uniforms=draws)
+        sess.generate(prompts, sp, FULL + 1, uniforms=draws)
         prof = sess.profile()
         sess.set_profiling(False)
+        sess.set_profiling(True)
+        sess.generate(prompts, sp, 0, uniforms=None)  # the prompt feed alone, to subtract
+        feed = sess.profile()
+        sess.set_profiling(False)
         alg = {k: 0.0 for k in prof}
-        for i in range(K):
+        for i in range(FULL):
             for k, v in algorithmic_bytes_per_step(dm, B, PROMPT_LEN + i + 1, w_bytes).items():
                 alg[k] += v
         kernels = {}
-        total_ms = sum(ms for ms, _ in prof.values())
-        for k, (ms, n) in prof.items():
-            if n == 0:
+        total_ms = sum(prof[k][0] - feed.get(k, (0.0, 0))[0] for k in prof)
+        for k, (ms_all, n_all) in prof.items():
+            ms = ms_all - feed.get(k, (0.0, 0))[0]
+            n = n_all - feed.get(k, (0.0, 0))[1]
+            if n <= 0:
                 continue
-            # profile pass covers the prompt feed too; scale bytes to decode launches only for the decode-only classes
-            kernels[k] = {"ms_total": round(ms, 3), "launches": n, "share": round(ms / total_ms, 4)}
-        # decode-only profile: subtract the prompt-feed pass by profiling it separately
-        sess.set_profiling(True)
-        sess.generate(prompts, sp, 0, uniforms=None)
-        feed = sess.profile()
-        sess.set_profiling(False)
-        dom, dom_ms = None, -1.0
-        for k in kernels:
-            ms = prof[k][0] - feed.get(k, (0.0, 0))[0]
-            n = prof[k][1] - feed.get(k, (0.0, 0))[1]
-            kernels[k].update({"decode_ms": round(ms, 3), "decode_launches": n,
-                               "achieved_gbs": round(alg[k] / (ms / 1e3) / 1e9, 1) if ms > 0 else None})
-            if ms > dom_ms:
-                dom, dom_ms = k, ms
-        n_dom = kernels[dom]["decode_launches"]
-        achieved = alg[dom] / (dom_ms / 1e3) / 1e9
+            per = alg[k] / n
+            kernels[k] = {"decode_ms": round(ms, 3), "decode_launches": n, "share": round(ms / total_ms, 4),
+                          "avg_launch_us": round(ms * 1e3 / n, 2),
+                          "algorithmic_bytes_per_launch": per,
+                          "achieved_gbs": round(alg[k] / (ms / 1e3) / 1e9, 1) if k in HBM_CLASSES else None,
+                          "hbm_frac": round(alg[k] / (ms / 1e3) / 1e9 / hbm_peak, 4) if k in HBM_CLASSES else None,
+                          "traffic": ncu_traffic(k, per)}
+        dom = max((k for k in kernels if k in HBM_CLASSES), key=lambda k: kernels[k]["decode_ms"])
+        kd = kernels[dom]
+        achieved = alg[dom] / (kd["decode_ms"] / 1e3) / 1e9
         line["kernels"] = kernels
-        line["roofline"] = {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                            "frac": achieved / hbm_peak, "peak_source": peak_kind,
-                            "algorithmic_bytes_per_launch": alg[dom] / n_dom,
-                            "avg_launch_us": dom_ms * 1e3 / n_dom,
-                            "traffic": ncu_traffic(dom, alg[dom] / n_dom)}
-        step_bytes = sum(sum(algorithmic_bytes_per_step(dm, B, PROMPT_LEN + i + 1, w_bytes).values()) for i in range(K))
-        line["step_roofline"] = {"algorithmic_bytes_per_step_avg": step_bytes / K,
-                                 "achieved_gbs": step_bytes / dev_s / 1e9, "frac": step_bytes / dev_s / 1e9 / hbm_peak}
+        line["roofline"] = {"kernel": dom, "kernel_name": KERNEL_NAMES.get(dom), "bound": "hbm", "achieved": achieved,
+                            "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_kind,
+                            "algorithmic_bytes_per_launch": kd["algorithmic_bytes_per_launch"],
+                            "avg_launch_us": kd["avg_launch_us"], "launches": kd["decode_launches"],
+                            "share_of_step": kd["share"], "traffic": kd["traffic"],
+                            "note": "class with the most device time among the HBM-bound classes, over the complete "
+                                    "decode (per-launch CUDA events on the session's stream, graphs off)"}
+        if "select" in kernels:
+            ks = kernels["select"]
+            line["select"] = {"kernel": "select_kernel", "bound": "on-chip (shared memory, one CTA per sequence)",
+                              "avg_launch_us": ks["avg_launch_us"], "launches": ks["decode_launches"],
+                              "ctas_per_launch": B, "share_of_step": ks["share"],
+                              "logits_read_gbs": round(alg["select"] / (ks["decode_ms"] / 1e3) / 1e9, 1)}
+        step_bytes = sum(sum(algorithmic_bytes_per_step(dm, B, PROMPT_LEN + i + 1, w_bytes).values())
+                         for i in range(FULL))
+        line["step_roofline"] = {"algorithmic_bytes_per_step_avg": step_bytes / FULL,
+                                 "achieved_gbs": step_bytes / full_s / 1e9, "frac": step_bytes / full_s / 1e9 / hbm_peak,
+                                 "over": f"the complete {FULL}-step decode"}
         line["eval"] = bench_scoring(sess, dm, B, tensor_peak, peak_kind)
         if world == 1:
+            sess.close()
+            sess = None
+            line["fp32_check"], line["bf16_vs_fp32"] = bench_fp32_check(g, path, local, dm, B, prompts, draws, sp, ids,
+                                                                        model, hbm_peak)
             line["batch1"] = bench_batch1(g, ck, local, hbm_peak)
+            line["config1"] = bench_config1(g, ck, local, hbm_peak)
+            line["config3"] = bench_config3(g, ck, local, hbm_peak)
+            line["config5"] = bench_config5(g, ck, local, hbm_peak)
             line["cpu_baseline"] = cpu_reference(K_sample=args.cpu_tokens, n_seq=None, timed_only=True)
 
-    sess.close()
+    if sess is not None:
+        sess.close()
     model.close()
     try:
         os.remove(path)
@@ -323,6 +385,175 @@ def ncu_traffic(kernel_class, algorithmic_bytes_per_launch):
     if not rec:
         return None
     return rec["traffic_over_algorithmic"] * algorithmic_bytes_per_launch
+
+
+def log_softmax64(x):
+    x = x.astype(np.float64)
+    x = x - x.max(axis=-1, keepdims=True)
+    return x - np.log(np.exp(x).sum(axis=-1, keepdims=True))
+
+
+def common_prefix_frac(a, b, n_prompt):
+    na, nb = a[n_prompt:], b[n_prompt:]
+    k = min(len(na), len(nb))
+    same = na[:k] == nb[:k]
+    return (int(np.argmin(same)) if not same.all() else k) / max(k, 1)
+
+
+def bench_fp32_check(g, path, device, dm, B, prompts, draws, sp, ids_bf16, model_bf16, hbm_peak):
+    """The benchmark workload on an fp32 session (projections as three TF32 products per term): speed, and the
+    distance of the bf16 run from it: last-prompt-position logits of every sequence, ids under the same draws."""
+    FULL = CONTEXT - PROMPT_LEN
+    s16 = g.BatchSession(model_bf16, B, CONTEXT)
+    lg16 = s16.prefill(prompts)
+    s16.close()
+    m32 = g.GPTModel.load(path, device, g.FP32)
+    s32 = g.BatchSession(m32, B, CONTEXT)
+    lg32 = s32.prefill(prompts)
+    s32.generate(prompts, sp, FULL + 1, uniforms=draws)  # warm-up
+    ids32, step_ms, pre_ms = s32.generate(prompts, sp, FULL + 1, uniforms=draws, timings=True)
+    s32.close()
+    m32.close()
+    dev_s = float(np.sum(step_ms[:FULL])) / 1e3
+    nbytes = sum(sum(algorithmic_bytes_per_step(dm, B, PROMPT_LEN + i + 1, 4).values()) for i in range(FULL))
+    speed = {"workload": f"the benchmark workload ({B} sequences, sampled, context {PROMPT_LEN}->{CONTEXT}) on an fp32 "
+                         "session", "tokens_per_s": B * FULL / dev_s, "ms_per_step": dev_s / FULL * 1e3,
+             "p50_ms_per_step": float(np.median(step_ms[:FULL])), "prefill_ms": pre_ms,
+             "hbm_frac": nbytes / dev_s / 1e9 / hbm_peak}
+    p32, p16 = log_softmax64(lg32), log_softmax64(lg16)
+    err = float(np.abs(lg16 - lg32).max() / np.abs(lg32).max())
+    figures = {"logits_max_abs_err_over_max_abs": err,
+               "mean_kl_fp32_vs_bf16": float((np.exp(p32) * (p32 - p16)).sum(axis=-1).mean()),
+               "first_id_agreement": float(np.mean([a[PROMPT_LEN] == b[PROMPT_LEN] for a, b in zip(ids32, ids_bf16)])),
+               "mean_common_prefix_of_rollout": float(np.mean([common_prefix_frac(a, b, PROMPT_LEN)
+                                                               for a, b in zip(ids32, ids_bf16)])),
+               "greedy_agreement_at_prompt_end": float(np.mean(lg32.argmax(axis=1) == lg16.argmax(axis=1))),
+               "over": f"{B} sequences: logits after the {PROMPT_LEN}-id prompt; sampled ids under identical draws"}
+    return speed, figures
+
+
+def decode_block(sess, dm, prompts, sp, max_new, wb, hbm_peak, uniforms=None, T=None):
+    """Runs one generation twice (warm-up, timed) and reports decode tokens/s, p50 ms per step and the HBM
+    fraction of the algorithmic bytes, integrated over the contexts of the steps actually run."""
+    sess.generate(prompts, sp, min(max_new, 8), uniforms=None if uniforms is None else uniforms[:, :min(max_new, 8)])
+    sess.generate(prompts, sp, max_new, uniforms=uniforms)
+    ids, step_ms, pre_ms = sess.generate(prompts, sp, max_new, uniforms=uniforms, timings=True)
+    lens = np.array([len(p) for p in prompts])
+    emitted = np.array([len(s) for s in ids]) - lens
+    n_steps = int(emitted.max()) - 1      # decode forwards; the last id of a sequence needs none
+    dev_s = float(np.sum(step_ms[:n_steps])) / 1e3
+    tokens = int(np.sum(emitted - 1))
+    nbytes = 0.0
+    for i in range(n_steps):
+        active = emitted - 1 > i
+        ctx_sum = int(np.sum(lens[active] + i + 1))
+        nbytes += sum(algorithmic_bytes_per_step(dm, int(active.sum()), 0, wb, ctx_sum=ctx_sum).values())
+    return {"tokens_per_s": tokens / dev_s, "decode_steps": n_steps, "ms_per_step": dev_s / n_steps * 1e3,
+            "p50_ms_per_step": float(np.median(step_ms[:n_steps])), "prefill_ms": pre_ms,
+            "hbm_frac": nbytes / dev_s / 1e9 / hbm_peak, "algorithmic_mb_per_step": nbytes / n_steps / 1e6}, ids
+
+
+def with_model(g, ck, preset, seed, device, precision, fn):
+    dm = ck.PRESETS[preset]
+    tmp = tempfile.mkdtemp(prefix="gradb_benchc_")
+    path = str(ck.write_synthetic(Path(tmp) / f"{preset}.bin", dm, seed))
+    try:
+        out = {}
+        for name, prec in precision:
+            model = g.GPTModel.load(path, device, prec)
+            try:
+                out[name] = fn(model, dm, 2 if prec == g.BF16 else 4)
+            finally:
+                model.close()
+        return out
+    finally:
+        os.remove(path)
+        os.rmdir(tmp)
+
+
+def bench_config1(g, ck, device, hbm_peak):
+    """`small` GPT-2 block, one sequence, fp32: 16-id prompt, greedy to context 96."""
+    prompt = np.random.default_rng(2001).integers(0, 5000, 16).astype(np.int32)
+
+    def run(model, dm, wb):
+        sess = g.BatchSession(model, 1, 1024)
+        out = {}
+        for pen in (1.0, 1.2):
+            blk, _ = decode_block(sess, dm, [prompt], g.Sampling(1, 1.0, pen, 0, 1.0), 80, wb, hbm_peak)
+            out[f"greedy_penalty_{pen}"] = blk
+        sess.close()
+        return out
+
+    res = with_model(g, ck, "small", 1001, device, (("f32", g.FP32),), run)
+    res["workload"] = "small d512 L6 H8 GELU2048 V5000 (21.5M), 1 sequence, 16-id prompt, greedy decode to context 96"
+    return res
+
+
+def bench_config3(g, ck, device, hbm_peak):
+    """`medium` GPT-2 block, 64 ragged prompts (8..64 ids), greedy to context 256, fp32 and bf16."""
+    rng = np.random.default_rng(2003)
+    lens = rng.integers(8, 65, 64)
+    prompts = [rng.integers(0, 16000, int(n)).astype(np.int32) for n in lens]
+    keep = {}
+
+    def run(model, dm, wb):
+        sess = g.BatchSession(model, 64, 256)
+        lg = sess.prefill(prompts)
+        blk, ids = decode_block(sess, dm, prompts, g.Sampling(1, 1.0, 1.0, 0, 1.0), 256 - 8 + 1, wb, hbm_peak)
+        keep[wb] = (lg, ids)
+        sess.close()
+        return blk
+
+    res = with_model(g, ck, "medium", 1003, device, (("f32", g.FP32), ("bf16", g.BF16)), run)
+    (lg32, ids32), (lg16, ids16) = keep[4], keep[2]
+    p32, p16 = log_softmax64(lg32), log_softmax64(lg16)
+    res["bf16_vs_fp32"] = {
+        "logits_max_abs_err_over_max_abs": float(np.abs(lg16 - lg32).max() / np.abs(lg32).max()),
+        "mean_kl_fp32_vs_bf16": float((np.exp(p32) * (p32 - p16)).sum(axis=-1).mean()),
+        "first_id_greedy_agreement": float(np.mean([a[n] == b[n] for a, b, n in zip(ids32, ids16, lens)])),
+        "mean_common_prefix_of_rollout": float(np.mean([common_prefix_frac(a, b, int(n))
+                                                        for a, b, n in zip(ids32, ids16, lens)]))}
+    res["workload"] = ("medium d768 L8 H12 GELU3072 V16000 (69.8M), 64 sequences, prompt lengths uniform in [8, 64], "
+                       "greedy decode until every context holds 256 ids")
+    return res
+
+
+def bench_config5(g, ck, device, hbm_peak):
+    """`modern` block with context 2048: 32 sequences, 1024-id prompts through the batched feed, greedy decode of
+    1024 ids; the attention class's share and HBM fraction come from a second, per-launch-timed pass."""
+    rng = np.random.default_rng(2005)
+    prompts = [rng.integers(0, 16000, 1024).astype(np.int32) for _ in range(32)]
+    greedy = g.Sampling(1, 1.0, 1.0, 0, 1.0)
+
+    def run(model, dm, wb):
+        sess = g.BatchSession(model, 32, 2048)
+        blk, _ = decode_block(sess, dm, prompts, greedy, 1024, wb, hbm_peak)
+        blk["prefill_tokens_per_s"] = 32 * 1024 / (blk["prefill_ms"] / 1e3)
+        flops = 2.0 * 32 * 1024 * (dm.layers * (4 * dm.d_model ** 2 + 3 * dm.d_model * dm.d_ff)
+                                   + dm.layers * 2 * dm.d_model * 1025 / 2) + 2.0 * 32 * dm.vocab * dm.d_model
+        blk["prefill_tflops"] = flops / (blk["prefill_ms"] / 1e3) / 1e12
+        sess.set_profiling(True)
+        sess.generate(prompts, greedy, 1024)
+        prof = sess.profile()
+        sess.set_profiling(False)
+        sess.set_profiling(True)
+        sess.generate(prompts, greedy, 0)
+        feed = sess.profile()
+        sess.set_profiling(False)
+        ms = prof["attn_decode"][0] - feed["attn_decode"][0]
+        n = prof["attn_decode"][1] - feed["attn_decode"][1]
+        total = sum(prof[k][0] - feed[k][0] for k in prof)
+        nbytes = sum(algorithmic_bytes_per_step(dm, 32, 1024 + i + 1, wb)["attn_decode"] for i in range(1023))
+        blk["attn_decode"] = {"share_of_step": ms / total, "avg_launch_us": ms * 1e3 / max(n, 1),
+                              "achieved_gbs": nbytes / (ms / 1e3) / 1e9, "hbm_frac": nbytes / (ms / 1e3) / 1e9 / hbm_peak,
+                              "contexts": "1025..2047"}
+        sess.close()
+        return blk
+
+    res = with_model(g, ck, "modern2k", 1005, device, (("bf16", g.BF16), ("f32", g.FP32)), run)
+    res["workload"] = ("modern d768 L8 H12 SwiGLU2048 V16000, context 2048, 32 sequences, 1024-id prompts (batched "
+                       "feed), greedy decode of 1024 ids")
+    return res
 
 
 def bench_scoring(sess, dm, B, tensor_peak, peak_kind):
@@ -497,6 +728,7 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=48, help="decode ids per sequence in the CPU sample")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="ids per prompt (default 32, the benchmark configuration; longer prompts are for profiling)")
+    ap.add_argument("--reps", type=int, default=0, help="repetitions of the complete decode (default: enough for 1 s)")
     ap.add_argument("--main-only", action="store_true",
                     help="only the timed workload: no per-kernel pass, batch-1 block or CPU baseline (for profilers)")
     args = ap.parse_args()

@@ -212,6 +212,54 @@ gradb_status gradb_select(gradb_session* session, const gradb_sampling* params, 
     });
 }
 
+gradb_status gradb_generate_stream(gradb_session* session, const int32_t* prompts_host, const int32_t* offsets_host,
+                                   int n_seq, const gradb_sampling* params, int max_new, gradb_draw_fn draw,
+                                   gradb_token_fn on_token, void* user, int32_t* emitted_host) {
+    return guarded([&] {
+        if (!session || !prompts_host || !offsets_host || !params) throw Error(GRADB_ERR_INVALID, "null argument");
+        session_generate_stream(session->impl, prompts_host, offsets_host, n_seq, *params, max_new, draw, on_token, user,
+                                emitted_host);
+    });
+}
+
+gradb_status gradb_session_admit(gradb_session* session, int n_admit, const int32_t* seqs_host,
+                                 const int32_t* prompts_host, const int32_t* offsets_host,
+                                 const int32_t* max_new_host, const float* const* uniforms_host, int reuse_prefix,
+                                 int32_t* reused_host) {
+    return guarded([&] {
+        if (!session || !seqs_host || !prompts_host || !offsets_host || !max_new_host) {
+            throw Error(GRADB_ERR_INVALID, "null argument");
+        }
+        session_admit(session->impl, n_admit, seqs_host, prompts_host, offsets_host, max_new_host, uniforms_host,
+                      reuse_prefix, reused_host);
+    });
+}
+
+gradb_status gradb_session_decode(gradb_session* session, const gradb_sampling* params, int n_steps,
+                                  const int32_t* stop_ids_host, int n_stop, int32_t* out_ids_host, int out_stride,
+                                  int32_t* out_count_host, int32_t* finished_host) {
+    return guarded([&] {
+        if (!session || !params || !out_ids_host || !out_count_host) throw Error(GRADB_ERR_INVALID, "null argument");
+        session_decode(session->impl, *params, n_steps, stop_ids_host, n_stop, out_ids_host, out_stride, out_count_host,
+                       finished_host);
+    });
+}
+
+gradb_status gradb_session_release(gradb_session* session, int seq) {
+    return guarded([&] {
+        if (!session) throw Error(GRADB_ERR_INVALID, "null session");
+        session_release(session->impl, seq);
+    });
+}
+
+gradb_status gradb_session_slot_ids(const gradb_session* session, int seq, int32_t* ids_host, int capacity,
+                                    int* count_out) {
+    return guarded([&] {
+        if (!session || !count_out || (capacity > 0 && !ids_host)) throw Error(GRADB_ERR_INVALID, "null argument");
+        *count_out = session_slot_ids(session->impl, seq, ids_host, capacity);
+    });
+}
+
 gradb_status gradb_score(gradb_session* session, const int32_t* inputs_host, const int32_t* targets_host, int n_windows,
                          int seq_len, float* row_logp_host, float* ms_out) {
     return guarded([&] {

@@ -765,12 +765,30 @@ __device__ bool bucket_sort_desc(const float* src, float* dst, int n, float mn, 
     return true;
 }
 
+// The chosen id joins the sequence's history; inside the generate loop it also becomes the next step's input
+// unless the sequence stops here (text_gen.cpp:48-63: context full or max_tokens ids emitted).
+__device__ __forceinline__ void record_pick(const SelectParams& p, int b, int* hist, int hlen, int pick) {
+    if (hlen < p.hist_stride) hist[hlen] = pick;
+    p.hist_len[b] = hlen + 1;
+    if (p.out_tok) p.out_tok[b] = pick;
+    if (p.loop_mode) {
+        const int g0 = p.gen[b], g = g0 + 1;
+        p.gen[b] = g;
+        bool stop = p.pos[b] >= p.capacity || g >= (p.max_new_seq ? p.max_new_seq[b] : p.max_new);
+        for (int i = 0; i < p.n_stop; i++) stop = stop || pick == p.stop_ids[i];
+        p.cur_tok[b] = stop ? kSkip : pick;
+        if (stop) p.done[b] = 1;
+        if (p.stream_ids && g0 < p.stream_stride) {
+            *reinterpret_cast<volatile int*>(p.stream_ids + (size_t)b * p.stream_stride + g0) = pick + 1;
+            __threadfence_system();
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams p) {
     extern __shared__ __align__(16) float smem[];
     __shared__ uint32_t scan_sh[2 * kSelWarps + 4];
     __shared__ float red_v[kSelWarps], red_lo[kSelWarps];
-    __shared__ int red_i[kSelWarps];
-    __shared__ int s_pick;
     __shared__ uint64_t s_exp_tab[32];
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     if (tid < 32) s_exp_tab[tid] = c_exp2_tab[tid];  // published to all threads by the barriers below
@@ -800,44 +818,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     __syncthreads();
 
     int pick = 0;
-    if (p.greedy) {
-        // first index of the maximum, strict > (text_gen.cpp:52-60)
-        float bv = -INFINITY;
-        int bi = 0x7fffffff;
-        for (int i = tid; i < V; i += kSelThreads) {
-            const float v = x[i];
-            if (v > bv || (v == bv && i < bi)) {
-                bv = v;
-                bi = i;
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) {
-                bv = ov;
-                bi = oi;
-            }
-        }
-        if (lane == 0) {
-            red_v[w] = bv;
-            red_i[w] = bi;
-        }
-        __syncthreads();
-        if (tid == 0) {
-            for (int i = 1; i < kSelWarps; i++) {
-                if (red_v[i] > bv || (red_v[i] == bv && red_i[i] < bi)) {
-                    bv = red_v[i];
-                    bi = red_i[i];
-                }
-            }
-            // a NaN in slot 0 is never displaced by the reference's comparison
-            s_pick = (x[0] != x[0] || bi == 0x7fffffff) ? 0 : bi;
-        }
-        __syncthreads();
-        pick = s_pick;
-    } else {
+    {
         const float inv_t = __fdiv_rn(1.0f, p.temperature);  // text_gen.cpp:136
         const bool use_k = p.top_k > 0 && p.top_k < V;
         const bool use_p = p.top_p < 1.0f;
@@ -931,18 +912,115 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         pick = dr.hit < V ? dr.hit : V - 1;
     }
 
-    if (tid == 0) {
-        if (hlen < p.hist_stride) hist[hlen] = pick;
-        p.hist_len[b] = hlen + 1;
-        if (p.out_tok) p.out_tok[b] = pick;
-        if (p.loop_mode) {
-            // text_gen.cpp:48-63: push the id, stop when the context is full or max_tokens ids were emitted
-            const int g = p.gen[b] + 1;
-            p.gen[b] = g;
-            const bool stop = p.pos[b] >= p.capacity || g >= p.max_new;
-            p.cur_tok[b] = stop ? kSkip : pick;
-            if (stop) p.done[b] = 1;
+    if (tid == 0) record_pick(p, b, hist, hlen, pick);
+}
+
+// Greedy selection without a vocabulary-sized staging buffer: the logits are read once from global memory, the
+// (at most 50) penalised entries are kept as a short list of (id, value) overrides in shared memory.
+// Any vocabulary size.
+constexpr int kGreedyThreads = 512;
+constexpr int kGreedyWarps = kGreedyThreads / 32;
+constexpr int kPenHash = 128;  // open-addressing table over the <= 50 distinct ids of the window
+
+__global__ void __launch_bounds__(kGreedyThreads) select_greedy_kernel(const SelectParams p) {
+    __shared__ int pen_id[kPenaltyWindow];
+    __shared__ float pen_val[kPenaltyWindow];
+    __shared__ int pen_n;
+    __shared__ int table[kPenHash];  // slot -> index into pen_id, -1 = empty
+    __shared__ float red_v[kGreedyWarps];
+    __shared__ int red_i[kGreedyWarps];
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int V = p.V;
+    pdl_trigger();
+    pdl_wait();
+    if (p.loop_mode && p.done[b]) return;
+    const float* lg = p.logits + (size_t)b * V;
+    int* hist = p.hist + (size_t)b * p.hist_stride;
+    const int hlen = p.hist_len[b];
+    if (tid < kPenHash) table[tid] = -1;
+    if (tid == 0) pen_n = 0;
+    __syncthreads();
+    // ---- repetition penalty: last min(50, n) ids, once per occurrence, in order (text_gen.cpp:20-31)
+    if (p.penalty != 1.0f && tid == 0) {
+        const int window = min(kPenaltyWindow, hlen);
+        int n = 0;
+        for (int k = hlen - window; k < hlen; k++) {
+            const int id = hist[k];
+            int slot = id & (kPenHash - 1);
+            while (table[slot] >= 0 && pen_id[table[slot]] != id) slot = (slot + 1) & (kPenHash - 1);
+            int e = table[slot];
+            if (e < 0) {
+                e = n++;
+                table[slot] = e;
+                pen_id[e] = id;
+                pen_val[e] = lg[id];
+            }
+            const float v = pen_val[e];
+            pen_val[e] = v > 0 ? __fdiv_rn(v, p.penalty) : __fmul_rn(v, p.penalty);
         }
+        pen_n = n;
+    }
+    __syncthreads();
+    const int n_pen = pen_n;
+    auto overridden = [&](int id) {
+        if (n_pen == 0) return false;
+        int slot = id & (kPenHash - 1);
+        while (table[slot] >= 0) {
+            if (pen_id[table[slot]] == id) return true;
+            slot = (slot + 1) & (kPenHash - 1);
+        }
+        return false;
+    };
+    // first index of the maximum, strict > (text_gen.cpp:52-60)
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    auto consider = [&](float v, int i) {
+        if (v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    };
+    if ((V & 3) == 0) {
+        const float4* lg4 = reinterpret_cast<const float4*>(lg);
+        for (int q = tid; q < V / 4; q += kGreedyThreads) {
+            const float4 v = __ldcs(lg4 + q);
+            const int i = q * 4;
+            if (!overridden(i)) consider(v.x, i);
+            if (!overridden(i + 1)) consider(v.y, i + 1);
+            if (!overridden(i + 2)) consider(v.z, i + 2);
+            if (!overridden(i + 3)) consider(v.w, i + 3);
+        }
+    } else {
+        for (int i = tid; i < V; i += kGreedyThreads) {
+            if (!overridden(i)) consider(lg[i], i);
+        }
+    }
+    if (tid < n_pen) consider(pen_val[tid], pen_id[tid]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    if (lane == 0) {
+        red_v[w] = bv;
+        red_i[w] = bi;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int i = 1; i < kGreedyWarps; i++) {
+            if (red_v[i] > bv || (red_v[i] == bv && red_i[i] < bi)) {
+                bv = red_v[i];
+                bi = red_i[i];
+            }
+        }
+        // a NaN in slot 0 is never displaced by the reference's comparison (penalising a NaN leaves a NaN)
+        const float x0 = lg[0];
+        const int pick = (x0 != x0 || bi == 0x7fffffff) ? 0 : bi;
+        record_pick(p, b, hist, hlen, pick);
     }
 }
 
@@ -955,6 +1033,8 @@ size_t select_smem_bytes(int V, int* n_pad_out) {
     return ((size_t)V + n_pad) * sizeof(float) + kBuckets * sizeof(int);
 }
 
+bool select_sampled_fits(int V) { return select_smem_bytes(V, nullptr) <= 200 * 1024; }
+
 void configure_select(int V) {
     const size_t bytes = select_smem_bytes(V, nullptr);
     if (bytes > 48 * 1024 && bytes <= 200 * 1024) {
@@ -964,9 +1044,17 @@ void configure_select(int V) {
 
 void launch_select(const SelectParams& p_in, int B, cudaStream_t st) {
     SelectParams p = p_in;
+    if (p.greedy) {
+        p.n_pad = 0;
+        launch_kernel(select_greedy_kernel, dim3(B), dim3(kGreedyThreads), 0, st, p);
+        count_launch();
+        GRADB_CUDA(cudaGetLastError());
+        return;
+    }
     const size_t bytes = select_smem_bytes(p.V, &p.n_pad);
     if (bytes > 200 * 1024) {
-        throw Error(GRADB_ERR_INVALID, "vocabulary too large for the on-device sampled selection stage (limit 16384 ids)");
+        throw Error(GRADB_ERR_INVALID,
+                    "vocabulary too large for the on-device sampled selection stage (limit 16384 ids; greedy has none)");
     }
     if (bytes > 48 * 1024 && !g_capturing) {
         GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));

@@ -26,9 +26,18 @@ struct SelectParams {
     int* done;     // [B]
     const int* pos;
     int capacity, max_new;
+    const int* max_new_seq;  // optional [B]: per-sequence limit on emitted ids instead of max_new
+    int n_stop;              // ids that end a sequence when chosen (the id is still emitted); the reference has none
+    int stop_ids[8];
+    // optional, generate loop only: mapped host memory [B][stream_stride]; the id chosen as a sequence's g-th new id
+    // is published at [b][g] as id + 1 (0 = not yet), so the host can hand it on while the loop runs ahead
+    int* stream_ids;
+    int stream_stride;
 };
 
 size_t select_smem_bytes(int V, int* n_pad_out);
+// Sampled selection keeps one sequence's values and their sorted copy in one CTA's shared memory.
+bool select_sampled_fits(int V);
 void configure_select(int V);
 void launch_select(const SelectParams& p, int B, cudaStream_t st);
 

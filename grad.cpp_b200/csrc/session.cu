@@ -49,7 +49,11 @@ void check_status(Session* s) {
     int code = 0;
     GRADB_CUDA(cudaMemcpy(&code, s->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (code != 0) {
+        // The kernels that gave up left their arrival tickets and barrier words half-way; start them afresh so the
+        // session stays usable.
         cudaMemset(s->status, 0, sizeof(int));
+        cudaMemset(s->attn_counters, 0, (size_t)s->B * s->H * sizeof(int));
+        if (s->b1_bar) cudaMemset(s->b1_bar, 0, 2 * sizeof(unsigned));
         throw Error(GRADB_ERR_DEVICE_WAIT, "a device-side wait expired (code " + std::to_string(code) + ")");
     }
 }
@@ -363,8 +367,14 @@ void ensure_uniforms(Session* s, size_t n) {
     }
 }
 
-void validate_sampling(const gradb_sampling& sp) {
-    if (!sp.greedy && !(sp.temperature > 0.0f)) throw Error(GRADB_ERR_INVALID, "temperature must be positive");
+// Checked before any state changes, so a call that cannot finish never feeds a prompt first.
+void validate_sampling(const Session* s, const gradb_sampling& sp) {
+    if (sp.greedy) return;
+    if (!(sp.temperature > 0.0f)) throw Error(GRADB_ERR_INVALID, "temperature must be positive");
+    if (!select_sampled_fits(s->V)) {
+        throw Error(GRADB_ERR_INVALID,
+                    "vocabulary too large for the on-device sampled selection stage (limit 16384 ids; greedy has none)");
+    }
 }
 
 // Token matrix for the prompt feed: row t holds token t of every sequence (or
@@ -814,6 +824,9 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         GRADB_CUDA(cudaEventCreate(&s->ev_begin));
         GRADB_CUDA(cudaEventCreate(&s->ev_end));
         s->h_pos.assign(B, 0);
+        s->h_ids.assign(B, {});
+        s->h_live.assign(B, 0);
+        s->h_gen.assign(B, 0);
         // The reference zero-fills its caches at construction (inference.cpp:130-135).
         GRADB_CUDA(cudaMemsetAsync(s->kcache, 0, cache * sizeof(float), s->stream));
         GRADB_CUDA(cudaMemsetAsync(s->vcache, 0, cache * sizeof(float), s->stream));
@@ -831,6 +844,10 @@ void destroy_session(Session* s) {
     cudaSetDevice(s->m->device);
     if (s->stream) cudaStreamSynchronize(s->stream);
     if (s->graph) cudaGraphExecDestroy(s->graph);
+    if (s->serve_graph) cudaGraphExecDestroy(s->serve_graph);
+    if (s->stream_ring) cudaFreeHost(s->stream_ring);
+    if (s->stream_u) cudaFreeHost(s->stream_u);
+    cudaFree(s->max_new_seq); cudaFree(s->serve_u);
     for (cudaEvent_t e : s->step_events) cudaEventDestroy(e);
     for (cudaEvent_t e : s->event_pool) cudaEventDestroy(e);
     for (const Session::Span& sp : s->spans) {
@@ -867,6 +884,9 @@ void reset_session(Session* s) {
     GRADB_CUDA(cudaMemsetAsync(s->done, 0, B * sizeof(int), s->stream));
     GRADB_CUDA(cudaMemsetAsync(s->tok, 0xff, B * sizeof(int), s->stream));
     std::fill(s->h_pos.begin(), s->h_pos.end(), 0);
+    for (auto& ids : s->h_ids) ids.clear();
+    std::fill(s->h_live.begin(), s->h_live.end(), 0);
+    std::fill(s->h_gen.begin(), s->h_gen.end(), 0);
 }
 
 void session_step(Session* s, const int32_t* tokens, int n_seq, float* logits_host) {
@@ -1005,7 +1025,7 @@ void session_set_history(Session* s, int seq, const int32_t* ids, int n) {
 void session_select(Session* s, const gradb_sampling& sp, const float* logits_host, const float* uniforms,
                     int n_seq, int32_t* tokens_out, float* probs_host) {
     if (n_seq < 1 || n_seq > s->B) throw Error(GRADB_ERR_INVALID, "n_seq out of range for this session");
-    validate_sampling(sp);
+    validate_sampling(s, sp);
     if (!sp.greedy && !uniforms) throw Error(GRADB_ERR_INVALID, "sampling needs one uniform draw per sequence");
     GRADB_CUDA(cudaSetDevice(s->m->device));
     if (logits_host) {
@@ -1036,7 +1056,7 @@ void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets
                       int out_stride, int32_t* out_len, float* step_ms, float* prefill_ms) {
     if (n_seq < 1 || n_seq > s->B) throw Error(GRADB_ERR_INVALID, "n_seq out of range for this session");
     if (max_new < 0) throw Error(GRADB_ERR_INVALID, "max_new must not be negative");
-    validate_sampling(sp);
+    validate_sampling(s, sp);
     if (!sp.greedy && max_new > 0 && !uniforms) {
         throw Error(GRADB_ERR_INVALID, "sampling needs n_seq*max_new uniform draws");
     }
@@ -1164,6 +1184,333 @@ void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets
         total += t;
     }
     s->last_ms = total;
+}
+
+// How many ids a sequence with a prompt of `len` ids emits: max_new, or fewer when its context fills first; the id
+// chosen when the context is full is still emitted (text_gen.cpp:61-63). Empty prompts emit nothing (text_gen.cpp:40).
+static int emit_count(const Session* s, int len, int max_new) { return len <= 0 ? 0 : std::min(max_new, s->T - len + 1); }
+
+void session_generate_stream(Session* s, const int32_t* prompts, const int32_t* offsets, int n_seq,
+                             const gradb_sampling& sp, int max_new, gradb_draw_fn draw, gradb_token_fn on_token,
+                             void* user, int32_t* emitted) {
+    if (n_seq < 1 || n_seq > s->B) throw Error(GRADB_ERR_INVALID, "n_seq out of range for this session");
+    if (max_new < 0) throw Error(GRADB_ERR_INVALID, "max_new must not be negative");
+    if (!on_token) throw Error(GRADB_ERR_INVALID, "streaming needs a token callback");
+    validate_sampling(s, sp);
+    if (!sp.greedy && max_new > 0 && !draw) throw Error(GRADB_ERR_INVALID, "sampling needs a draw callback");
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    reset_session(s);
+    int emit_max = 0;
+    std::vector<int> emit(n_seq, 0), given(n_seq, 0);
+    std::vector<char> stopped(n_seq, 0);
+    for (int b = 0; b < n_seq; b++) {
+        emit[b] = emit_count(s, offsets[b + 1] - offsets[b], max_new);
+        emit_max = std::max(emit_max, emit[b]);
+    }
+    const int steps = upload_prompt_matrix(s, prompts, offsets, n_seq);
+    const size_t cap = (size_t)std::max(max_new, 1);
+    if (cap > s->stream_cap) {
+        if (s->stream_ring) cudaFreeHost(s->stream_ring);
+        if (s->stream_u) cudaFreeHost(s->stream_u);
+        s->stream_ring = nullptr;
+        s->stream_u = nullptr;
+        s->stream_cap = 0;
+        GRADB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&s->stream_ring), (size_t)s->B * cap * sizeof(int),
+                                 cudaHostAllocMapped));
+        GRADB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&s->stream_u), (size_t)s->B * cap * sizeof(float),
+                                 cudaHostAllocMapped));
+        s->stream_cap = cap;
+    }
+    const size_t stride = s->stream_cap;
+    std::memset(s->stream_ring, 0, (size_t)s->B * stride * sizeof(int));
+    int* ring_dev = nullptr;
+    float* u_dev = nullptr;
+    GRADB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&ring_dev), s->stream_ring, 0));
+    GRADB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&u_dev), s->stream_u, 0));
+    bool any_empty = false;
+    for (int b = 0; b < n_seq; b++) {
+        s->h_stage[b] = emit[b] == 0 ? 1 : 0;
+        any_empty = any_empty || s->h_stage[b];
+    }
+    if (any_empty) {
+        GRADB_CUDA(cudaMemcpyAsync(s->done, s->h_stage, n_seq * sizeof(int), cudaMemcpyHostToDevice, s->stream));
+    }
+    GRADB_CUDA(cudaEventRecord(s->ev_begin, s->stream));
+    if (use_batched_feed(s, n_seq)) enqueue_prompt_feed_batched(s, prompts, offsets, n_seq);
+    else enqueue_prompt_feed(s, steps, n_seq);
+    GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
+
+    SelectParams p = make_select(s, sp);
+    p.loop_mode = 1;
+    p.uniforms = u_dev;
+    p.u_stride = (int)stride;
+    p.max_new = max_new;
+    p.out_tok = nullptr;
+    p.stream_ids = ring_dev;
+    p.stream_stride = (int)stride;
+    volatile const int* ring = s->stream_ring;
+    int* h_flag = s->h_stage + 2 * s->B;  // pinned; [0] = 1, [1] = kSkip: the words that end a sequence on the device
+    h_flag[0] = 1;
+    h_flag[1] = kSkip;
+    bool failed = false;
+    for (int i = 0; i < emit_max && !failed; i++) {
+        bool any = false;
+        for (int b = 0; b < n_seq; b++) {
+            if (stopped[b] || emit[b] <= i) continue;
+            any = true;
+            if (!sp.greedy) s->stream_u[(size_t)b * stride + i] = draw(user, b);
+        }
+        if (!any) break;
+        {
+            Timed t(s, KC_SELECT);
+            launch_select(p, n_seq, s->stream);
+        }
+        if (i + 1 < emit_max) enqueue_step(s, n_seq, s->tok, s->tok, false);
+        for (int b = 0; b < n_seq && !failed; b++) {
+            if (stopped[b] || emit[b] <= i) continue;
+            int v = 0;
+            for (long spin = 0; (v = ring[(size_t)b * stride + i]) == 0; spin++) {
+                if ((spin & 0xfff) == 0xfff && cudaStreamQuery(s->stream) != cudaErrorNotReady) {
+                    v = ring[(size_t)b * stride + i];  // the stream drained: either the id is there or the step failed
+                    if (v == 0) failed = true;
+                    break;
+                }
+            }
+            if (failed) break;
+            given[b]++;
+            if (on_token(user, b, i, v - 1) != 0) {
+                // no further ids for this sequence: mark it done and take it out of the next step
+                stopped[b] = 1;
+                GRADB_CUDA(cudaMemcpyAsync(s->done + b, h_flag, sizeof(int), cudaMemcpyHostToDevice, s->stream));
+                GRADB_CUDA(cudaMemcpyAsync(s->tok + b, h_flag + 1, sizeof(int), cudaMemcpyHostToDevice, s->stream));
+            }
+        }
+    }
+    GRADB_CUDA(cudaMemcpyAsync(s->h_stage, s->pos, n_seq * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+    collect_spans(s);
+    check_status(s);
+    if (failed) throw Error(GRADB_ERR_CUDA, "the decode loop ended without producing the next id");
+    for (int b = 0; b < n_seq; b++) {
+        s->h_pos[b] = s->h_stage[b];
+        if (emitted) emitted[b] = given[b];
+    }
+    GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
+}
+
+// ------------------------------------------------------------------------------------------------ serving
+
+static void ensure_serving(Session* s) {
+    if (s->max_new_seq) return;
+    dalloc(&s->max_new_seq, (size_t)s->B);
+    dalloc(&s->serve_u, (size_t)s->B * (s->T + 2));
+    GRADB_CUDA(cudaMemsetAsync(s->max_new_seq, 0, (size_t)s->B * sizeof(int), s->stream));
+}
+
+void session_admit(Session* s, int n_admit, const int32_t* seqs, const int32_t* prompts, const int32_t* offsets,
+                   const int32_t* max_new, const float* const* uniforms, int reuse_prefix, int32_t* reused_out) {
+    if (n_admit < 1 || n_admit > s->B) throw Error(GRADB_ERR_INVALID, "n_admit out of range for this session");
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    ensure_serving(s);
+    // Everything is validated before any slot changes.
+    int rows = 0;
+    std::vector<char> seen(s->B, 0);
+    for (int i = 0; i < n_admit; i++) {
+        const int b = seqs[i], len = offsets[i + 1] - offsets[i];
+        if (b < 0 || b >= s->B || seen[b]) throw Error(GRADB_ERR_INVALID, "slot index out of range or repeated");
+        seen[b] = 1;
+        if (len < 1) throw Error(GRADB_ERR_INVALID, "an admitted prompt must not be empty");
+        if (len > s->T) throw Error(GRADB_ERR_CONTEXT_FULL, "InferenceSession: context exceeds max_len");
+        if (max_new[i] < 0) throw Error(GRADB_ERR_INVALID, "max_new must not be negative");
+        for (int j = offsets[i]; j < offsets[i + 1]; j++) {
+            if (prompts[j] < 0 || prompts[j] >= s->V) {
+                throw Error(GRADB_ERR_BAD_TOKEN, "InferenceSession: token id out of vocab range");
+            }
+        }
+        rows = std::max(rows, b + 1);
+    }
+    // Per slot: how much of the cache stays, the slot's fresh loop state, the rest of the prompt as its feed.
+    std::vector<int32_t> feed_tok, feed_off(rows + 1, 0);
+    std::vector<int> keep(s->B, 0), first(s->B, -1);
+    for (int i = 0; i < n_admit; i++) first[seqs[i]] = i;
+    size_t total = 0;
+    for (int b = 0; b < rows; b++) {
+        feed_off[b] = (int32_t)feed_tok.size();
+        const int i = first[b];
+        if (i < 0) continue;
+        const int32_t* pr = prompts + offsets[i];
+        const int len = offsets[i + 1] - offsets[i];
+        int k = 0;
+        if (reuse_prefix) {
+            const std::vector<int>& old = s->h_ids[b];
+            const int lim = std::min({len - 1, s->h_pos[b], (int)old.size()});  // the last prompt id is always fed: its logits are needed
+            while (k < lim && old[k] == pr[k]) k++;
+        }
+        keep[b] = k;
+        if (reused_out) reused_out[i] = k;
+        feed_tok.insert(feed_tok.end(), pr + k, pr + len);
+        total += (size_t)(len - k);
+    }
+    feed_off[rows] = (int32_t)feed_tok.size();
+    // device state of the admitted slots: position and history length = kept prefix, nothing emitted, not done
+    std::vector<int> st(4 * (size_t)n_admit);
+    for (int i = 0; i < n_admit; i++) {
+        const int b = seqs[i];
+        const int vals[5] = {keep[b], keep[b], 0, 0, kSkip};
+        int* dst[5] = {s->pos + b, s->hist_len + b, s->gen + b, s->done + b, s->tok + b};
+        for (int f = 0; f < 5; f++) {
+            GRADB_CUDA(cudaMemcpyAsync(dst[f], &vals[f], sizeof(int), cudaMemcpyHostToDevice, s->stream));
+        }
+        GRADB_CUDA(cudaMemcpyAsync(s->max_new_seq + b, &max_new[i], sizeof(int), cudaMemcpyHostToDevice, s->stream));
+        if (uniforms && uniforms[i] && max_new[i] > 0) {
+            const int n = std::min(max_new[i], s->T + 2);
+            GRADB_CUDA(cudaMemcpyAsync(s->serve_u + (size_t)b * (s->T + 2), uniforms[i], n * sizeof(float),
+                                       cudaMemcpyHostToDevice, s->stream));
+        }
+        GRADB_CUDA(cudaStreamSynchronize(s->stream));  // `vals` and the caller's arrays are pageable
+        s->h_pos[b] = keep[b];
+        s->h_ids[b].assign(prompts + offsets[i], prompts + offsets[i + 1]);
+        s->h_live[b] = 1;
+        s->h_gen[b] = 0;
+    }
+    const int steps = upload_prompt_matrix(s, feed_tok.data(), feed_off.data(), rows);
+    GRADB_CUDA(cudaEventRecord(s->ev_begin, s->stream));
+    if (batched_feed_available(s) && total >= 16) enqueue_prompt_feed_batched(s, feed_tok.data(), feed_off.data(), rows);
+    else enqueue_prompt_feed(s, steps, rows);
+    GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+    collect_spans(s);
+    check_status(s);
+    GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
+    for (int b = 0; b < rows; b++) s->h_pos[b] += feed_off[b + 1] - feed_off[b];
+}
+
+void session_release(Session* s, int seq) {
+    if (seq < 0 || seq >= s->B) throw Error(GRADB_ERR_INVALID, "slot index out of range");
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    const int one = 1, skip = kSkip;
+    GRADB_CUDA(cudaMemcpyAsync(s->done + seq, &one, sizeof(int), cudaMemcpyHostToDevice, s->stream));
+    GRADB_CUDA(cudaMemcpyAsync(s->tok + seq, &skip, sizeof(int), cudaMemcpyHostToDevice, s->stream));
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+    s->h_live[seq] = 0;
+}
+
+int session_slot_ids(const Session* s, int seq, int32_t* ids_out, int capacity) {
+    if (seq < 0 || seq >= s->B) throw Error(GRADB_ERR_INVALID, "slot index out of range");
+    const std::vector<int>& ids = s->h_ids[seq];
+    for (int i = 0; i < (int)ids.size() && i < capacity; i++) ids_out[i] = ids[i];
+    return (int)ids.size();
+}
+
+void session_decode(Session* s, const gradb_sampling& sp, int n_steps, const int32_t* stop_ids, int n_stop,
+                    int32_t* out_ids, int out_stride, int32_t* out_count, int32_t* finished) {
+    if (n_steps < 1) throw Error(GRADB_ERR_INVALID, "n_steps must be positive");
+    if (n_stop < 0 || n_stop > 8 || (n_stop > 0 && !stop_ids)) throw Error(GRADB_ERR_INVALID, "at most 8 stop ids");
+    if (out_stride < n_steps) throw Error(GRADB_ERR_INVALID, "out_stride must hold n_steps ids");
+    validate_sampling(s, sp);
+    GRADB_CUDA(cudaSetDevice(s->m->device));
+    ensure_serving(s);
+    int rows = 0;
+    for (int b = 0; b < s->B; b++) {
+        if (s->h_live[b]) rows = b + 1;
+    }
+    for (int b = 0; b < s->B; b++) {
+        out_count[b] = 0;
+        if (finished) finished[b] = s->h_live[b] ? 0 : 1;
+    }
+    if (rows == 0) return;
+    SelectParams p = make_select(s, sp);
+    p.loop_mode = 1;
+    p.uniforms = s->serve_u;
+    p.u_stride = s->T + 2;
+    p.max_new = 0;
+    p.max_new_seq = s->max_new_seq;
+    p.out_tok = nullptr;
+    p.n_stop = n_stop;
+    for (int i = 0; i < n_stop; i++) p.stop_ids[i] = stop_ids[i];
+    // Vacant and finished slots below `rows` are marked done on the device, so neither kernel touches them.
+    for (int b = 0; b < rows; b++) s->h_stage[b] = s->h_live[b] ? 0 : 1;
+    GRADB_CUDA(cudaMemcpyAsync(s->done, s->h_stage, rows * sizeof(int), cudaMemcpyHostToDevice, s->stream));
+    GRADB_CUDA(cudaEventRecord(s->ev_begin, s->stream));
+    auto eager_iteration = [&] {
+        {
+            Timed t(s, KC_SELECT);
+            launch_select(p, rows, s->stream);
+        }
+        enqueue_step(s, rows, s->tok, s->tok, false);
+    };
+    int i = 0;
+    const bool graph_ok = s->use_graph && !s->profiling && n_steps > 2;
+    if (graph_ok) {
+        const bool same = s->serve_graph && s->serve_rows == rows && s->serve_n_stop == n_stop &&
+                          std::memcmp(&s->serve_params, &sp, sizeof(sp)) == 0 &&
+                          std::memcmp(s->serve_stop, p.stop_ids, sizeof(p.stop_ids)) == 0;
+        if (!same) {
+            if (s->serve_graph) {
+                cudaGraphExecDestroy(s->serve_graph);
+                s->serve_graph = nullptr;
+            }
+            // The first iteration runs eagerly, so every kernel of the step has its launch attributes before capture.
+            eager_iteration();
+            i = 1;
+            cudaGraph_t g = nullptr;
+            GRADB_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+            g_capturing = true;
+            try {
+                launch_select(p, rows, s->stream);
+                enqueue_step(s, rows, s->tok, s->tok, false);
+            } catch (...) {
+                g_capturing = false;
+                cudaStreamEndCapture(s->stream, &g);
+                if (g) cudaGraphDestroy(g);
+                throw;
+            }
+            g_capturing = false;
+            GRADB_CUDA(cudaStreamEndCapture(s->stream, &g));
+            const cudaError_t e = cudaGraphInstantiate(&s->serve_graph, g, 0);
+            cudaGraphDestroy(g);
+            if (e != cudaSuccess) throw Error(GRADB_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+            s->serve_params = sp;
+            s->serve_rows = rows;
+            s->serve_n_stop = n_stop;
+            std::memcpy(s->serve_stop, p.stop_ids, sizeof(p.stop_ids));
+        }
+    }
+    for (; i < n_steps; i++) {
+        if (graph_ok) {
+            GRADB_CUDA(cudaGraphLaunch(s->serve_graph, s->stream));
+            count_launch(s->use_b1 && rows == 1 ? 2 : 4 + 5 * s->L);
+        } else {
+            eager_iteration();
+        }
+    }
+    GRADB_CUDA(cudaEventRecord(s->ev_end, s->stream));
+    std::vector<int> lens(rows), done(rows), pos(rows);
+    std::vector<int> hist((size_t)rows * s->hist_stride);
+    GRADB_CUDA(cudaMemcpyAsync(lens.data(), s->hist_len, rows * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
+    GRADB_CUDA(cudaMemcpyAsync(done.data(), s->done, rows * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
+    GRADB_CUDA(cudaMemcpyAsync(pos.data(), s->pos, rows * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
+    GRADB_CUDA(cudaMemcpyAsync(hist.data(), s->hist, hist.size() * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
+    GRADB_CUDA(cudaStreamSynchronize(s->stream));
+    collect_spans(s);
+    check_status(s);
+    GRADB_CUDA(cudaEventElapsedTime(&s->last_ms, s->ev_begin, s->ev_end));
+    for (int b = 0; b < rows; b++) {
+        if (!s->h_live[b]) continue;
+        const int before = (int)s->h_ids[b].size();
+        const int after = std::min(lens[b], s->hist_stride);
+        const int* row = hist.data() + (size_t)b * s->hist_stride;
+        int n = 0;
+        for (int j = before; j < after; j++, n++) {
+            if (n < out_stride) out_ids[(size_t)b * out_stride + n] = row[j];
+            s->h_ids[b].push_back(row[j]);
+        }
+        out_count[b] = std::min(n, out_stride);
+        s->h_gen[b] += n;
+        s->h_pos[b] = pos[b];
+        if (done[b]) s->h_live[b] = 0;
+        if (finished) finished[b] = done[b] ? 1 : 0;
+    }
 }
 
 void session_set_profiling(Session* s, bool on) {

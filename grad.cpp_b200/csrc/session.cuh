@@ -82,6 +82,22 @@ struct Session {
     cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
     std::vector<cudaEvent_t> step_events;
 
+    // streaming generation: host-mapped ring of chosen ids and host-written draws
+    int* stream_ring = nullptr;   // pinned, mapped: [B][stream_cap]
+    float* stream_u = nullptr;    // pinned, mapped: [B][stream_cap]
+    size_t stream_cap = 0;
+
+    // serving (slots admitted and decoded independently): per-slot id lists as the host knows them, per-slot
+    // limits and draws on the device
+    std::vector<std::vector<int>> h_ids;  // ids fed to or chosen for each slot, in order
+    std::vector<char> h_live;             // admitted and not yet finished
+    std::vector<int> h_gen;               // new ids emitted since admission
+    int* max_new_seq = nullptr;           // device [B]
+    float* serve_u = nullptr;             // device [B][T + 2] draws, indexed by the slot's emitted-id count
+    cudaGraphExec_t serve_graph = nullptr;
+    gradb_sampling serve_params{};
+    int serve_rows = -1, serve_n_stop = -1, serve_stop[8] = {};
+
     // decode-step graph (select + step), rebuilt when its parameters change
     cudaGraphExec_t graph = nullptr;
     gradb_sampling graph_params{};
@@ -108,6 +124,18 @@ void session_set_history(Session* s, int seq, const int32_t* ids, int n);
 void session_generate(Session* s, const int32_t* prompts, const int32_t* offsets, int n_seq,
                       const gradb_sampling& sp, int max_new, const float* uniforms, int32_t* out_ids,
                       int out_stride, int32_t* out_len, float* step_ms, float* prefill_ms);
+// generate with every chosen id handed to `on_token` as soon as it exists (TextGen::generate_stream,
+// text_gen.cpp:93-120); draws are requested one per sampled id, right before it is needed.
+void session_generate_stream(Session* s, const int32_t* prompts, const int32_t* offsets, int n_seq,
+                             const gradb_sampling& sp, int max_new, gradb_draw_fn draw, gradb_token_fn on_token,
+                             void* user, int32_t* emitted);
+// Serving: slots are admitted, decoded and released independently of one another.
+void session_admit(Session* s, int n_admit, const int32_t* seqs, const int32_t* prompts, const int32_t* offsets,
+                   const int32_t* max_new, const float* const* uniforms, int reuse_prefix, int32_t* reused_out);
+void session_decode(Session* s, const gradb_sampling& sp, int n_steps, const int32_t* stop_ids, int n_stop,
+                    int32_t* out_ids, int out_stride, int32_t* out_count, int32_t* finished);
+void session_release(Session* s, int seq);
+int session_slot_ids(const Session* s, int seq, int32_t* ids_out, int capacity);
 // Teacher-forced scoring of n_windows windows of seq_len ids (any n_windows; scored max_batch at a
 // time from position 0): row_logp_host[w * seq_len + t] = log-probability of targets[w][t] after
 // inputs[w][0..t]. Returns the device time in ms.

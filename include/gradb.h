@@ -189,6 +189,60 @@ gradb_status gradb_generate(gradb_session* session, const int32_t* prompts_host,
                             const float* uniforms_host, int32_t* out_ids_host, int out_stride,
                             int32_t* out_len_host, float* step_ms_host, float* prefill_ms_host);
 
+/* TextGen::generate_stream (text_gen.cpp:93-120): generate as gradb_generate does, handing every
+ * chosen id to the caller as soon as the device has chosen it, while the forward step for that id
+ * is already running. Per new id i of sequence b, in order: (sampled mode) draw(user, b) is asked
+ * for the uniform in [0,1) of that id - after on_token returned for id i-1, the reference's order of
+ * events (text_gen.cpp:107-116) - then the selection and the next forward step are queued, and
+ * on_token(user, b, i, id) is called when the id arrives in host memory. A non-zero return from
+ * on_token ends that sequence (no further ids are chosen for it, no further draws requested).
+ * emitted_host (optional): [n_seq] ids handed to on_token per sequence. Resets the session first;
+ * the stop rule is gradb_generate's. Callbacks run on the calling thread and must not call into
+ * this session. */
+typedef float (*gradb_draw_fn)(void* user, int seq);
+typedef int (*gradb_token_fn)(void* user, int seq, int index, int32_t token);
+gradb_status gradb_generate_stream(gradb_session* session, const int32_t* prompts_host, const int32_t* offsets_host,
+                                   int n_seq, const gradb_sampling* params, int max_new, gradb_draw_fn draw,
+                                   gradb_token_fn on_token, void* user, int32_t* emitted_host);
+
+/* ---- serving: sequences that come and go ----------------------------------------------------
+ * The reference builds a fresh InferenceSession and re-feeds the whole prompt on every call
+ * (text_gen.cpp:42-46, 74-78, 100-104). A session here is max_batch slots that are filled,
+ * decoded and vacated independently, so a batch keeps running while single sequences finish and
+ * new prompts arrive. Results per slot equal an independent generate call on that prompt. */
+
+/* Starts n_admit prompts in the slots seqs_host[i] (each slot's previous sequence ends), feeding all
+ * of them in one batched prompt feed without touching the other slots. offsets_host: n_admit+1
+ * entries into prompts_host; prompts must not be empty. max_new_host[i]: ids to emit at most
+ * (max_tokens). uniforms_host[i]: max_new_host[i] draws for sampled decoding, or NULL (the array
+ * itself may be NULL when every sequence is decoded greedily).
+ * reuse_prefix != 0: positions of the slot's previous sequence that the new prompt repeats id for
+ * id keep their K/V rows and only the rest of the prompt is fed (a follow-up turn of the same
+ * conversation costs only its new ids). reused_host (optional): positions kept per prompt. */
+gradb_status gradb_session_admit(gradb_session* session, int n_admit, const int32_t* seqs_host,
+                                 const int32_t* prompts_host, const int32_t* offsets_host,
+                                 const int32_t* max_new_host, const float* const* uniforms_host, int reuse_prefix,
+                                 int32_t* reused_host);
+
+/* Runs n_steps decode iterations (choose an id, feed it) for every live slot, queued on the device
+ * without a host round trip. A slot finishes when it has emitted its max_new ids, when its context
+ * is full (the id chosen at the boundary is still emitted, text_gen.cpp:61-63), or when it chooses
+ * one of stop_ids_host (n_stop <= 8; the stop id is emitted; the reference has no such stop).
+ * Finished and vacant slots take no part. out_ids_host: [max_batch][out_stride] ids chosen during
+ * this call, out_count_host: [max_batch] how many, finished_host: [max_batch] 1 once a slot is done. */
+gradb_status gradb_session_decode(gradb_session* session, const gradb_sampling* params, int n_steps,
+                                  const int32_t* stop_ids_host, int n_stop, int32_t* out_ids_host, int out_stride,
+                                  int32_t* out_count_host, int32_t* finished_host);
+
+/* Ends the slot's sequence. Its cached positions stay available to a later gradb_session_admit
+ * with reuse_prefix. */
+gradb_status gradb_session_release(gradb_session* session, int seq);
+
+/* The ids of the slot's sequence so far (prompt followed by emitted ids); returns the count in
+ * count_out and copies at most capacity of them. */
+gradb_status gradb_session_slot_ids(const gradb_session* session, int seq, int32_t* ids_host, int capacity,
+                                    int* count_out);
+
 /* Teacher-forced scoring, the device half of `grad eval` (src/cli/eval.cpp:77-133): n_windows
  * windows of seq_len ids each are fed from position 0 (max_batch windows at a time; the session
  * is reset first and left holding the last group) and every position's logits are reduced on the

@@ -263,3 +263,41 @@ def test_bf16_weight_mode_stays_close(name, G, models, golden):
     got = np.stack([s.step(int(t)) for t in golden[f"{name}/tokens"]])
     err = rel_err(got, want)
     assert err < 3e-2, err
+
+
+@pytest.mark.parametrize("vocab,arch", [(20011, 1), (50257, 0)])
+def test_greedy_has_no_vocabulary_limit(vocab, arch, G, ck, port, tmp_path):
+    """Greedy selection reads the logits from global memory and keeps only the penalty window's entries on chip,
+    so vocabularies beyond one CTA's shared memory work (the reference's argmax is a plain loop,
+    text_gen.cpp:52-60; its checkpoints allow 2^24 ids). The sampled stage keeps its limit and refuses
+    before anything is fed."""
+    dm = ck.ModelDims(vocab, 128, 2, 2, 48, arch)
+    path = str(ck.write_synthetic(tmp_path / "bigvocab.bin", dm, 131, 0.08, True))
+    rng = np.random.default_rng(132)
+    prompts = [rng.integers(0, vocab, n).astype(np.int32) for n in (5, 1, 17)]
+    m = G.GPTModel.load(path)
+    om = port.load(path)
+    for pen in (1.0, 1.3):
+        got = G.TextGen(m).generate_greedy(prompts[0], 30, pen)
+        assert np.array_equal(got, port.generate(om, prompts[0], 30, greedy=True, penalty=pen)), pen
+    s = G.BatchSession(m, 3)
+    outs = s.generate(prompts, G.Sampling(1, 1.0, 1.3, 0, 1.0), 20)
+    for p, o in zip(prompts, outs):
+        assert np.array_equal(o, port.generate(om, p, 20, greedy=True, penalty=1.3))
+    # argmax with ties, a NaN and a penalised maximum on caller-supplied logits
+    lg = rng.standard_normal((3, vocab)).astype(np.float32)
+    lg[0, 7] = lg[0, vocab - 1] = lg[0].max() + 1.0          # tie: the first index wins
+    lg[1, 0] = np.nan                                          # a NaN in slot 0 stays the pick
+    lg[2, 11] = lg[2].max() + 0.5                              # the maximum sits in the penalty window
+    hist = [np.array([3, 5], np.int32), np.array([9], np.int32), np.array([11, 11, 4], np.int32)]
+    for i, h in enumerate(hist):
+        s.set_history(i, h)
+    got = s.select(G.Sampling(1, 1.0, 1.7, 0, 1.0), logits=lg)
+    for i, h in enumerate(hist):
+        assert got[i] == port.argmax(port.apply_penalty(lg[i], h, 1.7)), i
+    s.reset()
+    with pytest.raises(G.binding.GradbError) as e:
+        s.generate(prompts, G.Sampling(0, 0.8, 1.0, 0, 0.9), 4, uniforms=rng.random((3, 4), dtype=np.float32))
+    assert "16384" in str(e.value) and all(s.position(i) == 0 for i in range(3))
+    port.free(om)
+    s.close(); m.close()
