@@ -8,7 +8,6 @@ loudly if the CUDA library has not been built.
 from . import checkpoint  # noqa: F401
 from . import binding  # noqa: F401
 from . import sharding  # noqa: F401
-from . import tokenfile  # noqa: F401
 from .binding import (BF16, FP32, BatchSession, GPTModel, InferenceSession, Sampling, TextGen,  # noqa: F401
                       lib)
 

@@ -72,6 +72,14 @@ SIGNATURES = {
     "gradb_select_from_logits": (C.c_int, [C.c_void_p, C.POINTER(Sampling), _f32p, _f32p, C.c_int, _i32p, _f32p]),
     "gradb_generate": (C.c_int, [C.c_void_p, _i32p, _i32p, C.c_int, C.POINTER(Sampling), C.c_int, _f32p, _i32p,
                                  C.c_int, _i32p, _f32p, _f32p]),
+    "gradb_generate_stream": (C.c_int, [C.c_void_p, _i32p, _i32p, C.c_int, C.POINTER(Sampling), C.c_int, C.c_void_p,
+                                        C.c_void_p, C.c_void_p, _i32p]),
+    "gradb_session_admit": (C.c_int, [C.c_void_p, C.c_int, _i32p, _i32p, _i32p, _i32p, C.POINTER(_f32p), C.c_int,
+                                      _i32p]),
+    "gradb_session_decode": (C.c_int, [C.c_void_p, C.POINTER(Sampling), C.c_int, _i32p, C.c_int, _i32p, C.c_int, _i32p,
+                                       _i32p]),
+    "gradb_session_release": (C.c_int, [C.c_void_p, C.c_int]),
+    "gradb_session_slot_ids": (C.c_int, [C.c_void_p, C.c_int, _i32p, C.c_int, C.POINTER(C.c_int)]),
     "gradb_score": (C.c_int, [C.c_void_p, _i32p, _i32p, C.c_int, C.c_int, _f32p, _f32p]),
     "gradb_mean_loss": (C.c_int, [C.c_void_p, _i32p, _i32p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double), _f32p,
                                   _f32p]),
@@ -89,6 +97,9 @@ SIGNATURES = {
     "gradb_session_stage_trace": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.c_int, C.POINTER(C.c_int)]),
     "gradb_kernel_launches": (C.c_uint64, []),
 }
+
+DRAW_FN = C.CFUNCTYPE(C.c_float, C.c_void_p, C.c_int)
+TOKEN_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int32)
 
 _lib = None
 
@@ -292,6 +303,73 @@ class BatchSession:
             return seqs, step_ms, float(pre_ms.value)
         return seqs
 
+    def generate_stream(self, prompts, sampling: Sampling, max_new, on_token, draw=None):
+        """gradb_generate_stream: on_token(seq, index, id) is called as each id is chosen (a true return value ends
+        that sequence); draw(seq) supplies one uniform per sampled id, asked for right before it is needed.
+        Returns the ids handed out per sequence."""
+        flat, offs = _flatten(prompts)
+        n = len(prompts)
+        emitted = np.zeros(n, np.int32)
+        failure = []
+
+        def _tok(_user, seq, index, token):
+            try:
+                return 1 if on_token(seq, index, token) else 0
+            except BaseException as e:  # must not unwind through the C frames
+                failure.append(e)
+                return 1
+
+        def _draw(_user, seq):
+            try:
+                return float(draw(seq))
+            except BaseException as e:
+                failure.append(e)
+                return 0.0
+
+        tok_cb = TOKEN_FN(_tok)
+        draw_cb = DRAW_FN(_draw) if draw is not None else None
+        _check(lib().gradb_generate_stream(self._h, _p(flat, _i32p), _p(offs, _i32p), n, C.byref(sampling), max_new,
+                                           C.cast(draw_cb, C.c_void_p) if draw_cb else None,
+                                           C.cast(tok_cb, C.c_void_p), None, _p(emitted, _i32p)))
+        if failure:
+            raise failure[0]
+        return emitted
+
+    def admit(self, slots, prompts, max_new, uniforms=None, reuse_prefix=False):
+        """gradb_session_admit: starts prompts[i] in slot slots[i]; returns the cached positions kept per prompt."""
+        flat, offs = _flatten(prompts)
+        n = len(prompts)
+        sl = np.ascontiguousarray(slots, np.int32)
+        mn = np.ascontiguousarray(np.broadcast_to(max_new, (n,)), np.int32)
+        reused = np.zeros(n, np.int32)
+        uptr = None
+        if uniforms is not None:
+            keep = [None if u is None else np.ascontiguousarray(u, np.float32) for u in uniforms]
+            uptr = (_f32p * n)(*[_p(u, _f32p) if u is not None else None for u in keep])
+        _check(lib().gradb_session_admit(self._h, n, _p(sl, _i32p), _p(flat, _i32p), _p(offs, _i32p), _p(mn, _i32p), uptr,
+                                         int(reuse_prefix), _p(reused, _i32p)))
+        return reused
+
+    def decode(self, sampling: Sampling, n_steps, stop_ids=()):
+        """gradb_session_decode: ([new ids per slot], finished flags) for n_steps iterations over the live slots."""
+        B = self.max_batch
+        out = np.zeros((B, n_steps), np.int32)
+        cnt = np.zeros(B, np.int32)
+        fin = np.zeros(B, np.int32)
+        st = np.ascontiguousarray(stop_ids, np.int32) if len(stop_ids) else None
+        _check(lib().gradb_session_decode(self._h, C.byref(sampling), n_steps, _p(st, _i32p), len(stop_ids),
+                                          _p(out, _i32p), n_steps, _p(cnt, _i32p), _p(fin, _i32p)))
+        return [out[b, :cnt[b]].copy() for b in range(B)], fin.astype(bool)
+
+    def release(self, slot):
+        _check(lib().gradb_session_release(self._h, slot))
+
+    def slot_ids(self, slot):
+        n = C.c_int()
+        buf = np.zeros(self.capacity() + 2, np.int32)
+        _check(lib().gradb_session_slot_ids(self._h, slot, _p(buf, _i32p), len(buf), C.byref(n)))
+        return buf[:n.value].copy()
+
     def set_profiling(self, on: bool):
         _check(lib().gradb_session_set_profiling(self._h, int(on)))
 
@@ -379,9 +457,13 @@ class TextGen:
                                                                         (0, max_tokens - len(draws))))[0]
 
     def generate_stream(self, prompt_tokens, on_token, temperature=1.0, max_tokens=50, repetition_penalty=1.2,
-                        top_k=0, top_p=1.0, draws=None):
-        ids = self.generate_sample(prompt_tokens, temperature, max_tokens, repetition_penalty, top_k, top_p, draws)
-        new = ids[len(prompt_tokens):]
-        for t in new:
-            on_token(int(t))
-        return len(new)
+                        top_k=0, top_p=1.0, draws=None, rng=None):
+        """on_token(id) runs as each id is chosen (text_gen.cpp:107-116); returns how many were generated."""
+        if len(prompt_tokens) == 0:
+            return 0
+        it = iter(draws) if draws is not None else None
+        rng = rng or np.random.default_rng()
+        draw = (lambda seq: next(it)) if it is not None else (lambda seq: rng.random(dtype=np.float32))
+        sp = Sampling(0, temperature, repetition_penalty, top_k, top_p)
+        n = self._s.generate_stream([prompt_tokens], sp, max_tokens, lambda seq, i, t: on_token(int(t)), draw)
+        return int(n[0])

@@ -6,9 +6,8 @@
 //   grad::GPTModel::load / save        include/grad/transformer/gpt_model.h:83-86
 //   grad::InferenceSession             include/grad/transformer/inference.h:16-29
 //   grad::TextGen                      include/grad/transformer/text_gen.h:12-38
-//   grad::training::mean_loss          src/training/trainer.cpp:319-340 (what `grad eval` reports)
-//   grad::tokenfile, MappedTokenDataset include/grad/data/token_file.h:10-70
-//   grad::DataLoader                   include/grad/data/dataloader.h:23-46
+//   grad::training::mean_loss          src/training/trainer.cpp:319-340 (what `grad eval` reports), as a
+//                                      template over the loader, so grad.cpp's own DataLoader feeds it
 // Status codes come back as the reference's exception types and messages
 // (src/transformer/inference.cpp:151-156, src/transformer/gpt_model.cpp:385-387, 521-524).
 //
@@ -18,7 +17,7 @@
 #include <algorithm>
 #include <cstdint>
 #include <cstring>
-#include <fstream>
+#include <exception>
 #include <functional>
 #include <memory>
 #include <random>
@@ -146,15 +145,41 @@ public:
                                 float repetition_penalty = 1.2f, int top_k = 0, float top_p = 1.0f) {
         return to_string(sample_ids(prompt_tokens, temperature, max_tokens, repetition_penalty, top_k, top_p));
     }
-    // Calls on_text with each new token's text; returns how many were generated.
+    // Calls on_text with each new token's text as soon as the device has chosen it (the forward step for that id is
+    // already running); returns how many were generated. One draw is taken from the generator per id, after on_text
+    // returned for the previous one, as in the reference (text_gen.cpp:107-116). An exception thrown by on_text ends
+    // the generation and is rethrown here.
     int generate_stream(const std::vector<int>& prompt_tokens, const std::function<void(const std::string&)>& on_text,
                         float temperature = 1.0f, int max_tokens = 50, float repetition_penalty = 1.2f, int top_k = 0,
                         float top_p = 1.0f) {
-        const std::vector<int> ids =
-            sample_ids(prompt_tokens, temperature, max_tokens, repetition_penalty, top_k, top_p);
-        int n = 0;
-        for (size_t i = prompt_tokens.size(); i < ids.size(); i++, n++) on_text(to_string({ids[i]}));
-        return n;
+        if (prompt_tokens.empty()) return 0;
+        struct Ctx {
+            TextGen* self;
+            const std::function<void(const std::string&)>* on_text;
+            std::uniform_real_distribution<float> dis{0.0f, 1.0f};
+            std::exception_ptr error;
+        } ctx{this, &on_text, {}, nullptr};
+        const gradb_sampling sp{0, temperature, repetition_penalty, top_k, top_p};
+        const std::vector<int32_t> p32 = checked_ids(prompt_tokens);
+        const int32_t offsets[2] = {0, static_cast<int32_t>(p32.size())};
+        int32_t emitted = 0;
+        const gradb_status st = gradb_generate_stream(
+            session_, p32.data(), offsets, 1, &sp, max_tokens,
+            [](void* user, int) { return static_cast<Ctx*>(user)->dis(generator()); },
+            [](void* user, int, int, int32_t token) {
+                Ctx* c = static_cast<Ctx*>(user);
+                try {
+                    (*c->on_text)(c->self->to_string({static_cast<int>(token)}));
+                    return 0;
+                } catch (...) {  // must not unwind through the C frames
+                    c->error = std::current_exception();
+                    return 1;
+                }
+            },
+            &ctx, &emitted);
+        if (ctx.error) std::rethrow_exception(ctx.error);
+        detail::check(st);
+        return emitted;
     }
 
     // Id-level variants (prompt followed by the new ids).
@@ -166,9 +191,13 @@ public:
                                 float repetition_penalty, int top_k, float top_p) {
         // Same draw as the reference: one uniform_real_distribution<float>(0,1) sample of a process-wide
         // mt19937 per generated token (text_gen.cpp:195-199).
-        std::vector<float> u(static_cast<size_t>(std::max(max_tokens, 0)));
+        // Exactly as many draws as ids will be emitted (the loop ends early when the context fills,
+        // text_gen.cpp:61-63), so the generator is left where the reference would leave it.
+        const int room = gradb_session_capacity(session_) - static_cast<int>(prompt.size()) + 1;
+        const int emit = prompt.empty() ? 0 : std::max(0, std::min(max_tokens, room));
+        std::vector<float> u(static_cast<size_t>(std::max(max_tokens, 1)), 0.0f);
         std::uniform_real_distribution<float> dis(0.0f, 1.0f);
-        for (float& v : u) v = dis(generator());
+        for (int i = 0; i < emit; i++) u[static_cast<size_t>(i)] = dis(generator());
         const gradb_sampling sp{0, temperature, repetition_penalty, top_k, top_p};
         return run(prompt, sp, max_tokens, u.data());
     }
@@ -188,13 +217,18 @@ private:
         const int stride = static_cast<int>(prompt.size()) + std::max(max_tokens, 0) + 1;
         std::vector<int32_t> out(static_cast<size_t>(stride));
         int32_t len = 0;
-        std::vector<int32_t> p32(prompt.begin(), prompt.end());
-        for (int32_t t : p32) {
-            if (t < 0) throw std::out_of_range("InferenceSession: token id out of vocab range");
-        }
+        const std::vector<int32_t> p32 = checked_ids(prompt);
         detail::check(gradb_generate(session_, p32.data(), offsets, 1, &sp, max_tokens, u, out.data(), stride, &len,
                                      nullptr, nullptr));
         return std::vector<int>(out.begin(), out.begin() + len);
+    }
+    // The ABI treats negative ids as "skip"; the reference rejects them.
+    static std::vector<int32_t> checked_ids(const std::vector<int>& ids) {
+        std::vector<int32_t> out(ids.begin(), ids.end());
+        for (int32_t t : out) {
+            if (t < 0) throw std::out_of_range("InferenceSession: token id out of vocab range");
+        }
+        return out;
     }
     std::string to_string(const std::vector<int>& ids) const {
         if (decoder_ != nullptr) return decoder_->decode(ids);
@@ -207,194 +241,79 @@ private:
     const TokenDecoder* decoder_;
 };
 
-// ---- the data path of `grad eval`: token files, windows, batch order ----------------------------
-//
-// Pre-tokenized corpus files: "TOK1", uint32 vocab size, uint64 id count, then the ids as uint16
-// (include/grad/data/token_file.h:10-36, src/data/token_file.cpp:14-70).
-namespace tokenfile {
-
-inline void write(const std::string& path, const int* data, size_t count, int vocab_size) {
-    if (vocab_size <= 0 || vocab_size > 65536) {
-        throw std::invalid_argument("token file requires 0 < vocab_size <= 65536 (uint16 storage)");
-    }
-    std::ofstream file(path, std::ios::binary);
-    if (!file.is_open()) throw std::runtime_error("Cannot open for writing: " + path);
-    const uint32_t vocab = static_cast<uint32_t>(vocab_size);
-    const uint64_t count64 = count;
-    file.write("TOK1", 4);
-    file.write(reinterpret_cast<const char*>(&vocab), sizeof(vocab));
-    file.write(reinterpret_cast<const char*>(&count64), sizeof(count64));
-    std::vector<uint16_t> ids(count);
-    for (size_t i = 0; i < count; i++) {
-        if (data[i] < 0 || data[i] >= vocab_size) {
-            throw std::runtime_error("token id out of range for vocab while writing " + path);
-        }
-        ids[i] = static_cast<uint16_t>(data[i]);
-    }
-    file.write(reinterpret_cast<const char*>(ids.data()), static_cast<std::streamsize>(count * sizeof(uint16_t)));
-    if (!file.good()) throw std::runtime_error("Write failed: " + path);
-}
-inline void write(const std::string& path, const std::vector<int>& tokens, int vocab_size) {
-    write(path, tokens.data(), tokens.size(), vocab_size);
-}
-[[nodiscard]] inline bool exists(const std::string& path) { return std::ifstream(path, std::ios::binary).good(); }
-
-}  // namespace tokenfile
-
-// Windows of seq_length ids every `stride` ids over a token file; the target is the input shifted
-// by one (include/grad/data/token_file.h:45-70, src/data/token_file.cpp:83-176). The file is read
-// into memory once (the reference maps it); ids are checked against the header's vocab as each
-// window is read, with the reference's messages.
-class MappedTokenDataset {
-public:
-    MappedTokenDataset(const std::string& path, int seq_length, int stride = 1) {
-        if (stride < 1) throw std::invalid_argument("stride must be >= 1");
-        if (seq_length < 1) throw std::invalid_argument("seq_length must be >= 1");
-        seq_length_ = static_cast<size_t>(seq_length);
-        stride_ = static_cast<size_t>(stride);
-        std::ifstream file(path, std::ios::binary | std::ios::ate);
-        if (!file.is_open()) throw std::runtime_error("Cannot open token file: " + path);
-        const std::streamoff size = file.tellg();
-        constexpr size_t kHeaderBytes = 4 + sizeof(uint32_t) + sizeof(uint64_t);
-        if (size < 0 || static_cast<size_t>(size) < kHeaderBytes) {
-            throw std::runtime_error("Token file truncated or unreadable: " + path);
-        }
-        file.seekg(0);
-        char header[kHeaderBytes];
-        file.read(header, kHeaderBytes);
-        if (!file.good()) throw std::runtime_error("Token file truncated or unreadable: " + path);
-        if (std::memcmp(header, "TOK1", 4) != 0) throw std::runtime_error("Not a token file (bad magic): " + path);
-        uint32_t vocab;
-        uint64_t count;
-        std::memcpy(&vocab, header + 4, sizeof(vocab));
-        std::memcpy(&count, header + 4 + sizeof(vocab), sizeof(count));
-        if (vocab == 0 || vocab > 65536) {
-            throw std::runtime_error("Token file vocab " + std::to_string(vocab) + " outside (0, 65536]: " + path);
-        }
-        if (count > (static_cast<size_t>(size) - kHeaderBytes) / sizeof(uint16_t)) {
-            throw std::runtime_error("Token file shorter than its header claims: " + path);
-        }
-        vocab_size_ = static_cast<int>(vocab);
-        if (count < seq_length_ + 1) throw std::runtime_error("Not enough tokens for even one sequence: " + path);
-        tokens_.resize(static_cast<size_t>(count));
-        file.read(reinterpret_cast<char*>(tokens_.data()), static_cast<std::streamsize>(count * sizeof(uint16_t)));
-        if (!file.good()) throw std::runtime_error("Token file truncated or unreadable: " + path);
-    }
-
-    [[nodiscard]] size_t size() const { return (tokens_.size() - seq_length_ - 1) / stride_ + 1; }
-
-    [[nodiscard]] std::pair<std::vector<int>, std::vector<int>> get_item(size_t index) const {
-        if (index >= size()) throw std::out_of_range("MappedTokenDataset index out of range");
-        const size_t start = index * stride_;
-        const uint16_t* window = tokens_.data() + start;
-        for (size_t i = 0; i <= seq_length_; i++) {
-            if (window[i] >= vocab_size_) {
-                throw std::runtime_error("token id " + std::to_string(window[i]) + " at offset " +
-                                         std::to_string(start + i) + " is outside the file's vocab of " +
-                                         std::to_string(vocab_size_));
-            }
-        }
-        std::vector<int> input(seq_length_), target(seq_length_);
-        for (size_t i = 0; i < seq_length_; i++) {
-            input[i] = window[i];
-            target[i] = window[i + 1];
-        }
-        return {input, target};
-    }
-
-    [[nodiscard]] int vocabSize() const { return vocab_size_; }
-    [[nodiscard]] size_t tokenCount() const { return tokens_.size(); }
-    [[nodiscard]] int seqLength() const { return static_cast<int>(seq_length_); }
-
-private:
-    std::vector<uint16_t> tokens_;
-    int vocab_size_ = 0;
-    size_t seq_length_ = 0, stride_ = 0;
-};
-
-// A batch of windows: batch_size x seq_length ids each way (the reference's Batch holds the same
-// ids as float tensors, include/grad/data/dataloader.h:9-15).
-struct Batch {
-    size_t batch_size = 0, seq_length = 0;
-    std::vector<int32_t> input, target;
-};
-
-// Batch order of include/grad/data/dataloader.h:23-46 / src/data/dataloader.cpp:19-72: sequential
-// batches in window order with a ragged last batch, or (shuffle) every row's window drawn uniformly
-// from a std::mt19937 seeded with `seed`; the generator carries over a reset().
-class DataLoader {
-public:
-    DataLoader(std::shared_ptr<MappedTokenDataset> dataset, int batch_size, bool shuffle = true, unsigned int seed = 42)
-        : dataset_(std::move(dataset)), shuffle_(shuffle), rng_(seed) {
-        if (batch_size < 1) throw std::invalid_argument("batch_size must be >= 1");
-        batch_size_ = static_cast<size_t>(batch_size);
-    }
-    [[nodiscard]] bool has_next() const { return current_index_ < dataset_->size(); }
-    [[nodiscard]] Batch next_batch() {
-        if (!has_next()) throw std::runtime_error("No more batches available. Call reset() to start new epoch.");
-        const size_t n = std::min(batch_size_, dataset_->size() - current_index_);
-        Batch batch;
-        batch.batch_size = n;
-        batch.seq_length = static_cast<size_t>(dataset_->seqLength());
-        std::vector<size_t> indices(n);
-        if (shuffle_) {
-            std::uniform_int_distribution<size_t> pick(0, dataset_->size() - 1);
-            for (size_t b = 0; b < n; b++) indices[b] = pick(rng_);
-        } else {
-            for (size_t b = 0; b < n; b++) indices[b] = current_index_ + b;
-        }
-        for (size_t b = 0; b < n; b++) {
-            auto [input, target] = dataset_->get_item(indices[b]);
-            batch.input.insert(batch.input.end(), input.begin(), input.end());
-            batch.target.insert(batch.target.end(), target.begin(), target.end());
-        }
-        current_index_ += n;
-        return batch;
-    }
-    void reset() { current_index_ = 0; }
-    [[nodiscard]] size_t num_batches() const { return (dataset_->size() + batch_size_ - 1) / batch_size_; }
-    [[nodiscard]] size_t dataset_size() const { return dataset_->size(); }
-    [[nodiscard]] const std::shared_ptr<MappedTokenDataset>& dataset() const { return dataset_; }
-    [[nodiscard]] int batch_size() const { return static_cast<int>(batch_size_); }
-
-private:
-    std::shared_ptr<MappedTokenDataset> dataset_;
-    size_t batch_size_ = 1;
-    bool shuffle_;
-    size_t current_index_ = 0;
-    std::mt19937 rng_;
-};
-
 namespace training {
 
-// grad::training::mean_loss (src/training/trainer.cpp:319-340): the loader's next max_batches
-// batches (all that remain when max_batches <= 0), each scored with cross entropy averaged over its
-// rows, the batch losses averaged with the batches' window counts as weights; -1 with no batches.
-// All windows are scored in one device pass, resident_windows at a time; the per-batch averaging
-// is done afterwards in the reference's order.
-inline double mean_loss(const GPTModel& model, DataLoader& loader, int max_batches, int resident_windows = 64) {
-    std::vector<int32_t> in, tg;
-    size_t n = 0, seq = 0;
-    for (int batches = 0; loader.has_next(); batches++) {
-        if (max_batches > 0 && batches >= max_batches) break;
-        Batch batch = loader.next_batch();
+// How mean_loss reads one batch of a loader: appends the batch's input and target ids (row-major, rows x seq) and
+// reports its shape. The default suits batches that hold integer id vectors (`input`, `target`, `batch_size`,
+// `seq_length`); a grad.cpp build specialises it for grad::Batch, whose ids sit in float tensors
+// (include/grad/data/dataloader.h:9-15).
+template <typename BatchT>
+struct BatchIds {
+    static void append(const BatchT& batch, std::vector<int32_t>& in, std::vector<int32_t>& tg, size_t& rows,
+                       size_t& seq) {
         in.insert(in.end(), batch.input.begin(), batch.input.end());
         tg.insert(tg.end(), batch.target.begin(), batch.target.end());
-        n += batch.batch_size;
+        rows = batch.batch_size;
         seq = batch.seq_length;
     }
-    if (n == 0) return -1.0;
+};
+
+// grad::training::mean_loss (src/training/trainer.cpp:319-340) over any loader with the reference DataLoader's
+// has_next() / next_batch() / batch_size(): the loader's next max_batches batches (all that remain when
+// max_batches <= 0), each scored with cross entropy averaged over its rows, the batch losses averaged with the
+// batches' window counts as weights, accumulated in double in batch order; -1 with no batches.
+// Batches are read and scored a bounded number at a time (about resident_windows windows on the device and in
+// host memory), so a validation file of any length streams through.
+template <typename Loader>
+double mean_loss(const GPTModel& model, Loader& loader, int max_batches, int resident_windows = 64) {
+    const size_t batch_size = static_cast<size_t>(std::max(1, loader.batch_size()));
+    const size_t per_pass = std::max<size_t>(1, static_cast<size_t>(std::max(1, resident_windows)) / batch_size);
     gradb_session* session = nullptr;
-    const int resident = static_cast<int>(std::min<size_t>(n, static_cast<size_t>(std::max(1, resident_windows))));
-    detail::check(gradb_session_create(model.handle(), resident, 0, nullptr, &session));
-    double mean = -1.0;
-    // Only the loader's last batch can be ragged, so cutting the concatenation every batch_size windows
-    // reproduces its batches.
-    const gradb_status st = gradb_mean_loss(session, in.data(), tg.data(), static_cast<int>(n), static_cast<int>(seq),
-                                            loader.batch_size(), &mean, nullptr, nullptr);
-    gradb_session_free(session);
-    detail::check(st);
-    return mean;
+    struct Closer {
+        gradb_session*& s;
+        ~Closer() { gradb_session_free(s); }
+    } closer{session};
+    std::vector<int32_t> in, tg;
+    std::vector<float> losses;
+    std::vector<size_t> rows_of;
+    double weighted_loss = 0.0;
+    size_t rows_total = 0, seq = 0;
+    int batches = 0;
+    bool more = true;
+    while (more) {
+        in.clear();
+        tg.clear();
+        rows_of.clear();
+        size_t n = 0;
+        while (rows_of.size() < per_pass) {
+            if (!loader.has_next() || (max_batches > 0 && batches >= max_batches)) {
+                more = false;
+                break;
+            }
+            auto batch = loader.next_batch();
+            size_t rows = 0;
+            BatchIds<decltype(batch)>::append(batch, in, tg, rows, seq);
+            rows_of.push_back(rows);
+            n += rows;
+            batches++;
+        }
+        if (n == 0) break;
+        if (session == nullptr) {
+            const int resident = static_cast<int>(std::max(batch_size, std::min(per_pass * batch_size, n)));
+            detail::check(gradb_session_create(model.handle(), resident, 0, nullptr, &session));
+        }
+        // Only a loader's last batch can be ragged, so cutting the concatenation every batch_size windows
+        // reproduces its batches.
+        losses.assign(rows_of.size(), 0.0f);
+        double unused = 0.0;
+        detail::check(gradb_mean_loss(session, in.data(), tg.data(), static_cast<int>(n), static_cast<int>(seq),
+                                      static_cast<int>(batch_size), &unused, losses.data(), nullptr));
+        for (size_t i = 0; i < rows_of.size(); i++) {
+            weighted_loss += static_cast<double>(losses[i]) * static_cast<double>(rows_of[i]);
+            rows_total += rows_of[i];
+        }
+    }
+    return rows_total > 0 ? weighted_loss / static_cast<double>(rows_total) : -1.0;
 }
 
 }  // namespace training

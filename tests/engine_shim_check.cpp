@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "../include/gradb/engine.hpp"
+#include "support/token_data.hpp"
 
 int main(int argc, char** argv) {
     if (argc < 2) return 2;
@@ -50,6 +51,26 @@ int main(int argc, char** argv) {
     int streamed = 0;
     const int n = gen.generate_stream(prompt, [&](const std::string& s) { streamed += (int)s.size(); }, 0.9f, 5);
     std::printf("stream %d %d\n", n, streamed);
+    // streaming is real: an exception thrown from the third callback ends the generation there
+    int calls = 0;
+    try {
+        gen.generate_stream(prompt, [&](const std::string&) { if (++calls == 3) throw std::logic_error("enough"); }, 0.9f, 9);
+        std::printf("FAIL callback exception was swallowed\n");
+        return 1;
+    } catch (const std::logic_error& e) {
+        std::printf("stream stopped after %d: %s\n", calls, e.what());
+    }
+    // the generator is left where the reference leaves it: one draw per emitted id (here the context fills first)
+    {
+        std::vector<int> longp(static_cast<size_t>(model.getMaxLen() - 2), 1);
+        gradb::TextGen::seed(11);
+        (void)gen.sample_ids(longp, 0.8f, 10, 1.1f, 0, 1.0f);   // emits 3 ids
+        const std::vector<int> after = gen.sample_ids(prompt, 0.8f, 4, 1.1f, 0, 1.0f);
+        gradb::TextGen::seed(11);
+        (void)gen.sample_ids(longp, 0.8f, 3, 1.1f, 0, 1.0f);    // the same three draws, asked for exactly
+        const std::vector<int> again = gen.sample_ids(prompt, 0.8f, 4, 1.1f, 0, 1.0f);
+        std::printf("draws %s\n", after == again ? "aligned" : "misaligned");
+    }
     std::printf("empty '%s'\n", gen.generate_greedy({}, 5).c_str());
     // `grad eval` (src/cli/eval.cpp:77-133): token file -> windows of 5 ids, stride 5 -> batches of 3
     if (argc >= 3) {

@@ -1,4 +1,5 @@
-"""Pre-tokenized corpus files, the input of `grad eval`: "TOK1", uint32 vocab size, uint64 id count,
+"""Test support (not part of the product; a grad.cpp build reads token files with its own classes).
+Pre-tokenized corpus files, the input of `grad eval`: "TOK1", uint32 vocab size, uint64 id count,
 then the ids as uint16 (reference: src/data/token_file.cpp:14-16 header, :33-70 writer, :83-176
 reader and windows). Error messages are the reference's."""
 from __future__ import annotations

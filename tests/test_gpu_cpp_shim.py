@@ -40,6 +40,8 @@ def test_cpp_classes_match_oracle(golden_ckpt, port, tmp_path):
     sample = [int(x) for x in re.search(r"sample((?: \d+)+)", text).group(1).split()]
     assert len(sample) == 12 and sample[:4] == [3, 11, 7, 0]
     assert "stream 5 5" in text
+    assert "stream stopped after 3: enough" in text
+    assert "draws aligned" in text
     assert "empty ''" in text
     # `grad eval` through the C++ classes: token file -> loaders -> training::mean_loss, against the loss the
     # reference computes over the same loaders (tests/golden/tokenfile_golden.npz)

@@ -147,7 +147,7 @@ def test_eval_shape_windows_of_256_on_the_69m_model(G, ck, port, tmp_path, monke
 def test_eval_over_a_token_file_matches_reference(name, G, golden_ckpt):
     """`grad eval` end to end: the reference's token file -> windows -> device scoring -> the loss the
     reference reports for the same loader (sequential, ragged last batch, and its shuffled picks)."""
-    from grad_cpp_b200 import tokenfile
+    from support import tokenfile
     tg = np.load(ROOT / "tests" / "golden" / "tokenfile_golden.npz")
     dm, path = golden_ckpt(name)
     m = G.GPTModel.load(path, 0, G.FP32)

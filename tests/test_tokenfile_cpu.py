@@ -18,7 +18,7 @@ def tg():
 
 @pytest.fixture(scope="module")
 def tokenfile(pkg):
-    from grad_cpp_b200 import tokenfile as tf
+    from support import tokenfile as tf
     return tf
 
 

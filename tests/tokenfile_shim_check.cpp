@@ -1,10 +1,11 @@
-// The data classes of include/gradb/engine.hpp (token files, windows, batch order) driven the way
+// The test-support data classes (tests/support/token_data.hpp: token files, windows, batch order) driven the way
 // `grad eval` drives the reference's (src/cli/eval.cpp:77-92). No device work.
 // Usage: tokenfile_shim_check <token file> <scratch path>
 #include <cstdio>
 #include <string>
 
 #include "../include/gradb/engine.hpp"
+#include "support/token_data.hpp"
 
 static void dump(const char* tag, gradb::DataLoader& loader, int max_batches) {
     for (int b = 0; loader.has_next(); b++) {
