@@ -31,9 +31,11 @@ def build_port() -> None:
     subprocess.run(["make", "-C", str(HERE), "port"], check=True, capture_output=True)
 
 
-def build_ref(reference_root: str = "/root/reference") -> bool:
-    """Builds oracle/_ref when the reference sources are present. Returns availability."""
-    if Path(reference_root).is_dir():
+def build_ref(reference_root: str | None = None) -> bool:
+    """Builds oracle/_ref from the grad.cpp tree at `reference_root` (else the one GRADREF_ROOT names), when that
+    tree is present. Returns whether the compiled reference is available afterwards."""
+    reference_root = reference_root or os.environ.get("GRADREF_ROOT")
+    if reference_root and Path(reference_root).is_dir():
         subprocess.run(["make", "-C", str(HERE), "-j8", "ref", f"REF={reference_root}"], check=True,
                        capture_output=True)
     return ref_available()
