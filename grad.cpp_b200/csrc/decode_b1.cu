@@ -6,17 +6,21 @@
 // dependent stages of a few microseconds each. This kernel removes the per-stage
 // launch and the cold start of every stage's weight stream:
 //
-//  * one CTA per SM stays resident for the whole step; stages are separated by a
-//    grid-wide barrier (bounded spin on a global counter) instead of kernel launches;
+//  * one CTA per SM stays resident for the whole step; there is no grid-wide barrier: every
+//    value that crosses CTAs carries its own "ready" mark, and a consumer polls (bounded)
+//    exactly the values it needs, so a CTA whose inputs have arrived proceeds at once;
 //  * the weights are re-tiled when the model is loaded so that everything one CTA
 //    needs for one stage is a single contiguous block; a producer warp walks the
 //    step's fixed list of blocks and keeps a four-slot shared-memory ring full with
 //    bulk asynchronous copies (TMA, mbarrier completion). The HBM stream therefore
 //    runs ahead of the arithmetic, through barriers and reductions;
-//  * vectors exchanged between CTAs (q, attention partials, projection partials, the
-//    FFN activation) live in a small global workspace that stays in L2 and is read
-//    with cache-global loads; split-K partial sums are added by their consumers in a
-//    fixed order, so results do not depend on scheduling;
+//  * vectors exchanged between CTAs live in a small global workspace that stays in L2, in two
+//    forms. Point-to-point vectors (q, the new K/V row, attention partials) are stored as
+//    64-bit {value, epoch} words: one store publishes value and mark together, no fence, and a
+//    reader accepts a word only when it carries the epoch of the stage it waits for. Sums over
+//    many CTAs (output projection, FFN down) meet in 64-bit fixed-point accumulators whose low
+//    bits count the contributions: integer adds commute, so the sum does not depend on arrival
+//    order, and a reader accepts an element once its count is complete;
 //  * every CTA keeps its own copy of the residual stream in shared memory.
 //
 // Stages per layer: A norm1+QKV(+RoPE, cache write) | B attention over the cache,
@@ -35,9 +39,11 @@ namespace {
 constexpr int kCompute = 512;  // compute threads (16 warps)
 constexpr int kThreadsB1 = kCompute + 32;  // + producer warp
 constexpr int kWarpsB1 = kCompute / 32;
+constexpr int kHold = 2;  // vector elements per compute thread: d <= kHold * kCompute
 constexpr int kSlots = 4;
 constexpr int kSlotBytes = 48 * 1024;
-constexpr uint32_t kPollLimit = 1u << 22;
+constexpr uint32_t kPollLimit = 1u << 22;   // mbarrier waits (each try suspends for a while)
+constexpr uint32_t kSpinLimit = 1u << 20;   // polls of global memory (about a microsecond each)
 constexpr int kMaxLayersB1 = 32;  // layer tables are staged in shared memory
 // Elements of the fixed-point FFN accumulator sit one per 128-byte line: every CTA adds to every element at
 // about the same time, and same-line atomics queue up in one L2 slice.
@@ -47,11 +53,42 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 
 __device__ __forceinline__ void bar_compute() { asm volatile("bar.sync 1, %0;" ::"n"(kCompute) : "memory"); }
 
+// Barrier over the compute threads that also agrees on whether the kernel is giving up: every thread gets the same
+// answer, so all of them leave the stage loop together (a plain read of the flag could split them across a barrier).
+__device__ __forceinline__ bool cta_dead(volatile int* abort_flag) {
+    const uint32_t mine = (uint32_t)*abort_flag;
+    uint32_t any;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 p, %1, 0;\n"
+        "bar.red.or.pred q, 1, %2, p;\n"
+        "selp.u32 %0, 1, 0, q;\n"
+        "}\n"
+        : "=r"(any)
+        : "r"(mine), "n"(kCompute)
+        : "memory");
+    return any != 0;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+
+// Optional stage timestamps of CTA 0 (diagnostics): a no-op unless the session asked for a trace.
+struct Tracer {
+    unsigned long long* buf;
+    int n;
+    __device__ __forceinline__ void stamp() {
+        if (buf) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            buf[n++] = now;
+        }
+    }
+};
 
 struct Ring {
     uint64_t* full;
@@ -60,6 +97,8 @@ struct Ring {
     int* status;
     volatile int* abort_flag;
     uint32_t n;  // chunks consumed / produced so far
+    uint64_t policy;  // producer: L2 evict-first for the weight stream (read once per step; the exchange words and the
+                      // K/V rows are what should stay in L2)
 };
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, volatile int* abort_flag,
@@ -90,10 +129,11 @@ __device__ __forceinline__ void ring_push(Ring& r, const void* src, uint32_t byt
     if (!mbar_wait(&r.empty[s], ph ^ 1, r.status, r.abort_flag, 211)) return;
     const uint32_t bar = smem_u32(&r.full[s]);
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(r.slots + (size_t)s * kSlotBytes)),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_u32(r.slots + (size_t)s * kSlotBytes)),
+        "l"(src), "r"(bytes), "r"(bar), "l"(r.policy)
+        : "memory");
     r.n++;
 }
 
@@ -112,28 +152,157 @@ __device__ __forceinline__ void ring_release(Ring& r) {
     r.n++;
 }
 
-// Grid-wide barrier over the compute threads of all CTAs. Bounded: on expiry the
-// status word is set and the kernel unwinds.
-__device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target, int* status, volatile int* abort_flag) {
-    bar_compute();
-    if (threadIdx.x == 0) {
-        // release: everything this CTA wrote (ordered before by the CTA barrier) is visible to
-        // whoever later observes the count with an acquire load
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
-        uint32_t it = 0;
-        for (;;) {
-            unsigned cur;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(counter) : "memory");
-            if ((int)(cur - target) >= 0) break;
-            if (++it > kPollLimit || *abort_flag) {
-                atomicExch(status, 201);
-                *abort_flag = 1;
-                break;
+// ---- exchange between CTAs without a barrier
+// {value, epoch} words: the 64-bit store is single-copy atomic, so a reader sees the value that belongs to the mark.
+__device__ __forceinline__ void ll_store(unsigned long long* p, float v, uint32_t epoch) {
+    const unsigned long long w = ((unsigned long long)epoch << 32) | __float_as_uint(v);
+    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_vol64(const void* p) {
+    unsigned long long v;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// Waits (bounded) until every one of the N words carries `epoch`; on expiry the status word is set.
+template <int N>
+__device__ __forceinline__ void ll_wait(const unsigned long long* const (&ptr)[N], const bool (&want)[N], uint32_t epoch,
+                                        float (&out)[N], int* status, volatile int* abort_flag, int code) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        unsigned long long w[N];
+#pragma unroll
+        for (int i = 0; i < N; i++) w[i] = want[i] ? ld_vol64(ptr[i]) : ((unsigned long long)epoch << 32);
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < N; i++) ok = ok && (uint32_t)(w[i] >> 32) == epoch;
+        if (ok) {
+#pragma unroll
+            for (int i = 0; i < N; i++) out[i] = __uint_as_float((uint32_t)w[i]);
+            return;
+        }
+        if (*abort_flag) break;
+    }
+#pragma unroll
+    for (int i = 0; i < N; i++) out[i] = 0.f;
+    if (!*abort_flag) {
+        atomicExch(status, code);
+        *abort_flag = 1;
+    }
+}
+
+// Fixed-point accumulators: units of 2^-32 above kCountBits of contribution count.
+constexpr int kCountBits = 10;  // up to 1023 contributing CTAs
+__device__ __forceinline__ void acc_add(long long* p, float y) {
+    const long long q = __double2ll_rn((double)y * 4294967296.0);
+    const unsigned long long add = ((unsigned long long)q << kCountBits) + 1ull;
+    asm volatile("red.global.add.u64 [%0], %1;" ::"l"(p), "l"(add) : "memory");
+}
+__device__ __forceinline__ float acc_value(unsigned long long w) {
+    return (float)((double)((long long)w >> kCountBits) * 2.3283064365386963e-10);
+}
+
+// x_s += bias + the KS partial vectors part[ks][d] (marked words), added in slice order once all have arrived.
+__device__ bool add_partials(float* x_s, const float* bias, const unsigned long long* part, int KS, uint32_t epoch, int d,
+                             int* status, volatile int* abort_flag, int code) {
+    float bv[kHold];
+#pragma unroll
+    for (int i = 0; i < kHold; i++) {
+        const int k = threadIdx.x + i * kCompute;
+        bv[i] = (bias && k < d) ? __ldg(bias + k) : 0.f;
+    }
+    if (KS <= 4) {  // every word of this thread in one round of loads
+        const unsigned long long* ptr[4 * kHold];
+        bool want[4 * kHold];
+        float o[4 * kHold];
+#pragma unroll
+        for (int i = 0; i < kHold; i++) {
+            const int k = threadIdx.x + i * kCompute;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                ptr[4 * i + u] = part + (size_t)min(u, KS - 1) * d + min(k, d - 1);
+                want[4 * i + u] = k < d && u < KS;
+            }
+        }
+        ll_wait<4 * kHold>(ptr, want, epoch, o, status, abort_flag, code);
+#pragma unroll
+        for (int i = 0; i < kHold; i++) {
+            const int k = threadIdx.x + i * kCompute;
+            if (k < d) {
+                float acc = x_s[k] + bv[i];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    if (u < KS) acc += o[4 * i + u];
+                }
+                x_s[k] = acc;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kHold; i++) {
+            const int k = threadIdx.x + i * kCompute;
+            if (k < d) {
+                float acc = x_s[k] + bv[i];
+                for (int s0 = 0; s0 < KS; s0 += 4) {
+                    const unsigned long long* ptr[4];
+                    bool want[4];
+                    float o[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        ptr[u] = part + (size_t)min(s0 + u, KS - 1) * d + k;
+                        want[u] = s0 + u < KS;
+                    }
+                    ll_wait<4>(ptr, want, epoch, o, status, abort_flag, code);
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        if (s0 + u < KS) acc += o[u];
+                    }
+                }
+                x_s[k] = acc;
             }
         }
     }
-    bar_compute();
-    return *abort_flag == 0;
+    return cta_dead(abort_flag);
+}
+
+// x_s += bias + the accumulated vector, once all `expected` contributions of every element have landed.
+__device__ bool add_accumulated(float* x_s, const float* bias, const long long* acc, uint32_t expected, int d, int* status,
+                                volatile int* abort_flag, int code) {
+    float bv[kHold];
+    unsigned long long w[kHold];
+    bool pend[kHold];
+#pragma unroll
+    for (int i = 0; i < kHold; i++) {
+        const int k = threadIdx.x + i * kCompute;
+        pend[i] = k < d;
+        bv[i] = (bias && k < d) ? __ldg(bias + k) : 0.f;
+        w[i] = 0ull;
+    }
+    bool gave_up = true;
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        bool all = true;
+#pragma unroll
+        for (int i = 0; i < kHold; i++) {  // all loads of a round are issued together
+            if (pend[i]) w[i] = ld_vol64(acc + (size_t)(threadIdx.x + i * kCompute) * kAccStride);
+        }
+#pragma unroll
+        for (int i = 0; i < kHold; i++) {
+            if (pend[i]) pend[i] = (uint32_t)(w[i] & ((1u << kCountBits) - 1u)) != expected;
+            all = all && !pend[i];
+        }
+        if (all || *abort_flag) {
+            gave_up = !all;
+            break;
+        }
+    }
+    if (gave_up && !*abort_flag) {
+        atomicExch(status, code);
+        *abort_flag = 1;
+    }
+#pragma unroll
+    for (int i = 0; i < kHold; i++) {
+        const int k = threadIdx.x + i * kCompute;
+        if (k < d) x_s[k] = (x_s[k] + bv[i]) + acc_value(w[i]);
+    }
+    return cta_dead(abort_flag);
 }
 
 __device__ __forceinline__ float4 ld_tile4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -149,28 +318,46 @@ __device__ __forceinline__ float ld_tile1(const __nv_bfloat16* p) { return __bfl
 
 // out_s[0..CW) = in_s[0..rows) @ tile, the tile arriving through the ring in chunks of
 // whole rows. All compute threads call this together.
-// `rows` of the tile's Kt (zero padded) rows carry data.
+// `rows` of the tile's Kt (zero padded) rows carry data. CW is 16, 32 or 64.
 template <typename WT>
-__device__ void tile_matvec(Ring& ring, const float* in_s, int rows, int Kt, int CW, float* red_s, float* out_s) {
+__device__ void tile_matvec(Ring& ring, const float* in_s, int rows, int Kt, int CW, float* red_s, float* out_s,
+                            Tracer& tr) {
     const int t = threadIdx.x, lane = t & 31, w = t >> 5;
-    const int cg = CW / 4, R = kCompute / cg;
-    const int c4 = t % cg, r0 = t / cg;
-    const int chunk_rows = kSlotBytes / (CW * (int)sizeof(WT));
+    const int lg = 31 - __clz(CW) - 2;                 // log2 of the column groups (four columns each)
+    const int cg = 1 << lg, R = kCompute >> lg;
+    const int c4 = t & (cg - 1), r0 = t >> lg;
+    const int chunk_rows = (kSlotBytes / (int)sizeof(WT)) >> (lg + 2);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int base = 0; base < Kt; base += chunk_rows) {  // same chunking as the producer's
         const int n = min(chunk_rows, rows - base);
+        const bool last = base + chunk_rows >= Kt;
         const WT* tile = reinterpret_cast<const WT*>(ring_acquire(ring));
-#pragma unroll 4
-        for (int k = r0; k < n; k += R) {
-            const float4 wv = ld_tile4(tile + (size_t)k * CW + c4 * 4);
-            const float xv = in_s[base + k];
-            acc.x += xv * wv.x;
-            acc.y += xv * wv.y;
-            acc.z += xv * wv.z;
-            acc.w += xv * wv.w;
+        tr.stamp();
+        const WT* tp = tile + ((size_t)r0 << (lg + 2)) + c4 * 4;
+        const float* xp = in_s + base + r0;
+        const size_t tstep = (size_t)R << (lg + 2);
+        int k = r0;
+        for (; k + 3 * R < n; k += 4 * R) {  // four rows in flight
+            const float4 w0 = ld_tile4(tp), w1 = ld_tile4(tp + tstep), w2 = ld_tile4(tp + 2 * tstep),
+                         w3 = ld_tile4(tp + 3 * tstep);
+            const float x0 = xp[0], x1 = xp[R], x2 = xp[2 * R], x3 = xp[3 * R];
+            acc.x += x0 * w0.x; acc.y += x0 * w0.y; acc.z += x0 * w0.z; acc.w += x0 * w0.w;
+            acc.x += x1 * w1.x; acc.y += x1 * w1.y; acc.z += x1 * w1.z; acc.w += x1 * w1.w;
+            acc.x += x2 * w2.x; acc.y += x2 * w2.y; acc.z += x2 * w2.z; acc.w += x2 * w2.w;
+            acc.x += x3 * w3.x; acc.y += x3 * w3.y; acc.z += x3 * w3.z; acc.w += x3 * w3.w;
+            tp += 4 * tstep;
+            xp += 4 * R;
         }
-        ring_release(ring);
+        for (; k < n; k += R) {
+            const float4 wv = ld_tile4(tp);
+            const float xv = xp[0];
+            acc.x += xv * wv.x; acc.y += xv * wv.y; acc.z += xv * wv.z; acc.w += xv * wv.w;
+            tp += tstep;
+            xp += R;
+        }
+        if (!last) ring_release(ring);
     }
+    tr.stamp();
     for (int o = cg; o < 32; o <<= 1) {
         acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
         acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
@@ -178,7 +365,8 @@ __device__ void tile_matvec(Ring& ring, const float* in_s, int rows, int Kt, int
         acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
     }
     if (lane < cg) *reinterpret_cast<float4*>(&red_s[w * 64 + lane * 4]) = acc;
-    bar_compute();
+    // one barrier both hands the last slot back and publishes the per-warp sums
+    ring_release(ring);
     if (t < CW) {
         float s = 0.f;
 #pragma unroll
@@ -201,20 +389,30 @@ __device__ __forceinline__ float block_total(float v, float* sh) {
     return s;
 }
 
-// in_s = norm(x_s) (inference.cpp:30-58). gamma/beta are fetched before the reductions so their
-// latency overlaps them.
-__device__ void norm_vec(const float* x_s, float* in_s, const float* gamma, const float* beta, int d, int rms,
-                         float* sh) {
-    constexpr int kHold = 4;  // elements per thread kept in registers (d <= 2048); beyond that, loaded late
-    float gv[kHold], bv[kHold];
+// Gain and shift of a norm, fetched into registers a stage ahead of their use (an L2 round trip is most of what a
+// norm of a few hundred elements would otherwise take).
+struct NormVec {
+    float g[kHold], b[kHold];
+    __device__ __forceinline__ void fetch(const float* gamma, const float* beta, int d, int rms) {
+#pragma unroll
+        for (int i = 0; i < kHold; i++) {
+            const int k = threadIdx.x + i * kCompute;
+            g[i] = k < d ? __ldg(gamma + k) : 0.f;
+            b[i] = (k < d && !rms) ? __ldg(beta + k) : 0.f;
+        }
+    }
+};
+
+// in_s = norm(x_s) (inference.cpp:30-58).
+__device__ void norm_vec(const float* x_s, float* in_s, const NormVec& nv, int d, int rms, float* sh) {
+    float xv[kHold];
+    float s = 0.f;
 #pragma unroll
     for (int i = 0; i < kHold; i++) {
         const int k = threadIdx.x + i * kCompute;
-        gv[i] = k < d ? __ldg(gamma + k) : 0.f;
-        bv[i] = (k < d && !rms) ? __ldg(beta + k) : 0.f;
+        xv[i] = k < d ? x_s[k] : 0.f;
+        s += rms ? xv[i] * xv[i] : xv[i];
     }
-    float s = 0.f;
-    for (int k = threadIdx.x; k < d; k += kCompute) s += rms ? x_s[k] * x_s[k] : x_s[k];
     s = block_total(s, sh);
     float mean = 0.f, r;
     if (rms) {
@@ -222,9 +420,11 @@ __device__ void norm_vec(const float* x_s, float* in_s, const float* gamma, cons
     } else {
         mean = s / (float)d;
         float v = 0.f;
-        for (int k = threadIdx.x; k < d; k += kCompute) {
-            const float dl = x_s[k] - mean;
-            v += dl * dl;
+#pragma unroll
+        for (int i = 0; i < kHold; i++) {
+            const int k = threadIdx.x + i * kCompute;
+            const float dl = xv[i] - mean;
+            if (k < d) v += dl * dl;
         }
         v = block_total(v, sh);
         r = 1.0f / sqrtf(v / (float)d + 1e-5f);
@@ -232,42 +432,7 @@ __device__ void norm_vec(const float* x_s, float* in_s, const float* gamma, cons
 #pragma unroll
     for (int i = 0; i < kHold; i++) {
         const int k = threadIdx.x + i * kCompute;
-        if (k < d) in_s[k] = rms ? gv[i] * x_s[k] * r : gv[i] * (x_s[k] - mean) * r + bv[i];
-    }
-    for (int k = threadIdx.x + kHold * kCompute; k < d; k += kCompute) {
-        in_s[k] = rms ? __ldg(gamma + k) * x_s[k] * r : __ldg(gamma + k) * (x_s[k] - mean) * r + __ldg(beta + k);
-    }
-    bar_compute();
-}
-
-// x_s += bias + sum of KS partial vectors (fixed order)
-__device__ void add_partials(float* x_s, const float* bias, const float* part, int KS, int d) {
-    // All loads of an element are issued before the first add, so they share one trip to L2;
-    // the adds keep the slice order.
-    constexpr int kMaxKS = 16;
-    for (int k = threadIdx.x; k < d; k += kCompute) {
-        float pv[kMaxKS];
-        const float bv = bias ? __ldg(bias + k) : 0.f;
-#pragma unroll
-        for (int s = 0; s < kMaxKS; s++) pv[s] = s < KS ? __ldcg(part + (size_t)s * d + k) : 0.f;
-        float v = x_s[k] + bv;
-#pragma unroll
-        for (int s = 0; s < kMaxKS; s++) {
-            if (s < KS) v += pv[s];
-        }
-        x_s[k] = v;
-    }
-    bar_compute();
-}
-
-// x_s += bias + the fixed-point accumulator (units of 2^-32), read past L1: other CTAs' adds land in L2
-__device__ void add_fixed(float* x_s, const float* bias, const long long* acc, int d) {
-    for (int k = threadIdx.x; k < d; k += kCompute) {
-        const float bv = bias ? __ldg(bias + k) : 0.f;
-        const long long q = __ldcg(acc + (size_t)k * kAccStride);
-        float v = x_s[k] + bv;
-        v += (float)((double)q * 2.3283064365386963e-10);
-        x_s[k] = v;
+        if (k < d) in_s[k] = rms ? nv.g[i] * xv[i] * r : nv.g[i] * (xv[i] - mean) * r + nv.b[i];
     }
     bar_compute();
 }
@@ -287,7 +452,7 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
     if (token < 0) return;  // the sequence takes no part in this step (uniform over the grid)
     const int pos = p.pos[0];
     const bool do_logits = p.logit_tok[0] >= 0;
-    const unsigned base = *p.bar_base;
+    const unsigned step = p.sync[0];  // steps this session has run: names the epochs and the accumulator set of this launch
     const int d = p.d, hs = p.hs;
 
     uint8_t* slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -308,13 +473,16 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         abort_flag = 0;
+        // This CTA has read its launch state (token, position, step): the words may change once every CTA has.
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync + 1) : "memory");
     }
     __syncthreads();
-    Ring ring{full_bar, empty_bar, slots, p.status, &abort_flag, 0};
+    Ring ring{full_bar, empty_bar, slots, p.status, &abort_flag, 0, 0};
 
     if (t >= kCompute) {
         // ---------------------------------------------------------------- producer warp
         if (t == kCompute) {
+            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(ring.policy));
             const uint32_t wb = (uint32_t)p.wbytes;
             auto push_tile = [&](const void* basep, const B1Mat& m) {
                 const uint8_t* src = static_cast<const uint8_t*>(basep) + (size_t)g * m.tile_elems * wb;
@@ -355,23 +523,20 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
 
     // -------------------------------------------------------------------- compute warps
     const int lane = t & 31, w = t >> 5;
-    unsigned bar_i = 0;
-    int trace_i = 0;
-    auto stamp = [&]() {
-        if (p.trace && g == 0 && t == 0) {
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            p.trace[trace_i++] = now;
-        }
-    };
-    auto barrier = [&]() {
-        bar_i++;
-        stamp();  // stage work done
-        const bool okb = grid_barrier(p.bar_counter, base + bar_i * (unsigned)p.G, p.status, &abort_flag);
-        stamp();  // barrier passed
-        return okb;
-    };
+    Tracer tr{(p.trace && g == 0 && t == 0) ? p.trace : nullptr, 0};
+    auto stamp = [&]() { tr.stamp(); };
     stamp();
+
+    // Accumulators come in two sets, used by alternate steps. The set of the NEXT step is cleared here: its last
+    // readers finished with the previous launch, and its next adds come with the next one.
+    const size_t acc_set = (size_t)p.L * d * kAccStride;  // words per set: one FFN accumulator per layer
+    long long* acc_mine = p.acc + (size_t)(step & 1u) * acc_set;
+    {
+        long long* other = p.acc + (size_t)((step + 1u) & 1u) * acc_set;
+        for (int k = g * kCompute + t; k < p.L * d; k += p.G * kCompute) other[(size_t)k * kAccStride] = 0;
+    }
+    // Epoch of an exchange: unique per (step, layer, kind), never 0 (the workspace starts zeroed).
+    const uint32_t epoch0 = step * (uint32_t)(4 * p.L + 1) + 1u;
 
     // x = E[token] (+ P[pos])  (inference.cpp:159-182)
     for (int k = t; k < d; k += kCompute) {
@@ -381,17 +546,24 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
     }
     bar_compute();
 
-    const int S = p.attn_splits;
+    // context splits of the attention: one per 64 cached positions, so short contexts exchange few partials
+    const int S = max(1, min(p.attn_splits, (pos + 64) / 64));
     const float scale = 1.0f / sqrtf((float)hs);
-    bool alive = true;
 
-    for (int l = 0; l < p.L && alive; l++) {
+    NormVec nv1, nv2;  // gains/shifts of the next norm1 and norm2, fetched a stage early
+    nv1.fetch(layers_s[0].n1g, layers_s[0].n1b, d, p.modern);
+    for (int l = 0; l < p.L; l++) {
         const B1Layer* ly = layers_s + l;
         float* kc = p.kcache + (size_t)l * p.layer_cache_stride;
         float* vc = p.vcache + (size_t)l * p.layer_cache_stride;
+        long long* acc_f = acc_mine + (size_t)l * d * kAccStride;
+        const uint32_t ep_q = epoch0 + 4u * l, ep_kv = ep_q + 1u, ep_att = ep_q + 2u, ep_o = ep_q + 3u;
 
         // ---- A: (previous FFN output joins the residual) norm1, Q/K/V columns of this CTA
-        if (l > 0) add_fixed(x_s, (layers_s + l - 1)->b2, p.ffn_acc + (size_t)((l - 1) & 1) * d * kAccStride, d);
+        if (l > 0 && add_accumulated(x_s, (layers_s + l - 1)->b2, acc_f - (size_t)d * kAccStride, (uint32_t)p.up.tiles,
+                                     d, p.status, &abort_flag, 221)) {
+            break;
+        }
         if (g < p.qkv.tiles) {
             const int CW = p.qkv.CW;
             // this thread's output pair: fetch its bias and rotation before the heavy part
@@ -409,33 +581,36 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
                     sn = __ldg(p.rope_sin + (size_t)pos * (hs / 2) + c_in / 2);
                 }
             }
-            norm_vec(x_s, in_s, ly->n1g, ly->n1b, d, p.modern, sh);
-            tile_matvec<WT>(ring, in_s, d, p.qkv.Kt, p.qkv.CW, red_s, out_s);
+            stamp();
+            norm_vec(x_s, in_s, nv1, d, p.modern, sh);
+            stamp();
+            tile_matvec<WT>(ring, in_s, d, p.qkv.Kt, p.qkv.CW, red_s, out_s, tr);
+            stamp();
             if (mine) {
-                {
-                    float a0 = out_s[2 * t] + b0, a1 = out_s[2 * t + 1] + b1;
-                    if (p.rope_cos && which < 2) {  // inference.cpp:101-115
-                        const float r0 = a0 * cs - a1 * sn, r1 = a0 * sn + a1 * cs;
-                        a0 = r0;
-                        a1 = r1;
-                    }
-                    if (which == 0) {
-                        *reinterpret_cast<float2*>(p.q + n_in) = make_float2(a0, a1);
-                    } else {
-                        float* cache = which == 1 ? kc : vc;
-                        *reinterpret_cast<float2*>(cache + ((size_t)h * p.T + pos) * hs + c_in) = make_float2(a0, a1);
-                    }
+                float a0 = out_s[2 * t] + b0, a1 = out_s[2 * t + 1] + b1;
+                if (p.rope_cos && which < 2) {  // inference.cpp:101-115
+                    const float r0 = a0 * cs - a1 * sn, r1 = a0 * sn + a1 * cs;
+                    a0 = r0;
+                    a1 = r1;
+                }
+                if (which == 0) {
+                    ll_store(p.q_ll + n_in, a0, ep_q);
+                    ll_store(p.q_ll + n_in + 1, a1, ep_q);
+                } else {
+                    // the new row: to this step's readers through the marked copy, to later steps through the cache
+                    unsigned long long* row = p.kv_ll + (size_t)(which - 1) * d + n_in;
+                    ll_store(row, a0, ep_kv);
+                    ll_store(row + 1, a1, ep_kv);
+                    float* cache = which == 1 ? kc : vc;
+                    *reinterpret_cast<float2*>(cache + ((size_t)h * p.T + pos) * hs + c_in) = make_float2(a0, a1);
                 }
             }
         }
-        if (!(alive = barrier())) break;
+        if (cta_dead(&abort_flag)) break;  // also: out_s is free for the next stage
+        stamp();
 
         // ---- B: attention of (head, context split) g over the cached positions (inference.cpp:208-225)
-        // This layer's FFN accumulator is cleared here: its previous contents (layer l-2) were consumed
-        // before the barrier just passed, and the first add comes two barriers from now.
-        for (int k = g * kCompute + t; k < d; k += p.G * kCompute) {
-            p.ffn_acc[((size_t)(l & 1) * d + k) * kAccStride] = 0;
-        }
+        nv2.fetch(ly->n2g, ly->n2b, d, p.modern);
         if (g < p.H * S) {
             const int head = g / S, split = g % S;
             const int ctx = pos + 1;
@@ -443,22 +618,41 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
             const int t0 = split * cps, t1 = min(ctx, t0 + cps);
             const float* K = kc + (size_t)head * p.T * hs;
             const float* V = vc + (size_t)head * p.T * hs;
-            const float2 qv = __ldcg(reinterpret_cast<const float2*>(p.q + head * hs) + lane);
+            float2 qv;
+            {
+                const unsigned long long* const ptr[2] = {p.q_ll + head * hs + 2 * lane, p.q_ll + head * hs + 2 * lane + 1};
+                const bool want[2] = {true, true};
+                float o[2];
+                ll_wait<2>(ptr, want, ep_q, o, p.status, &abort_flag, 222);
+                qv = make_float2(o[0], o[1]);
+            }
+            stamp();
             float m_run = -INFINITY, l_run = 0.f, o0 = 0.f, o1 = 0.f;
-            // four positions per trip: their K and V rows are requested together
+            // four positions per trip: their K and V rows are requested together; the newest position's rows come
+            // from this step's producers
             for (int tt = t0 + w; tt < t1; tt += 4 * kWarpsB1) {
                 float2 kv[4], vv[4];
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const int tu = tt + u * kWarpsB1;
-                    if (tu < t1) {
+                    if (tu < t1 && tu != pos) {
                         kv[u] = __ldcg(reinterpret_cast<const float2*>(K + (size_t)tu * hs) + lane);
                         vv[u] = __ldcg(reinterpret_cast<const float2*>(V + (size_t)tu * hs) + lane);
                     }
                 }
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
-                    if (tt + u * kWarpsB1 < t1) {
+                    const int tu = tt + u * kWarpsB1;
+                    if (tu < t1) {
+                        if (tu == pos) {
+                            const unsigned long long* kr = p.kv_ll + head * hs + 2 * lane;
+                            const unsigned long long* const ptr[4] = {kr, kr + 1, kr + d, kr + d + 1};
+                            const bool want[4] = {true, true, true, true};
+                            float o[4];
+                            ll_wait<4>(ptr, want, ep_kv, o, p.status, &abort_flag, 223);
+                            kv[u] = make_float2(o[0], o[1]);
+                            vv[u] = make_float2(o[2], o[3]);
+                        }
                         const float sc = warp_sum(qv.x * kv[u].x + qv.y * kv[u].y) * scale;
                         const float m_new = fmaxf(m_run, sc);
                         const float corr = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
@@ -470,6 +664,7 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
                     }
                 }
             }
+            stamp();
             // combine the warps in order; red_s rows: [w][0..63] = o, then m and l
             red_s[w * 64 + 2 * lane] = o0;
             red_s[w * 64 + 2 * lane + 1] = o1;
@@ -490,15 +685,17 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
                     a0 += red_s[i * 64 + 2 * lane] * f;
                     a1 += red_s[i * 64 + 2 * lane + 1] * f;
                 }
-                float* part = p.attn_part + (size_t)g * (hs + 2);
-                *reinterpret_cast<float2*>(part + 2 * lane) = make_float2(a0, a1);
+                unsigned long long* part = p.attn_ll + (size_t)g * (hs + 2);
+                ll_store(part + 2 * lane, a0, ep_att);
+                ll_store(part + 2 * lane + 1, a1, ep_att);
                 if (lane == 0) {
-                    part[hs] = M;
-                    part[hs + 1] = Lsum;
+                    ll_store(part + hs, M, ep_att);
+                    ll_store(part + hs + 1, Lsum, ep_att);
                 }
             }
         }
-        if (!(alive = barrier())) break;
+        if (cta_dead(&abort_flag)) break;  // also: red_s / out_s are free for the next stage
+        stamp();
 
         // ---- C: output projection tile; its input rows are combined from the splits
         if (g < p.o.tiles) {
@@ -506,48 +703,64 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
             const int k0 = ks * p.o.Kt, rows = min(p.o.Kt, d - k0);
             for (int k = t; k < rows; k += kCompute) {
                 const int kk = k0 + k, head = kk / hs, dim = kk % hs;
-                const float* part = p.attn_part + (size_t)head * S * (hs + 2);
-                constexpr int kMaxS = 16;  // all loads first: one trip to L2 instead of three
-                float ms[kMaxS], ls[kMaxS], os[kMaxS];
+                const unsigned long long* part = p.attn_ll + (size_t)head * S * (hs + 2);
+                // splits four at a time: their (max, sum, value) words are requested together, then folded in order
+                float M = -INFINITY, Lsum = 0.f, acc = 0.f;
+                for (int s0 = 0; s0 < S; s0 += 4) {
+                    const unsigned long long* ptr[12];
+                    bool want[12];
+                    float o[12];
 #pragma unroll
-                for (int s = 0; s < kMaxS; s++) {
-                    const bool in = s < S;
-                    ms[s] = in ? __ldcg(part + s * (hs + 2) + hs) : -INFINITY;
-                    ls[s] = in ? __ldcg(part + s * (hs + 2) + hs + 1) : 0.f;
-                    os[s] = in ? __ldcg(part + s * (hs + 2) + dim) : 0.f;
-                }
-                float M = -INFINITY;
+                    for (int u = 0; u < 4; u++) {
+                        const unsigned long long* ps = part + (size_t)min(s0 + u, S - 1) * (hs + 2);
+                        ptr[3 * u] = ps + hs;
+                        ptr[3 * u + 1] = ps + hs + 1;
+                        ptr[3 * u + 2] = ps + dim;
+                        want[3 * u] = want[3 * u + 1] = want[3 * u + 2] = s0 + u < S;
+                    }
+                    ll_wait<12>(ptr, want, ep_att, o, p.status, &abort_flag, 224);
 #pragma unroll
-                for (int s = 0; s < kMaxS; s++) M = fmaxf(M, ms[s]);
-                float Lsum = 0.f, acc = 0.f;
-#pragma unroll
-                for (int s = 0; s < kMaxS; s++) {
-                    const float f = ms[s] == -INFINITY ? 0.f : expf(ms[s] - M);
-                    Lsum += ls[s] * f;
-                    acc += os[s] * f;
+                    for (int u = 0; u < 4; u++) {
+                        const float m = o[3 * u];
+                        if (s0 + u < S && m != -INFINITY) {  // an empty split carries no weight
+                            const float m_new = fmaxf(M, m);
+                            const float c = M == -INFINITY ? 0.f : expf(M - m_new);
+                            const float f = expf(m - m_new);
+                            Lsum = Lsum * c + o[3 * u + 1] * f;
+                            acc = acc * c + o[3 * u + 2] * f;
+                            M = m_new;
+                        }
+                    }
                 }
                 in_s[k] = acc / Lsum;
             }
             bar_compute();
-            tile_matvec<WT>(ring, in_s, rows, p.o.Kt, p.o.CW, red_s, out_s);
-            if (t < p.o.CW && ct * p.o.CW + t < d) p.opart[(size_t)ks * d + ct * p.o.CW + t] = out_s[t];
+            stamp();
+            tile_matvec<WT>(ring, in_s, rows, p.o.Kt, p.o.CW, red_s, out_s, tr);
+            if (t < p.o.CW && ct * p.o.CW + t < d) ll_store(p.o_ll + (size_t)ks * d + ct * p.o.CW + t, out_s[t], ep_o);
         }
-        if (!(alive = barrier())) break;
+        stamp();
 
-        // ---- D: x += attn @ Wo + bo; norm2; FFN up columns of this CTA
-        add_partials(x_s, ly->bo, p.opart, p.o.KS, d);
+        // ---- D: x += attn @ Wo + bo; norm2; FFN up columns of this CTA, then their share of FFN down
+        if (add_partials(x_s, ly->bo, p.o_ll, p.o.KS, ep_o, d, p.status, &abort_flag, 225)) break;
+        if (l + 1 < p.L) nv1.fetch(layers_s[l + 1].n1g, layers_s[l + 1].n1b, d, p.modern);
+        else nv1.fetch(p.fng, p.fnb, d, p.modern);
         if (g < p.up.tiles) {
-            norm_vec(x_s, in_s, ly->n2g, ly->n2b, d, p.modern, sh);
+            stamp();
+            norm_vec(x_s, in_s, nv2, d, p.modern, sh);
+            stamp();
             const int CW = p.up.CW;
             if (p.modern) {  // silu(gate) * up (inference.cpp:232-239)
-                tile_matvec<WT>(ring, in_s, d, p.up.Kt, CW, red_s, out2_s);
-                tile_matvec<WT>(ring, in_s, d, p.up.Kt, CW, red_s, out_s);
+                tile_matvec<WT>(ring, in_s, d, p.up.Kt, CW, red_s, out2_s, tr);
+                stamp();
+                tile_matvec<WT>(ring, in_s, d, p.up.Kt, CW, red_s, out_s, tr);
+                stamp();
                 if (t < CW) {
                     const float gt = out2_s[t];
                     hid_s[t] = g * CW + t < p.dff ? out_s[t] * (gt / (1.0f + expf(-gt))) : 0.f;
                 }
             } else {  // gelu(h @ W1 + b1) (inference.cpp:69-80, 242-244)
-                tile_matvec<WT>(ring, in_s, d, p.up.Kt, CW, red_s, out_s);
+                tile_matvec<WT>(ring, in_s, d, p.up.Kt, CW, red_s, out_s, tr);
                 if (t < CW) {
                     float hv = 0.f;
                     if (g * CW + t < p.dff) {
@@ -564,11 +777,12 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
             {
                 const int row0 = g * CW, nrows = min(CW, p.dff - row0);
                 const int chunk_rows = kSlotBytes / (d * (int)sizeof(WT));
-                constexpr int kColsPerThread = 4;  // d <= 4 * kCompute
-                float y[kColsPerThread] = {0.f, 0.f, 0.f, 0.f};
+                constexpr int kColsPerThread = kHold;
+                float y[kColsPerThread] = {};
                 for (int r = 0; r < nrows; r += chunk_rows) {
                     const int n = min(chunk_rows, nrows - r);
                     const WT* rows = reinterpret_cast<const WT*>(ring_acquire(ring));
+                    stamp();
 #pragma unroll
                     for (int c = 0; c < kColsPerThread; c++) {
                         const int col = t + c * kCompute;
@@ -580,25 +794,23 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
                     }
                     ring_release(ring);
                 }
-                long long* acc = p.ffn_acc + (size_t)(l & 1) * d * kAccStride;
+                stamp();
 #pragma unroll
                 for (int c = 0; c < kColsPerThread; c++) {
                     const int col = t + c * kCompute;
-                    if (col < d) {
-                        const long long q = __double2ll_rn((double)y[c] * 4294967296.0);
-                        asm volatile("red.global.add.u64 [%0], %1;" ::"l"(acc + (size_t)col * kAccStride), "l"(q) : "memory");
-                    }
+                    if (col < d) acc_add(acc_f + (size_t)col * kAccStride, y[c]);
                 }
             }
         }
-        if (!(alive = barrier())) break;
+        stamp();
     }
 
-    if (alive) {
+    if (!cta_dead(&abort_flag)) {
         // ---- final norm + tied-embedding logits (inference.cpp:251-254)
         if (do_logits) {
-            add_fixed(x_s, (layers_s + p.L - 1)->b2, p.ffn_acc + (size_t)((p.L - 1) & 1) * d * kAccStride, d);
-            norm_vec(x_s, in_s, p.fng, p.fnb, d, p.modern, sh);
+            (void)add_accumulated(x_s, (layers_s + p.L - 1)->b2, acc_mine + (size_t)(p.L - 1) * d * kAccStride,
+                                  (uint32_t)p.up.tiles, d, p.status, &abort_flag, 226);
+            norm_vec(x_s, in_s, nv1, d, p.modern, sh);
             const int r0 = g * p.logit_rows_per_cta, r1 = min(p.V, r0 + p.logit_rows_per_cta);
             for (int r = r0; r < r1; r += p.logit_chunk_rows) {
                 const int n = min(p.logit_chunk_rows, r1 - r);
@@ -618,15 +830,27 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
             }
         }
         stamp();
-        if (g == 0 && t == 0) {
+    }
+    if (g == 0 && t == 0) {
+        // The launch state moves on only when every CTA has read it (they all have, long ago: the wait is a formality
+        // that keeps a late starter from seeing the next step's position).
+        const unsigned want = (step + 1u) * (unsigned)p.G;
+        bool seen = false;
+        for (uint32_t it = 0; it < kSpinLimit && !seen; ++it) {
+            unsigned cur;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(p.sync + 1) : "memory");
+            seen = cur == want;
+        }
+        if (!seen) atomicExch(p.status, 227);
+        if (seen && !abort_flag) {
             p.pos[0] = pos + 1;
             if (p.append_hist) {
                 const int n = p.hist_len[0];
                 if (n < p.hist_stride) p.hist[n] = token;
                 p.hist_len[0] = n + 1;
             }
-            *p.bar_base = base + bar_i * (unsigned)p.G;
         }
+        p.sync[0] = step + 1u;
     }
 }
 
@@ -697,13 +921,14 @@ B1Plan* b1_make_plan(const DeviceModel* m) {
     const bool modern = ds.arch == GRADB_ARCH_MODERN;
     plan->G = m->sm_count;
     plan->wbytes = m->precision == GRADB_BF16 ? 2 : 4;
-    if (hs != 64 || d % 8 != 0 || d > 4 * kCompute || ds.num_heads > plan->G || ds.num_layers > kMaxLayersB1) return plan;  // not supported: the generic kernels run instead
+    if (hs != 64 || d % 8 != 0 || d > kHold * kCompute || ds.num_heads > plan->G || ds.num_layers > kMaxLayersB1) return plan;  // not supported: the generic kernels run instead
     // Q/K/V and FFN-up have non-linear epilogues, so their tiles span the whole reduction.
     plan->qkv = plan_matrix(d, 3 * d, plan->G, 1);
     plan->o = plan_matrix(d, d, plan->G, 16);
     plan->up = plan_matrix(d, f, plan->G, 1);
     if (!plan->qkv.tiles || !plan->o.tiles || !plan->up.tiles) return plan;
     if (plan->up.CW > 64 || kSlotBytes / (d * plan->wbytes) < 1) return plan;
+    if (plan->up.tiles >= (1 << kCountBits) || plan->o.KS >= (1 << kCountBits)) return plan;
     plan->logit_rows_per_cta = (ds.vocab_size + plan->G - 1) / plan->G;
     plan->logit_chunk_rows = kSlotBytes / (d * plan->wbytes);
     if (plan->logit_chunk_rows < 1) return plan;
@@ -756,11 +981,37 @@ void b1_free_plan(B1Plan* p) {
     delete p;
 }
 
-size_t b1_workspace_floats(const DeviceModel* m, const B1Plan* plan) {
-    const int d = m->desc.d_model, hs = d / m->desc.num_heads;
-    return (size_t)d                                                      // q
-           + (size_t)m->desc.num_heads * plan->attn_splits * (hs + 2)     // attention partials
-           + (size_t)plan->o.KS * d + 4 * (size_t)d * kAccStride + 64;  // + two fixed-point accumulators, one line per element
+namespace {
+struct B1Workspace {
+    size_t q, kv, attn, o, acc, sync, total;  // byte offsets
+};
+B1Workspace b1_layout(const DeviceModel* m, const B1Plan* plan) {
+    const size_t d = (size_t)m->desc.d_model, hs = d / m->desc.num_heads;
+    auto up = [](size_t v) { return (v + 127) & ~size_t(127); };
+    B1Workspace w{};
+    size_t at = 0;
+    w.q = at; at = up(at + d * 8);
+    w.kv = at; at = up(at + 2 * d * 8);
+    w.attn = at; at = up(at + (size_t)m->desc.num_heads * plan->attn_splits * (hs + 2) * 8);
+    w.o = at; at = up(at + (size_t)plan->o.KS * d * 8);
+    w.acc = at; at = up(at + 2 * (size_t)m->desc.num_layers * d * kAccStride * 8);
+    w.sync = at; at = up(at + 2 * sizeof(unsigned));
+    w.total = at;
+    return w;
+}
+}  // namespace
+
+size_t b1_workspace_bytes(const DeviceModel* m, const B1Plan* plan) { return b1_layout(m, plan).total; }
+
+void b1_bind_workspace(B1Params& p, void* workspace, const DeviceModel* m, const B1Plan* plan) {
+    const B1Workspace w = b1_layout(m, plan);
+    uint8_t* base = static_cast<uint8_t*>(workspace);
+    p.q_ll = reinterpret_cast<unsigned long long*>(base + w.q);
+    p.kv_ll = reinterpret_cast<unsigned long long*>(base + w.kv);
+    p.attn_ll = reinterpret_cast<unsigned long long*>(base + w.attn);
+    p.o_ll = reinterpret_cast<unsigned long long*>(base + w.o);
+    p.acc = reinterpret_cast<long long*>(base + w.acc);
+    p.sync = reinterpret_cast<unsigned*>(base + w.sync);
 }
 
 void launch_decode_b1(const B1Params& p, cudaStream_t st) {

@@ -40,22 +40,29 @@ struct B1Params {
     const float *pos_emb, *fng, *fnb, *rope_cos, *rope_sin;
     float *kcache, *vcache;  // [L][1][H][T][hs] of sequence 0
     size_t layer_cache_stride;
-    // exchange buffers (global, L2 resident)
-    float *q, *attn_part, *opart, *logits;
-    // FFN output of the layer, accumulated by every CTA in 2^-32 fixed point (integer adds commute, so the
-    // result does not depend on arrival order); two buffers of d, alternating by layer
-    long long* ffn_acc;
+    // exchange buffers (global, L2 resident), all starting zeroed
+    unsigned long long* q_ll;     // [d] {value, epoch}: the query of the current layer
+    unsigned long long* kv_ll;    // [2][d] the new K row and V row of the current layer
+    unsigned long long* attn_ll;  // [H * splits][hs + 2] attention partials: values, running max, running sum
+    unsigned long long* o_ll;     // [KS][d] output-projection partial vectors, one per K slice
+    float* logits;
+    // Sum over CTAs of the FFN output, in 2^-32 fixed point above a contribution count (integer adds commute, so the result does not
+    // depend on arrival order): [2 sets used by alternate steps][L][d], one 128-byte
+    // line per element
+    long long* acc;
     const int *tok, *logit_tok;
     int *pos, *hist, *hist_len;
     int hist_stride, append_hist;
-    unsigned *bar_counter, *bar_base;
+    unsigned* sync;  // [0] steps run so far, [1] CTAs that have read their launch state (G per step)
     int* status;
     unsigned long long* trace;  // optional: %globaltimer stamps of CTA 0 at every stage boundary
 };
 
 B1Plan* b1_make_plan(const DeviceModel* m);
 void b1_free_plan(B1Plan* p);
-size_t b1_workspace_floats(const DeviceModel* m, const B1Plan* plan);
+size_t b1_workspace_bytes(const DeviceModel* m, const B1Plan* plan);
+// Points the exchange buffers of `p` into a zeroed workspace of b1_workspace_bytes.
+void b1_bind_workspace(B1Params& p, void* workspace, const DeviceModel* m, const B1Plan* plan);
 void launch_decode_b1(const B1Params& p, cudaStream_t st);
 
 }  // namespace gradb

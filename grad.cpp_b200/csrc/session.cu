@@ -53,7 +53,7 @@ void check_status(Session* s) {
         // session stays usable.
         cudaMemset(s->status, 0, sizeof(int));
         cudaMemset(s->attn_counters, 0, (size_t)s->B * s->H * sizeof(int));
-        if (s->b1_bar) cudaMemset(s->b1_bar, 0, 2 * sizeof(unsigned));
+        if (s->b1_ws) cudaMemset(s->b1_ws, 0, s->b1_ws_bytes);
         throw Error(GRADB_ERR_DEVICE_WAIT, "a device-side wait expired (code " + std::to_string(code) + ")");
     }
 }
@@ -207,17 +207,11 @@ void enqueue_step_b1(Session* s, const int* tok_dev, const int* logit_tok_dev, b
     p.rope_sin = modern ? m->rope_sin : nullptr;
     p.kcache = s->kcache; p.vcache = s->vcache;
     p.layer_cache_stride = layer_cache_elems(s);
-    float* ws = s->b1_ws;
-    p.q = ws; ws += s->d;
-    p.attn_part = ws; ws += (size_t)s->H * plan->attn_splits * (s->hs + 2);
-    p.opart = ws; ws += (size_t)plan->o.KS * s->d;
-    ws = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(ws) + 15) & ~uintptr_t(15));
-    p.ffn_acc = reinterpret_cast<long long*>(ws);
+    b1_bind_workspace(p, s->b1_ws, m, plan);
     p.logits = s->logits;
     p.tok = tok_dev; p.logit_tok = logit_tok_dev;
     p.pos = s->pos; p.hist = s->hist; p.hist_len = s->hist_len;
     p.hist_stride = s->hist_stride; p.append_hist = append_history ? 1 : 0;
-    p.bar_counter = s->b1_bar; p.bar_base = s->b1_bar + 1;
     p.status = s->status;
     p.trace = s->b1_trace;
     Timed t(s, KC_STEP_B1);
@@ -769,9 +763,10 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         const char* nb1 = std::getenv("GRADB_NO_B1");
         s->use_b1 = s->B == 1 && m->b1 && m->b1->ok && !(nb1 && nb1[0] == '1');
         if (s->use_b1) {
-            dalloc(&s->b1_ws, b1_workspace_floats(m, m->b1));
-            dalloc(&s->b1_bar, 2);
-            GRADB_CUDA(cudaMemsetAsync(s->b1_bar, 0, 2 * sizeof(unsigned), s->stream));
+            // exchange words, accumulators and step counters of the persistent kernel: all start at zero
+            s->b1_ws_bytes = b1_workspace_bytes(m, m->b1);
+            dalloc(&s->b1_ws, s->b1_ws_bytes);
+            GRADB_CUDA(cudaMemsetAsync(s->b1_ws, 0, s->b1_ws_bytes, s->stream));
             const char* tr = std::getenv("GRADB_B1_TRACE");
             if (tr && tr[0] == '1') {
                 dalloc(&s->b1_trace, 1024);
@@ -861,7 +856,7 @@ void destroy_session(Session* s) {
     cudaFree(s->tok); cudaFree(s->pos); cudaFree(s->hist); cudaFree(s->hist_len);
     cudaFree(s->gen); cudaFree(s->done); cudaFree(s->out_tok); cudaFree(s->tok_matrix);
     cudaFree(s->uniforms); cudaFree(s->probs);
-    cudaFree(s->b1_ws); cudaFree(s->b1_bar); cudaFree(s->b1_trace);
+    cudaFree(s->b1_ws); cudaFree(s->b1_trace);
     cudaFree(s->feed.hS); cudaFree(s->feed.attnS); cudaFree(s->feed.ffnS);
     cudaFree(s->feed.x); cudaFree(s->feed.q); cudaFree(s->feed.attn); cudaFree(s->feed.h16); cudaFree(s->feed.attn16);
     cudaFree(s->feed.ffn16); cudaFree(s->feed.row_tok); cudaFree(s->feed.row_pos); cudaFree(s->feed.row_seq);

@@ -71,8 +71,8 @@ struct Session {
 
     // single-sequence persistent kernel: workspace and grid-barrier words
     bool use_b1 = false;
-    float* b1_ws = nullptr;
-    unsigned* b1_bar = nullptr;  // [0] arrival counter, [1] base of the next launch
+    uint8_t* b1_ws = nullptr;  // marked exchange words, fixed-point accumulators, step counters (decode_b1.cuh)
+    size_t b1_ws_bytes = 0;
     unsigned long long* b1_trace = nullptr;  // stage timestamps when GRADB_B1_TRACE=1
 
     // host mirrors / staging (pinned)
