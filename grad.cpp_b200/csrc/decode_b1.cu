@@ -36,10 +36,10 @@ namespace gradb {
 
 namespace {
 
-constexpr int kCompute = 512;  // compute threads (16 warps)
+constexpr int kCompute = 256;  // compute threads (8 warps)
 constexpr int kThreadsB1 = kCompute + 32;  // + producer warp
 constexpr int kWarpsB1 = kCompute / 32;
-constexpr int kHold = 2;  // vector elements per compute thread: d <= kHold * kCompute
+constexpr int kHold = 4;  // vector elements per compute thread: d <= kHold * kCompute
 constexpr int kSlots = 4;
 constexpr int kSlotBytes = 48 * 1024;
 constexpr uint32_t kPollLimit = 1u << 22;   // mbarrier waits (each try suspends for a while)
@@ -628,41 +628,58 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
             }
             stamp();
             float m_run = -INFINITY, l_run = 0.f, o0 = 0.f, o1 = 0.f;
-            // four positions per trip: their K and V rows are requested together; the newest position's rows come
+            // eight positions per trip: their K and V rows are requested together; the newest position's rows come
             // from this step's producers
-            for (int tt = t0 + w; tt < t1; tt += 4 * kWarpsB1) {
-                float2 kv[4], vv[4];
+            constexpr int kTrip = 8;
+            for (int tt = t0 + w; tt < t1; tt += kTrip * kWarpsB1) {
+                float2 kv[kTrip], vv[kTrip];
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < kTrip; u++) {
                     const int tu = tt + u * kWarpsB1;
                     if (tu < t1 && tu != pos) {
                         kv[u] = __ldcg(reinterpret_cast<const float2*>(K + (size_t)tu * hs) + lane);
                         vv[u] = __ldcg(reinterpret_cast<const float2*>(V + (size_t)tu * hs) + lane);
                     }
                 }
+                if (pos >= tt && pos < t1 && (pos - tt) % kWarpsB1 == 0) {  // warp-uniform: this trip holds the newest row
+                    const int u_new = (pos - tt) / kWarpsB1;
+                    const unsigned long long* kr = p.kv_ll + head * hs + 2 * lane;
+                    const unsigned long long* const ptr[4] = {kr, kr + 1, kr + d, kr + d + 1};
+                    const bool want[4] = {true, true, true, true};
+                    float o[4];
+                    ll_wait<4>(ptr, want, ep_kv, o, p.status, &abort_flag, 223);
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int tu = tt + u * kWarpsB1;
-                    if (tu < t1) {
-                        if (tu == pos) {
-                            const unsigned long long* kr = p.kv_ll + head * hs + 2 * lane;
-                            const unsigned long long* const ptr[4] = {kr, kr + 1, kr + d, kr + d + 1};
-                            const bool want[4] = {true, true, true, true};
-                            float o[4];
-                            ll_wait<4>(ptr, want, ep_kv, o, p.status, &abort_flag, 223);
+                    for (int u = 0; u < kTrip; u++) {
+                        if (u == u_new) {
                             kv[u] = make_float2(o[0], o[1]);
                             vv[u] = make_float2(o[2], o[3]);
                         }
-                        const float sc = warp_sum(qv.x * kv[u].x + qv.y * kv[u].y) * scale;
-                        const float m_new = fmaxf(m_run, sc);
-                        const float corr = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
-                        const float pr = expf(sc - m_new);
-                        l_run = l_run * corr + pr;
-                        o0 = o0 * corr + pr * vv[u].x;
-                        o1 = o1 * corr + pr * vv[u].y;
-                        m_run = m_new;
                     }
                 }
+                // scores of the whole trip first (independent reductions), then one rescale of the running state
+                float sc[kTrip];
+                float m_trip = -INFINITY;
+#pragma unroll
+                for (int u = 0; u < kTrip; u++) {
+                    const bool in = tt + u * kWarpsB1 < t1;
+                    sc[u] = in ? warp_sum(qv.x * kv[u].x + qv.y * kv[u].y) * scale : -INFINITY;
+                    m_trip = fmaxf(m_trip, sc[u]);
+                }
+                const float m_new = fmaxf(m_run, m_trip);
+                const float corr = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
+                l_run *= corr;
+                o0 *= corr;
+                o1 *= corr;
+#pragma unroll
+                for (int u = 0; u < kTrip; u++) {
+                    if (tt + u * kWarpsB1 < t1) {
+                        const float pr = expf(sc[u] - m_new);
+                        l_run += pr;
+                        o0 += pr * vv[u].x;
+                        o1 += pr * vv[u].y;
+                    }
+                }
+                m_run = m_new;
             }
             stamp();
             // combine the warps in order; red_s rows: [w][0..63] = o, then m and l
@@ -783,13 +800,16 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
                     const int n = min(chunk_rows, nrows - r);
                     const WT* rows = reinterpret_cast<const WT*>(ring_acquire(ring));
                     stamp();
+                    {
+                        // columns past d read column 0 and are dropped later, so the loop carries no branch
+                        const WT* wp[kColsPerThread];
 #pragma unroll
-                    for (int c = 0; c < kColsPerThread; c++) {
-                        const int col = t + c * kCompute;
-                        if (col < d) {
-                            float a = y[c];
-                            for (int i = 0; i < n; i++) a += hid_s[r + i] * ld_tile1(rows + (size_t)i * d + col);
-                            y[c] = a;
+                        for (int c = 0; c < kColsPerThread; c++) wp[c] = rows + (t + c * kCompute < d ? t + c * kCompute : 0);
+#pragma unroll 8
+                        for (int i = 0; i < n; i++) {
+                            const float hv = hid_s[r + i];
+#pragma unroll
+                            for (int c = 0; c < kColsPerThread; c++) y[c] += hv * ld_tile1(wp[c] + (size_t)i * d);
                         }
                     }
                     ring_release(ring);
