@@ -10,6 +10,7 @@ the C ABI; nothing here computes.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 import numpy as np
@@ -94,8 +95,15 @@ SIGNATURES = {
     "gradb_kernel_class_count": (C.c_int, []),
     "gradb_kernel_class_name": (C.c_char_p, [C.c_int]),
     "gradb_session_profile": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
-    "gradb_session_stage_trace": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.c_int, C.POINTER(C.c_int)]),
     "gradb_kernel_launches": (C.c_uint64, []),
+}
+
+# Only in the diagnostics build (libgradb_diag.so, csrc/gradb_diag.h); selected by GRADB_LIB=<path to that file>.
+DIAG_SIGNATURES = {
+    "gradb_session_stage_trace": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.c_int, C.POINTER(C.c_int)]),
+    "gradb_diag_attention_wait": (C.c_int, [C.c_void_p, C.c_uint, C.c_int]),
+    "gradb_diag_count_nonfinite": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_longlong)]),
+    "gradb_diag_poke_history": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int32]),
 }
 
 DRAW_FN = C.CFUNCTYPE(C.c_float, C.c_void_p, C.c_int)
@@ -108,14 +116,20 @@ def lib():
     """Loads the CUDA library. There is no fallback: a missing build is an error."""
     global _lib
     if _lib is None:
-        if not LIB_PATH.exists():
-            raise ImportError(f"{LIB_PATH} has not been built (python grad.cpp_b200/build.py); "
+        path = Path(os.environ.get("GRADB_LIB", LIB_PATH))
+        if not path.exists():
+            raise ImportError(f"{path} has not been built (python grad.cpp_b200/build.py); "
                               "this package has no CPU implementation")
-        L = C.CDLL(str(LIB_PATH))
+        L = C.CDLL(str(path))
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(L, name)
             fn.restype = res
             fn.argtypes = args
+        for name, (res, args) in DIAG_SIGNATURES.items():
+            if hasattr(L, name):
+                fn = getattr(L, name)
+                fn.restype = res
+                fn.argtypes = args
         _lib = L
     return _lib
 
@@ -382,10 +396,23 @@ class BatchSession:
         return {lib().gradb_kernel_class_name(i).decode(): (ms[i], int(cnt[i])) for i in range(n)}
 
     def stage_trace(self):
+        """Diagnostics build only."""
         buf = (C.c_uint64 * 1024)()
         n = C.c_int()
         _check(lib().gradb_session_stage_trace(self._h, buf, 1024, C.byref(n)))
         return np.array(buf[:n.value], np.uint64)
+
+    def diag_attention_wait(self, spin_limit, skip_tile):
+        """Diagnostics build only: make the attention kernel's tile wait expire (gradb_diag.h)."""
+        _check(lib().gradb_diag_attention_wait(self._h, spin_limit, skip_tile))
+
+    def diag_count_nonfinite(self, n_seq):
+        n = C.c_longlong()
+        _check(lib().gradb_diag_count_nonfinite(self._h, n_seq, C.byref(n)))
+        return int(n.value)
+
+    def diag_poke_history(self, seq, index, token):
+        _check(lib().gradb_diag_poke_history(self._h, seq, index, token))
 
     def last_ms(self):
         v = C.c_float()

@@ -13,6 +13,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libgradb.so"
+LIB_DIAG = HERE / "libgradb_diag.so"  # the diagnostics build (csrc/gradb_diag.h): index checks, traces, test hooks
 SOURCES = ["checkpoint.cpp", "model.cu", "step_kernels.cu", "attn_prefill.cu", "select_kernels.cu", "gemm_tc.cu", "decode_b1.cu", "session.cu", "capi.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "--expt-extended-lambda"]
@@ -25,17 +26,19 @@ def _stale(target: Path, deps) -> bool:
     return any(Path(d).stat().st_mtime > t for d in deps)
 
 
-def build(verbose: bool = False, force: bool = False) -> Path:
+def build(verbose: bool = False, force: bool = False, diagnostics: bool = False) -> Path:
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + [HERE.parent / "include" / "gradb.h"]
-    objdir = HERE / "build"
-    objdir.mkdir(exist_ok=True)
+    objdir = HERE / "build" / ("diag" if diagnostics else "product")
+    objdir.mkdir(parents=True, exist_ok=True)
+    lib = LIB_DIAG if diagnostics else LIB
+    flags = NVCC_FLAGS + (["-DGRADB_DIAGNOSTICS"] if diagnostics else [])
     objs, procs = [], []
     for src in SOURCES:
         obj = objdir / (src + ".o")
         objs.append(str(obj))
         if force or _stale(obj, [CSRC / src] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+            cmd = [nvcc, *flags, "-c", str(CSRC / src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -47,11 +50,12 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         failed = failed or p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    if procs or not LIB.exists():
-        subprocess.run([nvcc, "-shared", "-o", str(LIB), *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
+    if procs or not lib.exists():
+        subprocess.run([nvcc, "-shared", "-o", str(lib), *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
                        check=True)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, diagnostics=True))

@@ -4,6 +4,9 @@
 #include <cstring>
 
 #include "session.cuh"
+#if GRADB_DIAG
+#include "gradb_diag.h"
+#endif
 
 using namespace gradb;
 
@@ -434,6 +437,8 @@ gradb_status gradb_session_profile(const gradb_session* session, double* ms_out,
     return GRADB_OK;
 }
 
+#if GRADB_DIAG
+// ---- diagnostics build only (declared in csrc/gradb_diag.h) ------------------------------------------------------
 gradb_status gradb_session_stage_trace(gradb_session* session, uint64_t* stamps_out, int capacity, int* count_out) {
     return guarded([&] {
         if (!session || !stamps_out || !count_out) throw Error(GRADB_ERR_INVALID, "null argument");
@@ -452,6 +457,46 @@ gradb_status gradb_session_stage_trace(gradb_session* session, uint64_t* stamps_
         *count_out = n;
     });
 }
+
+gradb_status gradb_diag_attention_wait(gradb_session* session, unsigned spin_limit, int skip_tile) {
+    return guarded([&] {
+        if (!session) throw Error(GRADB_ERR_INVALID, "null session");
+        session->impl->diag_spin_limit = spin_limit;
+        session->impl->diag_skip_tile = skip_tile;
+        // the decode graphs bake kernel parameters: drop them so that the next loop captures the new ones
+        Session* s = session->impl;
+        if (s->graph) {
+            cudaGraphExecDestroy(s->graph);
+            s->graph = nullptr;
+        }
+        if (s->serve_graph) {
+            cudaGraphExecDestroy(s->serve_graph);
+            s->serve_graph = nullptr;
+        }
+    });
+}
+
+gradb_status gradb_diag_count_nonfinite(gradb_session* session, int n_seq, long long* count_out) {
+    return guarded([&] {
+        if (!session || !count_out) throw Error(GRADB_ERR_INVALID, "null argument");
+        Session* s = session->impl;
+        if (n_seq < 1 || n_seq > s->B) throw Error(GRADB_ERR_INVALID, "n_seq out of range for this session");
+        GRADB_CUDA(cudaSetDevice(s->m->device));
+        *count_out = count_nonfinite(s->logits, (size_t)n_seq * s->V, s->stream) +
+                     count_nonfinite(s->x, (size_t)n_seq * s->d, s->stream);
+    });
+}
+
+gradb_status gradb_diag_poke_history(gradb_session* session, int seq, int index, int32_t id) {
+    return guarded([&] {
+        if (!session) throw Error(GRADB_ERR_INVALID, "null session");
+        Session* s = session->impl;
+        if (seq < 0 || seq >= s->B || index < 0 || index >= s->hist_stride) throw Error(GRADB_ERR_INVALID, "bad index");
+        GRADB_CUDA(cudaSetDevice(s->m->device));
+        GRADB_CUDA(cudaMemcpy(s->hist + (size_t)seq * s->hist_stride + index, &id, sizeof(int), cudaMemcpyHostToDevice));
+    });
+}
+#endif  // GRADB_DIAG
 
 uint64_t gradb_kernel_launches(void) { return g_kernel_launches.load(); }
 

@@ -59,6 +59,20 @@ void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
 }
 #endif
 
+// Diagnostics build (-DGRADB_DIAGNOSTICS, libgradb_diag.so): device-side index checks that record a code in the
+// session's status word instead of making the access, a scan of outputs for non-finite values, the stage trace of
+// the single-sequence kernel, overrides of tile and split choices, and a hook that makes one bounded device wait
+// expire. None of it is compiled into the product library.
+#if defined(GRADB_DIAGNOSTICS)
+#define GRADB_DIAG 1
+#define GRADB_INDEX_OK(cond, status, code) ((cond) ? true : ((status) ? (atomicExch((status), (code)), false) : false))
+#else
+#define GRADB_DIAG 0
+#define GRADB_INDEX_OK(cond, status, code) (true)
+#endif
+// Status-word codes from 900 up are failed index checks; below that, bounded waits that expired.
+constexpr int kIndexCheckCodes = 900;
+
 // Sequences whose current token id is negative take no part in a step.
 constexpr int kSkip = -1;
 // Width of the repetition-penalty window (text_gen.cpp:22).

@@ -77,16 +77,18 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// Optional stage timestamps of CTA 0 (diagnostics): a no-op unless the session asked for a trace.
+// Stage timestamps of CTA 0: compiled in only in the diagnostics build, and there only when a trace was asked for.
 struct Tracer {
     unsigned long long* buf;
     int n;
     __device__ __forceinline__ void stamp() {
+#if GRADB_DIAG
         if (buf) {
             unsigned long long now;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
             buf[n++] = now;
         }
+#endif
     }
 };
 
@@ -451,6 +453,7 @@ __global__ void __launch_bounds__(kThreadsB1, 1) decode_b1_kernel(const B1Params
     const int token = p.tok[0];
     if (token < 0) return;  // the sequence takes no part in this step (uniform over the grid)
     const int pos = p.pos[0];
+    if (!GRADB_INDEX_OK(token < p.V && pos >= 0 && pos < p.T, p.status, 903)) return;  // uniform over the grid
     const bool do_logits = p.logit_tok[0] >= 0;
     const unsigned step = p.sync[0];  // steps this session has run: names the epochs and the accumulator set of this launch
     const int d = p.d, hs = p.hs;

@@ -925,10 +925,12 @@ void tc_configure_all() {
 }
 
 int tc_token_tile(int n_seq, int n_tiles, int want_ctas) {
-    if (const char* force = std::getenv("GRADB_TC_TILE")) {  // diagnostic: 32, 64 or 128
+#if GRADB_DIAG
+    if (const char* force = std::getenv("GRADB_TC_TILE")) {  // diagnostics build: 32, 64 or 128
         const int tn = std::atoi(force);
         if (tn == 32 || tn == 64 || tn == 128) return tn;
     }
+#endif
     for (int tn : {128, 64, 32}) {
         if (tn > 32 && tn >= 2 * n_seq) continue;  // do not pad a small batch to a wide tile
         if (n_tiles * ((n_seq + tn - 1) / tn) >= want_ctas || tn == 32) return tn;

@@ -1,0 +1,35 @@
+/* Entry points that exist only in the diagnostics build of the library (libgradb_diag.so, built with
+ * -DGRADB_DIAGNOSTICS). That build also checks device-side indices (a violated bound records a code in the session's
+ * status word, skips the access, and the call returns GRADB_ERR_INVALID "a device-side index check failed"), reads the
+ * overrides GRADB_TC_TILE / GRADB_ATTN_SPLITS and, with GRADB_B1_TRACE=1, records the single-sequence kernel's stage
+ * timestamps. None of this is in the product library or its header. */
+#ifndef GRADB_DIAG_H
+#define GRADB_DIAG_H
+
+#include "../../include/gradb.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Nanosecond timestamps CTA 0 of the single-sequence persistent kernel left at its stage boundaries during the most
+ * recent step (session created with GRADB_B1_TRACE=1). Returns how many were recorded. */
+gradb_status gradb_session_stage_trace(gradb_session* session, uint64_t* stamps_out, int capacity, int* count_out);
+
+/* Makes a bounded device-side wait run out, to exercise the status-word path: the pipelined cached-attention kernel
+ * polls each tile's arrival at most spin_limit times (0 = the normal limit) and every warp leaves out the copy of
+ * its skip_tile-th tile (-1 = none), so the wait for that tile expires; the kernel records code 301, waits for its
+ * other copies and returns; the call that launched it returns GRADB_ERR_DEVICE_WAIT. Nothing faults or hangs. */
+gradb_status gradb_diag_attention_wait(gradb_session* session, unsigned spin_limit, int skip_tile);
+
+/* Non-finite values among the session's current logits and residual rows of sequences 0..n_seq-1. */
+gradb_status gradb_diag_count_nonfinite(gradb_session* session, int n_seq, long long* count_out);
+
+/* Overwrites one entry of a sequence's id history on the device without the range check the product entry points
+ * make, so that the device-side index check of the penalty stage can be seen to catch it. */
+gradb_status gradb_diag_poke_history(gradb_session* session, int seq, int index, int32_t id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

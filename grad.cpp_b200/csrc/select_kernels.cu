@@ -811,6 +811,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         const int window = min(kPenaltyWindow, hlen);
         for (int k = hlen - window; k < hlen; k++) {
             const int id = hist[k];
+            if (!GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) continue;
             if (x[id] > 0) x[id] = __fdiv_rn(x[id], p.penalty);
             else x[id] = __fmul_rn(x[id], p.penalty);
         }
@@ -946,6 +947,7 @@ __global__ void __launch_bounds__(kGreedyThreads) select_greedy_kernel(const Sel
         int n = 0;
         for (int k = hlen - window; k < hlen; k++) {
             const int id = hist[k];
+            if (!GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) continue;
             int slot = id & (kPenHash - 1);
             while (table[slot] >= 0 && pen_id[table[slot]] != id) slot = (slot + 1) & (kPenHash - 1);
             int e = table[slot];

@@ -33,6 +33,7 @@ struct SelectParams {
     // is published at [b][g] as id + 1 (0 = not yet), so the host can hand it on while the loop runs ahead
     int* stream_ids;
     int stream_stride;
+    int* status;  // session status word (index checks of the diagnostics build)
 };
 
 size_t select_smem_bytes(int V, int* n_pad_out);

@@ -54,6 +54,9 @@ void check_status(Session* s) {
         cudaMemset(s->status, 0, sizeof(int));
         cudaMemset(s->attn_counters, 0, (size_t)s->B * s->H * sizeof(int));
         if (s->b1_ws) cudaMemset(s->b1_ws, 0, s->b1_ws_bytes);
+        if (code >= kIndexCheckCodes) {
+            throw Error(GRADB_ERR_INVALID, "a device-side index check failed (code " + std::to_string(code) + ")");
+        }
         throw Error(GRADB_ERR_DEVICE_WAIT, "a device-side wait expired (code " + std::to_string(code) + ")");
     }
 }
@@ -141,6 +144,7 @@ void enqueue_step_tc(Session* s, int n_seq, const int* tok_dev, const int* logit
             a.status = s->status;
             a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = d;
             a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
+            a.diag_spin_limit = s->diag_spin_limit; a.diag_skip_tile = s->diag_skip_tile;
             const bool split_inside = s32 && s->hs == 64;  // the pipelined kernel writes the hi/lo operand itself
             if (split_inside) { a.out_split = s->attnS; a.out_lo_elems = lo_d; }
             launch_attention(a, n_seq, s->attn_splits, st);
@@ -267,6 +271,7 @@ void enqueue_step(Session* s, int n_seq, const int* tok_dev, const int* logit_to
         a.status = s->status;
         a.H = s->H; a.hs = s->hs; a.T = s->T; a.d = s->d;
         a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));  // inference.cpp:184
+        a.diag_spin_limit = s->diag_spin_limit; a.diag_skip_tile = s->diag_skip_tile;
         {
             Timed t(s, KC_ATTN);
             launch_attention(a, n_seq, s->attn_splits, st);
@@ -349,6 +354,7 @@ SelectParams make_select(Session* s, const gradb_sampling& sp) {
     p.done = s->done;
     p.pos = s->pos;
     p.capacity = s->T;
+    p.status = s->status;
     return p;
 }
 
@@ -737,9 +743,11 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         // (measured: at 32 sequences x 12 heads and context ~1100, one split per unit beats seven).
         const int want = (2 * m->sm_count + s->B * s->H - 1) / (s->B * s->H);
         s->attn_splits = std::max(1, std::min({want, 16, (s->T + 31) / 32}));
+#if GRADB_DIAG
         if (const char* sp = std::getenv("GRADB_ATTN_SPLITS")) {
             s->attn_splits = std::max(1, std::min({std::atoi(sp), 16, (s->T + 31) / 32}));
         }
+#endif
         const size_t B = s->B;
         dalloc(&s->x, B * s->d);
         dalloc(&s->q, B * s->d);
@@ -767,11 +775,13 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
             s->b1_ws_bytes = b1_workspace_bytes(m, m->b1);
             dalloc(&s->b1_ws, s->b1_ws_bytes);
             GRADB_CUDA(cudaMemsetAsync(s->b1_ws, 0, s->b1_ws_bytes, s->stream));
+#if GRADB_DIAG
             const char* tr = std::getenv("GRADB_B1_TRACE");
             if (tr && tr[0] == '1') {
                 dalloc(&s->b1_trace, 1024);
                 GRADB_CUDA(cudaMemsetAsync(s->b1_trace, 0, 1024 * sizeof(unsigned long long), s->stream));
             }
+#endif
         }
         const char* npdl = std::getenv("GRADB_NO_PDL");
         s->use_pdl = !(npdl && npdl[0] == '1');
@@ -1010,6 +1020,9 @@ float session_score(Session* s, const int32_t* inputs, const int32_t* targets, i
 
 void session_set_history(Session* s, int seq, const int32_t* ids, int n) {
     if (seq < 0 || seq >= s->B || n < 0 || n > s->hist_stride) throw Error(GRADB_ERR_INVALID, "bad history");
+    for (int i = 0; i < n; i++) {  // the penalty indexes the logits with these ids
+        if (ids[i] < 0 || ids[i] >= s->V) throw Error(GRADB_ERR_BAD_TOKEN, "InferenceSession: token id out of vocab range");
+    }
     GRADB_CUDA(cudaSetDevice(s->m->device));
     GRADB_CUDA(cudaMemcpyAsync(s->hist + (size_t)seq * s->hist_stride, ids, n * sizeof(int), cudaMemcpyHostToDevice,
                                s->stream));

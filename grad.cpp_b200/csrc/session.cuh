@@ -75,6 +75,10 @@ struct Session {
     size_t b1_ws_bytes = 0;
     unsigned long long* b1_trace = nullptr;  // stage timestamps when GRADB_B1_TRACE=1
 
+    // diagnostics build: spin limit and left-out tile of the attention kernel's wait (see AttnParams)
+    uint32_t diag_spin_limit = 0;
+    int diag_skip_tile = -1;
+
     // host mirrors / staging (pinned)
     std::vector<int> h_pos;
     int* h_stage = nullptr;  // pinned, >= 4*B ints

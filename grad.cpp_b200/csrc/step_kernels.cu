@@ -652,7 +652,12 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 1) attn_decode64_pipe_kernel(
         const int stage = issued % kPipeStages;
         const int r0 = fc.tile * kPipeTileRows;
         const int nrows = min(kPipeTileRows, fc.ctx - r0);
-        if (lane == 0) {
+#if GRADB_DIAG
+        const bool leave_out = issued == p.diag_skip_tile;  // the hook that lets a wait run out
+#else
+        constexpr bool leave_out = false;
+#endif
+        if (lane == 0 && !leave_out) {
             const size_t off = (((size_t)fc.seq * p.H + fc.h) * p.T + r0) * HS;
             const uint32_t bytes = (uint32_t)nrows * HS * 4;
             const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&full_bar[w][stage]);
@@ -712,15 +717,35 @@ __global__ void __launch_bounds__(kPipeWarps * 32, 1) attn_decode64_pipe_kernel(
             {
                 const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&full_bar[w][stage]);
                 uint32_t ok = 0;
-                for (uint32_t it = 0; it < kPipeSpin && !ok; ++it) {
+#if GRADB_DIAG
+                const uint32_t spin = p.diag_spin_limit ? p.diag_spin_limit : kPipeSpin;
+#else
+                constexpr uint32_t spin = kPipeSpin;
+#endif
+                for (uint32_t it = 0; it < spin && !ok; ++it) {
                     asm volatile(
                         "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
                         : "=r"(ok)
                         : "r"(bar), "r"(parity)
                         : "memory");
                 }
-                if (!ok) {  // bounded: give up on this launch, the host sees the status word
+                if (!ok) {
+                    // Bounded: give up on this launch; the host sees the status word. Warps share nothing (own ring,
+                    // own barriers, no CTA-wide barrier anywhere in this kernel), so this warp may simply leave - after
+                    // the copies it still has in flight into its ring have landed (again bounded).
                     if (lane == 0 && p.status) atomicExch(p.status, 301);
+                    for (int c = consumed + 1; c < issued; c++) {
+                        const uint32_t ob = (uint32_t)__cvta_generic_to_shared(&full_bar[w][c % kPipeStages]);
+                        const uint32_t op = (c / kPipeStages) & 1;
+                        uint32_t landed = 0;
+                        for (uint32_t it = 0; it < kPipeSpin && !landed; ++it) {
+                            asm volatile(
+                                "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                                : "=r"(landed)
+                                : "r"(ob), "r"(op)
+                                : "memory");
+                        }
+                    }
                     return;
                 }
             }
@@ -1048,6 +1073,31 @@ void launch_attention_static(const AttnParams& p_in, int B, int splits, cudaStre
     attn_decode64_kernel<<<dim3(splits, p.H, B), kAttnWarps * 32, 0, st>>>(p);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
+}
+
+namespace {
+__global__ void count_nonfinite_kernel(const float* __restrict__ x, size_t n, unsigned long long* out) {
+    unsigned long long bad = 0;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = x[i];
+        bad += (v != v || fabsf(v) == INFINITY) ? 1ull : 0ull;
+    }
+    if (bad) atomicAdd(out, bad);
+}
+}  // namespace
+
+// NaN / Inf scan of a device buffer (diagnostics build's output check). Synchronises the stream.
+long long count_nonfinite(const float* x, size_t n, cudaStream_t st) {
+    unsigned long long* d = nullptr;
+    unsigned long long h = 0;
+    GRADB_CUDA(cudaMalloc(&d, sizeof(h)));
+    GRADB_CUDA(cudaMemsetAsync(d, 0, sizeof(h), st));
+    count_nonfinite_kernel<<<256, 256, 0, st>>>(x, n, d);
+    count_launch();
+    GRADB_CUDA(cudaMemcpyAsync(&h, d, sizeof(h), cudaMemcpyDeviceToHost, st));
+    GRADB_CUDA(cudaStreamSynchronize(st));
+    cudaFree(d);
+    return (long long)h;
 }
 
 // Opt the pipelined attention kernel into its shared memory up front (per device).

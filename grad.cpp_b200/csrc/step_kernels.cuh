@@ -52,8 +52,13 @@ struct AttnParams {
     int* status;      // optional: set non-zero if a bounded wait expires
     int H, hs, T, d;
     float scale;
+    // Diagnostics build only: spin limit of the pipelined kernel's tile wait (0 = the normal one) and the index of
+    // the tile, counted per warp from 0, whose copy is left out so that the wait for it expires (-1 = none).
+    uint32_t diag_spin_limit = 0;
+    int diag_skip_tile = -1;
 };
 
+long long count_nonfinite(const float* x, size_t n, cudaStream_t st);
 void launch_gather_last_rows(const float* rows, const int* row_last, const int* row_seq, float* x_seq, int d, int R,
                              cudaStream_t st);
 void launch_feed_bookkeeping(const int* row_tok, const int* row_pos, const int* row_seq, const int* seq_count, int* pos,

@@ -320,12 +320,6 @@ const char* gradb_kernel_class_name(int kernel_class);
 /* ms_out / launches_out: gradb_kernel_class_count() entries each. */
 gradb_status gradb_session_profile(const gradb_session* session, double* ms_out, uint64_t* launches_out);
 
-/* Diagnostic for the single-sequence persistent kernel: when the session was created with the
- * environment variable GRADB_B1_TRACE=1, the most recent step left nanosecond timestamps of
- * CTA 0 at every stage boundary (start, then "stage done" / "barrier passed" pairs). Returns
- * how many were recorded (0 when tracing is off). No counterpart in the reference. */
-gradb_status gradb_session_stage_trace(gradb_session* session, uint64_t* stamps_out, int capacity, int* count_out);
-
 /* Kernels launched by this library since it was loaded (every launch through
  * its own launcher is counted). */
 uint64_t gradb_kernel_launches(void);

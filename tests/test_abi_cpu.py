@@ -178,3 +178,23 @@ def test_exact_sum_arithmetic_matches_sequential_fp32(tmp_path):
                     "-o", str(exe)], check=True)
     out = subprocess.run([str(exe), "400", "7"], capture_output=True, text=True)
     assert out.returncode == 0, out.stderr
+
+
+def test_host_code_is_clean_under_address_and_undefined_behaviour_sanitizers(tmp_path):
+    """The checkpoint reader/writer over good and damaged files, and the exact-sum arithmetic shared with the
+    selection kernel, built with -fsanitize=address,undefined; any report aborts the run."""
+    import subprocess
+    san = ["-fsanitize=address,undefined", "-fno-sanitize-recover=all", "-fno-omit-frame-pointer", "-g", "-O1"]
+    exe = tmp_path / "checkpoint_sanitize_check"
+    subprocess.run(["g++", "-std=c++17", *san, str(ROOT / "tests" / "checkpoint_sanitize_check.cpp"),
+                    str(ROOT / "grad.cpp_b200" / "csrc" / "checkpoint.cpp"), "-o", str(exe)], check=True)
+    files = [str(GOLD / f"ref_{n}.bin") for n in ("tiny_gpt2", "tiny_modern", "tiny_gpt2_fp", "tiny_modern_fp")]
+    out = subprocess.run([str(exe), str(tmp_path / "scratch.bin"), *files], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = re.search(r"parsed (\d+) rejected (\d+)", out.stdout)
+    assert int(m.group(1)) >= 4 and int(m.group(2)) > 100, out.stdout
+    exe2 = tmp_path / "exact_sum_check_san"
+    subprocess.run(["g++", "-std=c++17", *san, "-ffp-contract=off", str(ROOT / "tests" / "exact_sum_check.cpp"),
+                    "-o", str(exe2)], check=True)
+    out = subprocess.run([str(exe2), "60", "7"], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
