@@ -12,8 +12,8 @@
 // One CTA = one 128-feature tile (two tiles for SwiGLU: gate and up) x one token
 // tile x one K split. Warp 0 lane 0 feeds a 4-stage shared-memory ring with TMA,
 // warp 1 lane 0 issues tcgen05.mma and releases stages with tcgen05.commit, and all
-// four warps run the epilogue from TMEM (bias, RoPE + cache write, GELU / SwiGLU,
-// residual add, logits) once the accumulator barrier fires.
+// sixteen warps (four per TMEM lane quarter) run the epilogue from TMEM (bias, RoPE +
+// cache write, GELU / SwiGLU, residual add, logits) once the accumulator barrier fires.
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel records a code in
 // the session's status word and falls through to the common exit, which frees

@@ -402,7 +402,17 @@ int upload_prompt_matrix(Session* s, const int32_t* tokens, const int32_t* offse
         dalloc(&s->tok_matrix, need);
         s->tok_matrix_cap = need;
     }
-    std::vector<int> host(need, kSkip);
+    // Pinned staging: the copy is asynchronous and the buffer is next written by a later call, after this call's
+    // final stream synchronise.
+    if (need > s->pin_tokmat_cap) {
+        if (s->pin_tokmat) cudaFreeHost(s->pin_tokmat);
+        s->pin_tokmat = nullptr;
+        s->pin_tokmat_cap = 0;
+        GRADB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&s->pin_tokmat), need * sizeof(int)));
+        s->pin_tokmat_cap = need;
+    }
+    int* host = s->pin_tokmat;
+    std::fill(host, host + need, kSkip);
     for (int b = 0; b < n_seq; b++) {
         const int len = offsets[b + 1] - offsets[b];
         for (int t = 0; t < len; t++) {
@@ -411,8 +421,7 @@ int upload_prompt_matrix(Session* s, const int32_t* tokens, const int32_t* offse
         }
     }
     if (need) {
-        GRADB_CUDA(cudaMemcpyAsync(s->tok_matrix, host.data(), need * sizeof(int), cudaMemcpyHostToDevice, s->stream));
-        GRADB_CUDA(cudaStreamSynchronize(s->stream));  // host vector goes out of scope
+        GRADB_CUDA(cudaMemcpyAsync(s->tok_matrix, host, need * sizeof(int), cudaMemcpyHostToDevice, s->stream));
     }
     return steps;
 }
@@ -501,12 +510,16 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
     };
 
     // per-sequence logits mask: id of the last prompt token, or skip
-    f.h_rows.resize((size_t)4 * f.cap + 2 * (size_t)s->B);
-    if (score_targets) {
-        ensure_score_buffers(s);
-        f.h_score.resize((size_t)2 * f.cap);
+    // pinned staging: rows (4 x cap), per-sequence counts and last ids (2 x B), scoring targets (2 x cap), tiles (cap int4)
+    if (!f.pin) {
+        const size_t ints = (size_t)4 * f.cap + 2 * (size_t)s->B + 4 + (size_t)2 * f.cap + (size_t)4 * f.cap;
+        GRADB_CUDA(cudaMallocHost(reinterpret_cast<void**>(&f.pin), ints * sizeof(int)));
     }
-    int* h_last = f.h_rows.data() + (size_t)4 * f.cap + s->B;
+    int* const h_rows = f.pin;
+    int* const h_score = h_rows + (((size_t)4 * f.cap + 2 * (size_t)s->B + 3) & ~size_t(3));  // keeps the tiles 16-byte aligned
+    int4* const h_tiles_pin = reinterpret_cast<int4*>(h_score + (size_t)2 * f.cap);
+    if (score_targets) ensure_score_buffers(s);
+    int* h_last = h_rows + (size_t)4 * f.cap + s->B;
     for (int b = 0; b < n_seq; b++) h_last[b] = offsets[b + 1] > offsets[b] ? tokens[offsets[b + 1] - 1] : kSkip;
     GRADB_CUDA(cudaMemcpyAsync(f.last_tok, h_last, n_seq * sizeof(int), cudaMemcpyHostToDevice, st));
 
@@ -531,7 +544,9 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
     }
     for (const Pass& pass : passes) {
         const int p0 = pass.p0, p1 = pass.p1;
-        int* h_tok = f.h_rows.data();
+        // the staging area is rewritten per pass: wait for the previous pass's copies (rare: prompts beyond one pass)
+        if (&pass != &passes.front()) GRADB_CUDA(cudaStreamSynchronize(st));
+        int* h_tok = h_rows;
         int* h_pos = h_tok + f.cap;
         int* h_seq = h_pos + f.cap;
         int* h_lastrow = h_seq + f.cap;
@@ -550,8 +565,8 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
                 h_seq[R] = b;
                 h_lastrow[R] = j == len - 1 ? h_tok[R] : kSkip;
                 if (score_targets) {
-                    f.h_score[R] = score_targets[offsets[b] + j];
-                    f.h_score[(size_t)f.cap + R] = offsets[b] + j;
+                    h_score[R] = score_targets[offsets[b] + j];
+                    h_score[(size_t)f.cap + R] = offsets[b] + j;
                 }
                 R++;
                 h_cnt[b]++;
@@ -569,15 +584,13 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
         if (tiled) {
             std::sort(f.h_tiles.begin(), f.h_tiles.end(),
                       [](const int4& a, const int4& b) { return a.z + a.w > b.z + b.w; });
-            GRADB_CUDA(cudaMemcpyAsync(f.tiles, f.h_tiles.data(), f.h_tiles.size() * sizeof(int4),
-                                       cudaMemcpyHostToDevice, st));
+            std::copy(f.h_tiles.begin(), f.h_tiles.end(), h_tiles_pin);
+            GRADB_CUDA(cudaMemcpyAsync(f.tiles, h_tiles_pin, f.h_tiles.size() * sizeof(int4), cudaMemcpyHostToDevice, st));
         }
         if (score_targets) {
-            GRADB_CUDA(cudaMemcpyAsync(f.row_tgt, f.h_score.data(), R * sizeof(int), cudaMemcpyHostToDevice, st));
-            GRADB_CUDA(cudaMemcpyAsync(f.row_dst, f.h_score.data() + f.cap, R * sizeof(int), cudaMemcpyHostToDevice,
-                                       st));
+            GRADB_CUDA(cudaMemcpyAsync(f.row_tgt, h_score, R * sizeof(int), cudaMemcpyHostToDevice, st));
+            GRADB_CUDA(cudaMemcpyAsync(f.row_dst, h_score + f.cap, R * sizeof(int), cudaMemcpyHostToDevice, st));
         }
-        GRADB_CUDA(cudaStreamSynchronize(st));  // the staging vector is reused by the next chunk
 
         auto tile_for = [&](int n_features) { return tc_token_tile(R, (n_features + 127) / 128, want); };
         {
@@ -876,6 +889,8 @@ void destroy_session(Session* s) {
     cudaFree(s->h16); cudaFree(s->attn16); cudaFree(s->ffn16); cudaFree(s->status);
     cudaFree(s->hS); cudaFree(s->attnS); cudaFree(s->ffnS);
     if (s->h_stage) cudaFreeHost(s->h_stage);
+    if (s->pin_tokmat) cudaFreeHost(s->pin_tokmat);
+    if (s->feed.pin) cudaFreeHost(s->feed.pin);
     if (s->own_stream && s->stream) cudaStreamDestroy(s->stream);
     delete s;
 }

@@ -32,6 +32,8 @@ struct Session {
     int *gen = nullptr, *done = nullptr, *out_tok = nullptr;
     int* tok_matrix = nullptr;  // prompt feed: [steps][2][B] (token rows, logits-mask rows)
     size_t tok_matrix_cap = 0;
+    int* pin_tokmat = nullptr;  // its pinned host staging
+    size_t pin_tokmat_cap = 0;
     float* uniforms = nullptr;
     size_t uniforms_cap = 0;
     float* probs = nullptr;  // [B][V], allocated on first use
@@ -57,14 +59,13 @@ struct Session {
         int *row_tok = nullptr, *row_pos = nullptr, *row_seq = nullptr, *row_last = nullptr, *seq_count = nullptr,
             *last_tok = nullptr;
         CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];
-        std::vector<int> h_rows;  // host staging: 4 * cap + 2 * B ints
+        int* pin = nullptr;  // pinned host staging of a pass: row tables, counts, scoring targets, tiles
         // teacher-forced scoring: all-row logits of a chunk, per-row target and destination
         int4* tiles = nullptr;  // query tiles of the current chunk (prompt attention)
         std::vector<int4> h_tiles;
         float* score_logits = nullptr;
         float *lse_part = nullptr, *lse_tgt = nullptr;  // fused scoring: per-tile (max, sum) pairs, target logits
         int *row_tgt = nullptr, *row_dst = nullptr;
-        std::vector<int> h_score;  // host staging: 2 * cap ints
     } feed;
     float* score_out = nullptr;  // [B * T] target log-probabilities of the windows being scored
     int* score_tgt = nullptr;    // [T][B] targets, position by position (step-by-step scoring)

@@ -553,10 +553,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode64_kernel(const At
 }
 
 // ---- pipelined variant -----------------------------------------------------------------
-// Head size 64, persistent: one CTA per SM, four independent warps. The (sequence, head,
+// Head size 64, persistent: one CTA per SM, seven independent warps. The (sequence, head,
 // context split) units are dealt round-robin to the grid's warps; each warp turns its units
-// into one flat sequence of 32-position tiles and keeps two tiles ahead of the arithmetic in a
-// private three-stage shared-memory ring filled by bulk asynchronous copies (one copy for the
+// into one flat sequence of 32-position tiles and keeps one tile ahead of the arithmetic in a
+// private two-stage shared-memory ring filled by bulk asynchronous copies (one copy for the
 // tile's K rows, one for its V rows: both are contiguous in the head-major cache). So the HBM
 // stream of a warp continues across unit boundaries instead of restarting per (sequence, head).
 // Scores: lane r owns row r of the tile and walks its 64 columns rotated by r, which keeps the
