@@ -26,7 +26,7 @@ namespace gradb {
 
 namespace {
 
-constexpr int kSelThreads = 1024;
+constexpr int kSelThreads = 512;  // two CTAs (sequences) per SM: one's serial stretches run under the other's parallel ones
 constexpr int kSelWarps = kSelThreads / 32;
 
 // 2^(i/32) as IEEE double bits with i<<47 subtracted, so that adding ki<<47
@@ -138,7 +138,7 @@ __device__ __forceinline__ void scan_pass(Term& term, Hit& hit, ScanShared* st, 
     if (lane == 31) wtot[w] = inc;
     __syncthreads();
     // scan of the 32 warp totals by every warp (lane i holds warp i's total)
-    IncPair wt = wtot[lane];
+    IncPair wt = lane < kSelWarps ? wtot[lane] : IncPair{0u, 0u};  // identity beyond the last warp
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         IncPair prev;
@@ -435,8 +435,10 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
         f_upto = 0;
     }
     __syncthreads();
-    const int start = f_start;
-    const float s0 = f_s0;
+    int start = f_start;
+    float s0 = f_s0;
+    // Windows of at most kFastMax terms, each swept as described above from the exact sum the previous one ended on.
+    for (;;) {
     if (f_hit < n || start >= n) {
         out.sum = s0;
         out.hit = f_hit;
@@ -446,10 +448,10 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
     // Chunks are 16-aligned in index space so a thread's terms are four 128-bit shared-memory loads
     // (a thread-per-chunk scalar pattern would put the whole warp on two banks).
     const int base0 = start & ~(kFastPer - 1);
-    if (n - base0 > kFastMax) return false;  // uniform
+    const int wn = min(n, base0 + kFastMax);  // end of this window
 
     // ---- chunk terms into registers, predicted prefix
-    const int beg = base0 + tid * kFastPer, end = min(n, beg + kFastPer);
+    const int beg = base0 + tid * kFastPer, end = min(wn, beg + kFastPer);
     // The prediction only has to be within ~1e-4 of the exact sum: pairwise fp32 sums (error a few
     // 2^-24 per level) are ample, and much cheaper than double precision here.
     float a[kFastPer];
@@ -457,7 +459,7 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
 #pragma unroll
         for (int j = 0; j < kFastPer / 4; j++) {
             // may read past n inside the shared-memory allocation; such lanes are masked below
-            const float4 v = beg < n ? *reinterpret_cast<const float4*>(arr + beg + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 v = beg < wn ? *reinterpret_cast<const float4*>(arr + beg + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
             a[4 * j] = v.x;
             a[4 * j + 1] = v.y;
             a[4 * j + 2] = v.z;
@@ -483,7 +485,7 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
     __syncthreads();
     float wpre;
     {   // exclusive scan of the 32 warp sums, by every warp
-        float wv = f_wd[lane];
+        float wv = lane < kSelWarps ? f_wd[lane] : 0.f;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const float v = __shfl_up_sync(0xffffffffu, wv, o);
@@ -527,9 +529,9 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
     __syncthreads();
     {
         SegVal wv;
-        wv.m.e = f_we[lane];
-        wv.m.o = f_wo[lane];
-        wv.head = f_wh[lane];
+        wv.m.e = lane < kSelWarps ? f_we[lane] : 0u;
+        wv.m.o = lane < kSelWarps ? f_wo[lane] : 0u;
+        wv.head = lane < kSelWarps ? f_wh[lane] : -1;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const SegVal pv = seg_shfl_up(wv, o);
@@ -548,9 +550,9 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
 
     // ---- the items (segments and unsafe chunks) in order: warp 0 turns the head bits into a list, so that the
     // serial walk below does no searching and can request the next item's data ahead of its arithmetic
-    const int chunks = (n - base0 + kFastPer - 1) / kFastPer;
+    const int chunks = (wn - base0 + kFastPer - 1) / kFastPer;
     if (w == 0) {
-        uint32_t bits = f_headbits[lane];
+        uint32_t bits = lane < kSelWarps ? f_headbits[lane] : 0u;
         const int cnt = __popc(bits);
         int pre = cnt;
 #pragma unroll
@@ -584,7 +586,7 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
             const int e_next = nxt < chunks ? info[nxt] : 0;
             const uint32_t me = seg_e[nxt - 1], mo = seg_o[nxt - 1];
             if (e < 0) {  // unsafe chunk: native adds
-                const int b0 = base0 + t * kFastPer, e0 = min(n, b0 + kFastPer);
+                const int b0 = base0 + t * kFastPer, e0 = min(wn, b0 + kFastPer);
                 float v[kFastPer];
 #pragma unroll
                 for (int i = 0; i < kFastPer; i++) v[i] = (b0 + i >= start && b0 + i < e0) ? term(b0 + i) : 0.0f;  // loads first
@@ -651,10 +653,11 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
         if (mine != 0x7fffffff) atomicMin(&f_hit, mine);
     }
     __syncthreads();
-    out.sum = f_s0;
-    out.hit = f_hit;
+    // this window is done: the next one starts where it ended, from its exact sum
+    start = wn;
+    s0 = f_s0;
     __syncthreads();
-    return true;
+    }
 }
 
 // The exact scan: the one-sweep fast path, or the pass-per-binade scan when it declines.
@@ -666,7 +669,8 @@ __device__ ScanResult exact_scan(int n, const float* arr, Hit hit, bool has_pred
     return seq_scan(n, [arr](int i) { return arr[i]; }, hit, sh);
 }
 
-// Bitonic sort, descending, of n_pad (power of two) floats in shared memory.
+// Bitonic sort, descending, of n_pad (power of two) floats held by this CTA (the rarely taken path sorts in global
+// memory: a CTA sees its own global writes after a barrier).
 __device__ void sort_desc(float* a, int n_pad) {
     for (int k = 2; k <= n_pad; k <<= 1) {
         for (int j = k >> 1; j > 0; j >>= 1) {
@@ -687,35 +691,18 @@ __device__ void sort_desc(float* a, int n_pad) {
 }
 
 constexpr int kBuckets = 4096;
-constexpr int kBucketMax = 96;  // larger buckets fall back to the bitonic sort
+constexpr int kBucketMax = 96;  // larger buckets of unequal values fall back to the bitonic sort
 
-// Descending sort of src[0..n) into dst[0..n) by value buckets: a monotone map
-// sends each key to one of kBuckets ranges, a histogram + prefix sum places the
-// ranges, and each (small) range is finished by insertion. Returns false, with
-// dst unspecified, when the keys are too clustered for that (many equal values)
-// or not finite; the caller then sorts bitonically.
-__device__ bool bucket_sort_desc(const float* src, float* dst, int n, float mn, float mx, int* hist) {
-    __shared__ int s_bad;
+// Exclusive prefix sum over hist[0..kBuckets) in place (bucket starts), kBuckets / kSelThreads consecutive buckets
+// per thread. All threads call it.
+__device__ void bucket_starts(int* hist) {
+    __shared__ int wsum[kSelWarps];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-    if (tid == 0) s_bad = 0;
-    for (int i = tid; i < kBuckets; i += kSelThreads) hist[i] = 0;
-    __syncthreads();
-    const float span = mx - mn;
-    if (!(span > 0.0f) || !(span < 3.0e38f)) return false;  // all equal, NaN or infinite keys
-    const float scale = (float)(kBuckets - 1) / span;
-    auto bucket_of = [&](float v) {
-        int bkt = (int)((mx - v) * scale);  // monotone in v: larger keys land in lower buckets
-        return min(max(bkt, 0), kBuckets - 1);
-    };
-    for (int i = tid; i < n; i += kSelThreads) atomicAdd(&hist[bucket_of(src[i])], 1);
-    __syncthreads();
-    // exclusive prefix sum of the histogram: 4 consecutive buckets per thread
     constexpr int kPer = kBuckets / kSelThreads;
     int c[kPer], tot = 0;
 #pragma unroll
     for (int i = 0; i < kPer; i++) {
         c[i] = hist[tid * kPer + i];
-        if (c[i] > kBucketMax) s_bad = 1;
         tot += c[i];
     }
     int inc = tot;
@@ -724,10 +711,9 @@ __device__ bool bucket_sort_desc(const float* src, float* dst, int n, float mn, 
         const int v = __shfl_up_sync(0xffffffffu, inc, o);
         if (lane >= o) inc += v;
     }
-    __shared__ int wsum[kSelWarps];
     if (lane == 31) wsum[w] = inc;
     __syncthreads();
-    int wv = wsum[lane];
+    int wv = lane < kSelWarps ? wsum[lane] : 0;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const int v = __shfl_up_sync(0xffffffffu, wv, o);
@@ -736,33 +722,210 @@ __device__ bool bucket_sort_desc(const float* src, float* dst, int n, float mn, 
     int base = __shfl_sync(0xffffffffu, wv, (w + 31) & 31);
     if (w == 0) base = 0;
     base += inc - tot;
-    if (s_bad) return false;  // uniform: s_bad was written before the barrier above
 #pragma unroll
     for (int i = 0; i < kPer; i++) {
-        hist[tid * kPer + i] = base;  // becomes the write cursor of the bucket
+        hist[tid * kPer + i] = base;
         base += c[i];
     }
     __syncthreads();
-    for (int i = tid; i < n; i += kSelThreads) {
-        const float v = src[i];
-        dst[atomicAdd(&hist[bucket_of(v)], 1)] = v;
+}
+
+// Descending sort of n probabilities (non-negative, finite). On entry x[0..n) (shared) and g[0..n) (global) hold the
+// same values in index order; on return x holds them sorted, g is untouched. Positive floats order like their bit
+// patterns, so a bucket is a range of bit patterns (an equal share of each binade: the values are exponentials of
+// roughly bell-shaped logits); zeros go to the tail unsorted; a histogram + prefix sum places the buckets, the
+// scatter reads the index-order copy in g while it overwrites x, and each small bucket is finished by insertion.
+// Buckets of many equal values (coarse logits) need no work. Returns false, with x unspecified, when the values are
+// not finite or too clustered; the caller then sorts g's copy bitonically.
+__device__ bool sort_probs_desc(float* x, const float* g, int n, int* hist) {
+    __shared__ uint32_t s_kmin, s_kmax;
+    __shared__ int s_nnz, s_bad;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        s_kmin = 0xffffffffu;
+        s_kmax = 0u;
+        s_nnz = 0;
+        s_bad = 0;
     }
+    for (int i = tid; i < kBuckets; i += kSelThreads) hist[i] = 0;
+    __syncthreads();
+    {
+        uint32_t kmin = 0xffffffffu, kmax = 0u;
+        int nnz = 0, bad = 0;
+        for (int i = tid; i < n; i += kSelThreads) {
+            const uint32_t k = __float_as_uint(x[i]);
+            if (k >= 0x7f800000u) bad = 1;  // NaN, infinity or a negative value
+            if (k != 0u) {
+                kmin = min(kmin, k);
+                kmax = max(kmax, k);
+                nnz++;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+            kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+            nnz += __shfl_xor_sync(0xffffffffu, nnz, o);
+            bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+        }
+        if ((tid & 31) == 0) {
+            atomicMin(&s_kmin, kmin);
+            atomicMax(&s_kmax, kmax);
+            atomicAdd(&s_nnz, nnz);
+            if (bad) s_bad = 1;
+        }
+    }
+    __syncthreads();
+    if (s_bad) return false;  // uniform; x is still intact
+    const int nnz = s_nnz;
+    if (nnz == 0) return true;  // all zero: sorted as it stands
+    const uint32_t kmax = s_kmax, span = kmax - s_kmin;
+    int shift = 0;
+    while ((span >> shift) >= (uint32_t)kBuckets) shift++;
+    for (int i = tid; i < n; i += kSelThreads) {
+        const uint32_t k = __float_as_uint(x[i]);
+        if (k != 0u) atomicAdd(&hist[(kmax - k) >> shift], 1);
+    }
+    __syncthreads();
+    bucket_starts(hist);
+    for (int i = tid; i < n; i += kSelThreads) {
+        const float v = g[i];
+        const uint32_t k = __float_as_uint(v);
+        if (k != 0u) x[atomicAdd(&hist[(kmax - k) >> shift], 1)] = v;
+    }
+    for (int i = nnz + tid; i < n; i += kSelThreads) x[i] = 0.0f;
     __syncthreads();
     // hist[b] is now the END of bucket b; finish each bucket by insertion (descending)
     for (int bkt = tid; bkt < kBuckets; bkt += kSelThreads) {
         const int lo = bkt == 0 ? 0 : hist[bkt - 1], hi = hist[bkt];
+        if (hi - lo > kBucketMax) {
+            const float first = x[lo];
+            bool same = true;
+            for (int i = lo + 1; i < hi && same; i++) same = x[i] == first;
+            if (!same) s_bad = 1;
+            continue;
+        }
         for (int i = lo + 1; i < hi; i++) {
-            const float v = dst[i];
+            const float v = x[i];
             int j = i - 1;
-            while (j >= lo && dst[j] < v) {
-                dst[j + 1] = dst[j];
+            while (j >= lo && x[j] < v) {
+                x[j + 1] = x[j];
                 j--;
             }
-            dst[j + 1] = v;
+            x[j + 1] = v;
         }
     }
     __syncthreads();
-    return true;
+    return s_bad == 0;
+}
+
+// Order-preserving map of finite floats to unsigned integers, and back.
+__device__ __forceinline__ uint32_t ordered_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float from_ordered_key(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// The k-th largest (1 <= k <= n) of x[0..n), what the reference reads off a full descending sort
+// (text_gen.cpp:138-150): the candidates' value range is cut into kBuckets equal parts, the part holding rank k is
+// found from a histogram, and the search continues inside that part's actual value range until it is one value.
+// NaNs take no part. All threads call it and get the same result.
+__device__ float select_kth_desc(const float* x, int n, int k, int* hist) {
+    __shared__ uint32_t s_lo, s_hi;
+    __shared__ int s_bucket, s_before;
+    const int tid = threadIdx.x;
+    constexpr int kPer = kBuckets / kSelThreads;
+    if (tid == 0) {
+        s_lo = 0xffffffffu;
+        s_hi = 0u;
+    }
+    __syncthreads();
+    {
+        uint32_t lo = 0xffffffffu, hi = 0u;
+        for (int i = tid; i < n; i += kSelThreads) {
+            const float v = x[i];
+            if (v == v) {
+                const uint32_t key = ordered_key(v);
+                lo = min(lo, key);
+                hi = max(hi, key);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+            hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+        }
+        if ((tid & 31) == 0) {
+            atomicMin(&s_lo, lo);
+            atomicMax(&s_hi, hi);
+        }
+    }
+    __syncthreads();
+    float lo = from_ordered_key(s_lo), hi = from_ordered_key(s_hi);
+    int rank = k;
+    for (int level = 0; level < 12; level++) {
+        const float span = hi - lo;
+        if (!(span > 0.0f) || !(span < 3.0e38f)) break;  // one value left (or nothing finite to separate)
+        const float scale = (float)(kBuckets - 1) / span;
+        auto bucket_of = [&](float v) {
+            const int bkt = (int)((hi - v) * scale);  // monotone: larger values land in lower buckets
+            return min(max(bkt, 0), kBuckets - 1);
+        };
+        for (int i = tid; i < kBuckets; i += kSelThreads) hist[i] = 0;
+        __syncthreads();
+        for (int i = tid; i < n; i += kSelThreads) {
+            const float v = x[i];
+            if (v >= lo && v <= hi) atomicAdd(&hist[bucket_of(v)], 1);
+        }
+        __syncthreads();
+        int counts[kPer];
+#pragma unroll
+        for (int i = 0; i < kPer; i++) counts[i] = hist[tid * kPer + i];
+        __syncthreads();
+        bucket_starts(hist);  // hist[b] = candidates in buckets before b
+#pragma unroll
+        for (int i = 0; i < kPer; i++) {
+            const int before = hist[tid * kPer + i];
+            if (counts[i] > 0 && before < rank && rank <= before + counts[i]) {
+                s_bucket = tid * kPer + i;
+                s_before = before;
+            }
+        }
+        if (tid == 0) {
+            s_lo = 0xffffffffu;
+            s_hi = 0u;
+        }
+        __syncthreads();
+        const int bkt = s_bucket;
+        rank -= s_before;
+        {
+            uint32_t klo = 0xffffffffu, khi = 0u;
+            for (int i = tid; i < n; i += kSelThreads) {
+                const float v = x[i];
+                if (v >= lo && v <= hi && bucket_of(v) == bkt) {
+                    const uint32_t key = ordered_key(v);
+                    klo = min(klo, key);
+                    khi = max(khi, key);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                klo = min(klo, __shfl_xor_sync(0xffffffffu, klo, o));
+                khi = max(khi, __shfl_xor_sync(0xffffffffu, khi, o));
+            }
+            if ((tid & 31) == 0) {
+                atomicMin(&s_lo, klo);
+                atomicMax(&s_hi, khi);
+            }
+        }
+        __syncthreads();
+        lo = from_ordered_key(s_lo);
+        hi = from_ordered_key(s_hi);
+        __syncthreads();
+    }
+    return hi;
 }
 
 // The chosen id joins the sequence's history; inside the generate loop it also becomes the next step's input
@@ -785,10 +948,13 @@ __device__ __forceinline__ void record_pick(const SelectParams& p, int b, int* h
     }
 }
 
-__global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams p) {
+// Sampled selection, one 512-thread CTA per sequence. Shared memory holds ONE vocabulary-sized array (so two
+// sequences share an SM): the values in index order, except while the nucleus cutoff is being found, when it holds
+// the sorted probabilities and the index-order copy waits in a global scratch row (L2 resident).
+__global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectParams p) {
     extern __shared__ __align__(16) float smem[];
     __shared__ uint32_t scan_sh[2 * kSelWarps + 4];
-    __shared__ float red_v[kSelWarps], red_lo[kSelWarps];
+    __shared__ float red_v[kSelWarps];
     __shared__ uint64_t s_exp_tab[32];
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     if (tid < 32) s_exp_tab[tid] = c_exp2_tab[tid];  // published to all threads by the barriers below
@@ -797,11 +963,12 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     pdl_wait();
     if (p.loop_mode && p.done[b]) return;
 
-    float* x = smem;           // [V]
-    float* sorted = smem + V;  // [n_pad]
-    uint32_t* work = reinterpret_cast<uint32_t*>(sorted + p.n_pad);  // 4096 words: sort histogram, then scan scratch
+    float* x = smem;                                                        // [V] (+ slack the scans may read)
+    uint32_t* work = reinterpret_cast<uint32_t*>(smem + p.n_pad);          // 4096 words: histograms, scan scratch
+    float* g = p.scratch + (size_t)b * p.scratch_stride;                   // [V] index-order copy, then [n_sort] sort area
     const float* lg = p.logits + (size_t)b * V;
     for (int i = tid; i < V; i += kSelThreads) x[i] = lg[i];
+    for (int i = V + tid; i < p.n_pad; i += kSelThreads) x[i] = 0.0f;
     __syncthreads();
 
     // ---- repetition penalty: last min(50, n) ids, once per occurrence, in order (text_gen.cpp:20-31)
@@ -818,100 +985,77 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
     }
     __syncthreads();
 
-    int pick = 0;
-    {
-        const float inv_t = __fdiv_rn(1.0f, p.temperature);  // text_gen.cpp:136
-        const bool use_k = p.top_k > 0 && p.top_k < V;
-        const bool use_p = p.top_p < 1.0f;
-        const int n_pad = p.n_pad;
-        for (int i = tid; i < V; i += kSelThreads) x[i] = __fmul_rn(x[i], inv_t);
-        __syncthreads();
-        float kth = -INFINITY;
-        float mx;
-        if (use_k || use_p) {
-            float m = -INFINITY, lo = INFINITY;
-            for (int i = tid; i < V; i += kSelThreads) {
-                m = fmaxf(m, x[i]);
-                lo = fminf(lo, x[i]);
-            }
-            m = warp_max(m);
-            lo = -warp_max(-lo);
-            if (lane == 0) {
-                red_v[w] = m;
-                red_lo[w] = lo;
-            }
-            __syncthreads();
-            m = red_v[0];
-            lo = red_lo[0];
-            for (int i = 1; i < kSelWarps; i++) {
-                m = fmaxf(m, red_v[i]);
-                lo = fminf(lo, red_lo[i]);
-            }
-            __syncthreads();
-            if (!bucket_sort_desc(x, sorted, V, lo, m, reinterpret_cast<int*>(sorted + n_pad))) {
-                __syncthreads();
-                for (int i = tid; i < n_pad; i += kSelThreads) sorted[i] = i < V ? x[i] : -INFINITY;
-                __syncthreads();
-                sort_desc(sorted, n_pad);
-            }
-            mx = sorted[0];
-            if (use_k) {  // text_gen.cpp:138-154: below the k-th largest value -> -1e10, ties kept
-                kth = sorted[p.top_k - 1];
-                for (int i = tid; i < V; i += kSelThreads) {
-                    if (x[i] < kth) x[i] = -1e10f;
-                }
-            }
-        } else {
-            float m = -INFINITY;
-            for (int i = tid; i < V; i += kSelThreads) m = fmaxf(m, x[i]);
-            m = warp_max(m);
-            if (lane == 0) red_v[w] = m;
-            __syncthreads();
-            m = red_v[0];
-            for (int i = 1; i < kSelWarps; i++) m = fmaxf(m, red_v[i]);
-            mx = m;
+    const float inv_t = __fdiv_rn(1.0f, p.temperature);  // text_gen.cpp:136
+    const bool use_k = p.top_k > 0 && p.top_k < V;
+    const bool use_p = p.top_p < 1.0f;
+    for (int i = tid; i < V; i += kSelThreads) x[i] = __fmul_rn(x[i], inv_t);
+    __syncthreads();
+    if (use_k) {  // text_gen.cpp:138-154: below the k-th largest value -> -1e10, ties kept
+        const float kth = select_kth_desc(x, V, p.top_k, reinterpret_cast<int*>(work));
+        for (int i = tid; i < V; i += kSelThreads) {
+            if (x[i] < kth) x[i] = -1e10f;
         }
         __syncthreads();
-        // softmax (tensor.cpp:434-448): exp(x - max), sequential sum in index order, times 1/sum
-        for (int i = tid; i < V; i += kSelThreads) x[i] = expf_libm(__fsub_rn(x[i], mx), s_exp_tab);
-        __syncthreads();
-        const ScanResult den = exact_scan(V, x, [](float) { return false; }, false, scan_sh, work);
-        const float inv_sum = __fdiv_rn(1.0f, den.sum);
-        for (int i = tid; i < V; i += kSelThreads) x[i] = __fmul_rn(x[i], inv_sum);
-        __syncthreads();
-
-        if (use_p) {  // text_gen.cpp:158-193
-            // The sorted probabilities are the same map applied to the sorted logits (it is monotone).
-            for (int i = tid; i < V; i += kSelThreads) {
-                float v = sorted[i];
-                if (use_k && v < kth) v = -1e10f;
-                sorted[i] = __fmul_rn(expf_libm(__fsub_rn(v, mx), s_exp_tab), inv_sum);
-            }
-            __syncthreads();
-            const float top_p = p.top_p;
-            const ScanResult cut = exact_scan(V, sorted, [top_p](float s) { return s >= top_p; }, true, scan_sh, work);
-            const int cutoff = cut.hit < V ? cut.hit : 0;  // never reached: index stays 0
-            const float cutoff_prob = sorted[cutoff];
-            __syncthreads();
-            for (int i = tid; i < V; i += kSelThreads) {
-                if (x[i] < cutoff_prob) x[i] = 0.0f;
-            }
-            __syncthreads();
-            const ScanResult kept = exact_scan(V, x, [](float) { return false; }, false, scan_sh, work);
-            if (kept.sum > 0.0f) {
-                const float tk = kept.sum;
-                for (int i = tid; i < V; i += kSelThreads) x[i] = __fdiv_rn(x[i], tk);
-            }
-            __syncthreads();
-        }
-        if (p.probs_out) {
-            for (int i = tid; i < V; i += kSelThreads) p.probs_out[(size_t)b * V + i] = x[i];
-        }
-        // draw (text_gen.cpp:199-208): first index with u <= running sum, else the last id
-        const float u = p.uniforms[(size_t)b * p.u_stride + (p.loop_mode ? p.gen[b] : 0)];
-        const ScanResult dr = exact_scan(V, x, [u](float s) { return u <= s; }, true, scan_sh, work);
-        pick = dr.hit < V ? dr.hit : V - 1;
     }
+    float mx;
+    {
+        float m = -INFINITY;
+        for (int i = tid; i < V; i += kSelThreads) m = fmaxf(m, x[i]);
+        m = warp_max(m);
+        if (lane == 0) red_v[w] = m;
+        __syncthreads();
+        m = red_v[0];
+        for (int i = 1; i < kSelWarps; i++) m = fmaxf(m, red_v[i]);
+        mx = m;
+    }
+    // softmax (tensor.cpp:434-448): exp(x - max), sequential sum in index order, times 1/sum
+    for (int i = tid; i < V; i += kSelThreads) x[i] = expf_libm(__fsub_rn(x[i], mx), s_exp_tab);
+    __syncthreads();
+    const ScanResult den = exact_scan(V, x, [](float) { return false; }, false, scan_sh, work);
+    const float inv_sum = __fdiv_rn(1.0f, den.sum);
+    for (int i = tid; i < V; i += kSelThreads) {
+        const float pr = __fmul_rn(x[i], inv_sum);
+        x[i] = pr;
+        if (use_p) g[i] = pr;
+    }
+    __syncthreads();
+
+    if (use_p) {  // text_gen.cpp:158-193
+        // The reference sorts (probability, id) pairs; only the sorted VALUES enter its running sum, so the
+        // probabilities are sorted directly.
+        if (!sort_probs_desc(x, g, V, reinterpret_cast<int*>(work))) {
+            __syncthreads();
+            float* area = g + V;  // bitonic sort of a padded copy in global memory: slow, and rare
+            for (int i = tid; i < p.n_sort; i += kSelThreads) area[i] = i < V ? g[i] : -INFINITY;
+            __syncthreads();
+            sort_desc(area, p.n_sort);
+            for (int i = tid; i < V; i += kSelThreads) x[i] = area[i];
+            __syncthreads();
+        }
+        const float top_p = p.top_p;
+        const ScanResult cut = exact_scan(V, x, [top_p](float s) { return s >= top_p; }, true, scan_sh, work);
+        const int cutoff = cut.hit < V ? cut.hit : 0;  // never reached: index stays 0
+        const float cutoff_prob = x[cutoff];
+        __syncthreads();
+        for (int i = tid; i < V; i += kSelThreads) {
+            const float pr = g[i];
+            x[i] = pr < cutoff_prob ? 0.0f : pr;
+        }
+        __syncthreads();
+        const ScanResult kept = exact_scan(V, x, [](float) { return false; }, false, scan_sh, work);
+        if (kept.sum > 0.0f) {
+            const float tk = kept.sum;
+            for (int i = tid; i < V; i += kSelThreads) x[i] = __fdiv_rn(x[i], tk);
+        }
+        __syncthreads();
+    }
+    if (p.probs_out) {
+        for (int i = tid; i < V; i += kSelThreads) p.probs_out[(size_t)b * V + i] = x[i];
+    }
+    // draw (text_gen.cpp:199-208): first index with u <= running sum, else the last id
+    const float u = p.uniforms[(size_t)b * p.u_stride + (p.loop_mode ? p.gen[b] : 0)];
+    const ScanResult dr = exact_scan(V, x, [u](float s) { return u <= s; }, true, scan_sh, work);
+    const int pick = dr.hit < V ? dr.hit : V - 1;
 
     if (tid == 0) record_pick(p, b, hist, hlen, pick);
 }
@@ -1028,11 +1172,19 @@ __global__ void __launch_bounds__(kGreedyThreads) select_greedy_kernel(const Sel
 
 }  // namespace
 
+// Shared memory of the sampled kernel: the vocabulary-sized array, padded to whole 16-term chunks plus one chunk the
+// scans may read past the end, and 4096 words of histogram / scan scratch.
 size_t select_smem_bytes(int V, int* n_pad_out) {
-    int n_pad = 1;
-    while (n_pad < V) n_pad <<= 1;
+    const int n_pad = (V + 15) / 16 * 16 + 16;
     if (n_pad_out) *n_pad_out = n_pad;
-    return ((size_t)V + n_pad) * sizeof(float) + kBuckets * sizeof(int);
+    return (size_t)n_pad * sizeof(float) + kBuckets * sizeof(int);
+}
+
+// Floats of global scratch per sequence: the index-order copy of the probabilities and the area of the fallback sort.
+size_t select_scratch_floats(int V) {
+    size_t n_sort = 1;
+    while (n_sort < (size_t)V) n_sort <<= 1;
+    return (size_t)V + n_sort;
 }
 
 bool select_sampled_fits(int V) { return select_smem_bytes(V, nullptr) <= 200 * 1024; }
@@ -1042,6 +1194,9 @@ void configure_select(int V) {
     if (bytes > 48 * 1024 && bytes <= 200 * 1024) {
         GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
+    // two sequences per SM need the large shared-memory configuration
+    GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    (int)cudaSharedmemCarveoutMaxShared));
 }
 
 void launch_select(const SelectParams& p_in, int B, cudaStream_t st) {
@@ -1056,8 +1211,11 @@ void launch_select(const SelectParams& p_in, int B, cudaStream_t st) {
     const size_t bytes = select_smem_bytes(p.V, &p.n_pad);
     if (bytes > 200 * 1024) {
         throw Error(GRADB_ERR_INVALID,
-                    "vocabulary too large for the on-device sampled selection stage (limit 16384 ids; greedy has none)");
+                    "vocabulary too large for the on-device sampled selection stage (limit 47000 ids; greedy has none)");
     }
+    if (!p.scratch) throw Error(GRADB_ERR_INVALID, "sampled selection needs its scratch rows");
+    p.scratch_stride = select_scratch_floats(p.V);
+    p.n_sort = (int)(p.scratch_stride - (size_t)p.V);
     if (bytes > 48 * 1024 && !g_capturing) {
         GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }

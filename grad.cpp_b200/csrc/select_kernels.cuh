@@ -7,7 +7,10 @@ namespace gradb {
 struct SelectParams {
     const float* logits;  // [B][V]
     int V;
-    int n_pad;  // filled by the launcher
+    int n_pad;  // filled by the launcher: floats of the shared-memory array
+    int n_sort;             // filled by the launcher: power of two >= V (area of the fallback sort)
+    float* scratch;         // [B][select_scratch_floats(V)] global scratch rows (sampled mode)
+    size_t scratch_stride;  // filled by the launcher
     int greedy;
     float temperature, penalty;
     int top_k;
@@ -37,6 +40,7 @@ struct SelectParams {
 };
 
 size_t select_smem_bytes(int V, int* n_pad_out);
+size_t select_scratch_floats(int V);
 // Sampled selection keeps one sequence's values and their sorted copy in one CTA's shared memory.
 bool select_sampled_fits(int V);
 void configure_select(int V);

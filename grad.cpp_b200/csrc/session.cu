@@ -355,6 +355,10 @@ SelectParams make_select(Session* s, const gradb_sampling& sp) {
     p.pos = s->pos;
     p.capacity = s->T;
     p.status = s->status;
+    if (!sp.greedy) {  // sampled selection keeps one row of global scratch per sequence
+        if (!s->select_scratch) dalloc(&s->select_scratch, (size_t)s->B * select_scratch_floats(s->V));
+        p.scratch = s->select_scratch;
+    }
     return p;
 }
 
@@ -373,7 +377,7 @@ void validate_sampling(const Session* s, const gradb_sampling& sp) {
     if (!(sp.temperature > 0.0f)) throw Error(GRADB_ERR_INVALID, "temperature must be positive");
     if (!select_sampled_fits(s->V)) {
         throw Error(GRADB_ERR_INVALID,
-                    "vocabulary too large for the on-device sampled selection stage (limit 16384 ids; greedy has none)");
+                    "vocabulary too large for the on-device sampled selection stage (limit 47000 ids; greedy has none)");
     }
 }
 
@@ -878,7 +882,7 @@ void destroy_session(Session* s) {
     cudaFree(s->kcache); cudaFree(s->vcache); cudaFree(s->attn_partial); cudaFree(s->attn_counters);
     cudaFree(s->tok); cudaFree(s->pos); cudaFree(s->hist); cudaFree(s->hist_len);
     cudaFree(s->gen); cudaFree(s->done); cudaFree(s->out_tok); cudaFree(s->tok_matrix);
-    cudaFree(s->uniforms); cudaFree(s->probs);
+    cudaFree(s->uniforms); cudaFree(s->probs); cudaFree(s->select_scratch);
     cudaFree(s->b1_ws); cudaFree(s->b1_trace);
     cudaFree(s->feed.hS); cudaFree(s->feed.attnS); cudaFree(s->feed.ffnS);
     cudaFree(s->feed.x); cudaFree(s->feed.q); cudaFree(s->feed.attn); cudaFree(s->feed.h16); cudaFree(s->feed.attn16);

@@ -37,6 +37,7 @@ struct Session {
     float* uniforms = nullptr;
     size_t uniforms_cap = 0;
     float* probs = nullptr;  // [B][V], allocated on first use
+    float* select_scratch = nullptr;  // sampled selection: [B][select_scratch_floats(V)], allocated on first use
 
     // tensor-core path: bf16 activations (GEMM B operands), their TMA descriptors, device status word
     bool use_tc = false;

@@ -269,8 +269,8 @@ def test_bf16_weight_mode_stays_close(name, G, models, golden):
 def test_greedy_has_no_vocabulary_limit(vocab, arch, G, ck, port, tmp_path):
     """Greedy selection reads the logits from global memory and keeps only the penalty window's entries on chip,
     so vocabularies beyond one CTA's shared memory work (the reference's argmax is a plain loop,
-    text_gen.cpp:52-60; its checkpoints allow 2^24 ids). The sampled stage keeps its limit and refuses
-    before anything is fed."""
+    text_gen.cpp:52-60; its checkpoints allow 2^24 ids). The sampled stage works up to about 47000 ids (its exact
+    scans run in windows) and beyond that refuses before anything is fed."""
     dm = ck.ModelDims(vocab, 128, 2, 2, 48, arch)
     path = str(ck.write_synthetic(tmp_path / "bigvocab.bin", dm, 131, 0.08, True))
     rng = np.random.default_rng(132)
@@ -296,8 +296,23 @@ def test_greedy_has_no_vocabulary_limit(vocab, arch, G, ck, port, tmp_path):
     for i, h in enumerate(hist):
         assert got[i] == port.argmax(port.apply_penalty(lg[i], h, 1.7)), i
     s.reset()
-    with pytest.raises(G.binding.GradbError) as e:
-        s.generate(prompts, G.Sampling(0, 0.8, 1.0, 0, 0.9), 4, uniforms=rng.random((3, 4), dtype=np.float32))
-    assert "16384" in str(e.value) and all(s.position(i) == 0 for i in range(3))
+    u = rng.random((3, 4), dtype=np.float32)
+    if vocab > 47000:   # the sampled stage keeps one sequence's values in one CTA's shared memory
+        with pytest.raises(G.binding.GradbError) as e:
+            s.generate(prompts, G.Sampling(0, 0.8, 1.0, 0, 0.9), 4, uniforms=u)
+        assert "47000" in str(e.value) and all(s.position(i) == 0 for i in range(3))
+    else:               # several windows of the exact scans; bit for bit on identical logits and draws
+        lg = (rng.standard_normal((3, vocab)) * 1.7).astype(np.float32)
+        for t, k, pp in ((0.8, 0, 0.9), (1.3, 50, 1.0), (0.7, 300, 0.95), (1.0, 0, 1.0)):
+            for i in range(3):
+                s.set_history(i, [])
+            got, probs = s.select(G.Sampling(0, t, 1.0, k, pp), uniforms=u[:, 0], logits=lg, want_probs=True)
+            for i in range(3):
+                tok, want = port.sample(lg[i], t, k, pp, float(u[i, 0]), want_probs=True)
+                assert got[i] == tok and np.array_equal(probs[i].view(np.uint32), want.view(np.uint32)), (t, k, pp, i)
+        out = s.generate(prompts, G.Sampling(0, 0.8, 1.1, 40, 0.9), 4, uniforms=u)
+        for p, o, ui in zip(prompts, out, u):
+            want = port.generate(om, p, 4, greedy=False, temperature=0.8, penalty=1.1, top_k=40, top_p=0.9, draws=ui)
+            assert np.array_equal(o, want)
     port.free(om)
     s.close(); m.close()
