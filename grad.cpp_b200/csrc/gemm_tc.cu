@@ -468,13 +468,17 @@ __global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(c
 // overlaps (tensor pipe 11-26 % busy). Here
 //   warp 0 (one lane)  streams A and B tiles through a deep ring, running ahead across tile boundaries,
 //   warp 1 (one lane)  issues the MMAs into one of TWO accumulators in TMEM,
-//   warps 2-9          drain the other accumulator (the shared epilogue; two warps per TMEM lane quarter,
-//                      half of the token columns each), so the epilogue of tile i runs under the main
-//                      loop of tile i+1. The epilogue is arithmetic- and latency-bound, hence eight warps.
+//   warps 2-17         drain the other accumulator (the shared epilogue; four warps per TMEM lane quarter,
+//                      a quarter of the token columns each), so the epilogue of tile i runs under the main
+//                      loop of tile i+1. The epilogue is arithmetic- and latency-bound, hence sixteen warps.
 // Tiles are dealt round-robin, feature tile fastest, so CTAs working at the same time share a token tile in L2.
 constexpr int kWideTN = 128;
 constexpr int wide_stages(int nw) { return nw == 1 ? 4 : 3; }  // 128 or 144 KB of ring
 constexpr int kWideStageTileBytes = kWideTN * kTileM * 4;      // + one fp32 output tile staged for the row-wise epilogue
+// Four epilogue warps per TMEM lane quarter: with eight warps in all the epilogue, not the MMA stream, set a tile's
+// time (scoring 65536 ids: 23.3 -> 20.6 ms with sixteen; 256-token tiles on top of that measured no gain).
+constexpr int kWideEpiWarps = 16;
+constexpr int kWideThreads = 64 + 32 * kWideEpiWarps;
 
 // Epilogue pass A of the persistent kernel: accumulator (TMEM, one lane per feature) -> fp32 tile in shared
 // memory laid out [token][feature], with the per-feature work done on the way (bias, GELU, SwiGLU).
@@ -532,7 +536,7 @@ __device__ __forceinline__ void wide_epilogue_rows(const TcGemmParams& p, const 
     const int half = p.hs / 2;
     float* kv_t = (which == 1 ? p.kcache : p.vcache) + (size_t)h * p.T * p.hs + c_in;
 #pragma unroll 8
-    for (int c = we; c < TN; c += 8) {
+    for (int c = we; c < TN; c += kWideEpiWarps) {
         if (s_tok[c] < 0) continue;  // warp-uniform
         float4 x = *reinterpret_cast<const float4*>(stg + c * kTileM + 4 * lane);
         if (EPI == TC_LSE && !f_in) x = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
@@ -585,7 +589,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 
 template <int EPI, int NW>
-__global__ void __launch_bounds__(320) gemm_bf16_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                 const __grid_constant__ CUtensorMap map_b,
                                                                 const TcGemmParams p, int tiles_n, int total_tiles) {
     constexpr int TN = kWideTN;
@@ -617,7 +621,7 @@ __global__ void __launch_bounds__(320) gemm_bf16_tc_wide_kernel(const __grid_con
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+            mbar_init(&acc_empty[b], kWideEpiWarps);  // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -693,8 +697,8 @@ __global__ void __launch_bounds__(320) gemm_bf16_tc_wide_kernel(const __grid_con
         }
         __syncwarp();
     } else {
-        // ---- eight epilogue warps: TMEM lane quarter = warp index modulo 4, two warps per quarter, each
-        // taking half of the tile's token columns
+        // ---- epilogue warps: TMEM lane quarter = warp index modulo 4, kWideEpiWarps / 4 warps per quarter, each
+        // taking an equal share of the tile's token columns
         const int q = warp & 3;
         const int t = q * 32 + lane;
         const int hf = (warp - 2) >> 2;
@@ -715,18 +719,18 @@ __global__ void __launch_bounds__(320) gemm_bf16_tc_wide_kernel(const __grid_con
             if (!mbar_wait(&acc_full[buf], (lt >> 1) & 1, p.status, 114)) s_fail = 1;
             // The epilogue warps only: publishes the staged ids and makes the give-up decision common,
             // so that no warp is left waiting at this barrier.
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");
             if (s_fail) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             wide_epilogue_stage<EPI, NW>(p, tmem_base + (uint32_t)(buf * kAccCols) + ((uint32_t)(q * 32) << 16), t, tile_n,
-                                         stg, hf * (TN / 2), (hf + 1) * (TN / 2));
+                                         stg, hf * (TN / (kWideEpiWarps / 4)), (hf + 1) * (TN / (kWideEpiWarps / 4)));
             // the accumulator is drained: hand it back before the row pass
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
-            asm volatile("bar.sync 1, 256;" ::: "memory");  // staged tile complete
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");  // staged tile complete
             wide_epilogue_rows<EPI>(p, stg, warp - 2, lane, tile_n, tile_b, s_tok[buf], s_pos[buf], s_off[buf]);
-            asm volatile("bar.sync 1, 256;" ::: "memory");  // staged tile free again
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");  // staged tile free again
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -949,7 +953,7 @@ void launch_wide(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams&
         GRADB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
     const int total = tiles_n * tiles_b;
-    launch_kernel(kernel, dim3(std::min(total, sm_count)), dim3(320), bytes, st, a, b, p, tiles_n, total);
+    launch_kernel(kernel, dim3(std::min(total, sm_count)), dim3(kWideThreads), bytes, st, a, b, p, tiles_n, total);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }
