@@ -14,7 +14,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libgradb.so"
 LIB_DIAG = HERE / "libgradb_diag.so"  # the diagnostics build (csrc/gradb_diag.h): index checks, traces, test hooks
-SOURCES = ["checkpoint.cpp", "model.cu", "step_kernels.cu", "attn_prefill.cu", "select_kernels.cu", "gemm_tc.cu", "decode_b1.cu", "session.cu", "capi.cu"]
+SOURCES = ["checkpoint.cpp", "model.cu", "step_kernels.cu", "attn_prefill.cu", "attn_prefill_tc.cu", "select_kernels.cu", "gemm_tc.cu", "decode_b1.cu", "session.cu", "capi.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "--expt-extended-lambda"]
 

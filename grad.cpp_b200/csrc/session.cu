@@ -430,12 +430,27 @@ int upload_prompt_matrix(Session* s, const int32_t* tokens, const int32_t* offse
     return steps;
 }
 
-constexpr int kFeedRows = 8192;  // prompt tokens processed at once by the batched feed
+// Prompt tokens processed at once by the batched feed: everything the session can hold, between 8192 rows (the
+// activations of a pass then stay in L2) and 65536 (long passes give the persistent GEMM tens of tiles per SM, so its
+// prologue, its last un-overlapped epilogue and the partly filled last round weigh little: scoring 65536 ids took
+// 20.4 ms in passes of 8192 rows, 18.5 in 16384, 17.9 in 32768, 17.3 in one). fp32 sessions stop at 16384: their
+// operands are twice as large and scoring keeps a pass's full logits. GRADB_FEED_ROWS overrides.
+constexpr size_t kFeedRowsMin = 8192, kFeedRowsMax = 65536, kFeedRowsMaxFp32 = 16384;
+
+size_t feed_rows_for(const Session* s) {
+    const size_t most = s->use_tc ? kFeedRowsMax : kFeedRowsMaxFp32;
+    size_t rows = std::min(most, std::max(kFeedRowsMin, (size_t)s->B * (size_t)s->T));
+    if (const char* e = std::getenv("GRADB_FEED_ROWS")) {
+        const long v = std::atol(e);
+        if (v >= 1024 && v <= (1 << 18)) rows = (size_t)v;
+    }
+    return (rows + 127) / 128 * 128;
+}
 
 void ensure_feed_buffers(Session* s) {
     Session::Feed& f = s->feed;
     if (f.cap) return;
-    const size_t R = kFeedRows;
+    const size_t R = feed_rows_for(s);
     dalloc(&f.x, R * s->d);
     dalloc(&f.q, R * s->d);
     dalloc(&f.attn, R * s->d);
@@ -456,6 +471,10 @@ void ensure_feed_buffers(Session* s) {
     dalloc(&f.last_tok, (size_t)s->B);
     dalloc(&f.tiles, R);
     prefill_attention_configure();
+    if (s->use_tc_attn) {
+        prefill_attention_tc_configure();
+        make_tensor_map_f32(&f.map_q, f.q, R, s->d, 128);
+    }
     for (int i = 0; i < 3; i++) {
         const uint32_t tn = 32u << i;
         if (s->use_tc32) {
@@ -507,6 +526,9 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
     const bool s32 = s->use_tc32;
     const int kind = s32 ? 1 : 0;
     const bool tiled_ok = !(no_tiled && no_tiled[0] == '1');
+    const char* no_tc_attn = std::getenv("GRADB_NO_TC_ATTN");
+    const bool tc_attn = s->use_tc_attn && !(no_tc_attn && no_tc_attn[0] == '1');
+    const int tile_rows = tc_attn ? 128 : 64;  // query positions per attention tile
     const size_t lo_d = (size_t)f.cap * d, lo_f = (size_t)f.cap * ff;
     auto norm_rows = [&](const float* x, const float* g, const float* b, const int* tk, int rows) {
         if (s32) launch_norm_split(x, g, b, tk, f.hS, lo_d, d, modern, 1e-5f, rows, st);
@@ -560,8 +582,9 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
         for (int b = 0; b < n_seq; b++) h_cnt[b] = 0;
         for (int b = pass.b0; b < pass.b1; b++) {
             const int len = offsets[b + 1] - offsets[b];
-            for (int j = p0; j < std::min(p1, len); j += 64) {
-                f.h_tiles.push_back(make_int4(b, R + (j - p0), s->h_pos[b] + j, std::min(64, std::min(p1, len) - j)));
+            for (int j = p0; j < std::min(p1, len); j += tile_rows) {
+                f.h_tiles.push_back(
+                    make_int4(b, R + (j - p0), s->h_pos[b] + j, std::min(tile_rows, std::min(p1, len) - j)));
             }
             for (int j = p0; j < std::min(p1, len); j++) {
                 h_tok[R] = tokens[offsets[b] + j];
@@ -626,10 +649,14 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
                 if (tiled) {
                     PrefillAttnParams a{};
                     a.q = f.q; a.kcache = kc; a.vcache = vc; a.out = s32 ? f.attn : nullptr; a.out16 = s32 ? nullptr : f.attn16;
-                    a.tiles = f.tiles; a.n_tiles = (int)f.h_tiles.size();
+                    a.tiles = f.tiles; a.n_tiles = (int)f.h_tiles.size(); a.status = s->status;
                     a.H = s->H; a.T = s->T; a.d = d;
                     a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
-                    launch_prefill_attention(a, st, s32);
+                    if (tc_attn) {
+                        launch_prefill_attention_tc(a, f.map_q, s->map_kcache, (long long)l * s->B * s->H * s->T, st);
+                    } else {
+                        launch_prefill_attention(a, st, s32);
+                    }
                     if (s32) launch_split_tf32(f.attn, f.attnS, lo_d, (size_t)R * d, st);
                 } else {
                     AttnParams a{};
@@ -824,6 +851,10 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
                 make_tensor_map_f32(&s->map_attn16[i], s->attnS, 2 * rows, s->d, tn);
                 make_tensor_map_f32(&s->map_ffn16[i], s->ffnS, 2 * rows, s->dff, tn);
             }
+        }
+        if (s->use_tc && s->hs == 64) {
+            s->use_tc_attn = true;
+            make_tensor_map_f32(&s->map_kcache, s->kcache, (uint64_t)s->L * B * s->H * s->T, 64, 128);
         }
         if (s->use_tc) {
             tc_configure_all();

@@ -50,6 +50,8 @@ struct Session {
     float *hS = nullptr, *attnS = nullptr, *ffnS = nullptr;
     int split_rows = 0;  // rows of one half
     int* status = nullptr;
+    bool use_tc_attn = false;  // prompt attention on tcgen05 (bf16 sessions, head size 64)
+    CUtensorMap map_kcache;    // fp32 map over the whole K cache as rows of 64 floats
 
     // batched prompt feed (one row per prompt token, all positions of a chunk at once)
     struct Feed {
@@ -60,6 +62,7 @@ struct Session {
         int *row_tok = nullptr, *row_pos = nullptr, *row_seq = nullptr, *row_last = nullptr, *seq_count = nullptr,
             *last_tok = nullptr;
         CUtensorMap map_h16[3], map_attn16[3], map_ffn16[3];
+        CUtensorMap map_q;  // fp32 map over the query rows (tensor-core prompt attention)
         int* pin = nullptr;  // pinned host staging of a pass: row tables, counts, scoring targets, tiles
         // teacher-forced scoring: all-row logits of a chunk, per-row target and destination
         int4* tiles = nullptr;  // query tiles of the current chunk (prompt attention)

@@ -124,7 +124,8 @@ def test_eval_shape_windows_of_256_on_the_69m_model(G, ck, port, tmp_path, monke
     s32 = G.BatchSession(m32, 8, 256)
     lp32 = s32.score(inp[:8], tgt[:8])
     s32.close(); m32.close()
-    assert float(np.abs(lp16[:8] - lp32).max()) < 2e-2
+    # bf16 weights and activations against fp32: rms near 5e-3 over the 2048 positions, the largest near 2e-2
+    assert float(np.sqrt(np.mean((lp16[:8] - lp32) ** 2))) < 7e-3 and float(np.abs(lp16[:8] - lp32).max()) < 3e-2
     om = port.load(path)
     _, _, want = port.mean_loss(om, inp[:1, :12], tgt[:1, :12], 8)
     port.free(om)
