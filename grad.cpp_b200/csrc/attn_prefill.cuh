@@ -28,7 +28,7 @@ void prefill_attention_configure();
 // tensor map over the whole K cache as rows of 64 floats, k_row0 = first row of this layer in it.
 void prefill_attention_tc_configure();
 void launch_prefill_attention_tc(const PrefillAttnParams& p, const CUtensorMap& map_q, const CUtensorMap& map_k,
-                                 long long k_row0, cudaStream_t st);
+                                 long long k_row0, int sm_count, cudaStream_t st);
 // fp32_grade: three TF32 MMAs per product on hi/lo operand pairs (fp32 sessions) instead of one.
 void launch_prefill_attention(const PrefillAttnParams& p, cudaStream_t st, bool fp32_grade = false);
 

@@ -3,25 +3,33 @@
 // sequences attend to the cache rows at or before them, inference.cpp:208-225), with the two products of every
 // (128 queries x 128 keys) tile issued as tcgen05.mma into TMEM instead of warp-level mma.sync.
 //
-// One CTA = one tile of up to 128 consecutive query positions of one (sequence, head); 256 threads, two per query row
-// (= TMEM lane: a warp reaches the lane quarter given by its index modulo 4), each owning half of the row's score
-// columns and half of its output dims. The cache stays fp32 and is fed to kind::tf32 MMAs as it lies (TF32 reads fp32 bit patterns):
+// A work item = one tile of up to 128 consecutive query positions of one (sequence, head). The kernel is
+// persistent: one CTA per SM takes items round-robin (head fastest; the host sorts the tiles longest first) and
+// treats its (item, key tile) pairs as ONE stream of elements, so that the copies of an item's first tiles, which
+// come from HBM, are in flight while the item before it is still being computed; with one CTA per SM and prompts of a
+// few hundred positions that latency was otherwise most of a CTA's life. 256 threads, two per query row (= TMEM
+// lane: a warp reaches the lane quarter given by its index modulo 4), each owning half of the row's score columns and
+// half of its output dims. The cache stays fp32 and is fed to kind::tf32 MMAs as it lies (TF32 reads fp32 bit patterns):
 //
 //   S[q, key] (TMEM, 128 cols) = Q[q, :] . K[key, :]      A = Q tile, B = K tile, both dim-contiguous (K-major),
 //                                                        brought by TMA tensor copies with the 128-byte swizzle
-//   softmax by the row's two threads: scale, causal mask, running max / sum, P = exp(S - max) -> TMEM (128 cols):
+//   softmax by the row's two threads: causal mask, running max / sum, P = exp(scale (S - max)) -> TMEM (128 cols):
 //                                                        the A operand of the second product is read from there,
 //                                                        so P never crosses shared memory
 //   O_tile[q, dim] (TMEM, 64 cols) = P[q, :] . V[:, dim]   B must be key-contiguous: the V tile (a contiguous block
 //                                                        of the head-major cache, one bulk copy) is transposed
-//                                                        through shared memory by the threads while S is computed
+//                                                        through shared memory by the threads
 //   o = o * exp(old max - new max) + O_tile              in registers (32 per thread)
 //
-// The K tile has two stages, so the scores of tile j+1 are issued as soon as every thread holds tile j's scores in
-// registers and run under tile j's exponentials; O_tile of tile j is collected at the start of tile j+1's pass, after
-// that tile's scores have been read. The next V tile is requested as soon as the transpose is done. All waits are
-// bounded; on expiry the status word is set and the CTA falls through to the common exit, which frees TMEM.
+// Q has two buffers (the item after next is fetched when an item's last scores are done) and K two stages: the
+// scores of element e+1 are issued as soon as every thread holds element e's scores in registers and run under its
+// exponentials; O_tile of element e is collected in element e+1's pass, and when that element opens a new item the
+// finished item's rows are normalised and written there. The next V tile is requested when the transpose is done;
+// tiles further ahead are prefetched towards L2. All waits are bounded; on expiry the status word is set and the
+// CTA falls through to the common exit, which frees TMEM.
 #include <cuda.h>
+
+#include <algorithm>
 
 #include "attn_prefill.cuh"
 
@@ -37,8 +45,8 @@ constexpr uint32_t kSpin = 1u << 20;
 constexpr int kAtomQ = kQT * 128;  // bytes of one swizzle atom of a 128-row operand: 32 floats per row
 constexpr int kAtomV = kHS * 128;  // bytes of one atom of the transposed V operand: 64 rows (dims) x 32 keys
 // shared-memory map (bytes from a 1024-aligned base)
-constexpr int kOffQ = 0;                       // 2 atoms
-constexpr int kOffK = kOffQ + 2 * kAtomQ;      // 2 stages of 2 atoms
+constexpr int kOffQ = 0;                       // 2 buffers of 2 atoms
+constexpr int kOffK = kOffQ + 4 * kAtomQ;      // 2 stages of 2 atoms
 constexpr int kOffVraw = kOffK + 4 * kAtomQ;   // [128 keys][64] as stored
 constexpr int kOffVt = kOffVraw + kKT * kHS * 4;  // 4 atoms (32 keys each)
 constexpr int kSmemBytes = kOffVt + 4 * kAtomV + 1024;
@@ -148,27 +156,48 @@ __device__ __forceinline__ uint32_t sw128(int r, int c16) {
     return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c16 ^ (r & 7)) << 4));
 }
 
+// One (query tile, head) of the launch: what a CTA works on between two output writes.
+struct Item {
+    int row0, pos0, nq, h, kv_len, n_kv;
+    long long head_row0;  // first cache row of this (sequence, head)
+};
+
 __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                       const __grid_constant__ CUtensorMap map_k,
                                                                       const PrefillAttnParams p, long long k_row0) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q, bar_k[2], bar_v, bar_s, bar_o;
+    __shared__ __align__(8) uint64_t bar_q[2], bar_k[2], bar_v, bar_s, bar_o;
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int s_fail;
-    __shared__ float s_x[2][kQT];  // the two column halves of a row exchange their maxima (and, at the end, sums)
+    __shared__ float s_x[2][kQT];  // the two column halves of a row exchange their maxima
+    __shared__ float s_l[2][kQT];  // ... and, when an item ends, their sums
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int row = (warp & 3) * 32 + lane;  // query row = TMEM lane
     const int hc = warp >> 2;                // which half of the score columns / output dims this thread owns
-    const int4 tile = p.tiles[blockIdx.x];
-    const int seq = tile.x, row0 = tile.y, pos0 = tile.z, nq = tile.w, h = blockIdx.y;
-    const int kv_len = pos0 + nq;
-    const int n_kv = (kv_len + kKT - 1) / kKT;
-    const long long head_row0 = ((long long)seq * p.H + h) * p.T;  // first cache row of this (sequence, head)
+    const int n_items = p.n_tiles * p.H;
+    const int my_count = (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;  // >= 1: grid <= items
+
+    // k-th item of this CTA: items are dealt round-robin, head fastest, so that CTAs working at the same time
+    // hold tiles of the same length (the host sorts the tiles longest first)
+    auto get_item = [&](int k) {
+        const int idx = (int)blockIdx.x + k * (int)gridDim.x;
+        const int4 tile = p.tiles[idx / p.H];
+        Item it;
+        it.h = idx % p.H;
+        it.row0 = tile.y;
+        it.pos0 = tile.z;
+        it.nq = tile.w;
+        it.kv_len = tile.z + tile.w;
+        it.n_kv = (it.kv_len + kKT - 1) / kKT;
+        it.head_row0 = ((long long)tile.x * p.H + it.h) * p.T;
+        return it;
+    };
 
     if (t == 0) {
         s_fail = 0;
-        mbar_init(&bar_q, 1);
+        mbar_init(&bar_q[0], 1);
+        mbar_init(&bar_q[1], 1);
         mbar_init(&bar_k[0], 1);
         mbar_init(&bar_k[1], 1);
         mbar_init(&bar_v, 1);
@@ -189,28 +218,57 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
     const uint32_t tmem_s = tmem_slot + kColS, tmem_p = tmem_slot + kColP, tmem_o = tmem_slot + kColO;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
 
-    // thread 0 only: the K tile of keys [j*128, j*128+128) of this head into stage j & 1, two 32-float halves
-    auto load_k = [&](int j) {
-        uint64_t* bar = &bar_k[j & 1];
-        uint8_t* dst = smem + kOffK + (j & 1) * 2 * kAtomQ;
+    // ---- thread 0 only. The CTA's work is one stream of (item, key tile) elements; element e uses K stage e & 1 and
+    // phase e of the V, S and O barriers; item k uses Q buffer k & 1.
+    auto load_q = [&](int k) {
+        const Item it = get_item(k);
+        uint64_t* bar = &bar_q[k & 1];
+        uint8_t* dst = smem + kOffQ + (k & 1) * 2 * kAtomQ;
         mbar_expect_tx(bar, 2 * kAtomQ);
-        const int y = (int)(k_row0 + head_row0 + (long long)j * kKT);
+        tma_load_2d(dst, &map_q, it.h * kHS, it.row0, bar);
+        tma_load_2d(dst + kAtomQ, &map_q, it.h * kHS + 32, it.row0, bar);
+    };
+    auto prefetch_q = [&](int k) {  // towards L2
+        const Item it = get_item(k);
+        asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(&map_q), "r"(it.h * kHS),
+                     "r"(it.row0)
+                     : "memory");
+        asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(&map_q),
+                     "r"(it.h * kHS + 32), "r"(it.row0)
+                     : "memory");
+    };
+    auto load_k = [&](const Item& it, int j, int e) {  // keys [j*128, j*128+128) of the item's head, two 32-float halves
+        uint64_t* bar = &bar_k[e & 1];
+        uint8_t* dst = smem + kOffK + (e & 1) * 2 * kAtomQ;
+        mbar_expect_tx(bar, 2 * kAtomQ);
+        const int y = (int)(k_row0 + it.head_row0 + (long long)j * kKT);
         tma_load_2d(dst, &map_k, 0, y, bar);
         tma_load_2d(dst + kAtomQ, &map_k, 32, y, bar);
     };
-    auto load_v = [&](int j) {  // thread 0 only: the rows of the V tile that exist, as one contiguous block
-        const int rows = min(kKT, kv_len - j * kKT);
+    auto load_v = [&](const Item& it, int j) {  // the rows of the V tile that exist, as one contiguous block
+        const int rows = min(kKT, it.kv_len - j * kKT);
         const uint32_t bytes = (uint32_t)rows * kHS * 4;
         mbar_expect_tx(&bar_v, bytes);
-        const float* src = p.vcache + (size_t)(head_row0 + (long long)j * kKT) * kHS;
+        const float* src = p.vcache + (size_t)(it.head_row0 + (long long)j * kKT) * kHS;
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                          smem_u32(smem + kOffVraw)),
                      "l"(src), "r"(bytes), "r"(smem_u32(&bar_v))
                      : "memory");
     };
-    // thread 0 only: S = Q K_j^T once stage j & 1 holds tile j (it was requested at least a tile ago)
-    auto issue_scores = [&](int j) {
-        if (!mbar_wait(&bar_k[j & 1], (uint32_t)((j >> 1) & 1), p.status, 402, &s_fail)) {
+    auto prefetch_kv = [&](const Item& it, int j) {  // towards L2, for the element two ahead of the copies above
+        const int rows = min(kKT, it.kv_len - j * kKT);
+        const uint32_t bytes = (uint32_t)rows * kHS * 4;
+        const size_t at = (size_t)(it.head_row0 + (long long)j * kKT) * kHS;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.vcache + at), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.kcache + at), "r"(bytes) : "memory");
+    };
+    // S = Q_k K^T for element e (first of its item when j == 0); its operands were requested at least an element ago
+    auto issue_scores = [&](int k, int j, int e) {
+        if (j == 0 && !mbar_wait(&bar_q[k & 1], (uint32_t)((k >> 1) & 1), p.status, 401, &s_fail)) {
+            s_fail = 1;
+            return;
+        }
+        if (!mbar_wait(&bar_k[e & 1], (uint32_t)((e >> 1) & 1), p.status, 402, &s_fail)) {
             s_fail = 1;
             return;
         }
@@ -218,51 +276,91 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         constexpr uint32_t idesc = umma_idesc_tf32(kQT, kKT);
 #pragma unroll
         for (int a = 0; a < 2; a++) {  // 32 dims per atom, 8 per instruction
-            const uint64_t qd = umma_desc_sw128(smem + kOffQ + a * kAtomQ);
-            const uint64_t kd = umma_desc_sw128(smem + kOffK + ((j & 1) * 2 + a) * kAtomQ);
+            const uint64_t qd = umma_desc_sw128(smem + kOffQ + ((k & 1) * 2 + a) * kAtomQ);
+            const uint64_t kd = umma_desc_sw128(smem + kOffK + ((e & 1) * 2 + a) * kAtomQ);
 #pragma unroll
             for (int kk = 0; kk < 4; kk++) umma_tf32(tmem_s, qd + 2 * kk, kd + 2 * kk, idesc, (a | kk) != 0 ? 1u : 0u);
         }
         umma_commit(&bar_s);
     };
+    // the element after (k, j); false past the CTA's last one
+    auto step = [&](int& k, int& j, int n_kv) {
+        if (++j >= n_kv) {
+            j = 0;
+            ++k;
+        }
+        return k < my_count;
+    };
+
+    Item it = get_item(0);
+    int k = 0, j = 0;
     if (t == 0) {
-        mbar_expect_tx(&bar_q, 2 * kAtomQ);
-        tma_load_2d(smem + kOffQ, &map_q, h * kHS, row0, &bar_q);
-        tma_load_2d(smem + kOffQ + kAtomQ, &map_q, h * kHS + 32, row0, &bar_q);
-        load_k(0);
-        if (n_kv > 1) load_k(1);
-        load_v(0);
-        if (mbar_wait(&bar_q, 0, p.status, 401, &s_fail)) issue_scores(0);
-        else s_fail = 1;
+        load_q(0);
+        if (my_count > 1) load_q(1);
+        load_k(it, 0, 0);
+        load_v(it, 0);
+        int k1 = 0, j1 = 0;
+        if (step(k1, j1, it.n_kv)) {
+            const Item it1 = k1 == 0 ? it : get_item(k1);
+            load_k(it1, j1, 1);
+            int k2 = k1, j2 = j1;
+            if (step(k2, j2, it1.n_kv)) prefetch_kv(k2 == k1 ? it1 : get_item(k2), j2);
+        }
+        issue_scores(0, 0, 0);
     }
 
     float o[kHS / 2];
 #pragma unroll
     for (int i = 0; i < kHS / 2; i++) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's columns only; the halves meet at the end
+    float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's columns only; the halves meet when the item ends
     float corr_prev = 0.f;                 // factor that goes with the O_tile still to be collected
     const float scale2 = p.scale * 1.4426950408889634f;  // exp(x) = ex2(x * log2 e)
-    const int qpos = pos0 + row;  // the position this row's query sits at (rows past the tile's end compute, unused)
+    int done_row0 = 0, done_nq = 0, done_h = 0;          // the item whose last O_tile is still to be collected
     bool ok = true;
-    // O_tile of the previous tile: o = o * (its correction) + O_tile
-    auto collect = [&](int j_prev) {
-        if (!mbar_wait(&bar_o, (uint32_t)(j_prev & 1), p.status, 405, &s_fail)) s_fail = 1;
+    // O_tile of the previous element: o = o * (its correction) + O_tile
+    auto collect = [&](int e_prev) {
+        if (!mbar_wait(&bar_o, (uint32_t)(e_prev & 1), p.status, 405, &s_fail)) s_fail = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         float ot[32];
         tmem_ld32(tmem_o + lane_off + hc * 32, ot);
 #pragma unroll
         for (int i = 0; i < 32; i++) o[i] = o[i] * corr_prev + ot[i];
     };
+    // rows of the finished item: o / (sum of both halves), this thread's 32 dims
+    auto write_out = [&](float l_other) {
+        if (row >= done_nq) return;
+        const float inv = 1.0f / (l_run + l_other);
+        const size_t at = (size_t)(done_row0 + row) * p.d + done_h * kHS + hc * 32;
+        if (p.out16) {
+            uint4* dst = reinterpret_cast<uint4*>(p.out16 + at);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                __nv_bfloat162 b[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) b[q] = __floats2bfloat162_rn(o[8 * i + 2 * q] * inv, o[8 * i + 2 * q + 1] * inv);
+                dst[i] = *reinterpret_cast<const uint4*>(b);
+            }
+        }
+        if (p.out) {
+            float4* dst = reinterpret_cast<float4*>(p.out + at);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+            }
+        }
+    };
 
-    for (int j = 0; j < n_kv; j++) {
-        const uint32_t ph = (uint32_t)(j & 1);
+    int e = 0;
+    for (;; e++) {
+        const uint32_t ph = (uint32_t)(e & 1);
         // ---- this thread's 64 score columns of its row, into registers
         if (!mbar_wait(&bar_s, ph, p.status, 404, &s_fail)) s_fail = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // Scores stay unscaled: exp(scale * (s - max)) is one multiply-add and one ex2 per entry. A 32-column block
         // that lies wholly above the diagonal for every row of this warp is neither read nor exponentiated.
         const int key0 = j * kKT + hc * 64;
-        const int warp_q0 = pos0 + (warp & 3) * 32;  // first query position of this warp's rows
+        const int warp_q0 = it.pos0 + (warp & 3) * 32;  // first query position of this warp's rows
+        const int qpos = it.pos0 + row;  // this row's position (rows past the tile's end compute, unused)
         float sc[64];
         float m_half = -INFINITY;
 #pragma unroll
@@ -286,39 +384,39 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
             }
         }
         s_x[hc][row] = m_half;
+        if (j == 0) s_l[hc][row] = l_run;  // the finished item's sum (nothing yet before the first)
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();  // maxima exchanged; the score accumulator and this tile's K stage are free
+        __syncthreads();  // maxima exchanged; the score accumulator and this element's K stage are free
         if (s_fail) {
             ok = false;
             break;
         }
-        if (t == 0) {  // the next tile's scores run under this tile's exponentials
-            if (j + 2 < n_kv) load_k(j + 2);
-            if (j + 1 < n_kv) issue_scores(j + 1);
-        }
-        if (j > 0) collect(j - 1);  // after this the P and transposed-V buffers are free as well
-
-        // ---- V tile -> key-contiguous operand. Lane = dim (reads are consecutive words), one key per step.
-        if (!mbar_wait(&bar_v, ph, p.status, 403, &s_fail)) s_fail = 1;
-        {
-            const int rows = min(kKT, kv_len - j * kKT);
-            const float* vraw = reinterpret_cast<const float*>(smem + kOffVraw);
-            // four keys at a time: each lane gathers its dim's four values and stores them as one 16-byte chunk
-#pragma unroll
-            for (int g = warp; g < kKT / 4; g += kThreads / 32) {
-                float a[4], b[4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int key = g * 4 + i;
-                    const bool live = key < rows;  // rows past the context are zero: a masked 0 times stale bits must stay 0
-                    a[i] = live ? vraw[key * kHS + lane] : 0.f;
-                    b[i] = live ? vraw[key * kHS + 32 + lane] : 0.f;
+        if (t == 0) {  // the next element's scores run under this one's exponentials
+            int k1 = k, j1 = j;
+            if (step(k1, j1, it.n_kv)) {
+                const Item it1 = k1 == k ? it : get_item(k1);
+                int k2 = k1, j2 = j1;
+                if (step(k2, j2, it1.n_kv)) {
+                    const Item it2 = k2 == k1 ? it1 : get_item(k2);
+                    load_k(it2, j2, e + 2);
+                    int k3 = k2, j3 = j2;
+                    if (step(k3, j3, it2.n_kv)) prefetch_kv(k3 == k2 ? it2 : get_item(k3), j3);
                 }
-                uint8_t* atom = smem + kOffVt + (g >> 3) * kAtomV;
-                *reinterpret_cast<float4*>(atom + sw128(lane, g & 7)) = make_float4(a[0], a[1], a[2], a[3]);
-                *reinterpret_cast<float4*>(atom + sw128(lane + 32, g & 7)) = make_float4(b[0], b[1], b[2], b[3]);
+                issue_scores(k1, j1, e + 1);
             }
+            // this item's last scores are done, so its Q buffer is free: fetch the item after next into it
+            if (j == it.n_kv - 1 && k + 2 < my_count) load_q(k + 2);
+            if (j == 0 && k + 3 < my_count) prefetch_q(k + 3);
         }
+        if (e > 0) collect(e - 1);  // after this the P and transposed-V buffers are free as well
+        if (j == 0 && e > 0) {      // that was the previous item's last O_tile
+            write_out(s_l[hc ^ 1][row]);
+#pragma unroll
+            for (int i = 0; i < kHS / 2; i++) o[i] = 0.f;
+            m_run = -INFINITY;
+            l_run = 0.f;
+        }
+
         // ---- exponentials of this thread's columns -> P
         // Every row sees key 0, so the running maximum is finite from the first tile on and a masked entry
         // (-inf) comes out of ex2 as an exact zero.
@@ -341,10 +439,31 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
             }
             tmem_st32(tmem_p + lane_off + hc * 64 + c * 32, pv);
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         l_run = l_run * corr + l_tile;
         m_run = m_new;
         corr_prev = corr;
+
+        // ---- V tile -> key-contiguous operand. Lane = dim (reads are consecutive words), four keys per store.
+        if (!mbar_wait(&bar_v, ph, p.status, 403, &s_fail)) s_fail = 1;
+        {
+            const int rows = min(kKT, it.kv_len - j * kKT);
+            const float* vraw = reinterpret_cast<const float*>(smem + kOffVraw);
+#pragma unroll
+            for (int g = warp; g < kKT / 4; g += kThreads / 32) {
+                float a[4], b[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int key = g * 4 + i;
+                    const bool live = key < rows;  // rows past the context are zero: a masked 0 times stale bits must stay 0
+                    a[i] = live ? vraw[key * kHS + lane] : 0.f;
+                    b[i] = live ? vraw[key * kHS + 32 + lane] : 0.f;
+                }
+                uint8_t* atom = smem + kOffVt + (g >> 3) * kAtomV;
+                *reinterpret_cast<float4*>(atom + sw128(lane, g & 7)) = make_float4(a[0], a[1], a[2], a[3]);
+                *reinterpret_cast<float4*>(atom + sw128(lane + 32, g & 7)) = make_float4(b[0], b[1], b[2], b[3]);
+            }
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         // the transposed V was written by ordinary stores: order them before the tensor core's reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -353,9 +472,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
             ok = false;
             break;
         }
-        // ---- O_tile = P V (collected at the start of the next pass, or after the loop)
+        // ---- O_tile = P V (collected in the next element's pass, or after the loop)
+        int k1 = k, j1 = j;
+        const bool more = step(k1, j1, it.n_kv);
         if (t == 0) {
-            if (j + 1 < n_kv) load_v(j + 1);
+            if (more) load_v(k1 == k ? it : get_item(k1), j1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             constexpr uint32_t idesc = umma_idesc_tf32(kQT, kHS);
 #pragma unroll
@@ -367,35 +488,24 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
             }
             umma_commit(&bar_o);
         }
+        if (k1 != k) {
+            done_row0 = it.row0;
+            done_nq = it.nq;
+            done_h = it.h;
+        }
+        if (!more) break;
+        if (k1 != k) it = get_item(k1);
+        k = k1;
+        j = j1;
     }
     if (ok) {
-        collect(n_kv - 1);
+        collect(e);
         if (s_fail) ok = false;
     }
-
-    s_x[hc][row] = l_run;
+    s_l[hc][row] = l_run;
     __syncthreads();
-    if (ok && row < nq) {
-        const float inv = 1.0f / (l_run + s_x[hc ^ 1][row]);
-        const size_t at = (size_t)(row0 + row) * p.d + h * kHS + hc * 32;
-        if (p.out16) {
-            uint4* dst = reinterpret_cast<uint4*>(p.out16 + at);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                __nv_bfloat162 b[4];
-#pragma unroll
-                for (int k = 0; k < 4; k++) b[k] = __floats2bfloat162_rn(o[8 * i + 2 * k] * inv, o[8 * i + 2 * k + 1] * inv);
-                dst[i] = *reinterpret_cast<const uint4*>(b);
-            }
-        }
-        if (p.out) {
-            float4* dst = reinterpret_cast<float4*>(p.out + at);
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
-            }
-        }
-    }
+    if (ok) write_out(s_l[hc ^ 1][row]);
+
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
@@ -413,10 +523,11 @@ void prefill_attention_tc_configure() {
 // tiles: up to 128 positions each. map_q: fp32 map over the query rows (boxes of 32 columns x 128 rows); map_k: fp32
 // map over the whole K cache as rows of 64 floats; k_row0: first row of this layer in it.
 void launch_prefill_attention_tc(const PrefillAttnParams& p, const CUtensorMap& map_q, const CUtensorMap& map_k,
-                                 long long k_row0, cudaStream_t st) {
+                                 long long k_row0, int sm_count, cudaStream_t st) {
     if (p.n_tiles <= 0) return;
-    launch_kernel(attn_prefill_tc_kernel, dim3(p.n_tiles, p.H), dim3(kThreads), (size_t)kSmemBytes, st, map_q, map_k, p,
-                  k_row0);
+    const int items = p.n_tiles * p.H;
+    launch_kernel(attn_prefill_tc_kernel, dim3(std::min(items, sm_count)), dim3(kThreads), (size_t)kSmemBytes, st, map_q,
+                  map_k, p, k_row0);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }

@@ -487,6 +487,15 @@ gradb_status gradb_diag_count_nonfinite(gradb_session* session, int n_seq, long 
     });
 }
 
+gradb_status gradb_diag_wide_clocks(uint64_t* out128, int reset) {
+    return guarded([&] {
+        if (!out128) throw Error(GRADB_ERR_INVALID, "null argument");
+        unsigned long long v[128];
+        wide_clocks_read(v, reset != 0);
+        for (int i = 0; i < 128; i++) out128[i] = v[i];
+    });
+}
+
 gradb_status gradb_diag_poke_history(gradb_session* session, int seq, int index, int32_t id) {
     return guarded([&] {
         if (!session) throw Error(GRADB_ERR_INVALID, "null session");

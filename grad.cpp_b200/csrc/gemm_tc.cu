@@ -588,6 +588,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Diagnostics build: CTA 0's three roles add up the clock cycles they spend in each part of a tile
+// (read through gradb_diag_wide_clocks).
+#if GRADB_DIAG
+__device__ unsigned long long g_wide_clock[8 * 16];  // [epilogue kind][counter]
+#define WIDE_CLK(x) const long long x = clock64()
+#define WIDE_ADD(i, v) do { if (blockIdx.x == 0) atomicAdd(&g_wide_clock[EPI * 16 + (i)], (unsigned long long)(v)); } while (0)
+#else
+#define WIDE_CLK(x)
+#define WIDE_ADD(i, v)
+#endif
+
 template <int EPI, int NW>
 __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                 const __grid_constant__ CUtensorMap map_b,
@@ -643,12 +654,16 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
             // ---- TMA producer
             bool ok = true;
             int it = 0;
+            WIDE_CLK(p_begin);
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int tile_n = tile % tiles_n, tile_b = tile / tiles_n;
                 for (int k = 0; k < k_iters; k++, it++) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
+                    WIDE_CLK(w0);
                     ok = mbar_wait(&empty_bar[s], ph ^ 1, p.status, 111);
+                    WIDE_CLK(w1);
+                    WIDE_ADD(4, w1 - w0);
                     if (!ok) break;
                     uint8_t* st = smem + (size_t)s * kStageBytes;
                     mbar_expect_tx(&full_bar[s], kStageBytes);
@@ -660,6 +675,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                     tma_load_2d(st + kABytes, &map_b, k * kBlockK, tile_b * TN, &full_bar[s]);
                 }
             }
+            WIDE_CLK(p_end);
+            WIDE_ADD(5, p_end - p_begin);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -668,16 +685,24 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
             constexpr uint32_t idesc = umma_idesc_bf16(kTileM, TN);
             bool ok = true;
             int it = 0, lt = 0;
+            WIDE_CLK(m_begin);
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, lt++) {
                 const int buf = lt & 1;
+                WIDE_CLK(a0);
                 ok = mbar_wait(&acc_empty[buf], ((lt >> 1) & 1) ^ 1, p.status, 112);  // drained two tiles ago
+                WIDE_CLK(a1);
+                WIDE_ADD(0, 1);
+                WIDE_ADD(1, a1 - a0);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem_base + (uint32_t)(buf * kAccCols);
                 for (int k = 0; k < k_iters; k++, it++) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
+                    WIDE_CLK(f0);
                     ok = mbar_wait(&full_bar[s], ph, p.status, 113);
+                    WIDE_CLK(f1);
+                    WIDE_ADD(2, f1 - f0);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     uint8_t* st = smem + (size_t)s * kStageBytes;
@@ -694,6 +719,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                 }
                 if (ok) umma_commit(&acc_full[buf]);
             }
+            WIDE_CLK(m_end);
+            WIDE_ADD(3, m_end - m_begin);
         }
         __syncwarp();
     } else {
@@ -716,7 +743,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                 s_pos[buf][e] = ps;
                 s_off[buf][e] = (((long long)sq * p.H) * p.T + ps) * p.hs;
             }
+            WIDE_CLK(e0);
             if (!mbar_wait(&acc_full[buf], (lt >> 1) & 1, p.status, 114)) s_fail = 1;
+            WIDE_CLK(e1);
             // The epilogue warps only: publishes the staged ids and makes the give-up decision common,
             // so that no warp is left waiting at this barrier.
             asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");
@@ -728,9 +757,22 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            WIDE_CLK(e2);
             asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");  // staged tile complete
+            WIDE_CLK(e3);
             wide_epilogue_rows<EPI>(p, stg, warp - 2, lane, tile_n, tile_b, s_tok[buf], s_pos[buf], s_off[buf]);
+            WIDE_CLK(e4);
             asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");  // staged tile free again
+            WIDE_CLK(e5);
+#if GRADB_DIAG
+            if (warp == 2 && lane == 0) {
+                WIDE_ADD(6, e1 - e0);
+                WIDE_ADD(7, e2 - e1);
+                WIDE_ADD(8, e3 - e2);
+                WIDE_ADD(9, e4 - e3);
+                WIDE_ADD(10, e5 - e4);
+            }
+#endif
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -969,6 +1011,17 @@ bool tc_many_rows(const TcGemmParams& p, int token_tile) {
     const int n_tiles = (p.N + kTileM - 1) / kTileM, tiles_b = (p.B + kWideTN - 1) / kWideTN;
     return p.N % 4 == 0 && n_tiles * tiles_b >= 2 * sm_count;
 }
+
+#if GRADB_DIAG
+void wide_clocks_read(unsigned long long* out128, bool reset) {
+    GRADB_CUDA(cudaDeviceSynchronize());
+    GRADB_CUDA(cudaMemcpyFromSymbol(out128, g_wide_clock, sizeof(unsigned long long) * 128));
+    if (reset) {
+        unsigned long long zero[128] = {};
+        GRADB_CUDA(cudaMemcpyToSymbol(g_wide_clock, zero, sizeof(zero)));
+    }
+}
+#endif
 
 void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int token_tile,
                     int k_splits, cudaStream_t st, int kind) {

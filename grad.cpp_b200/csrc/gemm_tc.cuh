@@ -38,6 +38,9 @@ void make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
 int tc_token_tile(int n_seq, int n_tiles, int want_ctas);
 void tc_configure_all();
 // kind 0: bf16 operands; kind 1: fp32 operands as TF32 hi/lo pairs, three MMAs per product (fp32-grade result).
+#if GRADB_DIAG
+void wide_clocks_read(unsigned long long* out128, bool reset);  // diagnostics build: per-role clocks of the many-row GEMM
+#endif
 void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const TcGemmParams& p, int token_tile,
                     int k_splits, cudaStream_t st, int kind = 0);
 // True when launch_tc_gemm would run the many-row persistent kernel for this shape (needed by TC_LSE callers).

@@ -29,6 +29,13 @@ gradb_status gradb_diag_count_nonfinite(gradb_session* session, int n_seq, long 
  * make, so that the device-side index check of the penalty stage can be seen to catch it. */
 gradb_status gradb_diag_poke_history(gradb_session* session, int seq, int index, int32_t id);
 
+/* Clock cycles CTA 0 of the persistent many-row GEMM has spent per role since the last reset, summed over launches,
+ * as 8 rows of 16 counters, one row per epilogue kind (0 Q|K|V, 1 residual, 2 GELU, 3 SwiGLU, 4 logits, 5 log-sum-exp):
+ * [0] tiles, MMA lane: [1] waiting for a drained accumulator, [2] waiting for operands, [3] whole loop;
+ * TMA lane: [4] waiting for a free ring stage, [5] whole loop; first epilogue warp: [6] waiting for an accumulator,
+ * [7] accumulator -> staged tile, [8] barrier, [9] row pass, [10] barrier. */
+gradb_status gradb_diag_wide_clocks(uint64_t* out128, int reset);
+
 #ifdef __cplusplus
 }
 #endif

@@ -653,7 +653,7 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
                     a.H = s->H; a.T = s->T; a.d = d;
                     a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
                     if (tc_attn) {
-                        launch_prefill_attention_tc(a, f.map_q, s->map_kcache, (long long)l * s->B * s->H * s->T, st);
+                        launch_prefill_attention_tc(a, f.map_q, s->map_kcache, (long long)l * s->B * s->H * s->T, m->sm_count, st);
                     } else {
                         launch_prefill_attention(a, st, s32);
                     }
