@@ -472,9 +472,16 @@ __global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(c
 //                      a quarter of the token columns each), so the epilogue of tile i runs under the main
 //                      loop of tile i+1. The epilogue is arithmetic- and latency-bound, hence sixteen warps.
 // Tiles are dealt round-robin, feature tile fastest, so CTAs working at the same time share a token tile in L2.
+// Token tile: 128, or 256 for the single-weight-tile projections when there are enough rows (one MMA then covers
+// 128 x 256 outputs, which needs a quarter fewer operand bytes per multiply-add from L2 and from shared memory; the
+// operands, not the arithmetic, set the main loop's pace). The epilogue always works on 128 tokens at a time.
 constexpr int kWideTN = 128;
-constexpr int wide_stages(int nw) { return nw == 1 ? 4 : 3; }  // 128 or 144 KB of ring
-constexpr int kWideStageTileBytes = kWideTN * kTileM * 4;      // + one fp32 output tile staged for the row-wise epilogue
+constexpr int kWideHalf = 128;  // tokens per epilogue round = rows of the staged tile
+constexpr int wide_stages(int nw, int tn) { return nw == 1 && tn == 128 ? 4 : 3; }  // 128 or 144 KB of ring
+constexpr int kWideStageTileBytes = kWideHalf * kTileM * 4;    // + one fp32 output tile staged for the row-wise epilogue
+constexpr size_t wide_smem_bytes(int nw, int tn) {
+    return (size_t)wide_stages(nw, tn) * (nw * kTileM * kBlockK * 2 + tn * kBlockK * 2) + kWideStageTileBytes + 1024;
+}
 // Four epilogue warps per TMEM lane quarter: with eight warps in all the epilogue, not the MMA stream, set a tile's
 // time (scoring 65536 ids: 23.3 -> 20.6 ms with sixteen; 256-token tiles on top of that measured no gain).
 constexpr int kWideEpiWarps = 16;
@@ -483,10 +490,9 @@ constexpr int kWideThreads = 64 + 32 * kWideEpiWarps;
 // Epilogue pass A of the persistent kernel: accumulator (TMEM, one lane per feature) -> fp32 tile in shared
 // memory laid out [token][feature], with the per-feature work done on the way (bias, GELU, SwiGLU).
 // Thread t = feature, columns [c_begin, c_end). Consecutive lanes write consecutive words: no bank conflicts.
-template <int EPI, int NW>
+template <int EPI, int NW, int TN>
 __device__ __forceinline__ void wide_epilogue_stage(const TcGemmParams& p, uint32_t lane_addr, int t, int tile_n,
                                                     float* stg, int c_begin, int c_end) {
-    constexpr int TN = kWideTN;
     const int n = tile_n * kTileM + t;
     const bool n_ok = n < p.N;
     float bias = 0.f;
@@ -496,12 +502,13 @@ __device__ __forceinline__ void wide_epilogue_stage(const TcGemmParams& p, uint3
     } else if (EPI == TC_RESID || EPI == TC_GELU) {
         if (n_ok && p.bias[0]) bias = p.bias[0][n];
     }
-    for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-        float v[32], v2[32];
-        tmem_ld32(lane_addr + c0, v);
-        if (NW == 2) tmem_ld32(lane_addr + TN + c0, v2);
+    constexpr int CW = NW == 2 ? 16 : 32;  // columns per TMEM load: the SwiGLU pair holds two of them at once
+    for (int c0 = c_begin; c0 < c_end; c0 += CW) {
+        float v[CW], v2[CW];
+        tmem_ld<CW>(lane_addr + c0, v);
+        if (NW == 2) tmem_ld<CW>(lane_addr + TN + c0, v2);
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
+        for (int j = 0; j < CW; j++) {
             float val = v[j] + bias;
             if (EPI == TC_GELU) {
                 const float u = 0.79788456f * (val + 0.044715f * val * val * val);
@@ -517,69 +524,153 @@ __device__ __forceinline__ void wide_epilogue_stage(const TcGemmParams& p, uint3
 
 // Epilogue pass B: the staged tile, one token row per warp at a time, four consecutive features per lane:
 // everything that depends on the token (RoPE angle, cache row, residual row) is fetched once per row and the
-// stores are 128-bit and row-contiguous. `we` = epilogue warp 0..7.
+// stores are 128-bit and row-contiguous. A warp owns rows we, we + 16, ... of the 128 (eight of them), and the
+// pass comes in two parts: wide_rows_fetch issues the eight rows' global loads that do not depend on the
+// accumulator (RoPE angles, residual rows) and is called before the staged tile is waited for, so their latency
+// runs under the accumulator wait and pass A; wide_rows_finish does the rest. A row past the batch (id < 0)
+// reads row 0 of the tile and position 0, and is not stored.
+constexpr int kWideRowsPerWarp = kWideHalf / kWideEpiWarps;
+constexpr int kWideRowBatch = 4;  // rows whose fetched values are held at a time (registers: 96 per thread)
+
 template <int EPI>
-__device__ __forceinline__ void wide_epilogue_rows(const TcGemmParams& p, const float* stg, int we, int lane, int tile_n,
-                                                   int tile_b, const int* s_tok, const int* s_pos,
-                                                   const long long* s_off) {
-    constexpr int TN = kWideTN;
-    const int f = tile_n * kTileM + 4 * lane;  // first of this lane's four features
-    const bool f_in = f < p.N;                 // N is a multiple of 4 on this path
-    if (EPI != TC_LSE && !f_in) return;        // (the log-sum-exp pass keeps every lane for its shuffles)
-    int which = 0, n_in = f;
-    if (EPI == TC_QKV) {
-        which = f / p.d;  // a 128-feature tile lies inside one of Q, K, V (d is a multiple of 128 on this path)
-        n_in = f - which * p.d;
+struct WideRowCtx {
+    int f, n_in, c_in, which;
+    bool f_in, rope;
+    float* kv_t;
+    __device__ __forceinline__ WideRowCtx(const TcGemmParams& p, int lane, int tile_n) {
+        f = tile_n * kTileM + 4 * lane;  // first of this lane's four features
+        f_in = f < p.N;                  // N is a multiple of 4 on this path
+        which = 0;
+        n_in = f;
+        if (EPI == TC_QKV) {
+            which = f / p.d;  // a 128-feature tile lies inside one of Q, K, V (d is a multiple of 128 on this path)
+            n_in = f - which * p.d;
+        }
+        const int h = n_in / p.hs;
+        c_in = n_in % p.hs;
+        rope = EPI == TC_QKV && p.rope_cos != nullptr && which < 2;
+        kv_t = (which == 1 ? p.kcache : p.vcache) + (size_t)h * p.T * p.hs + c_in;
     }
-    const int h = n_in / p.hs, c_in = n_in % p.hs;
-    const bool rope = EPI == TC_QKV && p.rope_cos != nullptr && which < 2;
-    const int half = p.hs / 2;
-    float* kv_t = (which == 1 ? p.kcache : p.vcache) + (size_t)h * p.T * p.hs + c_in;
-#pragma unroll 8
-    for (int c = we; c < TN; c += kWideEpiWarps) {
+};
+
+template <int EPI>
+__device__ __forceinline__ void wide_rows_fetch(const TcGemmParams& p, const WideRowCtx<EPI>& cx, int we, int i0,
+                                                int row_base, const int* s_tok, const int* s_pos,
+                                                float4 (&pre)[kWideRowBatch]) {
+    if (!cx.f_in) return;
+    if (EPI == TC_QKV && cx.rope) {
+        // pairs (2j, 2j+1) of a head rotate by the angle of index j (inference.cpp:101-115)
+        const int half = p.hs / 2;
+#pragma unroll
+        for (int i = 0; i < kWideRowBatch; i++) {
+            const int c = we + (i0 + i) * kWideEpiWarps;
+            const int pos = s_tok[c] >= 0 ? s_pos[c] : 0;
+            const float2 cs = __ldg(reinterpret_cast<const float2*>(p.rope_cos + (size_t)pos * half + cx.c_in / 2));
+            const float2 sn = __ldg(reinterpret_cast<const float2*>(p.rope_sin + (size_t)pos * half + cx.c_in / 2));
+            pre[i] = make_float4(cs.x, cs.y, sn.x, sn.y);
+        }
+    } else if (EPI == TC_RESID) {
+#pragma unroll
+        for (int i = 0; i < kWideRowBatch; i++) {
+            const int c = we + (i0 + i) * kWideEpiWarps;
+            const size_t row = (size_t)(row_base + (s_tok[c] >= 0 ? c : 0)) * p.ld_out;
+            pre[i] = *reinterpret_cast<const float4*>(p.out_f32 + row + cx.f);
+        }
+    }
+}
+
+template <int EPI>
+__device__ __forceinline__ void wide_rows_lse(const TcGemmParams& p, const WideRowCtx<EPI>& cx, const float* stg, int we,
+                                              int lane, int tile_n, int row_base, const int* s_tok, const int* s_pos) {
+    constexpr int R = kWideRowsPerWarp;
+    {
+        // This tile's share of each row's log-sum-exp, and the target's logit if it lives here. The row maxima
+        // come from one warp-wide instruction each; the eight rows' sums are reduced together, exchanging half of
+        // the rows at each of the first three butterfly steps (9 shuffles instead of 40): afterwards the four lanes
+        // with (lane >> 2) == i hold row i's sum.
+        float4 x[R];
+        float m[R], sum[R];
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            x[i] = *reinterpret_cast<const float4*>(stg + (we + i * kWideEpiWarps) * kTileM + 4 * lane);
+            if (!cx.f_in) x[i] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            const float m4 = fmaxf(fmaxf(x[i].x, x[i].y), fmaxf(x[i].z, x[i].w));
+            asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(m[i]) : "f"(m4));
+            sum[i] = (expf(x[i].x - m[i]) + expf(x[i].y - m[i])) + (expf(x[i].z - m[i]) + expf(x[i].w - m[i]));
+        }
+        float w4[4], w2[2];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const bool up = lane & 16;
+            const float got = __shfl_xor_sync(0xffffffffu, up ? sum[i] : sum[i + 4], 16);
+            w4[i] = (up ? sum[i + 4] : sum[i]) + got;
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const bool up = lane & 8;
+            const float got = __shfl_xor_sync(0xffffffffu, up ? w4[i] : w4[i + 2], 8);
+            w2[i] = (up ? w4[i + 2] : w4[i]) + got;
+        }
+        float tot;
+        {
+            const bool up = lane & 4;
+            const float got = __shfl_xor_sync(0xffffffffu, up ? w2[0] : w2[1], 4);
+            tot = (up ? w2[1] : w2[0]) + got;
+        }
+        tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+        const int mine = lane >> 2;  // the row whose sum this lane holds
+        float m_mine = m[0];
+#pragma unroll
+        for (int i = 1; i < R; i++) m_mine = mine == i ? m[i] : m_mine;
+        {
+            const int c = we + mine * kWideEpiWarps;
+            if ((lane & 3) == 0 && s_tok[c] >= 0) {
+                *reinterpret_cast<float2*>(p.out_f32 + (size_t)(row_base + c) * p.ld_out + 2 * tile_n) = make_float2(m_mine, tot);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            const int c = we + i * kWideEpiWarps;
+            if (s_tok[c] < 0) continue;
+            const int tg = s_pos[c] - cx.f;  // `pos` carries the target id on this path
+            if (tg >= 0 && tg < 4) p.lse_tgt[row_base + c] = tg == 0 ? x[i].x : (tg == 1 ? x[i].y : (tg == 2 ? x[i].z : x[i].w));
+        }
+    }
+}
+
+template <int EPI>
+__device__ __forceinline__ void wide_rows_finish(const TcGemmParams& p, const WideRowCtx<EPI>& cx, const float* stg, int we,
+                                                 int lane, int i0, int row_base, const int* s_tok, const long long* s_off,
+                                                 const float4 (&pre)[kWideRowBatch]) {
+    if (!cx.f_in) return;
+#pragma unroll
+    for (int i = 0; i < kWideRowBatch; i++) {
+        const int c = we + (i0 + i) * kWideEpiWarps;
         if (s_tok[c] < 0) continue;  // warp-uniform
         float4 x = *reinterpret_cast<const float4*>(stg + c * kTileM + 4 * lane);
-        if (EPI == TC_LSE && !f_in) x = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-        const size_t row = (size_t)(tile_b * TN + c) * p.ld_out;
+        const size_t row = (size_t)(row_base + c) * p.ld_out;
         if (EPI == TC_QKV) {
-            if (rope) {
-                // pairs (2j, 2j+1) of a head rotate by the angle of index j (inference.cpp:101-115)
-                const int pos = s_pos[c];
-                const float2 cs = __ldg(reinterpret_cast<const float2*>(p.rope_cos + (size_t)pos * half + c_in / 2));
-                const float2 sn = __ldg(reinterpret_cast<const float2*>(p.rope_sin + (size_t)pos * half + c_in / 2));
-                const float a0 = x.x, b0 = x.y, a1 = x.z, b1 = x.w;
-                x.x = a0 * cs.x - b0 * sn.x;
-                x.y = a0 * sn.x + b0 * cs.x;
-                x.z = a1 * cs.y - b1 * sn.y;
-                x.w = a1 * sn.y + b1 * cs.y;
+            if (cx.rope) {
+                const float a0 = x.x, b0 = x.y, a1 = x.z, b1 = x.w;  // pre = (cos j, cos j+1, sin j, sin j+1)
+                x.x = a0 * pre[i].x - b0 * pre[i].z;
+                x.y = a0 * pre[i].z + b0 * pre[i].x;
+                x.z = a1 * pre[i].y - b1 * pre[i].w;
+                x.w = a1 * pre[i].w + b1 * pre[i].y;
             }
-            if (which == 0) *reinterpret_cast<float4*>(p.out_f32 + row + n_in) = x;
-            else *reinterpret_cast<float4*>(kv_t + s_off[c]) = x;
+            if (cx.which == 0) *reinterpret_cast<float4*>(p.out_f32 + row + cx.n_in) = x;
+            else *reinterpret_cast<float4*>(cx.kv_t + s_off[c]) = x;
         } else if (EPI == TC_RESID) {
-            float4* y = reinterpret_cast<float4*>(p.out_f32 + row + f);
-            const float4 r = *y;
-            x.x += r.x; x.y += r.y; x.z += r.z; x.w += r.w;
-            *y = x;
+            *reinterpret_cast<float4*>(p.out_f32 + row + cx.f) =
+                make_float4(x.x + pre[i].x, x.y + pre[i].y, x.z + pre[i].z, x.w + pre[i].w);
         } else if (EPI == TC_GELU || EPI == TC_SWIGLU) {
             const __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
             uint2 pk;
             pk.x = *reinterpret_cast<const uint32_t*>(&lo);
             pk.y = *reinterpret_cast<const uint32_t*>(&hi);
-            *reinterpret_cast<uint2*>(p.out_bf16 + row + f) = pk;
-        } else if (EPI == TC_LSE) {
-            // this tile's share of the row's log-sum-exp, and the target's logit if it lives here
-            float m = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            float sum = (expf(x.x - m) + expf(x.y - m)) + (expf(x.z - m) + expf(x.w - m));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            const size_t r = (size_t)(tile_b * TN + c);
-            if (lane == 0) *reinterpret_cast<float2*>(p.out_f32 + r * p.ld_out + 2 * tile_n) = make_float2(m, sum);
-            const int tg = s_pos[c] - f;  // `pos` carries the target id on this path
-            if (tg >= 0 && tg < 4) p.lse_tgt[r] = tg == 0 ? x.x : (tg == 1 ? x.y : (tg == 2 ? x.z : x.w));
+            *reinterpret_cast<uint2*>(p.out_bf16 + row + cx.f) = pk;
         } else {  // TC_LOGITS
-            *reinterpret_cast<float4*>(p.out_f32 + row + f) = x;
+            *reinterpret_cast<float4*>(p.out_f32 + row + cx.f) = x;
         }
     }
 }
@@ -599,12 +690,11 @@ __device__ unsigned long long g_wide_clock[8 * 16];  // [epilogue kind][counter]
 #define WIDE_ADD(i, v)
 #endif
 
-template <int EPI, int NW>
+template <int EPI, int NW, int TN>
 __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                 const __grid_constant__ CUtensorMap map_b,
                                                                 const TcGemmParams p, int tiles_n, int total_tiles) {
-    constexpr int TN = kWideTN;
-    constexpr int kStages = wide_stages(NW);
+    constexpr int kStages = wide_stages(NW, TN);
     constexpr int kABytes = NW * kTileM * kBlockK * 2;
     constexpr int kBBytes = TN * kBlockK * 2;
     constexpr int kStageBytes = kABytes + kBBytes;
@@ -672,7 +762,12 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                         tma_load_2d(st + w * (kTileM * kBlockK * 2), &map_a, k * kBlockK, (tile_n * NW + w) * kTileM,
                                     &full_bar[s]);
                     }
-                    tma_load_2d(st + kABytes, &map_b, k * kBlockK, tile_b * TN, &full_bar[s]);
+                    // the activation map's box is 128 rows: one or two of them, contiguous in the stage
+#pragma unroll
+                    for (int hb = 0; hb < TN / kWideHalf; hb++) {
+                        tma_load_2d(st + kABytes + hb * (kWideHalf * kBlockK * 2), &map_b, k * kBlockK,
+                                    tile_b * TN + hb * kWideHalf, &full_bar[s]);
+                    }
                 }
             }
             WIDE_CLK(p_end);
@@ -743,34 +838,66 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                 s_pos[buf][e] = ps;
                 s_off[buf][e] = (((long long)sq * p.H) * p.T + ps) * p.hs;
             }
+            // publishes the staged ids to the epilogue warps (and, with the barrier at the end of the previous
+            // tile, orders their reuse)
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");
+            const WideRowCtx<EPI> cx(p, lane, tile_n);
+            float4 pre[kWideRowBatch], pre2[kWideRowBatch];
+            wide_rows_fetch<EPI>(p, cx, warp - 2, 0, tile_b * TN, s_tok[buf], s_pos[buf], pre);
             WIDE_CLK(e0);
             if (!mbar_wait(&acc_full[buf], (lt >> 1) & 1, p.status, 114)) s_fail = 1;
             WIDE_CLK(e1);
-            // The epilogue warps only: publishes the staged ids and makes the give-up decision common,
-            // so that no warp is left waiting at this barrier.
+            // The epilogue warps only: makes the give-up decision common, so that no warp is left waiting
             asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");
             if (s_fail) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            wide_epilogue_stage<EPI, NW>(p, tmem_base + (uint32_t)(buf * kAccCols) + ((uint32_t)(q * 32) << 16), t, tile_n,
-                                         stg, hf * (TN / (kWideEpiWarps / 4)), (hf + 1) * (TN / (kWideEpiWarps / 4)));
-            // the accumulator is drained: hand it back before the row pass
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
-            WIDE_CLK(e2);
-            asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");  // staged tile complete
-            WIDE_CLK(e3);
-            wide_epilogue_rows<EPI>(p, stg, warp - 2, lane, tile_n, tile_b, s_tok[buf], s_pos[buf], s_off[buf]);
-            WIDE_CLK(e4);
-            asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");  // staged tile free again
-            WIDE_CLK(e5);
+#if GRADB_DIAG
+            long long t_a = 0, t_b = 0, t_bar = 0;
+#endif
+#pragma unroll
+            for (int hb = 0; hb < TN / kWideHalf; hb++) {  // 128 tokens at a time through the staged tile
+                WIDE_CLK(h0);
+                const int row_base = tile_b * TN + hb * kWideHalf;
+                const int* const tok_h = s_tok[buf] + hb * kWideHalf;
+                const int* const pos_h = s_pos[buf] + hb * kWideHalf;
+                if (hb > 0) wide_rows_fetch<EPI>(p, cx, warp - 2, 0, row_base, tok_h, pos_h, pre);
+                wide_epilogue_stage<EPI, NW, TN>(
+                    p, tmem_base + (uint32_t)(buf * kAccCols + hb * kWideHalf) + ((uint32_t)(q * 32) << 16), t, tile_n, stg,
+                    hf * (kWideHalf / (kWideEpiWarps / 4)), (hf + 1) * (kWideHalf / (kWideEpiWarps / 4)));
+                if (hb == TN / kWideHalf - 1) {
+                    // the accumulator is drained: hand it back before the row pass
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                }
+                WIDE_CLK(h1);
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");  // staged tile complete
+                WIDE_CLK(h2);
+                if (EPI == TC_LSE) {
+                    wide_rows_lse<EPI>(p, cx, stg, warp - 2, lane, tile_n, row_base, tok_h, pos_h);
+                } else {
+                    // the second batch's loads are in flight while the first is written
+                    static_assert(kWideRowsPerWarp == 2 * kWideRowBatch, "two batches per warp");
+                    wide_rows_fetch<EPI>(p, cx, warp - 2, kWideRowBatch, row_base, tok_h, pos_h, pre2);
+                    wide_rows_finish<EPI>(p, cx, stg, warp - 2, lane, 0, row_base, tok_h, s_off[buf] + hb * kWideHalf, pre);
+                    wide_rows_finish<EPI>(p, cx, stg, warp - 2, lane, kWideRowBatch, row_base, tok_h,
+                                          s_off[buf] + hb * kWideHalf, pre2);
+                }
+                WIDE_CLK(h3);
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");  // staged tile free again
+                WIDE_CLK(h4);
+#if GRADB_DIAG
+                t_a += h1 - h0;
+                t_b += h3 - h2;
+                t_bar += (h2 - h1) + (h4 - h3);
+#endif
+            }
 #if GRADB_DIAG
             if (warp == 2 && lane == 0) {
                 WIDE_ADD(6, e1 - e0);
-                WIDE_ADD(7, e2 - e1);
-                WIDE_ADD(8, e3 - e2);
-                WIDE_ADD(9, e4 - e3);
-                WIDE_ADD(10, e5 - e4);
+                WIDE_ADD(7, t_a);
+                WIDE_ADD(8, t_bar);
+                WIDE_ADD(9, t_b);
             }
 #endif
         }
@@ -985,19 +1112,30 @@ int tc_token_tile(int n_seq, int n_tiles, int want_ctas) {
 }
 
 namespace {
-template <int EPI, int NW>
-void launch_wide(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, int tiles_n, int tiles_b, int sm_count,
+template <int EPI, int NW, int TN>
+void launch_wide(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, int tiles_n, int sm_count,
                  cudaStream_t st) {
-    constexpr size_t bytes =
-        (size_t)wide_stages(NW) * (NW * kTileM * kBlockK * 2 + kWideTN * kBlockK * 2) + kWideStageTileBytes + 1024;
-    auto kernel = gemm_bf16_tc_wide_kernel<EPI, NW>;
+    constexpr size_t bytes = wide_smem_bytes(NW, TN);
+    auto kernel = gemm_bf16_tc_wide_kernel<EPI, NW, TN>;
     if (!g_capturing) {
         GRADB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
-    const int total = tiles_n * tiles_b;
+    const int total = tiles_n * ((p.B + TN - 1) / TN);
     launch_kernel(kernel, dim3(std::min(total, sm_count)), dim3(kWideThreads), bytes, st, a, b, p, tiles_n, total);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
+}
+
+// 256-token tiles once they still leave every SM four tiles or more (GRADB_WIDE_TN=128 keeps the narrow tile)
+template <int EPI>
+void launch_wide_single(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, int tiles_n, int sm_count,
+                        cudaStream_t st) {
+    static const bool narrow = [] {
+        const char* e = std::getenv("GRADB_WIDE_TN");
+        return e && std::atoi(e) == 128;
+    }();
+    if (!narrow && tiles_n * ((p.B + 255) / 256) >= 4 * sm_count) launch_wide<EPI, 1, 256>(a, b, p, tiles_n, sm_count, st);
+    else launch_wide<EPI, 1, 128>(a, b, p, tiles_n, sm_count, st);
 }
 }  // namespace
 
@@ -1042,12 +1180,12 @@ void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b,
                               (epi != TC_QKV || (p.d % kTileM == 0 && p.hs % 4 == 0));
         if (!wide_off && shape_ok && n_tiles * tiles_b >= 2 * sm_count) {
             switch (epi) {
-                case TC_QKV: launch_wide<TC_QKV, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
-                case TC_RESID: launch_wide<TC_RESID, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
-                case TC_GELU: launch_wide<TC_GELU, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
-                case TC_SWIGLU: launch_wide<TC_SWIGLU, 2>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
-                case TC_LOGITS: launch_wide<TC_LOGITS, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
-                case TC_LSE: launch_wide<TC_LSE, 1>(map_a, map_b, p, n_tiles, tiles_b, sm_count, st); return;
+                case TC_QKV: launch_wide_single<TC_QKV>(map_a, map_b, p, n_tiles, sm_count, st); return;
+                case TC_RESID: launch_wide_single<TC_RESID>(map_a, map_b, p, n_tiles, sm_count, st); return;
+                case TC_GELU: launch_wide_single<TC_GELU>(map_a, map_b, p, n_tiles, sm_count, st); return;
+                case TC_SWIGLU: launch_wide<TC_SWIGLU, 2, 128>(map_a, map_b, p, n_tiles, sm_count, st); return;
+                case TC_LOGITS: launch_wide_single<TC_LOGITS>(map_a, map_b, p, n_tiles, sm_count, st); return;
+                case TC_LSE: launch_wide_single<TC_LSE>(map_a, map_b, p, n_tiles, sm_count, st); return;
                 default: break;
             }
         }

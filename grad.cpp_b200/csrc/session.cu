@@ -444,7 +444,7 @@ size_t feed_rows_for(const Session* s) {
         const long v = std::atol(e);
         if (v >= 1024 && v <= (1 << 18)) rows = (size_t)v;
     }
-    return (rows + 127) / 128 * 128;
+    return (rows + 255) / 256 * 256;
 }
 
 void ensure_feed_buffers(Session* s) {
@@ -837,7 +837,7 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         s->use_tc32 = m->tc32_ok && s->B >= 16 && !(ntc && ntc[0] == '1') && !(ntc32 && ntc32[0] == '1');
         if (s->use_tc32) {
             tc_configure_all();
-            const size_t rows = (size_t)((s->B + 127) / 128) * 128;
+            const size_t rows = (size_t)((s->B + 255) / 256) * 256;
             s->split_rows = (int)rows;
             dalloc(&s->hS, 2 * rows * s->d);
             dalloc(&s->attnS, 2 * rows * s->d);
@@ -858,8 +858,8 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         }
         if (s->use_tc) {
             tc_configure_all();
-            // rows padded to a whole 128-row tile so a TMA box never starts outside the buffer
-            const size_t rows = (size_t)((s->B + 127) / 128) * 128;
+            // rows padded to a whole 256-token tile so a TMA box never starts outside the buffer
+            const size_t rows = (size_t)((s->B + 255) / 256) * 256;
             dalloc(&s->h16, rows * s->d);
             dalloc(&s->attn16, rows * s->d);
             dalloc(&s->ffn16, rows * s->dff);
