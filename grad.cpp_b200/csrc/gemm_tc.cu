@@ -502,7 +502,8 @@ __device__ __forceinline__ void wide_epilogue_stage(const TcGemmParams& p, uint3
     } else if (EPI == TC_RESID || EPI == TC_GELU) {
         if (n_ok && p.bias[0]) bias = p.bias[0][n];
     }
-    constexpr int CW = NW == 2 ? 16 : 32;  // columns per TMEM load: the SwiGLU pair holds two of them at once
+    // columns per TMEM load: the SwiGLU pair holds two loads at once, and the 256-token variants carry more state
+    constexpr int CW = (NW == 2 || (TN == 256 && EPI != TC_QKV)) ? 16 : 32;
     for (int c0 = c_begin; c0 < c_end; c0 += CW) {
         float v[CW], v2[CW];
         tmem_ld<CW>(lane_addr + c0, v);
@@ -582,56 +583,53 @@ __device__ __forceinline__ void wide_rows_fetch(const TcGemmParams& p, const Wid
 template <int EPI>
 __device__ __forceinline__ void wide_rows_lse(const TcGemmParams& p, const WideRowCtx<EPI>& cx, const float* stg, int we,
                                               int lane, int tile_n, int row_base, const int* s_tok, const int* s_pos) {
-    constexpr int R = kWideRowsPerWarp;
-    {
-        // This tile's share of each row's log-sum-exp, and the target's logit if it lives here. The row maxima
-        // come from one warp-wide instruction each; the eight rows' sums are reduced together, exchanging half of
-        // the rows at each of the first three butterfly steps (9 shuffles instead of 40): afterwards the four lanes
-        // with (lane >> 2) == i hold row i's sum.
+    // This tile's share of each row's log-sum-exp, and the target's logit if it lives here. The row maxima come
+    // from one warp-wide instruction each; four rows' sums are reduced together, exchanging half of the rows at each
+    // of the first two butterfly steps (6 shuffles instead of 20): afterwards the eight lanes with (lane >> 3) == i
+    // hold row i's sum.
+    constexpr int R = kWideRowBatch;
+    static_assert(R == 4, "the butterfly below is written for four rows");
+#pragma unroll 1
+    for (int i0 = 0; i0 < kWideRowsPerWarp; i0 += R) {
         float4 x[R];
         float m[R], sum[R];
 #pragma unroll
         for (int i = 0; i < R; i++) {
-            x[i] = *reinterpret_cast<const float4*>(stg + (we + i * kWideEpiWarps) * kTileM + 4 * lane);
+            x[i] = *reinterpret_cast<const float4*>(stg + (we + (i0 + i) * kWideEpiWarps) * kTileM + 4 * lane);
             if (!cx.f_in) x[i] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
             const float m4 = fmaxf(fmaxf(x[i].x, x[i].y), fmaxf(x[i].z, x[i].w));
             asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(m[i]) : "f"(m4));
             sum[i] = (expf(x[i].x - m[i]) + expf(x[i].y - m[i])) + (expf(x[i].z - m[i]) + expf(x[i].w - m[i]));
         }
-        float w4[4], w2[2];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const bool up = lane & 16;
-            const float got = __shfl_xor_sync(0xffffffffu, up ? sum[i] : sum[i + 4], 16);
-            w4[i] = (up ? sum[i + 4] : sum[i]) + got;
-        }
+        float w2[2];
 #pragma unroll
         for (int i = 0; i < 2; i++) {
-            const bool up = lane & 8;
-            const float got = __shfl_xor_sync(0xffffffffu, up ? w4[i] : w4[i + 2], 8);
-            w2[i] = (up ? w4[i + 2] : w4[i]) + got;
+            const bool up = lane & 16;
+            const float got = __shfl_xor_sync(0xffffffffu, up ? sum[i] : sum[i + 2], 16);
+            w2[i] = (up ? sum[i + 2] : sum[i]) + got;
         }
         float tot;
         {
-            const bool up = lane & 4;
-            const float got = __shfl_xor_sync(0xffffffffu, up ? w2[0] : w2[1], 4);
+            const bool up = lane & 8;
+            const float got = __shfl_xor_sync(0xffffffffu, up ? w2[0] : w2[1], 8);
             tot = (up ? w2[1] : w2[0]) + got;
         }
+        tot += __shfl_xor_sync(0xffffffffu, tot, 4);
         tot += __shfl_xor_sync(0xffffffffu, tot, 2);
         tot += __shfl_xor_sync(0xffffffffu, tot, 1);
-        const int mine = lane >> 2;  // the row whose sum this lane holds
+        const int mine = lane >> 3;  // the row of this batch whose sum this lane holds
         float m_mine = m[0];
 #pragma unroll
         for (int i = 1; i < R; i++) m_mine = mine == i ? m[i] : m_mine;
         {
-            const int c = we + mine * kWideEpiWarps;
-            if ((lane & 3) == 0 && s_tok[c] >= 0) {
+            const int c = we + (i0 + mine) * kWideEpiWarps;
+            if ((lane & 7) == 0 && s_tok[c] >= 0) {
                 *reinterpret_cast<float2*>(p.out_f32 + (size_t)(row_base + c) * p.ld_out + 2 * tile_n) = make_float2(m_mine, tot);
             }
         }
 #pragma unroll
         for (int i = 0; i < R; i++) {
-            const int c = we + i * kWideEpiWarps;
+            const int c = we + (i0 + i) * kWideEpiWarps;
             if (s_tok[c] < 0) continue;
             const int tg = s_pos[c] - cx.f;  // `pos` carries the target id on this path
             if (tg >= 0 && tg < 4) p.lse_tgt[row_base + c] = tg == 0 ? x[i].x : (tg == 1 ? x[i].y : (tg == 2 ? x[i].z : x[i].w));
@@ -854,7 +852,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
 #if GRADB_DIAG
             long long t_a = 0, t_b = 0, t_bar = 0;
 #endif
-#pragma unroll
+#pragma unroll 1
             for (int hb = 0; hb < TN / kWideHalf; hb++) {  // 128 tokens at a time through the staged tile
                 WIDE_CLK(h0);
                 const int row_base = tile_b * TN + hb * kWideHalf;
