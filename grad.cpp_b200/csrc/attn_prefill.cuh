@@ -27,6 +27,9 @@ void prefill_attention_configure();
 // of up to 128 positions; map_q = fp32 tensor map over the query rows (boxes of 32 columns x 128 rows), map_k = fp32
 // tensor map over the whole K cache as rows of 64 floats, k_row0 = first row of this layer in it.
 void prefill_attention_tc_configure();
+#if GRADB_DIAG
+void attn_clocks_read(unsigned long long* out16, bool reset);  // diagnostics build: per-phase clocks of the kernel below
+#endif
 void launch_prefill_attention_tc(const PrefillAttnParams& p, const CUtensorMap& map_q, const CUtensorMap& map_k,
                                  long long k_row0, int sm_count, cudaStream_t st);
 // fp32_grade: three TF32 MMAs per product on hi/lo operand pairs (fp32 sessions) instead of one.

@@ -21,10 +21,12 @@
 //                                                        through shared memory by the threads
 //   o = o * exp(old max - new max) + O_tile              in registers (32 per thread)
 //
-// Q has two buffers (the item after next is fetched when an item's last scores are done) and K two stages: the
-// scores of element e+1 are issued as soon as every thread holds element e's scores in registers and run under its
-// exponentials; O_tile of element e is collected in element e+1's pass, and when that element opens a new item the
-// finished item's rows are normalised and written there. The next V tile is requested when the transpose is done;
+// Q has two buffers (the item after next is fetched when an item's last scores are done), K two stages and P two
+// buffers in TMEM: the scores of element e+1 are issued as soon as every thread holds element e's scores in registers
+// and run under its exponentials; O_tile of element e is collected in element e+1's pass after that element's
+// exponentials (so the second product has a whole softmax to finish in), and when that element opens a new item the
+// finished item's rows are normalised and written there. A CTA's tiles are copied to shared memory first, so the
+// one thread that issues copies and MMAs never waits for a global load. The next V tile is requested when the transpose is done;
 // tiles further ahead are prefetched towards L2. All waits are bounded; on expiry the status word is set and the
 // CTA falls through to the common exit, which frees TMEM.
 #include <cuda.h>
@@ -50,8 +52,9 @@ constexpr int kOffK = kOffQ + 4 * kAtomQ;      // 2 stages of 2 atoms
 constexpr int kOffVraw = kOffK + 4 * kAtomQ;   // [128 keys][64] as stored
 constexpr int kOffVt = kOffVraw + kKT * kHS * 4;  // 4 atoms (32 keys each)
 constexpr int kSmemBytes = kOffVt + 4 * kAtomV + 1024;
-// tensor-memory map (columns): S, P, O_tile
-constexpr uint32_t kColS = 0, kColP = 128, kColO = 256, kTmemCols = 512;
+// tensor-memory map (columns): S, P (element e uses buffer e & 1), O_tile
+constexpr uint32_t kColS = 0, kColP = 128, kColO = 384, kTmemCols = 512;  // P: two buffers of 128 columns
+constexpr int kMaxListed = 192;  // items of a CTA whose tiles are kept in shared memory
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -156,6 +159,17 @@ __device__ __forceinline__ uint32_t sw128(int r, int c16) {
     return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c16 ^ (r & 7)) << 4));
 }
 
+// Diagnostics build: CTA 0 adds up the clock cycles one of its warps spends in each part of an element
+// (read through gradb_diag_attn_clocks).
+#if GRADB_DIAG
+__device__ unsigned long long g_attn_clock[16];
+#define ATT_CLK(x) const long long x = clock64()
+#define ATT_ADD(i, v) do { if (blockIdx.x == 0 && t == 160) atomicAdd(&g_attn_clock[i], (unsigned long long)(v)); } while (0)
+#else
+#define ATT_CLK(x)
+#define ATT_ADD(i, v)
+#endif
+
 // One (query tile, head) of the launch: what a CTA works on between two output writes.
 struct Item {
     int row0, pos0, nq, h, kv_len, n_kv;
@@ -171,6 +185,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
     __shared__ volatile int s_fail;
     __shared__ float s_x[2][kQT];  // the two column halves of a row exchange their maxima
     __shared__ float s_l[2][kQT];  // ... and, when an item ends, their sums
+    __shared__ int4 s_tiles[kMaxListed];  // this CTA's first items: tile lookups stay off the issuing thread's path
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int row = (warp & 3) * 32 + lane;  // query row = TMEM lane
@@ -182,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
     // hold tiles of the same length (the host sorts the tiles longest first)
     auto get_item = [&](int k) {
         const int idx = (int)blockIdx.x + k * (int)gridDim.x;
-        const int4 tile = p.tiles[idx / p.H];
+        const int4 tile = k < kMaxListed ? s_tiles[k] : p.tiles[idx / p.H];
         Item it;
         it.h = idx % p.H;
         it.row0 = tile.y;
@@ -194,6 +209,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         return it;
     };
 
+    for (int k = t; k < min(my_count, kMaxListed); k += kThreads) {
+        s_tiles[k] = p.tiles[((int)blockIdx.x + k * (int)gridDim.x) / p.H];
+    }
     if (t == 0) {
         s_fail = 0;
         mbar_init(&bar_q[0], 1);
@@ -327,9 +345,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         for (int i = 0; i < 32; i++) o[i] = o[i] * corr_prev + ot[i];
     };
     // rows of the finished item: o / (sum of both halves), this thread's 32 dims
-    auto write_out = [&](float l_other) {
+    auto write_out = [&](float l_mine, float l_other) {
         if (row >= done_nq) return;
-        const float inv = 1.0f / (l_run + l_other);
+        const float inv = 1.0f / (l_mine + l_other);
         const size_t at = (size_t)(done_row0 + row) * p.d + done_h * kHS + hc * 32;
         if (p.out16) {
             uint4* dst = reinterpret_cast<uint4*>(p.out16 + at);
@@ -354,7 +372,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
     for (;; e++) {
         const uint32_t ph = (uint32_t)(e & 1);
         // ---- this thread's 64 score columns of its row, into registers
+        ATT_CLK(c0);
         if (!mbar_wait(&bar_s, ph, p.status, 404, &s_fail)) s_fail = 1;
+        ATT_CLK(c1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // Scores stay unscaled: exp(scale * (s - max)) is one multiply-add and one ex2 per entry. A 32-column block
         // that lies wholly above the diagonal for every row of this warp is neither read nor exponentiated.
@@ -386,7 +406,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         s_x[hc][row] = m_half;
         if (j == 0) s_l[hc][row] = l_run;  // the finished item's sum (nothing yet before the first)
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        ATT_CLK(c2);
         __syncthreads();  // maxima exchanged; the score accumulator and this element's K stage are free
+        ATT_CLK(c3);
         if (s_fail) {
             ok = false;
             break;
@@ -408,18 +430,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
             if (j == it.n_kv - 1 && k + 2 < my_count) load_q(k + 2);
             if (j == 0 && k + 3 < my_count) prefetch_q(k + 3);
         }
-        if (e > 0) collect(e - 1);  // after this the P and transposed-V buffers are free as well
-        if (j == 0 && e > 0) {      // that was the previous item's last O_tile
-            write_out(s_l[hc ^ 1][row]);
-#pragma unroll
-            for (int i = 0; i < kHS / 2; i++) o[i] = 0.f;
+        ATT_CLK(c4);
+        // ---- exponentials of this thread's columns -> P (buffer e & 1: the previous element's P may still be read)
+        // Every row sees key 0, so the running maximum is finite from the first tile on and a masked entry
+        // (-inf) comes out of ex2 as an exact zero.
+        const float l_done = l_run;  // (if this element opens an item: the finished item's sum)
+        if (j == 0) {
             m_run = -INFINITY;
             l_run = 0.f;
         }
-
-        // ---- exponentials of this thread's columns -> P
-        // Every row sees key 0, so the running maximum is finite from the first tile on and a masked entry
-        // (-inf) comes out of ex2 as an exact zero.
         const float m_new = fmaxf(m_run, fmaxf(m_half, s_x[hc ^ 1][row]));
         const float corr = ex2_approx((m_run - m_new) * scale2);  // first tile: ex2(-inf) = 0
         const float off = -m_new * scale2;
@@ -437,14 +456,25 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
 #pragma unroll
                 for (int i = 0; i < 32; i++) pv[i] = 0.f;
             }
-            tmem_st32(tmem_p + lane_off + hc * 64 + c * 32, pv);
+            tmem_st32(tmem_p + (uint32_t)((e & 1) * 128) + lane_off + hc * 64 + c * 32, pv);
         }
         l_run = l_run * corr + l_tile;
         m_run = m_new;
+        ATT_CLK(c5);
+        // ---- the previous element's O_tile, by now long complete; after this the transposed-V buffer is free
+        if (e > 0) collect(e - 1);
         corr_prev = corr;
+        ATT_CLK(c5b);
+        if (j == 0 && e > 0) {  // that was the previous item's last O_tile
+            write_out(l_done, s_l[hc ^ 1][row]);
+#pragma unroll
+            for (int i = 0; i < kHS / 2; i++) o[i] = 0.f;
+        }
 
         // ---- V tile -> key-contiguous operand. Lane = dim (reads are consecutive words), four keys per store.
+        ATT_CLK(c6);
         if (!mbar_wait(&bar_v, ph, p.status, 403, &s_fail)) s_fail = 1;
+        ATT_CLK(c7);
         {
             const int rows = min(kKT, it.kv_len - j * kKT);
             const float* vraw = reinterpret_cast<const float*>(smem + kOffVraw);
@@ -463,11 +493,25 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
                 *reinterpret_cast<float4*>(atom + sw128(lane + 32, g & 7)) = make_float4(b[0], b[1], b[2], b[3]);
             }
         }
+        ATT_CLK(c8);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         // the transposed V was written by ordinary stores: order them before the tensor core's reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        ATT_CLK(c9);
         __syncthreads();  // also: the raw V tile is free
+        ATT_CLK(c10);
+        ATT_ADD(0, 1);
+        ATT_ADD(1, c1 - c0);   // wait for the scores
+        ATT_ADD(2, c2 - c1);   // scores -> registers, mask, max
+        ATT_ADD(3, c3 - c2);   // first barrier
+        ATT_ADD(4, c5b - c5);  // previous O_tile (wait + read + rescale)
+        ATT_ADD(5, c6 - c5b);  // item change: write-out
+        ATT_ADD(6, c5 - c4);   // exponentials -> P
+        ATT_ADD(7, c7 - c6);   // wait for V
+        ATT_ADD(8, c8 - c7);   // transpose
+        ATT_ADD(9, c9 - c8);   // store wait + fences
+        ATT_ADD(10, c10 - c9); // second barrier
         if (s_fail) {
             ok = false;
             break;
@@ -484,7 +528,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
                 const uint64_t vd = umma_desc_sw128(smem + kOffVt + a * kAtomV);
 #pragma unroll
                 for (int kk = 0; kk < 4; kk++)
-                    umma_tf32_ta(tmem_o, tmem_p + (uint32_t)(a * 32 + kk * 8), vd + 2 * kk, idesc, (a | kk) != 0 ? 1u : 0u);
+                    umma_tf32_ta(tmem_o, tmem_p + (uint32_t)((e & 1) * 128 + a * 32 + kk * 8), vd + 2 * kk, idesc,
+                                 (a | kk) != 0 ? 1u : 0u);
             }
             umma_commit(&bar_o);
         }
@@ -504,7 +549,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
     }
     s_l[hc][row] = l_run;
     __syncthreads();
-    if (ok) write_out(s_l[hc ^ 1][row]);
+    if (ok) write_out(l_run, s_l[hc ^ 1][row]);
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -515,6 +560,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
 }
 
 }  // namespace
+
+#if GRADB_DIAG
+void attn_clocks_read(unsigned long long* out16, bool reset) {
+    GRADB_CUDA(cudaDeviceSynchronize());
+    GRADB_CUDA(cudaMemcpyFromSymbol(out16, g_attn_clock, sizeof(unsigned long long) * 16));
+    if (reset) {
+        unsigned long long zero[16] = {};
+        GRADB_CUDA(cudaMemcpyToSymbol(g_attn_clock, zero, sizeof(zero)));
+    }
+}
+#endif
 
 void prefill_attention_tc_configure() {
     GRADB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));

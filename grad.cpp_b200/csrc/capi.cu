@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "session.cuh"
+#include "attn_prefill.cuh"
 #if GRADB_DIAG
 #include "gradb_diag.h"
 #endif
@@ -493,6 +494,15 @@ gradb_status gradb_diag_wide_clocks(uint64_t* out128, int reset) {
         unsigned long long v[128];
         wide_clocks_read(v, reset != 0);
         for (int i = 0; i < 128; i++) out128[i] = v[i];
+    });
+}
+
+gradb_status gradb_diag_attn_clocks(uint64_t* out16, int reset) {
+    return guarded([&] {
+        if (!out16) throw Error(GRADB_ERR_INVALID, "null argument");
+        unsigned long long v[16];
+        attn_clocks_read(v, reset != 0);
+        for (int i = 0; i < 16; i++) out16[i] = v[i];
     });
 }
 

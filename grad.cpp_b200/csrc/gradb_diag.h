@@ -36,6 +36,12 @@ gradb_status gradb_diag_poke_history(gradb_session* session, int seq, int index,
  * [7] accumulator -> staged tile, [8] barrier, [9] row pass, [10] barrier. */
 gradb_status gradb_diag_wide_clocks(uint64_t* out128, int reset);
 
+/* Clock cycles one warp of CTA 0 of the tensor-core prompt attention kernel has spent per part of an element (one
+ * 128 x 128 tile of scores) since the last reset: [0] elements, [1] waiting for the scores, [2] scores -> registers,
+ * mask and maximum, [3] first barrier, [4] previous O_tile, [5] write-out at an item change, [6] exponentials -> P,
+ * [7] waiting for V, [8] transpose, [9] store wait and fences, [10] second barrier. */
+gradb_status gradb_diag_attn_clocks(uint64_t* out16, int reset);
+
 #ifdef __cplusplus
 }
 #endif
