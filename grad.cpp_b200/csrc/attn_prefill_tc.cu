@@ -26,7 +26,7 @@
 // and run under its exponentials; O_tile of element e is collected in element e+1's pass after that element's
 // exponentials (so the second product has a whole softmax to finish in), and when that element opens a new item the
 // finished item's rows are normalised and written there. A CTA's tiles are copied to shared memory first, so the
-// one thread that issues copies and MMAs never waits for a global load. The next V tile is requested when the transpose is done;
+// threads that issue copies and MMAs (three of them, in different warps, one job each) never wait for a global load. The next V tile is requested when the transpose is done;
 // tiles further ahead are prefetched towards L2. All waits are bounded; on expiry the status word is set and the
 // CTA falls through to the common exit, which frees TMEM.
 #include <cuda.h>
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
     const uint32_t tmem_s = tmem_slot + kColS, tmem_p = tmem_slot + kColP, tmem_o = tmem_slot + kColO;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
 
-    // ---- thread 0 only. The CTA's work is one stream of (item, key tile) elements; element e uses K stage e & 1 and
+    // ---- issuing threads only (first lanes of warps 0, 1, 2). The CTA's work is one stream of (item, key tile) elements; element e uses K stage e & 1 and
     // phase e of the V, S and O barriers; item k uses Q buffer k & 1.
     auto load_q = [&](int k) {
         const Item it = get_item(k);
@@ -413,7 +413,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
             ok = false;
             break;
         }
+        // Issuing costs its thread some tens of cycles per instruction, and the whole CTA waits for the slowest warp
+        // at the next barrier: the three jobs go to the first lanes of three different warps.
         if (t == 0) {  // the next element's scores run under this one's exponentials
+            int k1 = k, j1 = j;
+            if (step(k1, j1, it.n_kv)) issue_scores(k1, j1, e + 1);
+        } else if (t == 64) {  // copies: the K tile two elements ahead, Q two items ahead, prefetches beyond
             int k1 = k, j1 = j;
             if (step(k1, j1, it.n_kv)) {
                 const Item it1 = k1 == k ? it : get_item(k1);
@@ -424,7 +429,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
                     int k3 = k2, j3 = j2;
                     if (step(k3, j3, it2.n_kv)) prefetch_kv(k3 == k2 ? it2 : get_item(k3), j3);
                 }
-                issue_scores(k1, j1, e + 1);
             }
             // this item's last scores are done, so its Q buffer is free: fetch the item after next into it
             if (j == it.n_kv - 1 && k + 2 < my_count) load_q(k + 2);
@@ -519,7 +523,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         // ---- O_tile = P V (collected in the next element's pass, or after the loop)
         int k1 = k, j1 = j;
         const bool more = step(k1, j1, it.n_kv);
-        if (t == 0) {
+        if (t == 32) {  // (the second product's issuer)
             if (more) load_v(k1 == k ? it : get_item(k1), j1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             constexpr uint32_t idesc = umma_idesc_tf32(kQT, kHS);
