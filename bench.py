@@ -217,6 +217,13 @@ def run_ours(args):
     stream = torch.cuda.Stream()
     sess = g.BatchSession(model, B, CONTEXT, stream=stream.cuda_stream)
     prompts = [seq_prompt(rank * B + i, dm.vocab) for i in range(B)]
+    if args.eval_only:
+        _, peak, kind = peaks()
+        if rank == 0:
+            print(json.dumps({"eval": bench_scoring(sess, dm, B, peak, kind)}))
+        sess.close()
+        model.close()
+        return
     sp = g.Sampling(0, SAMPLER["temperature"], SAMPLER["penalty"], SAMPLER["top_k"], SAMPLER["top_p"])
     draws = np.stack([seq_draws(rank * B + i, FULL + 1) for i in range(B)])
 
@@ -731,6 +738,9 @@ def main():
     ap.add_argument("--reps", type=int, default=0, help="repetitions of the complete decode (default: enough for 1 s)")
     ap.add_argument("--main-only", action="store_true",
                     help="only the timed workload: no per-kernel pass, batch-1 block or CPU baseline (for profilers)")
+    ap.add_argument("--eval-only", action="store_true",
+                    help="only the scoring block (256 windows x 256 ids) on one GPU, printed as one JSON line (for "
+                         "profilers: the many-row GEMM and the prompt attention kernels)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     PROMPT_LEN = max(1, min(args.prompt_len, CONTEXT - 2))

@@ -5,7 +5,9 @@ the product library is what every other test loads.
   left out): the kernel records its code and returns, the call reports GRADB_ERR_DEVICE_WAIT, nothing faults, and
   the same session decodes correctly afterwards;
 * a device-side index check catches an id that was planted in the history behind the host checks;
-* outputs hold no NaN or Inf; the single-sequence kernel's stage trace is recorded."""
+* outputs hold no NaN or Inf; the single-sequence kernel's stage trace is recorded;
+* the per-role clock counters of the many-row GEMM and the per-phase counters of the tensor-core prompt attention
+  are filled by a scoring pass and a long prompt feed on the 69.0M model (printed with -s: cycles per tile / element)."""
 import os
 import subprocess
 import sys
@@ -104,8 +106,87 @@ def test_diagnostics_build_wait_expiry_index_checks_and_trace(tmp_path):
     assert out.returncode == 0 and "ALL OK" in out.stdout and "FAIL" not in out.stdout, out.stdout + out.stderr[-3000:]
 
 
+CLOCKS = textwrap.dedent('''
+    import ctypes as C
+    import sys
+    import numpy as np
+    sys.path.insert(0, sys.argv[1] + "/tests"); sys.path.insert(0, sys.argv[1])
+    from conftest import load_package
+    g = load_package()
+    from grad_cpp_b200 import checkpoint as ck
+    L = g.lib()
+    GEMM = ["tiles", "mma: wait for a drained accumulator", "mma: wait for operands", "mma: whole loop",
+            "tma: wait for a free stage", "tma: whole loop", "epilogue: wait for an accumulator",
+            "epilogue: accumulator -> staged tile", "epilogue: barriers", "epilogue: row pass"]
+    ATTN = ["elements", "wait for the scores", "scores -> registers, mask, max", "first barrier", "previous O_tile",
+            "write-out at an item change", "exponentials -> P", "wait for V", "transpose", "store wait + fences",
+            "second barrier"]
+
+    def gemm(tag):
+        buf = (C.c_uint64 * 128)()
+        assert L.gradb_diag_wide_clocks(buf, 1) == 0
+        v = np.array(buf[:], dtype=np.float64).reshape(8, 16)
+        seen = 0
+        for e, name in enumerate(["Q|K|V", "residual", "GELU", "SwiGLU", "logits", "log-sum-exp"]):
+            if v[e, 0] == 0:
+                continue
+            seen += 1
+            per = {n: int(v[e, i] / v[e, 0]) for i, n in enumerate(GEMM) if i}
+            print(tag, name, "tiles of CTA 0:", int(v[e, 0]), "cycles per tile:", per)
+            assert per["mma: whole loop"] > 0 and per["epilogue: row pass"] > 0
+        return seen
+
+    def attn(tag):
+        buf = (C.c_uint64 * 16)()
+        assert L.gradb_diag_attn_clocks(buf, 1) == 0
+        v = np.array(buf[:], dtype=np.float64)
+        assert v[0] > 0, "the tensor-core prompt attention did not run"
+        per = {n: int(v[i] / v[0]) for i, n in enumerate(ATTN) if i}
+        print(tag, "elements of CTA 0:", int(v[0]), "cycles per element:", per, "sum", int(v[1:11].sum() / v[0]))
+
+    dm = ck.PRESETS["modern"]
+    path = sys.argv[2] + "/modern.bin"
+    ck.write_synthetic(path, dm, 1004)
+    m = g.GPTModel.load(path, 0, g.BF16)
+    s = g.BatchSession(m, 256, 256)
+    stream = np.random.default_rng(9).integers(0, dm.vocab, 256 * 256 + 1).astype(np.int32)
+    inp = np.stack([stream[i * 256:i * 256 + 256] for i in range(256)])
+    tgt = np.stack([stream[i * 256 + 1:i * 256 + 257] for i in range(256)])
+    s.mean_loss(inp, tgt, 8)
+    gemm("warm-up"); attn("warm-up")
+    s.mean_loss(inp, tgt, 8)
+    assert gemm("scoring 256 x 256 ids:") == 4
+    attn("scoring 256 x 256 ids:")
+    s.close(); m.close()
+
+    dm2 = ck.PRESETS["modern2k"]
+    path2 = sys.argv[2] + "/modern2k.bin"
+    ck.write_synthetic(path2, dm2, 1005)
+    m = g.GPTModel.load(path2, 0, g.BF16)
+    s = g.BatchSession(m, 32, 2048)
+    prompts = [np.random.default_rng(100 + i).integers(0, dm2.vocab, 1024).astype(np.int32) for i in range(32)]
+    s.prefill(prompts, want_logits=False); s.reset()
+    gemm("warm-up"); attn("warm-up")
+    s.prefill(prompts, want_logits=False)
+    assert gemm("feed of 32 x 1024 ids:") == 3
+    attn("feed of 32 x 1024 ids:")
+    print("ALL OK")
+''')
+
+
+def test_role_clocks_of_the_many_row_gemm_and_the_prompt_attention(tmp_path):
+    if not DIAG.exists():
+        pytest.skip("diagnostics library not built")
+    env = dict(os.environ, GRADB_LIB=str(DIAG))
+    out = subprocess.run([sys.executable, "-c", CLOCKS, str(ROOT), str(tmp_path)], env=env, capture_output=True,
+                         text=True, timeout=600)
+    print(out.stdout)
+    assert out.returncode == 0 and "ALL OK" in out.stdout, out.stdout + out.stderr[-3000:]
+
+
 def test_product_library_has_no_diagnostic_entry_points(pkg):
     import ctypes
     L = ctypes.CDLL(str(ROOT / "grad.cpp_b200" / "libgradb.so"))
-    for name in ("gradb_session_stage_trace", "gradb_diag_attention_wait", "gradb_diag_poke_history"):
+    for name in ("gradb_session_stage_trace", "gradb_diag_attention_wait", "gradb_diag_poke_history",
+                 "gradb_diag_wide_clocks", "gradb_diag_attn_clocks"):
         assert not hasattr(L, name), name
