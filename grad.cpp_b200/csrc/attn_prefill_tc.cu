@@ -54,7 +54,11 @@ constexpr int kOffVt = kOffVraw + kKT * kHS * 4;  // 4 atoms (32 keys each)
 constexpr int kSmemBytes = kOffVt + 4 * kAtomV + 1024;
 // tensor-memory map (columns): S, P (element e uses buffer e & 1), O_tile
 constexpr uint32_t kColS = 0, kColP = 128, kColO = 384, kTmemCols = 512;  // P: two buffers of 128 columns
+#if GRADB_DIAG
+constexpr int kMaxListed = 4;    // diagnostics build: small, so that its tests also take the global-memory lookups
+#else
 constexpr int kMaxListed = 192;  // items of a CTA whose tiles are kept in shared memory
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

@@ -157,6 +157,8 @@ CLOCKS = textwrap.dedent('''
     s.mean_loss(inp, tgt, 8)
     assert gemm("scoring 256 x 256 ids:") == 4
     attn("scoring 256 x 256 ids:")
+    # this build lists only four tiles per CTA in shared memory: the rest of the 41 are looked up in global memory
+    np.save(sys.argv[2] + "/lp_diag.npy", s.score(inp, tgt)[:16])
     s.close(); m.close()
 
     dm2 = ck.PRESETS["modern2k"]
@@ -182,6 +184,21 @@ def test_role_clocks_of_the_many_row_gemm_and_the_prompt_attention(tmp_path):
                          text=True, timeout=600)
     print(out.stdout)
     assert out.returncode == 0 and "ALL OK" in out.stdout, out.stdout + out.stderr[-3000:]
+    # the same pass on the product library (all tiles listed in shared memory) gives the same log-probabilities
+    import numpy as np
+    from conftest import load_package
+    g = load_package()
+    from grad_cpp_b200 import checkpoint as ck
+    g.lib()
+    dm = ck.PRESETS["modern"]
+    m = g.GPTModel.load(str(tmp_path / "modern.bin"), 0, g.BF16)
+    s = g.BatchSession(m, 256, 256)
+    stream = np.random.default_rng(9).integers(0, dm.vocab, 256 * 256 + 1).astype(np.int32)
+    inp = np.stack([stream[i * 256:i * 256 + 256] for i in range(256)])
+    tgt = np.stack([stream[i * 256 + 1:i * 256 + 257] for i in range(256)])
+    lp = s.score(inp, tgt)[:16]
+    s.close(); m.close()
+    assert np.abs(lp - np.load(tmp_path / "lp_diag.npy")).max() < 1e-5
 
 
 def test_product_library_has_no_diagnostic_entry_points(pkg):

@@ -197,3 +197,32 @@ def test_sampled_slots_stop_ids_and_prefix_reuse(G, golden_ckpt, port):
         s.admit([1], [np.zeros(dm.max_len + 1, np.int32)], 3)
     port.free(om)
     s.close(); m.close()
+
+
+def test_bf16_prefix_reuse_feeds_from_a_position_inside_a_tile(G, ck, tmp_path):
+    """bf16 sessions run prompt attention on the tensor-core kernel; a follow-up prompt that keeps 150 cached
+    positions makes its query tile start at position 150 (not a multiple of the 128-position tile) with 100 rows.
+    The K/V rows the feed writes in the last layer (which depend on every layer's attention output) must equal
+    those of a fresh feed of the whole prompt up to bf16 rounding, and the greedy continuation must agree."""
+    dm = ck.PRESETS["modern"]
+    path = str(ck.write_synthetic(tmp_path / "modern.bin", dm, 1002))
+    rng = np.random.default_rng(46)
+    long = rng.integers(0, dm.vocab, 250).astype(np.int32)
+    others = [rng.integers(0, dm.vocab, int(n)).astype(np.int32) for n in rng.integers(20, 200, 17)]
+    greedy = G.Sampling(1, 1.0, 1.2, 0, 1.0)
+    m = G.GPTModel.load(path, 0, G.BF16)
+    a = G.BatchSession(m, 18, 256)
+    a.admit([5], [long[:150]], 1)
+    a.decode(greedy, 1)                      # slot 5 now holds the 150 prompt positions (the emitted id was never fed)
+    reused = a.admit([5] + [i for i in range(18) if i != 5], [long] + others, 4, reuse_prefix=True)
+    assert reused[0] == 150 and all(r == 0 for r in reused[1:])
+    b = G.BatchSession(m, 18, 256)
+    b.admit([5] + [i for i in range(18) if i != 5], [long] + others, 4)
+    for pos in (0, 149, 150, 200, 249):
+        for which in (0, 1):
+            ra, rb = a.cache_row(5, dm.layers - 1, which, pos), b.cache_row(5, dm.layers - 1, which, pos)
+            assert np.abs(ra - rb).max() <= 2e-2 * max(np.abs(rb).max(), 1e-6), (pos, which)
+    na, _ = a.decode(greedy, 4)
+    nb, _ = b.decode(greedy, 4)
+    assert list(na[5]) == list(nb[5])
+    a.close(); b.close(); m.close()
