@@ -477,10 +477,14 @@ __global__ void __launch_bounds__(128 * epi_warps_for(TN)) gemm_bf16_tc_kernel(c
 // operands, not the arithmetic, set the main loop's pace). The epilogue always works on 128 tokens at a time.
 constexpr int kWideTN = 128;
 constexpr int kWideHalf = 128;  // tokens per epilogue round = rows of the staged tile
-constexpr int wide_stages(int nw, int tn) { return nw == 1 && tn == 128 ? 4 : 3; }  // 128 or 144 KB of ring
+// CG 2: two CTAs of a cluster (the two SMs of a TPC) work as one MMA unit (cta_group::2): the pair computes 256
+// features x 256 tokens per tile, each CTA holding its own 128 weight rows and HALF of the token tile, so a CTA
+// loads 32 KB per K block for the 128 x 256 outputs it keeps instead of 48 KB, and the ring has room for four stages.
+constexpr int wide_stages(int nw, int tn, int cg = 1) { return cg == 2 || (nw == 1 && tn == 128) ? 4 : 3; }
 constexpr int kWideStageTileBytes = kWideHalf * kTileM * 4;    // + one fp32 output tile staged for the row-wise epilogue
-constexpr size_t wide_smem_bytes(int nw, int tn) {
-    return (size_t)wide_stages(nw, tn) * (nw * kTileM * kBlockK * 2 + tn * kBlockK * 2) + kWideStageTileBytes + 1024;
+constexpr size_t wide_smem_bytes(int nw, int tn, int cg = 1) {
+    return (size_t)wide_stages(nw, tn, cg) * (nw * kTileM * kBlockK * 2 + tn / cg * kBlockK * 2) + kWideStageTileBytes +
+           1024;
 }
 // Four epilogue warps per TMEM lane quarter: with eight warps in all the epilogue, not the MMA stream, set a tile's
 // time (scoring 65536 ids: 23.3 -> 20.6 ms with sixteen; 256-token tiles on top of that measured no gain).
@@ -589,6 +593,7 @@ __device__ __forceinline__ void wide_rows_lse(const TcGemmParams& p, const WideR
     // hold row i's sum.
     constexpr int R = kWideRowBatch;
     static_assert(R == 4, "the butterfly below is written for four rows");
+    if (tile_n * kTileM >= p.N) return;  // the odd CTA of the last pair when the tile count is odd: nothing to leave
 #pragma unroll 1
     for (int i0 = 0; i0 < kWideRowsPerWarp; i0 += R) {
         float4 x[R];
@@ -688,13 +693,52 @@ __device__ unsigned long long g_wide_clock[8 * 16];  // [epilogue kind][counter]
 #define WIDE_ADD(i, v)
 #endif
 
-template <int EPI, int NW, int TN>
+// ---- CTA-pair forms. The even CTA of the pair leads: it issues the MMAs, and the "stage full" and "accumulator
+// drained" barriers that it waits on are its own, signalled by both CTAs (a shared-memory address with bit 24
+// cleared names the same offset in the pair's even CTA).
+constexpr uint32_t kPairLeaderMask = 0xFEFFFFFFu;
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Plain (not multicast) tensor copy into this CTA's shared memory whose bytes are counted on the leader's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar) & kPairLeaderMask)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// Arrives on the barrier at this offset in BOTH CTAs of the pair once the MMAs issued so far are complete.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_u32(bar)),
+        "h"((uint16_t)3)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kPairLeaderMask) : "memory");
+}
+
+template <int EPI, int NW, int TN, int CG = 1>
 __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                 const __grid_constant__ CUtensorMap map_b,
                                                                 const TcGemmParams p, int tiles_n, int total_tiles) {
-    constexpr int kStages = wide_stages(NW, TN);
+    static_assert(CG == 1 || (NW == 1 && TN == 256), "CTA pairs: one weight tile per CTA, 256 tokens per pair");
+    constexpr int kStages = wide_stages(NW, TN, CG);
     constexpr int kABytes = NW * kTileM * kBlockK * 2;
-    constexpr int kBBytes = TN * kBlockK * 2;
+    constexpr int kBBytes = TN / CG * kBlockK * 2;  // a CTA of a pair holds half of the token tile
     constexpr int kStageBytes = kABytes + kBBytes;
     constexpr int kAccCols = NW * TN;          // one accumulator
     constexpr int kTmemCols = 2 * kAccCols;    // two of them: 256 or 512 columns
@@ -710,6 +754,10 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
     float* stg = reinterpret_cast<float*>(smem + (size_t)kStages * kStageBytes);  // [TN][128] fp32 output tile
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_iters = p.K / kBlockK;
+    // Work units: tiles for a lone CTA; for a pair, units of two neighbouring feature tiles (tiles_n counts units),
+    // of which this CTA keeps the one with its rank.
+    const int rank = CG == 2 ? (int)cluster_cta_rank() : 0;
+    const int worker = (int)blockIdx.x / CG, n_workers = (int)gridDim.x / CG;
 
     pdl_trigger();
     if (threadIdx.x == 0) {
@@ -720,19 +768,27 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], kWideEpiWarps);  // one arrival per epilogue warp
+            mbar_init(&acc_empty[b], CG * kWideEpiWarps);  // one arrival per epilogue warp (of both CTAs of a pair)
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
         __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                     "r"((uint32_t)kTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (CG == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                         "r"((uint32_t)kTmemCols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                         "r"((uint32_t)kTmemCols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (CG == 2) cluster_sync_all();  // the peer's barriers exist before anything is signalled across
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
     pdl_wait();
@@ -743,8 +799,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
             bool ok = true;
             int it = 0;
             WIDE_CLK(p_begin);
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int tile_n = tile % tiles_n, tile_b = tile / tiles_n;
+            for (int tile = worker; tile < total_tiles && ok; tile += n_workers) {
+                const int tile_n = (tile % tiles_n) * CG + rank, tile_b = tile / tiles_n;
                 for (int k = 0; k < k_iters; k++, it++) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
@@ -754,6 +810,14 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                     WIDE_ADD(4, w1 - w0);
                     if (!ok) break;
                     uint8_t* st = smem + (size_t)s * kStageBytes;
+                    if (CG == 2) {
+                        // both CTAs' bytes are counted on the leader's barrier; each copies its weight rows and its
+                        // half of the token tile into its own shared memory
+                        if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * kStageBytes);
+                        tma_load_2d_pair(st, &map_a, k * kBlockK, tile_n * kTileM, &full_bar[s]);
+                        tma_load_2d_pair(st + kABytes, &map_b, k * kBlockK, tile_b * TN + rank * kWideHalf, &full_bar[s]);
+                        continue;
+                    }
                     mbar_expect_tx(&full_bar[s], kStageBytes);
 #pragma unroll
                     for (int w = 0; w < NW; w++) {
@@ -773,13 +837,13 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
-            // ---- MMA issuer
-            constexpr uint32_t idesc = umma_idesc_bf16(kTileM, TN);
+        if (lane == 0 && rank == 0) {
+            // ---- MMA issuer (of a pair: the leader's; the instruction runs on both SMs)
+            constexpr uint32_t idesc = umma_idesc_bf16(kTileM * CG, TN);
             bool ok = true;
             int it = 0, lt = 0;
             WIDE_CLK(m_begin);
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, lt++) {
+            for (int tile = worker; tile < total_tiles && ok; tile += n_workers, lt++) {
                 const int buf = lt & 1;
                 WIDE_CLK(a0);
                 ok = mbar_wait(&acc_empty[buf], ((lt >> 1) & 1) ^ 1, p.status, 112);  // drained two tiles ago
@@ -805,12 +869,17 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                         const uint64_t adesc = umma_desc_sw128(st + w * (kTileM * kBlockK * 2));
 #pragma unroll
                         for (int kk = 0; kk < kBlockK / 16; kk++) {
-                            umma_bf16(acc + w * TN, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+                            if (CG == 2) umma_bf16_pair(acc, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+                            else umma_bf16(acc + w * TN, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
                         }
                     }
-                    umma_commit(&empty_bar[s]);
+                    if (CG == 2) umma_commit_pair(&empty_bar[s]);
+                    else umma_commit(&empty_bar[s]);
                 }
-                if (ok) umma_commit(&acc_full[buf]);
+                if (ok) {
+                    if (CG == 2) umma_commit_pair(&acc_full[buf]);
+                    else umma_commit(&acc_full[buf]);
+                }
             }
             WIDE_CLK(m_end);
             WIDE_ADD(3, m_end - m_begin);
@@ -824,8 +893,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
         const int hf = (warp - 2) >> 2;
         const int e = (warp - 2) * 32 + lane;  // the first 128 stage one token of the tile each
         int lt = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, lt++) {
-            const int tile_n = tile % tiles_n, tile_b = tile / tiles_n;
+        for (int tile = worker; tile < total_tiles; tile += n_workers, lt++) {
+            const int tile_n = (tile % tiles_n) * CG + rank, tile_b = tile / tiles_n;
             const int buf = lt & 1;
             if (e < TN) {
                 const int b = tile_b * TN + e;
@@ -866,7 +935,10 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                     // the accumulator is drained: hand it back before the row pass
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    if (lane == 0) {
+                        if (CG == 2) mbar_arrive_leader(&acc_empty[buf]);
+                        else mbar_arrive(&acc_empty[buf]);
+                    }
                 }
                 WIDE_CLK(h1);
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");  // staged tile complete
@@ -902,10 +974,16 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (CG == 2) cluster_sync_all();  // neither CTA frees tensor memory or leaves while the other may still signal it
     if (warp == 1) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
-                     : "memory");
+        if (CG == 2) {
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                         : "memory");
+        } else {
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                         : "memory");
+        }
     }
 }
 
@@ -1124,7 +1202,48 @@ void launch_wide(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams&
     GRADB_CUDA(cudaGetLastError());
 }
 
-// 256-token tiles once they still leave every SM four tiles or more (GRADB_WIDE_TN=128 keeps the narrow tile)
+// CTA pairs: a cluster of two per work unit (two neighbouring feature tiles x 256 tokens).
+template <int EPI>
+void launch_wide_pair(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, int tiles_n, int sm_count,
+                      cudaStream_t st) {
+    constexpr size_t bytes = wide_smem_bytes(1, 256, 2);
+    auto kernel = gemm_bf16_tc_wide_kernel<EPI, 1, 256, 2>;
+    if (!g_capturing) {
+        GRADB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    }
+    const int units_n = (tiles_n + 1) / 2;
+    const int total = units_n * ((p.B + 255) / 256);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * (sm_count / 2));
+    cfg.blockDim = dim3(kWideThreads);
+    cfg.dynamicSmemBytes = bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // Clusters that can be resident together (not every pair of SMs forms one): a persistent grid must not be larger,
+    // or the clusters left over would run their statically dealt units in a second round.
+    static int resident = 0;
+    if (!resident) {
+        int n = 0;
+        GRADB_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+        resident = std::max(1, std::min(n, sm_count / 2));
+    }
+    cfg.gridDim = dim3(2 * std::min(total, resident));
+    cfg.numAttrs = g_pdl ? 2 : 1;
+    GRADB_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, b, p, units_n, total));
+    count_launch();
+    GRADB_CUDA(cudaGetLastError());
+}
+
+// 256-token tiles once they still leave every SM four tiles or more, as CTA pairs unless GRADB_WIDE_PAIRS=0
+// (GRADB_WIDE_TN=128 keeps the narrow tile).
 template <int EPI>
 void launch_wide_single(const CUtensorMap& a, const CUtensorMap& b, const TcGemmParams& p, int tiles_n, int sm_count,
                         cudaStream_t st) {
@@ -1132,8 +1251,16 @@ void launch_wide_single(const CUtensorMap& a, const CUtensorMap& b, const TcGemm
         const char* e = std::getenv("GRADB_WIDE_TN");
         return e && std::atoi(e) == 128;
     }();
-    if (!narrow && tiles_n * ((p.B + 255) / 256) >= 4 * sm_count) launch_wide<EPI, 1, 256>(a, b, p, tiles_n, sm_count, st);
-    else launch_wide<EPI, 1, 128>(a, b, p, tiles_n, sm_count, st);
+    static const bool pairs = [] {
+        const char* e = std::getenv("GRADB_WIDE_PAIRS");
+        return !(e && e[0] == '0');
+    }();
+    if (!narrow && tiles_n * ((p.B + 255) / 256) >= 4 * sm_count) {
+        if (pairs) launch_wide_pair<EPI>(a, b, p, tiles_n, sm_count, st);
+        else launch_wide<EPI, 1, 256>(a, b, p, tiles_n, sm_count, st);
+    } else {
+        launch_wide<EPI, 1, 128>(a, b, p, tiles_n, sm_count, st);
+    }
 }
 }  // namespace
 
