@@ -33,7 +33,10 @@ gradb_status gradb_diag_poke_history(gradb_session* session, int seq, int index,
  * as 8 rows of 16 counters, one row per epilogue kind (0 Q|K|V, 1 residual, 2 GELU, 3 SwiGLU, 4 logits, 5 log-sum-exp):
  * [0] tiles, MMA lane: [1] waiting for a drained accumulator, [2] waiting for operands, [3] whole loop;
  * TMA lane: [4] waiting for a free ring stage, [5] whole loop; first epilogue warp: [6] waiting for an accumulator,
- * [7] accumulator -> staged tile, [8] barrier, [9] row pass, [10] barrier. */
+ * [7] accumulator -> staged tile, [8] barrier, [9] row pass, [10] barrier.
+ * The call also reads GRADB_DIAG_WIDE_SKIP (bits: 1 no accumulator -> staged tile pass, 2 no row pass, 4 no MMAs,
+ * 8 no copies and no waiting for them) for the launches that follow: parts of the kernel timed alone, results
+ * meaningless. */
 gradb_status gradb_diag_wide_clocks(uint64_t* out128, int reset);
 
 /* Clock cycles one warp of CTA 0 of the tensor-core prompt attention kernel has spent per part of an element (one

@@ -153,7 +153,7 @@ CLOCKS = textwrap.dedent('''
     inp = np.stack([stream[i * 256:i * 256 + 256] for i in range(256)])
     tgt = np.stack([stream[i * 256 + 1:i * 256 + 257] for i in range(256)])
     s.mean_loss(inp, tgt, 8)
-    gemm("warm-up"); attn("warm-up")
+    gemm("warm-up"); attn("warm-up")   # (reading the counters also applies GRADB_DIAG_WIDE_SKIP, if set)
     s.mean_loss(inp, tgt, 8)
     assert gemm("scoring 256 x 256 ids:") == 4
     attn("scoring 256 x 256 ids:")
@@ -184,6 +184,8 @@ def test_role_clocks_of_the_many_row_gemm_and_the_prompt_attention(tmp_path):
                          text=True, timeout=600)
     print(out.stdout)
     assert out.returncode == 0 and "ALL OK" in out.stdout, out.stdout + out.stderr[-3000:]
+    if os.environ.get("GRADB_DIAG_WIDE_SKIP"):
+        return  # parts of the GEMM were left out to time the others alone: the numbers above are all there is
     # the same pass on the product library (all tiles listed in shared memory) gives the same log-probabilities
     import numpy as np
     from conftest import load_package
