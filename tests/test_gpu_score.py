@@ -177,7 +177,7 @@ from conftest import load_package
 g = load_package()
 from grad_cpp_b200 import checkpoint as ck
 g.lib()
-dm = ck.PRESETS["modern"]
+dm = ck.PRESETS[sys.argv[4]]
 n, S = 128, 256
 stream = np.random.default_rng(2012).integers(0, dm.vocab, n * S + 1).astype(np.int32)
 inp = np.stack([stream[i * S:i * S + S] for i in range(n)])
@@ -188,25 +188,37 @@ np.save(sys.argv[3], s.score(inp, tgt))
 """
 
 
-def test_cta_pair_gemm_equals_the_single_cta_gemm(ck, tmp_path):
+@pytest.mark.parametrize("preset", ["modern", "medium"])
+def test_cta_pair_gemm_equals_the_single_cta_gemm(preset, G, ck, tmp_path):
     """32768 rows in one pass: every single-weight-tile projection (Q|K|V, the two residual projections, the
     log-sum-exp logits, whose 125 feature tiles leave the last pair's odd CTA without a tile) runs on clusters of
     two CTAs with cta_group::2 MMAs. The same arithmetic in the same order as the one-CTA kernel with 256-token
-    tiles (GRADB_WIDE_PAIRS=0, read once per process, hence the child processes): equal log-probabilities."""
+    tiles (GRADB_WIDE_PAIRS=0, read once per process, hence the child processes): equal log-probabilities. `medium`
+    is the GPT-2 block: biases, LayerNorm and the GELU epilogue (24 feature tiles) on pairs as well. The first
+    windows are also scored by an fp32 session."""
     import os
     import subprocess
     import sys
     from pathlib import Path
     root = Path(__file__).resolve().parents[1]
-    dm = ck.PRESETS["modern"]
-    path = str(ck.write_synthetic(tmp_path / "modern.bin", dm, 1004))
+    dm = ck.PRESETS[preset]
+    path = str(ck.write_synthetic(tmp_path / "model.bin", dm, 1004))
     outs = []
     for name, extra in (("pairs", {}), ("single", {"GRADB_WIDE_PAIRS": "0"})):
         out = tmp_path / f"lp_{name}.npy"
-        r = subprocess.run([sys.executable, "-c", PAIRS_SCRIPT, str(root), path, str(out)], env=dict(os.environ, **extra),
-                           capture_output=True, text=True, timeout=600)
+        r = subprocess.run([sys.executable, "-c", PAIRS_SCRIPT, str(root), path, str(out), preset],
+                           env=dict(os.environ, **extra), capture_output=True, text=True, timeout=600)
         assert r.returncode == 0, r.stderr[-3000:]
         outs.append(np.load(out))
     assert np.isfinite(outs[0]).all()
     assert abs(float(-outs[0].mean()) - (np.log(dm.vocab) + dm.d_model * 0.02 ** 2 / 2)) < 0.03
     assert np.abs(outs[0] - outs[1]).max() < 1e-6
+    n, S = 4, 256
+    stream = np.random.default_rng(2012).integers(0, dm.vocab, 128 * S + 1).astype(np.int32)
+    inp = np.stack([stream[i * S:i * S + S] for i in range(n)])
+    tgt = np.stack([stream[i * S + 1:i * S + S + 1] for i in range(n)])
+    m32 = G.GPTModel.load(path, 0, G.FP32)
+    s32 = G.BatchSession(m32, 4, 256)
+    lp32 = s32.score(inp, tgt)
+    s32.close(); m32.close()
+    assert float(np.sqrt(np.mean((outs[0][:n] - lp32) ** 2))) < 7e-3 and float(np.abs(outs[0][:n] - lp32).max()) < 3e-2
