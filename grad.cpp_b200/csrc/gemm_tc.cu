@@ -1068,6 +1068,88 @@ __global__ void __launch_bounds__(256) norm_rows_kernel(const float* __restrict_
     }
 }
 
+// The same for thousands of rows (prompt feed, scoring): one warp per row, the row held in registers (read once,
+// 128-bit loads, 64-bit bf16 stores), rows dealt to warps grid-stride. The row sum is formed in a different order than
+// in the one-CTA-per-row kernel, so the two may differ in the last bit of a bf16 output.
+constexpr int kNormWarpRows = 2048;   // rows from which this kernel is used
+constexpr int kNormWarpChunks = 16;   // 128-element chunks a row may have (d <= 2048)
+// SPLIT: the fp32-mode operand, every value as a TF32 hi/lo pair (out32[i] and out32[lo_elems + i]).
+template <int MAXC, bool SPLIT>  // 128-element chunks held per lane: 8 (rows to 1024 elements, more warps resident) or 16
+__global__ void __launch_bounds__(256) norm_rows_warp_kernel(const float* __restrict__ X, const float* __restrict__ gamma,
+                                                             const float* __restrict__ beta, const int* __restrict__ tok,
+                                                             __nv_bfloat16* __restrict__ out, float* __restrict__ out32,
+                                                             size_t lo_elems, int d, int rms, float eps, int rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int chunks = d / 128;
+    const float inv_d = 1.0f / (float)d;
+    for (int b = blockIdx.x * 8 + (threadIdx.x >> 5); b < rows; b += gridDim.x * 8) {
+        if (tok[b] < 0) continue;
+        const float4* xr = reinterpret_cast<const float4*>(X + (size_t)b * d);
+        float4 x[MAXC];
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < MAXC; c++) {
+            if (c < chunks) {
+                x[c] = xr[c * 32 + lane];
+                s += rms ? (x[c].x * x[c].x + x[c].y * x[c].y) + (x[c].z * x[c].z + x[c].w * x[c].w)
+                         : (x[c].x + x[c].y) + (x[c].z + x[c].w);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        float mean = 0.f, scale;
+        if (rms) {
+            scale = 1.0f / sqrtf(s * inv_d + eps);
+        } else {
+            mean = s * inv_d;
+            float v2 = 0.f;
+#pragma unroll
+            for (int c = 0; c < MAXC; c++) {
+                if (c < chunks) {
+                    const float a = x[c].x - mean, e = x[c].y - mean, f = x[c].z - mean, g = x[c].w - mean;
+                    v2 += (a * a + e * e) + (f * f + g * g);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v2 += __shfl_xor_sync(0xffffffffu, v2, o);
+            scale = 1.0f / sqrtf(v2 * inv_d + eps);
+        }
+        uint2* orow = SPLIT ? nullptr : reinterpret_cast<uint2*>(out + (size_t)b * d);
+#pragma unroll
+        for (int c = 0; c < MAXC; c++) {
+            if (c < chunks) {
+                const float4 g = reinterpret_cast<const float4*>(gamma)[c * 32 + lane];
+                float4 y;
+                if (rms) {
+                    y = make_float4(g.x * x[c].x * scale, g.y * x[c].y * scale, g.z * x[c].z * scale, g.w * x[c].w * scale);
+                } else {
+                    const float4 bt = reinterpret_cast<const float4*>(beta)[c * 32 + lane];
+                    y = make_float4(g.x * (x[c].x - mean) * scale + bt.x, g.y * (x[c].y - mean) * scale + bt.y,
+                                    g.z * (x[c].z - mean) * scale + bt.z, g.w * (x[c].w - mean) * scale + bt.w);
+                }
+                if (SPLIT) {
+                    float4 h, l;
+                    split_tf32(y.x, h.x, l.x);
+                    split_tf32(y.y, h.y, l.y);
+                    split_tf32(y.z, h.z, l.z);
+                    split_tf32(y.w, h.w, l.w);
+                    const size_t at = (size_t)b * d + (size_t)(c * 32 + lane) * 4;
+                    *reinterpret_cast<float4*>(out32 + at) = h;
+                    *reinterpret_cast<float4*>(out32 + lo_elems + at) = l;
+                } else {
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                    orow[c * 32 + lane] = pk;
+                }
+            }
+        }
+    }
+}
+
 // W (K, N) fp32 row-major -> W^T (N_pad, K) bf16 row-major, with a row mapping for the
 // interleaved gate/up layout.
 __global__ void transpose_bf16_kernel(const float* __restrict__ W, __nv_bfloat16* __restrict__ out, int K, int N,
@@ -1351,20 +1433,38 @@ void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b,
     }
 }
 
-void launch_norm_bf16(const float* X, const float* gamma, const float* beta, const int* tok, __nv_bfloat16* out, int d,
-                      int rms, float eps, int B, cudaStream_t st) {
-    launch_kernel(norm_rows_kernel<false>, dim3(B), dim3(256), 0, st, X, gamma, beta, tok, out, (float*)nullptr, (size_t)0, d,
-                  rms, eps);
+namespace {
+// The warp-per-row kernel from kNormWarpRows rows on, the one-CTA-per-row kernel below that (and for row lengths
+// that are not a multiple of 128 or exceed 2048).
+template <bool SPLIT>
+void launch_norm_any(const float* X, const float* gamma, const float* beta, const int* tok, __nv_bfloat16* out16,
+                     float* out32, size_t lo_elems, int d, int rms, float eps, int B, cudaStream_t st) {
+    if (B >= kNormWarpRows && d % 128 == 0 && d <= 128 * kNormWarpChunks) {
+        const dim3 grid(std::min((B + 7) / 8, 148 * 8));
+        if (d <= 1024) {
+            launch_kernel(norm_rows_warp_kernel<8, SPLIT>, grid, dim3(256), 0, st, X, gamma, beta, tok, out16, out32, lo_elems,
+                          d, rms, eps, B);
+        } else {
+            launch_kernel(norm_rows_warp_kernel<16, SPLIT>, grid, dim3(256), 0, st, X, gamma, beta, tok, out16, out32, lo_elems,
+                          d, rms, eps, B);
+        }
+    } else {
+        launch_kernel(norm_rows_kernel<SPLIT>, dim3(B), dim3(256), 0, st, X, gamma, beta, tok, out16, out32, lo_elems, d, rms,
+                      eps);
+    }
     count_launch();
     GRADB_CUDA(cudaGetLastError());
+}
+}  // namespace
+
+void launch_norm_bf16(const float* X, const float* gamma, const float* beta, const int* tok, __nv_bfloat16* out, int d,
+                      int rms, float eps, int B, cudaStream_t st) {
+    launch_norm_any<false>(X, gamma, beta, tok, out, nullptr, 0, d, rms, eps, B, st);
 }
 
 void launch_norm_split(const float* X, const float* gamma, const float* beta, const int* tok, float* out, size_t lo_elems,
                        int d, int rms, float eps, int B, cudaStream_t st) {
-    launch_kernel(norm_rows_kernel<true>, dim3(B), dim3(256), 0, st, X, gamma, beta, tok, (__nv_bfloat16*)nullptr, out,
-                  lo_elems, d, rms, eps);
-    count_launch();
-    GRADB_CUDA(cudaGetLastError());
+    launch_norm_any<true>(X, gamma, beta, tok, nullptr, out, lo_elems, d, rms, eps, B, st);
 }
 
 namespace {

@@ -432,7 +432,7 @@ int upload_prompt_matrix(Session* s, const int32_t* tokens, const int32_t* offse
 
 // Prompt tokens processed at once by the batched feed: everything the session can hold, between 8192 rows (the
 // activations of a pass then stay in L2) and 65536 (long passes give the persistent GEMM tens of tiles per SM, so its
-// prologue, its last un-overlapped epilogue and the partly filled last round weigh little: scoring 65536 ids took
+// prologue, its last un-overlapped epilogue and the partly filled last wave of tiles weigh little: scoring 65536 ids took
 // 20.4 ms in passes of 8192 rows, 18.5 in 16384, 17.9 in 32768, 17.3 in one). fp32 sessions stop at 16384: their
 // operands are twice as large and scoring keeps a pass's full logits. GRADB_FEED_ROWS overrides.
 constexpr size_t kFeedRowsMin = 8192, kFeedRowsMax = 65536, kFeedRowsMaxFp32 = 16384;
