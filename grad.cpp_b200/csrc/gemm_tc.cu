@@ -688,12 +688,14 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // GRADB_DIAG_WIDE_SKIP leaves parts of the kernel out so that the others can be timed alone (results are then
 // meaningless): 1 no accumulator -> staged tile pass, 2 no row pass, 4 no MMAs, 8 no copies and no waiting for them.
 __device__ int g_wide_skip;
+#define WIDE_SKIP() (g_wide_skip)
 __device__ unsigned long long g_wide_clock[8 * 16];  // [epilogue kind][counter]
 #define WIDE_CLK(x) const long long x = clock64()
 #define WIDE_ADD(i, v) do { if (blockIdx.x == 0) atomicAdd(&g_wide_clock[EPI * 16 + (i)], (unsigned long long)(v)); } while (0)
 #else
 #define WIDE_CLK(x)
 #define WIDE_ADD(i, v)
+#define WIDE_SKIP() 0
 #endif
 
 // ---- CTA-pair forms. The even CTA of the pair leads: it issues the MMAs, and the "stage full" and "accumulator
@@ -802,9 +804,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
             bool ok = true;
             int it = 0;
             WIDE_CLK(p_begin);
-#if GRADB_DIAG
-            if (g_wide_skip & 8) ok = false;
-#endif
+            if (WIDE_SKIP() & 8) ok = false;
             for (int tile = worker; tile < total_tiles && ok; tile += n_workers) {
                 const int tile_n = (tile % tiles_n) * CG + rank, tile_b = tile / tiles_n;
                 for (int k = 0; k < k_iters; k++, it++) {
@@ -863,13 +863,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
                     WIDE_CLK(f0);
-#if GRADB_DIAG
-                    const int xskip = g_wide_skip;
-                    if (!(xskip & 8))
-#else
-                    constexpr int xskip = 0;
-#endif
-                    ok = mbar_wait(&full_bar[s], ph, p.status, 113);
+                    const int skip = WIDE_SKIP();  // 0 in the product build
+                    if (!(skip & 8)) ok = mbar_wait(&full_bar[s], ph, p.status, 113);
                     WIDE_CLK(f1);
                     WIDE_ADD(2, f1 - f0);
                     if (!ok) break;
@@ -881,12 +876,12 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                         const uint64_t adesc = umma_desc_sw128(st + w * (kTileM * kBlockK * 2));
 #pragma unroll
                         for (int kk = 0; kk < kBlockK / 16; kk++) {
-                            if (xskip & 4) continue;
+                            if (skip & 4) continue;
                             if (CG == 2) umma_bf16_pair(acc, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
                             else umma_bf16(acc + w * TN, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
                         }
                     }
-                    if (xskip & 8) continue;
+                    if (skip & 8) continue;
                     if (CG == 2) umma_commit_pair(&empty_bar[s]);
                     else umma_commit(&empty_bar[s]);
                 }
@@ -938,19 +933,16 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
 #pragma unroll 1
             for (int hb = 0; hb < TN / kWideHalf; hb++) {  // 128 tokens at a time through the staged tile
                 WIDE_CLK(h0);
-#if GRADB_DIAG
-                const int skip = g_wide_skip;
-#else
-                constexpr int skip = 0;
-#endif
+                const int skip = WIDE_SKIP();  // 0 in the product build
                 const int row_base = tile_b * TN + hb * kWideHalf;
                 const int* const tok_h = s_tok[buf] + hb * kWideHalf;
                 const int* const pos_h = s_pos[buf] + hb * kWideHalf;
                 if (hb > 0) wide_rows_fetch<EPI>(p, cx, warp - 2, 0, row_base, tok_h, pos_h, pre);
-                if (!(skip & 1))
-                wide_epilogue_stage<EPI, NW, TN>(
-                    p, tmem_base + (uint32_t)(buf * kAccCols + hb * kWideHalf) + ((uint32_t)(q * 32) << 16), t, tile_n, stg,
-                    hf * (kWideHalf / (kWideEpiWarps / 4)), (hf + 1) * (kWideHalf / (kWideEpiWarps / 4)));
+                if (!(skip & 1)) {
+                    wide_epilogue_stage<EPI, NW, TN>(
+                        p, tmem_base + (uint32_t)(buf * kAccCols + hb * kWideHalf) + ((uint32_t)(q * 32) << 16), t, tile_n,
+                        stg, hf * (kWideHalf / (kWideEpiWarps / 4)), (hf + 1) * (kWideHalf / (kWideEpiWarps / 4)));
+                }
                 if (hb == TN / kWideHalf - 1) {
                     // the accumulator is drained: hand it back before the row pass
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -964,6 +956,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) gemm_bf16_tc_wide_kernel(cons
                 asm volatile("bar.sync 1, %0;" ::"n"(32 * kWideEpiWarps) : "memory");  // staged tile complete
                 WIDE_CLK(h2);
                 if (skip & 2) {
+                    // (diagnostics: row pass left out)
                 } else if (EPI == TC_LSE) {
                     wide_rows_lse<EPI>(p, cx, stg, warp - 2, lane, tile_n, row_base, tok_h, pos_h);
                 } else {
