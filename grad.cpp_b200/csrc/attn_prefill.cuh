@@ -31,7 +31,7 @@ void prefill_attention_tc_configure();
 void attn_clocks_read(unsigned long long* out16, bool reset);  // diagnostics build: per-phase clocks of the kernel below
 #endif
 void launch_prefill_attention_tc(const PrefillAttnParams& p, const CUtensorMap& map_q, const CUtensorMap& map_k,
-                                 long long k_row0, int sm_count, cudaStream_t st);
+                                 const CUtensorMap& map_v, long long k_row0, int sm_count, cudaStream_t st);
 // fp32_grade: three TF32 MMAs per product on hi/lo operand pairs (fp32 sessions) instead of one.
 void launch_prefill_attention(const PrefillAttnParams& p, cudaStream_t st, bool fp32_grade = false);
 

@@ -16,13 +16,14 @@
 //   softmax by the row's two threads: causal mask, running max / sum, P = exp(scale (S - max)) -> TMEM (128 cols):
 //                                                        the A operand of the second product is read from there,
 //                                                        so P never crosses shared memory
-//   O_tile[q, dim] (TMEM, 64 cols) = P[q, :] . V[:, dim]   B must be key-contiguous: the V tile (a contiguous block
-//                                                        of the head-major cache, one bulk copy) is transposed
-//                                                        through shared memory by the threads
+//   O_tile[q, dim] (TMEM, 64 cols) = P[q, :] . V[:, dim]   B = V tile as it lies in the cache (keys x dims, brought by
+//                                                        the same tensor copies as K): the operand is declared
+//                                                        MN-major (dims contiguous, keys the K index), so no
+//                                                        transposed copy is made
 //   o = o * exp(old max - new max) + O_tile              in registers (32 per thread)
 //
-// Q has two buffers (the item after next is fetched when an item's last scores are done), K two stages and P two
-// buffers in TMEM: the scores of element e+1 are issued as soon as every thread holds element e's scores in registers
+// Q has two buffers (the item after next is fetched when an item's last scores are done), K and V two stages each and
+// P two buffers in TMEM: the scores of element e+1 are issued as soon as every thread holds element e's scores in registers
 // and run under its exponentials; O_tile of element e is collected in element e+1's pass after that element's
 // exponentials (so the second product has a whole softmax to finish in), and when that element opens a new item the
 // finished item's rows are normalised and written there. A CTA's tiles are copied to shared memory first, so the
@@ -45,13 +46,11 @@ constexpr int kKT = 128;   // keys per tile
 constexpr int kHS = 64;
 constexpr uint32_t kSpin = 1u << 20;
 constexpr int kAtomQ = kQT * 128;  // bytes of one swizzle atom of a 128-row operand: 32 floats per row
-constexpr int kAtomV = kHS * 128;  // bytes of one atom of the transposed V operand: 64 rows (dims) x 32 keys
 // shared-memory map (bytes from a 1024-aligned base)
 constexpr int kOffQ = 0;                       // 2 buffers of 2 atoms
 constexpr int kOffK = kOffQ + 4 * kAtomQ;      // 2 stages of 2 atoms
-constexpr int kOffVraw = kOffK + 4 * kAtomQ;   // [128 keys][64] as stored
-constexpr int kOffVt = kOffVraw + kKT * kHS * 4;  // 4 atoms (32 keys each)
-constexpr int kSmemBytes = kOffVt + 4 * kAtomV + 1024;
+constexpr int kOffV = kOffK + 4 * kAtomQ;      // 2 stages of 2 atoms: [128 keys][32 dims] each, as stored
+constexpr int kSmemBytes = kOffV + 4 * kAtomQ + 1024;
 // tensor-memory map (columns): S, P (element e uses buffer e & 1), O_tile
 constexpr uint32_t kColS = 0, kColP = 128, kColO = 384, kTmemCols = 512;  // P: two buffers of 128 columns
 #if GRADB_DIAG
@@ -100,9 +99,24 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem_tile) {
     d |= (uint64_t)2 << 61;
     return d;
 }
+// MN-major 32-bit operand. The only layout the tensor core takes for it is the 128-byte swizzle in 32-byte units:
+// rows are K indices (here keys), 128 bytes = 32 consecutive MN elements (here dims) each, the four 32-byte chunks of
+// a row exchanged by (row mod 4) -- what a tensor copy with the "128B, 32B atom" swizzle writes. 4-row groups are
+// 512 bytes apart (stride byte offset); the next 32 MN elements start `mn_atom_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn32(const void* smem_tile, uint32_t mn_atom_bytes) {
+    const uint32_t addr = smem_u32(smem_tile);
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(mn_atom_bytes >> 4) << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;
+    return d;
+}
 __host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+constexpr uint32_t kIdescBMnMajor = 1u << 16;  // B read MN-major (N contiguous) instead of K-major
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
     asm volatile(
         "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
@@ -158,11 +172,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
-// Byte offset of the 16-byte chunk `c16` (0..7) of row `r` inside a swizzle atom (128-byte rows, 8-row groups).
-__device__ __forceinline__ uint32_t sw128(int r, int c16) {
-    return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c16 ^ (r & 7)) << 4));
-}
-
 // Diagnostics build: CTA 0 adds up the clock cycles one of its warps spends in each part of an element
 // (read through gradb_diag_attn_clocks).
 #if GRADB_DIAG
@@ -182,9 +191,10 @@ struct Item {
 
 __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                       const __grid_constant__ CUtensorMap map_k,
+                                                                      const __grid_constant__ CUtensorMap map_v,
                                                                       const PrefillAttnParams p, long long k_row0) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q[2], bar_k[2], bar_v, bar_s, bar_o;
+    __shared__ __align__(8) uint64_t bar_q[2], bar_k[2], bar_v[2], bar_s, bar_o;
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int s_fail;
     __shared__ float s_x[2][kQT];  // the two column halves of a row exchange their maxima
@@ -222,7 +232,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         mbar_init(&bar_q[1], 1);
         mbar_init(&bar_k[0], 1);
         mbar_init(&bar_k[1], 1);
-        mbar_init(&bar_v, 1);
+        mbar_init(&bar_v[0], 1);
+        mbar_init(&bar_v[1], 1);
         mbar_init(&bar_s, 1);
         mbar_init(&bar_o, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -267,15 +278,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         tma_load_2d(dst, &map_k, 0, y, bar);
         tma_load_2d(dst + kAtomQ, &map_k, 32, y, bar);
     };
-    auto load_v = [&](const Item& it, int j) {  // the rows of the V tile that exist, as one contiguous block
-        const int rows = min(kKT, it.kv_len - j * kKT);
-        const uint32_t bytes = (uint32_t)rows * kHS * 4;
-        mbar_expect_tx(&bar_v, bytes);
-        const float* src = p.vcache + (size_t)(it.head_row0 + (long long)j * kKT) * kHS;
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                         smem_u32(smem + kOffVraw)),
-                     "l"(src), "r"(bytes), "r"(smem_u32(&bar_v))
-                     : "memory");
+    auto load_v = [&](const Item& it, int j, int e) {  // the same rows of V, as they lie (keys x dims), stage e & 1
+        uint64_t* bar = &bar_v[e & 1];
+        uint8_t* dst = smem + kOffV + (e & 1) * 2 * kAtomQ;
+        mbar_expect_tx(bar, 2 * kAtomQ);
+        const int y = (int)(k_row0 + it.head_row0 + (long long)j * kKT);
+        tma_load_2d(dst, &map_v, 0, y, bar);
+        tma_load_2d(dst + kAtomQ, &map_v, 32, y, bar);
     };
     auto prefetch_kv = [&](const Item& it, int j) {  // towards L2, for the element two ahead of the copies above
         const int rows = min(kKT, it.kv_len - j * kKT);
@@ -320,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         load_q(0);
         if (my_count > 1) load_q(1);
         load_k(it, 0, 0);
-        load_v(it, 0);
+        load_v(it, 0, 0);
         int k1 = 0, j1 = 0;
         if (step(k1, j1, it.n_kv)) {
             const Item it1 = k1 == 0 ? it : get_item(k1);
@@ -479,35 +488,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
             for (int i = 0; i < kHS / 2; i++) o[i] = 0.f;
         }
 
-        // ---- V tile -> key-contiguous operand. Lane = dim (reads are consecutive words), four keys per store.
         ATT_CLK(c6);
-        if (!mbar_wait(&bar_v, ph, p.status, 403, &s_fail)) s_fail = 1;
         ATT_CLK(c7);
-        {
-            const int rows = min(kKT, it.kv_len - j * kKT);
-            const float* vraw = reinterpret_cast<const float*>(smem + kOffVraw);
-#pragma unroll
-            for (int g = warp; g < kKT / 4; g += kThreads / 32) {
-                float a[4], b[4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int key = g * 4 + i;
-                    const bool live = key < rows;  // rows past the context are zero: a masked 0 times stale bits must stay 0
-                    a[i] = live ? vraw[key * kHS + lane] : 0.f;
-                    b[i] = live ? vraw[key * kHS + 32 + lane] : 0.f;
-                }
-                uint8_t* atom = smem + kOffVt + (g >> 3) * kAtomV;
-                *reinterpret_cast<float4*>(atom + sw128(lane, g & 7)) = make_float4(a[0], a[1], a[2], a[3]);
-                *reinterpret_cast<float4*>(atom + sw128(lane + 32, g & 7)) = make_float4(b[0], b[1], b[2], b[3]);
-            }
-        }
         ATT_CLK(c8);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        // the transposed V was written by ordinary stores: order them before the tensor core's reads
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         ATT_CLK(c9);
-        __syncthreads();  // also: the raw V tile is free
+        __syncthreads();  // P is complete in tensor memory
         ATT_CLK(c10);
         ATT_ADD(0, 1);
         ATT_ADD(1, c1 - c0);   // wait for the scores
@@ -516,28 +503,29 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         ATT_ADD(4, c5b - c5);  // previous O_tile (wait + read + rescale)
         ATT_ADD(5, c6 - c5b);  // item change: write-out
         ATT_ADD(6, c5 - c4);   // exponentials -> P
-        ATT_ADD(7, c7 - c6);   // wait for V
-        ATT_ADD(8, c8 - c7);   // transpose
+        ATT_ADD(7, c7 - c6);   // (unused)
+        ATT_ADD(8, c8 - c7);   // (unused)
         ATT_ADD(9, c9 - c8);   // store wait + fences
         ATT_ADD(10, c10 - c9); // second barrier
         if (s_fail) {
             ok = false;
             break;
         }
-        // ---- O_tile = P V (collected in the next element's pass, or after the loop)
+        // ---- O_tile = P V (collected in the next element's pass, or after the loop). V is the B operand as it
+        // lies in the cache: keys are its K index, dims contiguous (MN-major), two 32-dim atoms side by side.
         int k1 = k, j1 = j;
         const bool more = step(k1, j1, it.n_kv);
         if (t == 32) {  // (the second product's issuer)
-            if (more) load_v(k1 == k ? it : get_item(k1), j1);
+            // the other V stage was last read by the previous element's product, collected above
+            if (more) load_v(k1 == k ? it : get_item(k1), j1, e + 1);
+            if (!mbar_wait(&bar_v[e & 1], (uint32_t)((e >> 1) & 1), p.status, 403, &s_fail)) s_fail = 1;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            constexpr uint32_t idesc = umma_idesc_tf32(kQT, kHS);
+            constexpr uint32_t idesc = umma_idesc_tf32(kQT, kHS) | kIdescBMnMajor;
+            const uint64_t vd = umma_desc_sw128_mn32(smem + kOffV + (e & 1) * 2 * kAtomQ, kAtomQ);
 #pragma unroll
-            for (int a = 0; a < 4; a++) {  // 32 keys per atom, 8 per instruction
-                const uint64_t vd = umma_desc_sw128(smem + kOffVt + a * kAtomV);
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++)
-                    umma_tf32_ta(tmem_o, tmem_p + (uint32_t)((e & 1) * 128 + a * 32 + kk * 8), vd + 2 * kk, idesc,
-                                 (a | kk) != 0 ? 1u : 0u);
+            for (int ks = 0; ks < kKT / 8; ks++) {  // 8 keys per instruction = 1024 bytes of rows
+                umma_tf32_ta(tmem_o, tmem_p + (uint32_t)((e & 1) * 128 + ks * 8), vd + (uint64_t)(ks * (1024 >> 4)), idesc,
+                             ks != 0 ? 1u : 0u);
             }
             umma_commit(&bar_o);
         }
@@ -587,11 +575,11 @@ void prefill_attention_tc_configure() {
 // tiles: up to 128 positions each. map_q: fp32 map over the query rows (boxes of 32 columns x 128 rows); map_k: fp32
 // map over the whole K cache as rows of 64 floats; k_row0: first row of this layer in it.
 void launch_prefill_attention_tc(const PrefillAttnParams& p, const CUtensorMap& map_q, const CUtensorMap& map_k,
-                                 long long k_row0, int sm_count, cudaStream_t st) {
+                                 const CUtensorMap& map_v, long long k_row0, int sm_count, cudaStream_t st) {
     if (p.n_tiles <= 0) return;
     const int items = p.n_tiles * p.H;
     launch_kernel(attn_prefill_tc_kernel, dim3(std::min(items, sm_count)), dim3(kThreads), (size_t)kSmemBytes, st, map_q,
-                  map_k, p, k_row0);
+                  map_k, map_v, p, k_row0);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }

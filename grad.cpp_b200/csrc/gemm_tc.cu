@@ -1228,7 +1228,8 @@ void make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
     if (r != CUDA_SUCCESS) throw Error(GRADB_ERR_CUDA, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
 }
 
-void make_tensor_map_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+void make_tensor_map_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                         bool atom32) {
     auto fn = encode_fn();
     if (!fn) throw Error(GRADB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const cuuint64_t dims[2] = {cols, rows};
@@ -1236,8 +1237,9 @@ void make_tensor_map_f32(CUtensorMap* map, const void* base, uint64_t rows, uint
     const cuuint32_t box[2] = {32, box_rows};  // 32 floats = one 128-byte swizzle row
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) throw Error(GRADB_ERR_CUDA, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
 }
 

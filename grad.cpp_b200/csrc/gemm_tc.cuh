@@ -45,8 +45,10 @@ void launch_tc_gemm(int epi, const CUtensorMap& map_a, const CUtensorMap& map_b,
                     int k_splits, cudaStream_t st, int kind = 0);
 // True when launch_tc_gemm would run the many-row persistent kernel for this shape (needed by TC_LSE callers).
 bool tc_many_rows(const TcGemmParams& p, int token_tile);
-// 2-D fp32 tensor map over a row-major (rows, cols) matrix: boxes of 32 columns x box_rows, 128-byte swizzle.
-void make_tensor_map_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+// 2-D fp32 tensor map over a row-major (rows, cols) matrix: boxes of 32 columns x box_rows, 128-byte swizzle
+// (atom32: in 32-byte units, the form a 32-bit MN-major MMA operand needs; otherwise in 16-byte units).
+void make_tensor_map_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                         bool atom32 = false);
 // Normalised rows as TF32 hi/lo pairs: out[0][row][d] and out[1][row][d], the halves lo_elems apart.
 void launch_norm_split(const float* X, const float* gamma, const float* beta, const int* tok, float* out, size_t lo_elems,
                        int d, int rms, float eps, int B, cudaStream_t st);

@@ -653,7 +653,8 @@ void enqueue_prompt_feed_batched(Session* s, const int32_t* tokens, const int32_
                     a.H = s->H; a.T = s->T; a.d = d;
                     a.scale = 1.0f / std::sqrt(static_cast<float>(s->hs));
                     if (tc_attn) {
-                        launch_prefill_attention_tc(a, f.map_q, s->map_kcache, (long long)l * s->B * s->H * s->T, m->sm_count, st);
+                        launch_prefill_attention_tc(a, f.map_q, s->map_kcache, s->map_vcache, (long long)l * s->B * s->H * s->T,
+                                                    m->sm_count, st);
                     } else {
                         launch_prefill_attention(a, st, s32);
                     }
@@ -855,6 +856,7 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         if (s->use_tc && s->hs == 64) {
             s->use_tc_attn = true;
             make_tensor_map_f32(&s->map_kcache, s->kcache, (uint64_t)s->L * B * s->H * s->T, 64, 128);
+            make_tensor_map_f32(&s->map_vcache, s->vcache, (uint64_t)s->L * B * s->H * s->T, 64, 128, true);
         }
         if (s->use_tc) {
             tc_configure_all();

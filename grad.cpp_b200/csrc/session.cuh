@@ -52,6 +52,7 @@ struct Session {
     int* status = nullptr;
     bool use_tc_attn = false;  // prompt attention on tcgen05 (bf16 sessions, head size 64)
     CUtensorMap map_kcache;    // fp32 map over the whole K cache as rows of 64 floats
+    CUtensorMap map_vcache;    // the same over the V cache, swizzled in 32-byte units (MN-major operand of the P V product)
 
     // batched prompt feed (one row per prompt token, all positions of a chunk at once)
     struct Feed {
