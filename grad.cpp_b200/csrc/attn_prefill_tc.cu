@@ -7,9 +7,13 @@
 // persistent: one CTA per SM takes items round-robin (head fastest; the host sorts the tiles longest first) and
 // treats its (item, key tile) pairs as ONE stream of elements, so that the copies of an item's first tiles, which
 // come from HBM, are in flight while the item before it is still being computed; with one CTA per SM and prompts of a
-// few hundred positions that latency was otherwise most of a CTA's life. 256 threads, two per query row (= TMEM
-// lane: a warp reaches the lane quarter given by its index modulo 4), each owning half of the row's score columns and
-// half of its output dims. The cache stays fp32 and is fed to kind::tf32 MMAs as it lies (TF32 reads fp32 bit patterns):
+// few hundred positions that latency was otherwise most of a CTA's life. Eight softmax warps, two threads per query
+// row (= TMEM lane: a warp reaches the lane quarter given by its index modulo 4), each thread owning half of the row's
+// score columns and half of its output dims; the first lanes of two more warps issue everything asynchronous: one the
+// Q and K copies and the score MMAs, the other the V copies and the second product's MMAs. Issuing costs its thread
+// some tens of cycles per instruction (the instruction queue fills at the rate the tensor core drains it), so it is
+// kept off the softmax warps' path; mbarriers tell the issuers when the scores have been read and when P is written.
+// The cache stays fp32 and is fed to kind::tf32 MMAs as it lies (TF32 reads fp32 bit patterns):
 //
 //   S[q, key] (TMEM, 128 cols) = Q[q, :] . K[key, :]      A = Q tile, B = K tile, both dim-contiguous (K-major),
 //                                                        brought by TMA tensor copies with the 128-byte swizzle
@@ -22,14 +26,15 @@
 //                                                        transposed copy is made
 //   o = o * exp(old max - new max) + O_tile              in registers (32 per thread)
 //
-// Q has two buffers (the item after next is fetched when an item's last scores are done), K and V two stages each and
-// P two buffers in TMEM: the scores of element e+1 are issued as soon as every thread holds element e's scores in registers
-// and run under its exponentials; O_tile of element e is collected in element e+1's pass after that element's
+// Q has two buffers (the item after next is fetched when an item's last scores are done), K and V two stages each,
+// P and O_tile two buffers each in TMEM: the scores of element e+1 are issued as soon as every thread holds element
+// e's scores in registers and run under its exponentials; O_tile of element e is collected in element e+1's pass after that element's
 // exponentials (so the second product has a whole softmax to finish in), and when that element opens a new item the
 // finished item's rows are normalised and written there. A CTA's tiles are copied to shared memory first, so the
-// threads that issue copies and MMAs (three of them, in different warps, one job each) never wait for a global load. The next V tile is requested when the transpose is done;
-// tiles further ahead are prefetched towards L2. All waits are bounded; on expiry the status word is set and the
-// CTA falls through to the common exit, which frees TMEM.
+// issuing threads never wait for a global load. Tiles further ahead are prefetched towards L2. Cache rows past a
+// sequence's context are multiplied by exact zeros of P, so they must be finite: the caches are zeroed when a session
+// is created and only ever receive finite rows. All waits are bounded; on expiry the status word is set and the CTA
+// falls through to the common exit, which frees TMEM.
 #include <cuda.h>
 
 #include <algorithm>
@@ -41,7 +46,8 @@ namespace gradb {
 namespace {
 
 constexpr int kQT = 128;   // queries per CTA = TMEM lanes
-constexpr int kThreads = 256;
+constexpr int kSoftmaxThreads = 256;        // two per query row
+constexpr int kThreads = kSoftmaxThreads + 64;  // + two warps whose first lanes issue the copies and the MMAs
 constexpr int kKT = 128;   // keys per tile
 constexpr int kHS = 64;
 constexpr uint32_t kSpin = 1u << 20;
@@ -51,8 +57,8 @@ constexpr int kOffQ = 0;                       // 2 buffers of 2 atoms
 constexpr int kOffK = kOffQ + 4 * kAtomQ;      // 2 stages of 2 atoms
 constexpr int kOffV = kOffK + 4 * kAtomQ;      // 2 stages of 2 atoms: [128 keys][32 dims] each, as stored
 constexpr int kSmemBytes = kOffV + 4 * kAtomQ + 1024;
-// tensor-memory map (columns): S, P (element e uses buffer e & 1), O_tile
-constexpr uint32_t kColS = 0, kColP = 128, kColO = 384, kTmemCols = 512;  // P: two buffers of 128 columns
+// tensor-memory map (columns): S, P and O_tile (element e uses their buffers e & 1)
+constexpr uint32_t kColS = 0, kColP = 128, kColO = 384, kTmemCols = 512;  // P: 2 x 128 columns, O_tile: 2 x 64
 #if GRADB_DIAG
 constexpr int kMaxListed = 4;    // diagnostics build: small, so that its tests also take the global-memory lookups
 #else
@@ -65,6 +71,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait; also ends (false) when another thread of the CTA has already given up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code, volatile int* fail) {
@@ -172,6 +181,24 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// Barrier of the softmax warps that also makes the give-up decision common: every thread contributes what it
+// read of the flag before arriving and all of them get the same answer, so none is left alone at a later barrier.
+__device__ __forceinline__ bool softmax_barrier_dead(volatile int* fail) {
+    const uint32_t mine = (uint32_t)*fail;
+    uint32_t any;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 p, %1, 0;\n"
+        "bar.red.or.pred q, 1, %2, p;\n"
+        "selp.u32 %0, 1, 0, q;\n"
+        "}\n"
+        : "=r"(any)
+        : "r"(mine), "n"(kSoftmaxThreads)
+        : "memory");
+    return any != 0;
+}
+
 // Diagnostics build: CTA 0 adds up the clock cycles one of its warps spends in each part of an element
 // (read through gradb_diag_attn_clocks).
 #if GRADB_DIAG
@@ -194,11 +221,16 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
                                                                       const __grid_constant__ CUtensorMap map_v,
                                                                       const PrefillAttnParams p, long long k_row0) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q[2], bar_k[2], bar_v[2], bar_s, bar_o;
+    // (two O barriers, by element parity: a thread tells the issuer that P is written before it collects the previous
+    // O_tile, so a single barrier could complete two phases while that thread still waits for the first)
+    __shared__ __align__(8) uint64_t bar_q[2], bar_k[2], bar_v[2], bar_s, bar_o[2];
+    // softmax warps -> issuers: scores read; P written (by element parity, for the same reason as the O barriers:
+    // nothing stops the softmax warps from announcing the next P before the issuer has looked at this one)
+    __shared__ __align__(8) uint64_t bar_sfree, bar_pready[2];
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int s_fail;
-    __shared__ float s_x[2][kQT];  // the two column halves of a row exchange their maxima
-    __shared__ float s_l[2][kQT];  // ... and, when an item ends, their sums
+    __shared__ float s_x[2][2][kQT];  // [element parity][half][row]: the two column halves of a row exchange their maxima
+    __shared__ float s_l[2][2][kQT];  // [item parity][half][row]: ... and, when an item ends, their sums
     __shared__ int4 s_tiles[kMaxListed];  // this CTA's first items: tile lookups stay off the issuing thread's path
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -235,7 +267,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         mbar_init(&bar_v[0], 1);
         mbar_init(&bar_v[1], 1);
         mbar_init(&bar_s, 1);
-        mbar_init(&bar_o, 1);
+        mbar_init(&bar_o[0], 1);
+        mbar_init(&bar_o[1], 1);
+        mbar_init(&bar_sfree, kSoftmaxThreads / 32);  // one arrival per softmax warp
+        mbar_init(&bar_pready[0], kSoftmaxThreads / 32);
+        mbar_init(&bar_pready[1], kSoftmaxThreads / 32);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -251,7 +287,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
     const uint32_t tmem_s = tmem_slot + kColS, tmem_p = tmem_slot + kColP, tmem_o = tmem_slot + kColO;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
 
-    // ---- issuing threads only (first lanes of warps 0, 1, 2). The CTA's work is one stream of (item, key tile) elements; element e uses K stage e & 1 and
+    // ---- issuing threads only (first lanes of the two issuer warps). The CTA's work is one stream of (item, key tile) elements; element e uses K stage e & 1 and
     // phase e of the V, S and O barriers; item k uses Q buffer k & 1.
     auto load_q = [&](int k) {
         const Item it = get_item(k);
@@ -325,227 +361,253 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
 
     Item it = get_item(0);
     int k = 0, j = 0;
-    if (t == 0) {
-        load_q(0);
-        if (my_count > 1) load_q(1);
-        load_k(it, 0, 0);
-        load_v(it, 0, 0);
-        int k1 = 0, j1 = 0;
-        if (step(k1, j1, it.n_kv)) {
-            const Item it1 = k1 == 0 ? it : get_item(k1);
-            load_k(it1, j1, 1);
-            int k2 = k1, j2 = j1;
-            if (step(k2, j2, it1.n_kv)) prefetch_kv(k2 == k1 ? it1 : get_item(k2), j2);
-        }
-        issue_scores(0, 0, 0);
-    }
-
-    float o[kHS / 2];
-#pragma unroll
-    for (int i = 0; i < kHS / 2; i++) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's columns only; the halves meet when the item ends
-    float corr_prev = 0.f;                 // factor that goes with the O_tile still to be collected
-    const float scale2 = p.scale * 1.4426950408889634f;  // exp(x) = ex2(x * log2 e)
-    int done_row0 = 0, done_nq = 0, done_h = 0;          // the item whose last O_tile is still to be collected
-    bool ok = true;
-    // O_tile of the previous element: o = o * (its correction) + O_tile
-    auto collect = [&](int e_prev) {
-        if (!mbar_wait(&bar_o, (uint32_t)(e_prev & 1), p.status, 405, &s_fail)) s_fail = 1;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        float ot[32];
-        tmem_ld32(tmem_o + lane_off + hc * 32, ot);
-#pragma unroll
-        for (int i = 0; i < 32; i++) o[i] = o[i] * corr_prev + ot[i];
-    };
-    // rows of the finished item: o / (sum of both halves), this thread's 32 dims
-    auto write_out = [&](float l_mine, float l_other) {
-        if (row >= done_nq) return;
-        const float inv = 1.0f / (l_mine + l_other);
-        const size_t at = (size_t)(done_row0 + row) * p.d + done_h * kHS + hc * 32;
-        if (p.out16) {
-            uint4* dst = reinterpret_cast<uint4*>(p.out16 + at);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                __nv_bfloat162 b[4];
-#pragma unroll
-                for (int q = 0; q < 4; q++) b[q] = __floats2bfloat162_rn(o[8 * i + 2 * q] * inv, o[8 * i + 2 * q + 1] * inv);
-                dst[i] = *reinterpret_cast<const uint4*>(b);
-            }
-        }
-        if (p.out) {
-            float4* dst = reinterpret_cast<float4*>(p.out + at);
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
-            }
-        }
-    };
-
-    int e = 0;
-    for (;; e++) {
-        const uint32_t ph = (uint32_t)(e & 1);
-        // ---- this thread's 64 score columns of its row, into registers
-        ATT_CLK(c0);
-        if (!mbar_wait(&bar_s, ph, p.status, 404, &s_fail)) s_fail = 1;
-        ATT_CLK(c1);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // Scores stay unscaled: exp(scale * (s - max)) is one multiply-add and one ex2 per entry. A 32-column block
-        // that lies wholly above the diagonal for every row of this warp is neither read nor exponentiated.
-        const int key0 = j * kKT + hc * 64;
-        const int warp_q0 = it.pos0 + (warp & 3) * 32;  // first query position of this warp's rows
-        const int qpos = it.pos0 + row;  // this row's position (rows past the tile's end compute, unused)
-        float sc[64];
-        float m_half = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 2; c++) {
-            const int kc = key0 + c * 32;
-            if (kc <= warp_q0 + 31) {  // warp-uniform
-                float part[32];
-                tmem_ld32(tmem_s + lane_off + hc * 64 + c * 32, part);
-                if (kc + 31 > warp_q0) {  // the diagonal crosses this block
-#pragma unroll
-                    for (int i = 0; i < 32; i++) part[i] = kc + i <= qpos ? part[i] : -INFINITY;
-                }
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    sc[c * 32 + i] = part[i];
-                    m_half = fmaxf(m_half, part[i]);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; i++) sc[c * 32 + i] = -INFINITY;
-            }
-        }
-        s_x[hc][row] = m_half;
-        if (j == 0) s_l[hc][row] = l_run;  // the finished item's sum (nothing yet before the first)
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        ATT_CLK(c2);
-        __syncthreads();  // maxima exchanged; the score accumulator and this element's K stage are free
-        ATT_CLK(c3);
-        if (s_fail) {
-            ok = false;
-            break;
-        }
-        // Issuing costs its thread some tens of cycles per instruction, and the whole CTA waits for the slowest warp
-        // at the next barrier: the three jobs go to the first lanes of three different warps.
-        if (t == 0) {  // the next element's scores run under this one's exponentials
-            int k1 = k, j1 = j;
-            if (step(k1, j1, it.n_kv)) issue_scores(k1, j1, e + 1);
-        } else if (t == 64) {  // copies: the K tile two elements ahead, Q two items ahead, prefetches beyond
-            int k1 = k, j1 = j;
-            if (step(k1, j1, it.n_kv)) {
-                const Item it1 = k1 == k ? it : get_item(k1);
-                int k2 = k1, j2 = j1;
-                if (step(k2, j2, it1.n_kv)) {
-                    const Item it2 = k2 == k1 ? it1 : get_item(k2);
-                    load_k(it2, j2, e + 2);
-                    int k3 = k2, j3 = j2;
-                    if (step(k3, j3, it2.n_kv)) prefetch_kv(k3 == k2 ? it2 : get_item(k3), j3);
+    if (warp == kSoftmaxThreads / 32) {
+        // ================= issuer warp A (one lane): copies of Q and K, and the score MMAs =================
+        if (lane == 0) {
+            load_q(0);
+            if (my_count > 1) load_q(1);
+            load_k(it, 0, 0);
+            {
+                int k1 = 0, j1 = 0;
+                if (step(k1, j1, it.n_kv)) {
+                    const Item it1 = k1 == 0 ? it : get_item(k1);
+                    load_k(it1, j1, 1);
+                    int k2 = k1, j2 = j1;
+                    if (step(k2, j2, it1.n_kv)) prefetch_kv(k2 == k1 ? it1 : get_item(k2), j2);
                 }
             }
-            // this item's last scores are done, so its Q buffer is free: fetch the item after next into it
-            if (j == it.n_kv - 1 && k + 2 < my_count) load_q(k + 2);
-            if (j == 0 && k + 3 < my_count) prefetch_q(k + 3);
-        }
-        ATT_CLK(c4);
-        // ---- exponentials of this thread's columns -> P (buffer e & 1: the previous element's P may still be read)
-        // Every row sees key 0, so the running maximum is finite from the first tile on and a masked entry
-        // (-inf) comes out of ex2 as an exact zero.
-        const float l_done = l_run;  // (if this element opens an item: the finished item's sum)
-        if (j == 0) {
-            m_run = -INFINITY;
-            l_run = 0.f;
-        }
-        const float m_new = fmaxf(m_run, fmaxf(m_half, s_x[hc ^ 1][row]));
-        const float corr = ex2_approx((m_run - m_new) * scale2);  // first tile: ex2(-inf) = 0
-        const float off = -m_new * scale2;
-        float l_tile = 0.f;
-#pragma unroll
-        for (int c = 0; c < 2; c++) {
-            float pv[32];
-            if (key0 + c * 32 <= warp_q0 + 31) {
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    pv[i] = ex2_approx(fmaf(sc[c * 32 + i], scale2, off));
-                    l_tile += pv[i];
+            issue_scores(0, 0, 0);
+            for (int e = 0;; e++) {
+                // every softmax thread holds element e's scores: the accumulator and this element's K stage are free
+                if (!mbar_wait(&bar_sfree, (uint32_t)(e & 1), p.status, 406, &s_fail)) {
+                    s_fail = 1;
+                    break;
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; i++) pv[i] = 0.f;
+                int k1 = k, j1 = j;
+                const bool more = step(k1, j1, it.n_kv);
+                Item it1 = it;
+                if (more) {
+                    if (k1 != k) it1 = get_item(k1);
+                    issue_scores(k1, j1, e + 1);  // runs under element e's exponentials
+                    int k2 = k1, j2 = j1;
+                    if (step(k2, j2, it1.n_kv)) {
+                        const Item it2 = k2 == k1 ? it1 : get_item(k2);
+                        load_k(it2, j2, e + 2);
+                        int k3 = k2, j3 = j2;
+                        if (step(k3, j3, it2.n_kv)) prefetch_kv(k3 == k2 ? it2 : get_item(k3), j3);
+                    }
+                }
+                // this item's last scores are done, so its Q buffer is free: fetch the item after next into it
+                if (j == it.n_kv - 1 && k + 2 < my_count) load_q(k + 2);
+                if (j == 0 && k + 3 < my_count) prefetch_q(k + 3);
+                if (!more || s_fail) break;
+                it = it1;
+                k = k1;
+                j = j1;
             }
-            tmem_st32(tmem_p + (uint32_t)((e & 1) * 128) + lane_off + hc * 64 + c * 32, pv);
         }
-        l_run = l_run * corr + l_tile;
-        m_run = m_new;
-        ATT_CLK(c5);
-        // ---- the previous element's O_tile, by now long complete; after this the transposed-V buffer is free
-        if (e > 0) collect(e - 1);
-        corr_prev = corr;
-        ATT_CLK(c5b);
-        if (j == 0 && e > 0) {  // that was the previous item's last O_tile
-            write_out(l_done, s_l[hc ^ 1][row]);
+        __syncwarp();
+    } else if (warp == kSoftmaxThreads / 32 + 1) {
+        // ================= issuer warp B (one lane): copies of V, and the second product's MMAs =================
+        if (lane == 0) {
+            load_v(it, 0, 0);
+            for (int e = 0;; e++) {
+                int k1 = k, j1 = j;
+                const bool more = step(k1, j1, it.n_kv);
+                const Item it1 = (more && k1 != k) ? get_item(k1) : it;
+                // the other V stage was last read by element e-1's product
+                if (e > 0 && !mbar_wait(&bar_o[(e - 1) & 1], (uint32_t)(((e - 1) >> 1) & 1), p.status, 408, &s_fail)) {
+                    s_fail = 1;
+                    break;
+                }
+                if (more) load_v(it1, j1, e + 1);
+                // P of element e is complete in tensor memory
+                if (!mbar_wait(&bar_pready[e & 1], (uint32_t)((e >> 1) & 1), p.status, 407, &s_fail) ||
+                    !mbar_wait(&bar_v[e & 1], (uint32_t)((e >> 1) & 1), p.status, 403, &s_fail)) {
+                    s_fail = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // O_tile = P V. V is the B operand as it lies in the cache: keys are its K index, dims contiguous
+                // (MN-major), two 32-dim atoms side by side.
+                constexpr uint32_t idesc = umma_idesc_tf32(kQT, kHS) | kIdescBMnMajor;
+                const uint64_t vd = umma_desc_sw128_mn32(smem + kOffV + (e & 1) * 2 * kAtomQ, kAtomQ);
 #pragma unroll
-            for (int i = 0; i < kHS / 2; i++) o[i] = 0.f;
+                for (int ks = 0; ks < kKT / 8; ks++) {  // 8 keys per instruction = 1024 bytes of rows
+                    umma_tf32_ta(tmem_o + (uint32_t)((e & 1) * kHS), tmem_p + (uint32_t)((e & 1) * 128 + ks * 8),
+                                 vd + (uint64_t)(ks * (1024 >> 4)), idesc, ks != 0 ? 1u : 0u);
+                }
+                umma_commit(&bar_o[e & 1]);
+                if (!more || s_fail) break;
+                it = it1;
+                k = k1;
+                j = j1;
+            }
         }
-
-        ATT_CLK(c6);
-        ATT_CLK(c7);
-        ATT_CLK(c8);
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        ATT_CLK(c9);
-        __syncthreads();  // P is complete in tensor memory
-        ATT_CLK(c10);
-        ATT_ADD(0, 1);
-        ATT_ADD(1, c1 - c0);   // wait for the scores
-        ATT_ADD(2, c2 - c1);   // scores -> registers, mask, max
-        ATT_ADD(3, c3 - c2);   // first barrier
-        ATT_ADD(4, c5b - c5);  // previous O_tile (wait + read + rescale)
-        ATT_ADD(5, c6 - c5b);  // item change: write-out
-        ATT_ADD(6, c5 - c4);   // exponentials -> P
-        ATT_ADD(7, c7 - c6);   // (unused)
-        ATT_ADD(8, c8 - c7);   // (unused)
-        ATT_ADD(9, c9 - c8);   // store wait + fences
-        ATT_ADD(10, c10 - c9); // second barrier
-        if (s_fail) {
-            ok = false;
-            break;
-        }
-        // ---- O_tile = P V (collected in the next element's pass, or after the loop). V is the B operand as it
-        // lies in the cache: keys are its K index, dims contiguous (MN-major), two 32-dim atoms side by side.
-        int k1 = k, j1 = j;
-        const bool more = step(k1, j1, it.n_kv);
-        if (t == 32) {  // (the second product's issuer)
-            // the other V stage was last read by the previous element's product, collected above
-            if (more) load_v(k1 == k ? it : get_item(k1), j1, e + 1);
-            if (!mbar_wait(&bar_v[e & 1], (uint32_t)((e >> 1) & 1), p.status, 403, &s_fail)) s_fail = 1;
+        __syncwarp();
+    } else {
+        // ================= softmax warps =================
+        float o[kHS / 2];
+#pragma unroll
+        for (int i = 0; i < kHS / 2; i++) o[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's columns only; the halves meet when the item ends
+        float corr_prev = 0.f;                 // factor that goes with the O_tile still to be collected
+        const float scale2 = p.scale * 1.4426950408889634f;  // exp(x) = ex2(x * log2 e)
+        int done_row0 = 0, done_nq = 0, done_h = 0;          // the item whose last O_tile is still to be collected
+        bool ok = true;
+        // O_tile of the previous element: o = o * (its correction) + O_tile
+        auto collect = [&](int e_prev) {
+            if (!mbar_wait(&bar_o[e_prev & 1], (uint32_t)((e_prev >> 1) & 1), p.status, 405, &s_fail)) s_fail = 1;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            constexpr uint32_t idesc = umma_idesc_tf32(kQT, kHS) | kIdescBMnMajor;
-            const uint64_t vd = umma_desc_sw128_mn32(smem + kOffV + (e & 1) * 2 * kAtomQ, kAtomQ);
+            float ot[32];
+            tmem_ld32(tmem_o + (uint32_t)((e_prev & 1) * kHS) + lane_off + hc * 32, ot);
 #pragma unroll
-            for (int ks = 0; ks < kKT / 8; ks++) {  // 8 keys per instruction = 1024 bytes of rows
-                umma_tf32_ta(tmem_o, tmem_p + (uint32_t)((e & 1) * 128 + ks * 8), vd + (uint64_t)(ks * (1024 >> 4)), idesc,
-                             ks != 0 ? 1u : 0u);
+            for (int i = 0; i < 32; i++) o[i] = o[i] * corr_prev + ot[i];
+        };
+        // rows of the finished item: o / (sum of both halves), this thread's 32 dims
+        auto write_out = [&](float l_mine, float l_other) {
+            if (row >= done_nq) return;
+            const float inv = 1.0f / (l_mine + l_other);
+            const size_t at = (size_t)(done_row0 + row) * p.d + done_h * kHS + hc * 32;
+            if (p.out16) {
+                uint4* dst = reinterpret_cast<uint4*>(p.out16 + at);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    __nv_bfloat162 b[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) b[q] = __floats2bfloat162_rn(o[8 * i + 2 * q] * inv, o[8 * i + 2 * q + 1] * inv);
+                    dst[i] = *reinterpret_cast<const uint4*>(b);
+                }
             }
-            umma_commit(&bar_o);
+            if (p.out) {
+                float4* dst = reinterpret_cast<float4*>(p.out + at);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+                }
+            }
+        };
+
+        int e = 0;
+        for (;; e++) {
+            // ---- this thread's 64 score columns of its row, into registers
+            ATT_CLK(c0);
+            if (!mbar_wait(&bar_s, (uint32_t)(e & 1), p.status, 404, &s_fail)) s_fail = 1;
+            ATT_CLK(c1);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // Scores stay unscaled: exp(scale * (s - max)) is one multiply-add and one ex2 per entry. A 32-column
+            // block that lies wholly above the diagonal for every row of this warp is neither read nor exponentiated.
+            const int key0 = j * kKT + hc * 64;
+            const int warp_q0 = it.pos0 + (warp & 3) * 32;  // first query position of this warp's rows
+            const int qpos = it.pos0 + row;  // this row's position (rows past the tile's end compute, unused)
+            float sc[64];
+            float m_half = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                const int kc = key0 + c * 32;
+                if (kc <= warp_q0 + 31) {  // warp-uniform
+                    float part[32];
+                    tmem_ld32(tmem_s + lane_off + hc * 64 + c * 32, part);
+                    if (kc + 31 > warp_q0) {  // the diagonal crosses this block
+#pragma unroll
+                        for (int i = 0; i < 32; i++) part[i] = kc + i <= qpos ? part[i] : -INFINITY;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        sc[c * 32 + i] = part[i];
+                        m_half = fmaxf(m_half, part[i]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) sc[c * 32 + i] = -INFINITY;
+                }
+            }
+            // the scores are in registers: tell issuer A (one arrival per warp)
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_sfree);
+            s_x[e & 1][hc][row] = m_half;
+            if (j == 0) s_l[k & 1][hc][row] = l_run;  // the finished item's sum (nothing yet before the first)
+            ATT_CLK(c2);
+            const bool dead = softmax_barrier_dead(&s_fail);  // maxima (and sums) exchanged
+            ATT_CLK(c3);
+            if (dead) {
+                ok = false;
+                break;
+            }
+            ATT_CLK(c4);
+            // ---- exponentials of this thread's columns -> P (buffer e & 1: the previous element's P may still be read)
+            // Every row sees key 0, so the running maximum is finite from the first tile on and a masked entry
+            // (-inf) comes out of ex2 as an exact zero.
+            const float l_done = l_run;  // (if this element opens an item: the finished item's sum)
+            if (j == 0) {
+                m_run = -INFINITY;
+                l_run = 0.f;
+            }
+            const float m_new = fmaxf(m_run, fmaxf(m_half, s_x[e & 1][hc ^ 1][row]));
+            const float corr = ex2_approx((m_run - m_new) * scale2);  // first tile: ex2(-inf) = 0
+            const float off = -m_new * scale2;
+            float l_tile = 0.f;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                float pv[32];
+                if (key0 + c * 32 <= warp_q0 + 31) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        pv[i] = ex2_approx(fmaf(sc[c * 32 + i], scale2, off));
+                        l_tile += pv[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) pv[i] = 0.f;
+                }
+                tmem_st32(tmem_p + (uint32_t)((e & 1) * 128) + lane_off + hc * 64 + c * 32, pv);
+            }
+            l_run = l_run * corr + l_tile;
+            m_run = m_new;
+            // P is written: tell issuer B (one arrival per warp)
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_pready[e & 1]);
+            ATT_CLK(c5);
+            // ---- the previous element's O_tile, by now long complete
+            if (e > 0) collect(e - 1);
+            corr_prev = corr;
+            ATT_CLK(c5b);
+            if (j == 0 && e > 0) {  // that was the previous item's last O_tile
+                write_out(l_done, s_l[k & 1][hc ^ 1][row]);
+#pragma unroll
+                for (int i = 0; i < kHS / 2; i++) o[i] = 0.f;
+            }
+            ATT_CLK(c6);
+            ATT_ADD(0, 1);
+            ATT_ADD(1, c1 - c0);   // wait for the scores
+            ATT_ADD(2, c2 - c1);   // scores -> registers, mask, max
+            ATT_ADD(3, c3 - c2);   // barrier (maxima exchanged)
+            ATT_ADD(4, c5b - c5);  // previous O_tile (wait + read + rescale)
+            ATT_ADD(5, c6 - c5b);  // item change: write-out
+            ATT_ADD(6, c5 - c4);   // exponentials -> P, store wait, arrival
+            int k1 = k, j1 = j;
+            const bool more = step(k1, j1, it.n_kv);
+            if (k1 != k) {
+                done_row0 = it.row0;
+                done_nq = it.nq;
+                done_h = it.h;
+            }
+            if (!more) break;
+            if (k1 != k) it = get_item(k1);
+            k = k1;
+            j = j1;
         }
-        if (k1 != k) {
-            done_row0 = it.row0;
-            done_nq = it.nq;
-            done_h = it.h;
+        if (ok) {
+            collect(e);
+            if (s_fail) ok = false;
         }
-        if (!more) break;
-        if (k1 != k) it = get_item(k1);
-        k = k1;
-        j = j1;
+        s_l[(k + 1) & 1][hc][row] = l_run;
+        asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+        if (ok) write_out(l_run, s_l[(k + 1) & 1][hc ^ 1][row]);
     }
-    if (ok) {
-        collect(e);
-        if (s_fail) ok = false;
-    }
-    s_l[hc][row] = l_run;
-    __syncthreads();
-    if (ok) write_out(l_run, s_l[hc ^ 1][row]);
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
