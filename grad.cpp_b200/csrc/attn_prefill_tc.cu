@@ -231,7 +231,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
     __shared__ volatile int s_fail;
     __shared__ float s_x[2][2][kQT];  // [element parity][half][row]: the two column halves of a row exchange their maxima
     __shared__ float s_l[2][2][kQT];  // [item parity][half][row]: ... and, when an item ends, their sums
-    __shared__ int4 s_tiles[kMaxListed];  // this CTA's first items: tile lookups stay off the issuing thread's path
+    __shared__ int4 s_tiles[kMaxListed];  // this CTA's first items: tile lookups stay off the issuing threads' path
+    __shared__ int s_head[kMaxListed];    // ... and their heads (no division there either)
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int row = (warp & 3) * 32 + lane;  // query row = TMEM lane
@@ -242,10 +243,16 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
     // k-th item of this CTA: items are dealt round-robin, head fastest, so that CTAs working at the same time
     // hold tiles of the same length (the host sorts the tiles longest first)
     auto get_item = [&](int k) {
-        const int idx = (int)blockIdx.x + k * (int)gridDim.x;
-        const int4 tile = k < kMaxListed ? s_tiles[k] : p.tiles[idx / p.H];
+        int4 tile;
         Item it;
-        it.h = idx % p.H;
+        if (k < kMaxListed) {
+            tile = s_tiles[k];
+            it.h = s_head[k];
+        } else {
+            const int idx = (int)blockIdx.x + k * (int)gridDim.x;
+            tile = p.tiles[idx / p.H];
+            it.h = idx % p.H;
+        }
         it.row0 = tile.y;
         it.pos0 = tile.z;
         it.nq = tile.w;
@@ -256,7 +263,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
     };
 
     for (int k = t; k < min(my_count, kMaxListed); k += kThreads) {
-        s_tiles[k] = p.tiles[((int)blockIdx.x + k * (int)gridDim.x) / p.H];
+        const int idx = (int)blockIdx.x + k * (int)gridDim.x;
+        s_tiles[k] = p.tiles[idx / p.H];
+        s_head[k] = idx % p.H;
     }
     if (t == 0) {
         s_fail = 0;
@@ -393,13 +402,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
                     if (step(k2, j2, it1.n_kv)) {
                         const Item it2 = k2 == k1 ? it1 : get_item(k2);
                         load_k(it2, j2, e + 2);
-                        int k3 = k2, j3 = j2;
-                        if (step(k3, j3, it2.n_kv)) prefetch_kv(k3 == k2 ? it2 : get_item(k3), j3);
                     }
                 }
                 // this item's last scores are done, so its Q buffer is free: fetch the item after next into it
                 if (j == it.n_kv - 1 && k + 2 < my_count) load_q(k + 2);
-                if (j == 0 && k + 3 < my_count) prefetch_q(k + 3);
                 if (!more || s_fail) break;
                 it = it1;
                 k = k1;
@@ -408,7 +414,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
         }
         __syncwarp();
     } else if (warp == kSoftmaxThreads / 32 + 1) {
-        // ================= issuer warp B (one lane): copies of V, and the second product's MMAs =================
+        // ================= issuer warp B (one lane): copies of V, prefetches, and the second product's MMAs ==========
         if (lane == 0) {
             load_v(it, 0, 0);
             for (int e = 0;; e++) {
@@ -438,6 +444,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
                                  vd + (uint64_t)(ks * (1024 >> 4)), idesc, ks != 0 ? 1u : 0u);
                 }
                 umma_commit(&bar_o[e & 1]);
+                // towards L2, off the path of the product above: the K and V tiles three elements ahead, the Q tile
+                // three items ahead
+                if (more) {
+                    int k2 = k1, j2 = j1;
+                    if (step(k2, j2, it1.n_kv)) {
+                        const Item it2 = k2 == k1 ? it1 : get_item(k2);
+                        int k3 = k2, j3 = j2;
+                        if (step(k3, j3, it2.n_kv)) prefetch_kv(k3 == k2 ? it2 : get_item(k3), j3);
+                    }
+                }
+                if (j == 0 && k + 3 < my_count) prefetch_q(k + 3);
                 if (!more || s_fail) break;
                 it = it1;
                 k = k1;
