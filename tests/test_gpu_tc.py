@@ -103,6 +103,28 @@ def test_tiled_prompt_attention_matches_per_position_attention(name, n_seq, G, g
     a_s.close(); b_s.close(); m16.close()
 
 
+def test_tensor_core_prompt_attention_on_long_ragged_prompts(G, ck, tmp_path, monkeypatch):
+    """The same comparison at lengths that end just before, on and just after the 128-position tiles of the
+    tcgen05 prompt attention (up to eight key tiles per query tile, partial last tiles, a one-id prompt), on the
+    69.0M block with context 2048: last-position logits against the feed whose every position streams its prefix
+    through the decode attention kernel in fp32."""
+    dm = ck.PRESETS["modern2k"]
+    path = str(ck.write_synthetic(tmp_path / "modern2k.bin", dm, 1005))
+    rng = np.random.default_rng(25)
+    lens = [1, 2, 63, 64, 127, 128, 129, 130, 255, 256, 257, 300, 383, 384, 385, 511, 512, 513, 700, 1023, 1024, 1025]
+    prompts = [rng.integers(0, dm.vocab, n).astype(np.int32) for n in lens]
+    m16 = G.GPTModel.load(path, 0, G.BF16)
+    a_s = G.BatchSession(m16, len(lens), 1100)
+    a = a_s.prefill(prompts)
+    a_s.close()
+    monkeypatch.setenv("GRADB_NO_TILED_ATTN", "1")
+    b_s = G.BatchSession(m16, len(lens), 1100)
+    b = b_s.prefill(prompts)
+    b_s.close(); m16.close()
+    for i, n in enumerate(lens):
+        assert rel_err(a[i], b[i]) < 1e-2, (n, rel_err(a[i], b[i]))
+
+
 def test_tensor_core_and_streaming_bf16_paths_agree(G, golden_ckpt, monkeypatch):
     dm, path = golden_ckpt("hs64_modern")
     rng = np.random.default_rng(22)
