@@ -948,6 +948,103 @@ __device__ __forceinline__ void record_pick(const SelectParams& p, int b, int* h
     }
 }
 
+// The rest of sample_from_logits (text_gen.cpp:156-208) when the top-k filter left n <= kSmallMax candidates: their
+// ids (ascending) in idx, their tempered logits in val; srt: room for the next power of two of floats. Softmax over
+// the candidates (every other entry is an exact zero), nucleus cutoff on the sorted values, renormalisation, draw --
+// the sums formed term by term in index order by one thread, as the reference forms them. x (vocabulary-sized) is
+// only used to lay out the probabilities when the caller asked for them. All threads call it; returns the pick.
+constexpr int kSmallMax = 256;
+__device__ int select_among_few(const SelectParams& p, int b, int n, const int* idx, float* val, float* srt, float* red_v,
+                                const uint64_t* exp_tab, float* x) {
+    __shared__ float s_scalar;
+    __shared__ int s_pick;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    // max (tensor.cpp:434-440; the filtered entries, -1e10, lie below every candidate)
+    float m = -INFINITY;
+    for (int j = tid; j < n; j += kSelThreads) m = fmaxf(m, val[j]);
+    m = warp_max(m);
+    if (lane == 0) red_v[w] = m;
+    __syncthreads();
+    float mx = red_v[0];
+    for (int i = 1; i < kSelWarps; i++) mx = fmaxf(mx, red_v[i]);
+    for (int j = tid; j < n; j += kSelThreads) val[j] = expf_libm(__fsub_rn(val[j], mx), exp_tab);
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.0f;
+        for (int j = 0; j < n; j++) sum = __fadd_rn(sum, val[j]);
+        s_scalar = sum;
+    }
+    __syncthreads();
+    const float inv_sum = __fdiv_rn(1.0f, s_scalar);
+    for (int j = tid; j < n; j += kSelThreads) val[j] = __fmul_rn(val[j], inv_sum);
+    __syncthreads();
+    if (p.top_p < 1.0f) {  // text_gen.cpp:158-193
+        int n_pad = 2;
+        while (n_pad < n) n_pad <<= 1;
+        for (int j = tid; j < n_pad; j += kSelThreads) srt[j] = j < n ? val[j] : -INFINITY;
+        __syncthreads();
+        sort_desc(srt, n_pad);
+        __syncthreads();
+        if (tid == 0) {
+            float sum = 0.0f;
+            int cutoff = 0;  // stays 0 when the running sum never reaches p (the zeros after the candidates add nothing)
+            for (int j = 0; j < n; j++) {
+                sum = __fadd_rn(sum, srt[j]);
+                if (sum >= p.top_p) {
+                    cutoff = j;
+                    break;
+                }
+            }
+            s_scalar = srt[cutoff];
+        }
+        __syncthreads();
+        const float cutoff_prob = s_scalar;
+        for (int j = tid; j < n; j += kSelThreads) {
+            if (val[j] < cutoff_prob) val[j] = 0.0f;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float sum = 0.0f;
+            for (int j = 0; j < n; j++) sum = __fadd_rn(sum, val[j]);
+            s_scalar = sum;
+        }
+        __syncthreads();
+        const float kept = s_scalar;
+        if (kept > 0.0f) {
+            for (int j = tid; j < n; j += kSelThreads) val[j] = __fdiv_rn(val[j], kept);
+        }
+        __syncthreads();
+    }
+    if (p.probs_out) {
+        for (int i = tid; i < p.V; i += kSelThreads) x[i] = 0.0f;
+        __syncthreads();
+        for (int j = tid; j < n; j += kSelThreads) x[idx[j]] = val[j];
+        __syncthreads();
+        for (int i = tid; i < p.V; i += kSelThreads) p.probs_out[(size_t)b * p.V + i] = x[i];
+    }
+    // draw (text_gen.cpp:199-208): first index with u <= running sum, else the last id. Index 0 already satisfies
+    // u <= 0 + x[0] when u is not positive, candidate or not.
+    if (tid == 0) {
+        const float u = p.uniforms[(size_t)b * p.u_stride + (p.loop_mode ? p.gen[b] : 0)];
+        int pick = p.V - 1;
+        if (u <= 0.0f) {
+            pick = 0;
+        } else {
+            float sum = 0.0f;
+            for (int j = 0; j < n; j++) {
+                sum = __fadd_rn(sum, val[j]);
+                if (u <= sum) {
+                    pick = idx[j];
+                    break;
+                }
+            }
+        }
+        s_pick = pick;
+    }
+    __syncthreads();
+    return s_pick;
+}
+
 // Sampled selection, one 512-thread CTA per sequence. Shared memory holds ONE vocabulary-sized array (so two
 // sequences share an SM): the values in index order, except while the nucleus cutoff is being found, when it holds
 // the sorted probabilities and the index-order copy waits in a global scratch row (L2 resident).
@@ -992,6 +1089,54 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     __syncthreads();
     if (use_k) {  // text_gen.cpp:138-154: below the k-th largest value -> -1e10, ties kept
         const float kth = select_kth_desc(x, V, p.top_k, reinterpret_cast<int*>(work));
+        __syncthreads();  // the histogram area is free again
+        // Few survivors (the usual top-k): everything after the filter only ever sees them. The filtered entries
+        // become exp(-1e10 - max) = +0 exactly, and adding +0 never changes a running sum, so the sequential sums
+        // of the reference are those of the survivors in index order; one thread forms them natively.
+        {
+            __shared__ int s_cnt[kSelWarps + 1];
+            const int per = (V + kSelThreads - 1) / kSelThreads;
+            const int lo = min(V, tid * per), hi = min(V, lo + per);
+            int cnt = 0;
+            bool odd = false;  // a NaN among the values: leave it to the general path
+            for (int i = lo; i < hi; i++) {
+                const float v = x[i];
+                cnt += !(v < kth);
+                odd |= v != v;
+            }
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            if (lane == 31) s_cnt[w] = incl;
+            const bool any_odd = __syncthreads_or(odd);
+            int before = 0, total = 0;
+            for (int i = 0; i < kSelWarps; i++) {
+                before += i < w ? s_cnt[i] : 0;
+                total += s_cnt[i];
+            }
+            if (!any_odd && total <= kSmallMax && kth > -1e10f) {
+                int* s_idx = reinterpret_cast<int*>(work);
+                float* s_val = reinterpret_cast<float*>(work + kSmallMax);
+                int at = before + incl - cnt;
+                for (int i = lo; i < hi; i++) {
+                    const float v = x[i];
+                    if (!(v < kth)) {
+                        s_idx[at] = i;
+                        s_val[at] = v;
+                        at++;
+                    }
+                }
+                __syncthreads();
+                const int pick = select_among_few(p, b, total, s_idx, s_val, reinterpret_cast<float*>(work + 2 * kSmallMax),
+                                                  red_v, s_exp_tab, x);
+                if (tid == 0) record_pick(p, b, hist, hlen, pick);
+                return;
+            }
+            __syncthreads();  // (s_cnt is read by all before anyone moves on)
+        }
         for (int i = tid; i < V; i += kSelThreads) {
             if (x[i] < kth) x[i] = -1e10f;
         }

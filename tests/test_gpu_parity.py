@@ -177,6 +177,15 @@ def test_selection_stage_random_sweep_against_oracle(G, models, port):
         want, want_probs = port.sample(lg, t, k, p, u, want_probs=True)
         assert int(got[0]) == want, (i, t, k, p, u)
         assert np.array_equal(probs[0].view(np.uint32), want_probs.view(np.uint32)), i
+    # the ends of the draw: u = 0 is satisfied at index 0 whatever its probability, a draw beyond the total mass
+    # falls through to the last id -- with few candidates after top-k (their own code path) and with all of them
+    lg = rng.standard_normal(16000, dtype=np.float32) * np.float32(2.0)
+    for k in (40, 0):
+        for u in (np.float32(0.0), np.float32(1.0), np.float32(1e-30)):
+            sp = G.Sampling(0, np.float32(0.8), 1.0, k, np.float32(0.9))
+            got, _ = s.select(sp, uniforms=[u], logits=lg[None, :], want_probs=True)
+            want, _ = port.sample(lg, np.float32(0.8), k, np.float32(0.9), u, want_probs=True)
+            assert int(got[0]) == want, (k, u, int(got[0]), want)
 
 
 def test_penalty_and_argmax_match_oracle(G, models, port):
