@@ -1071,13 +1071,20 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     // ---- repetition penalty: last min(50, n) ids, once per occurrence, in order (text_gen.cpp:20-31)
     int* hist = p.hist + (size_t)b * p.hist_stride;
     const int hlen = p.hist_len[b];
-    if (p.penalty != 1.0f && tid == 0) {
+    if (p.penalty != 1.0f) {
+        // the window's ids are fetched side by side (fifty dependent global loads in one thread cost more than the
+        // rest of a single-sequence selection); one thread then applies them in order
+        __shared__ int s_pen_id[kPenaltyWindow];
         const int window = min(kPenaltyWindow, hlen);
-        for (int k = hlen - window; k < hlen; k++) {
-            const int id = hist[k];
-            if (!GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) continue;
-            if (x[id] > 0) x[id] = __fdiv_rn(x[id], p.penalty);
-            else x[id] = __fmul_rn(x[id], p.penalty);
+        if (tid < window) s_pen_id[tid] = hist[hlen - window + tid];
+        __syncthreads();
+        if (tid == 0) {
+            for (int k = 0; k < window; k++) {
+                const int id = s_pen_id[k];
+                if (!GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) continue;
+                if (x[id] > 0) x[id] = __fdiv_rn(x[id], p.penalty);
+                else x[id] = __fmul_rn(x[id], p.penalty);
+            }
         }
     }
     __syncthreads();
@@ -1231,25 +1238,37 @@ __global__ void __launch_bounds__(kGreedyThreads) select_greedy_kernel(const Sel
     if (tid == 0) pen_n = 0;
     __syncthreads();
     // ---- repetition penalty: last min(50, n) ids, once per occurrence, in order (text_gen.cpp:20-31)
-    if (p.penalty != 1.0f && tid == 0) {
+    if (p.penalty != 1.0f) {
+        // the window's ids and their logits are fetched side by side (a hundred dependent global loads in one thread
+        // cost more than the rest of a single-sequence selection); one thread then applies them in order
+        __shared__ int s_pen_id[kPenaltyWindow];
+        __shared__ float s_pen_lg[kPenaltyWindow];
         const int window = min(kPenaltyWindow, hlen);
-        int n = 0;
-        for (int k = hlen - window; k < hlen; k++) {
-            const int id = hist[k];
-            if (!GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) continue;
-            int slot = id & (kPenHash - 1);
-            while (table[slot] >= 0 && pen_id[table[slot]] != id) slot = (slot + 1) & (kPenHash - 1);
-            int e = table[slot];
-            if (e < 0) {
-                e = n++;
-                table[slot] = e;
-                pen_id[e] = id;
-                pen_val[e] = lg[id];
-            }
-            const float v = pen_val[e];
-            pen_val[e] = v > 0 ? __fdiv_rn(v, p.penalty) : __fmul_rn(v, p.penalty);
+        if (tid < window) {
+            const int id = hist[hlen - window + tid];
+            s_pen_id[tid] = id;
+            s_pen_lg[tid] = (id >= 0 && id < V) ? lg[id] : 0.0f;
         }
-        pen_n = n;
+        __syncthreads();
+        if (tid == 0) {
+            int n = 0;
+            for (int k = 0; k < window; k++) {
+                const int id = s_pen_id[k];
+                if (!GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) continue;
+                int slot = id & (kPenHash - 1);
+                while (table[slot] >= 0 && pen_id[table[slot]] != id) slot = (slot + 1) & (kPenHash - 1);
+                int e = table[slot];
+                if (e < 0) {
+                    e = n++;
+                    table[slot] = e;
+                    pen_id[e] = id;
+                    pen_val[e] = s_pen_lg[k];
+                }
+                const float v = pen_val[e];
+                pen_val[e] = v > 0 ? __fdiv_rn(v, p.penalty) : __fmul_rn(v, p.penalty);
+            }
+            pen_n = n;
+        }
     }
     __syncthreads();
     const int n_pen = pen_n;
