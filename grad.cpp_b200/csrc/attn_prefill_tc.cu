@@ -487,13 +487,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prefill_tc_kernel(const __gr
             const float inv = 1.0f / (l_mine + l_other);
             const size_t at = (size_t)(done_row0 + row) * p.d + done_h * kHS + hc * 32;
             if (p.out16) {
-                uint4* dst = reinterpret_cast<uint4*>(p.out16 + at);
+                // 64 bytes per thread, rows 1.5 KB apart: two 256-bit stores fill whole 32-byte sectors
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    __nv_bfloat162 b[4];
+                for (int i = 0; i < 2; i++) {
+                    uint32_t w8[8];
 #pragma unroll
-                    for (int q = 0; q < 4; q++) b[q] = __floats2bfloat162_rn(o[8 * i + 2 * q] * inv, o[8 * i + 2 * q + 1] * inv);
-                    dst[i] = *reinterpret_cast<const uint4*>(b);
+                    for (int q = 0; q < 8; q++) {
+                        const __nv_bfloat162 b = __floats2bfloat162_rn(o[16 * i + 2 * q] * inv, o[16 * i + 2 * q + 1] * inv);
+                        w8[q] = *reinterpret_cast<const uint32_t*>(&b);
+                    }
+                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p.out16 + at + 16 * i),
+                                 "r"(w8[0]), "r"(w8[1]), "r"(w8[2]), "r"(w8[3]), "r"(w8[4]), "r"(w8[5]), "r"(w8[6]), "r"(w8[7])
+                                 : "memory");
                 }
             }
             if (p.out) {
