@@ -1072,18 +1072,28 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     int* hist = p.hist + (size_t)b * p.hist_stride;
     const int hlen = p.hist_len[b];
     if (p.penalty != 1.0f) {
-        // the window's ids are fetched side by side (fifty dependent global loads in one thread cost more than the
-        // rest of a single-sequence selection); one thread then applies them in order
+        // The reference walks the window in order and penalises an id once per occurrence. Different ids do not
+        // interact and the repeated penalties of one id are applied in sequence by one thread (the window position
+        // of its first occurrence), so the positions work side by side with the reference's result.
         __shared__ int s_pen_id[kPenaltyWindow];
         const int window = min(kPenaltyWindow, hlen);
         if (tid < window) s_pen_id[tid] = hist[hlen - window + tid];
         __syncthreads();
-        if (tid == 0) {
-            for (int k = 0; k < window; k++) {
-                const int id = s_pen_id[k];
-                if (!GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) continue;
-                if (x[id] > 0) x[id] = __fdiv_rn(x[id], p.penalty);
-                else x[id] = __fmul_rn(x[id], p.penalty);
+        if (tid < window) {
+            const int id = s_pen_id[tid];
+            if (GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) {
+                bool first = true;
+                int count = 0;
+                for (int k = 0; k < window; k++) {
+                    const bool same = s_pen_id[k] == id;
+                    first = first && !(same && k < tid);
+                    count += same;
+                }
+                if (first) {
+                    float v = x[id];
+                    for (int c = 0; c < count; c++) v = v > 0 ? __fdiv_rn(v, p.penalty) : __fmul_rn(v, p.penalty);
+                    x[id] = v;
+                }
             }
         }
     }
@@ -1218,6 +1228,7 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
 constexpr int kGreedyThreads = 512;
 constexpr int kGreedyWarps = kGreedyThreads / 32;
 constexpr int kPenHash = 128;  // open-addressing table over the <= 50 distinct ids of the window
+constexpr int kPenBitWords = 2048;  // bitmap of overridden ids for vocabularies to 65536
 
 __global__ void __launch_bounds__(kGreedyThreads) select_greedy_kernel(const SelectParams p) {
     __shared__ int pen_id[kPenaltyWindow];
@@ -1239,41 +1250,58 @@ __global__ void __launch_bounds__(kGreedyThreads) select_greedy_kernel(const Sel
     __syncthreads();
     // ---- repetition penalty: last min(50, n) ids, once per occurrence, in order (text_gen.cpp:20-31)
     if (p.penalty != 1.0f) {
-        // the window's ids and their logits are fetched side by side (a hundred dependent global loads in one thread
-        // cost more than the rest of a single-sequence selection); one thread then applies them in order
+        // The reference walks the window in order and penalises an id once per occurrence. Different ids do not
+        // interact and the repeated penalties of one id are applied in sequence by one thread (the window position
+        // of its first occurrence), so the positions work side by side with the reference's result; the penalised
+        // values become a short list of overrides.
         __shared__ int s_pen_id[kPenaltyWindow];
-        __shared__ float s_pen_lg[kPenaltyWindow];
         const int window = min(kPenaltyWindow, hlen);
+        int id = -1;
         if (tid < window) {
-            const int id = hist[hlen - window + tid];
+            id = hist[hlen - window + tid];
             s_pen_id[tid] = id;
-            s_pen_lg[tid] = (id >= 0 && id < V) ? lg[id] : 0.0f;
         }
         __syncthreads();
-        if (tid == 0) {
-            int n = 0;
+        if (tid < window && GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) {
+            bool first = true;
+            int count = 0;
             for (int k = 0; k < window; k++) {
-                const int id = s_pen_id[k];
-                if (!GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) continue;
-                int slot = id & (kPenHash - 1);
-                while (table[slot] >= 0 && pen_id[table[slot]] != id) slot = (slot + 1) & (kPenHash - 1);
-                int e = table[slot];
-                if (e < 0) {
-                    e = n++;
-                    table[slot] = e;
-                    pen_id[e] = id;
-                    pen_val[e] = s_pen_lg[k];
-                }
-                const float v = pen_val[e];
-                pen_val[e] = v > 0 ? __fdiv_rn(v, p.penalty) : __fmul_rn(v, p.penalty);
+                const bool same = s_pen_id[k] == id;
+                first = first && !(same && k < tid);
+                count += same;
             }
-            pen_n = n;
+            if (first) {
+                float v = lg[id];
+                for (int c = 0; c < count; c++) v = v > 0 ? __fdiv_rn(v, p.penalty) : __fmul_rn(v, p.penalty);
+                const int e = atomicAdd(&pen_n, 1);
+                pen_id[e] = id;
+                pen_val[e] = v;
+            }
+        }
+        __syncthreads();
+        if (tid == 0 && V > kPenBitWords * 32) {  // very large vocabularies look the overrides up in a hash table
+            for (int e = 0; e < pen_n; e++) {
+                int slot = pen_id[e] & (kPenHash - 1);
+                while (table[slot] >= 0) slot = (slot + 1) & (kPenHash - 1);
+                table[slot] = e;
+            }
         }
     }
     __syncthreads();
     const int n_pen = pen_n;
+    // Which ids are overridden: one bit per id (vocabularies to 65536: a single shared-memory word answers for the
+    // four ids of a 128-bit load), beyond that the hash table again.
+    __shared__ uint32_t pen_bits[kPenBitWords];
+    const bool use_bits = n_pen > 0 && V <= kPenBitWords * 32;
+    if (use_bits) {
+        for (int i = tid; i < (V + 31) / 32; i += kGreedyThreads) pen_bits[i] = 0u;
+        __syncthreads();
+        if (tid < n_pen) atomicOr(&pen_bits[pen_id[tid] >> 5], 1u << (pen_id[tid] & 31));
+        __syncthreads();
+    }
     auto overridden = [&](int id) {
         if (n_pen == 0) return false;
+        if (use_bits) return ((pen_bits[id >> 5] >> (id & 31)) & 1u) != 0u;
         int slot = id & (kPenHash - 1);
         while (table[slot] >= 0) {
             if (pen_id[table[slot]] == id) return true;
@@ -1295,6 +1323,13 @@ __global__ void __launch_bounds__(kGreedyThreads) select_greedy_kernel(const Sel
         for (int q = tid; q < V / 4; q += kGreedyThreads) {
             const float4 v = __ldcs(lg4 + q);
             const int i = q * 4;
+            if (n_pen == 0 || (use_bits && ((pen_bits[i >> 5] >> (i & 31)) & 0xFu) == 0u)) {  // none of the four
+                consider(v.x, i);
+                consider(v.y, i + 1);
+                consider(v.z, i + 2);
+                consider(v.w, i + 3);
+                continue;
+            }
             if (!overridden(i)) consider(v.x, i);
             if (!overridden(i + 1)) consider(v.y, i + 1);
             if (!overridden(i + 2)) consider(v.z, i + 2);
