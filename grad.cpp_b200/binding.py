@@ -106,6 +106,7 @@ DIAG_SIGNATURES = {
     "gradb_diag_poke_history": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int32]),
     "gradb_diag_wide_clocks": (C.c_int, [C.POINTER(C.c_uint64), C.c_int]),
     "gradb_diag_attn_clocks": (C.c_int, [C.POINTER(C.c_uint64), C.c_int]),
+    "gradb_diag_select_clocks": (C.c_int, [C.POINTER(C.c_uint64), C.c_int]),
 }
 
 DRAW_FN = C.CFUNCTYPE(C.c_float, C.c_void_p, C.c_int)

@@ -506,6 +506,15 @@ gradb_status gradb_diag_attn_clocks(uint64_t* out16, int reset) {
     });
 }
 
+gradb_status gradb_diag_select_clocks(uint64_t* out16, int reset) {
+    return guarded([&] {
+        if (!out16) throw Error(GRADB_ERR_INVALID, "null argument");
+        unsigned long long v[16];
+        select_clocks_read(v, reset != 0);
+        for (int i = 0; i < 16; i++) out16[i] = v[i];
+    });
+}
+
 gradb_status gradb_diag_poke_history(gradb_session* session, int seq, int index, int32_t id) {
     return guarded([&] {
         if (!session) throw Error(GRADB_ERR_INVALID, "null session");

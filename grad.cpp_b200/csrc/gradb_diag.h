@@ -45,6 +45,11 @@ gradb_status gradb_diag_wide_clocks(uint64_t* out128, int reset);
  * [7] waiting for V, [8] transpose, [9] store wait and fences, [10] second barrier. */
 gradb_status gradb_diag_attn_clocks(uint64_t* out16, int reset);
 
+/* Clock cycles sequence 0's CTA of the sampled selection kernel has spent per part since the last reset, for calls
+ * that take the few-candidates path after top-k: [0] calls, [1] logits -> shared memory, [2] penalty, [3] temperature,
+ * [4] k-th value, [5] count and compact, [6] softmax / nucleus / draw on the survivors, [7] bookkeeping. */
+gradb_status gradb_diag_select_clocks(uint64_t* out16, int reset);
+
 #ifdef __cplusplus
 }
 #endif

@@ -834,7 +834,8 @@ __device__ __forceinline__ float from_ordered_key(uint32_t k) {
 // NaNs take no part. All threads call it and get the same result.
 __device__ float select_kth_desc(const float* x, int n, int k, int* hist) {
     __shared__ uint32_t s_lo, s_hi;
-    __shared__ int s_bucket, s_before;
+    __shared__ int s_bucket, s_before, s_count, s_few_n;
+    constexpr int kKthFew = 256;
     const int tid = threadIdx.x;
     constexpr int kPer = kBuckets / kSelThreads;
     if (tid == 0) {
@@ -891,15 +892,40 @@ __device__ float select_kth_desc(const float* x, int n, int k, int* hist) {
             if (counts[i] > 0 && before < rank && rank <= before + counts[i]) {
                 s_bucket = tid * kPer + i;
                 s_before = before;
+                s_count = counts[i];
             }
         }
         if (tid == 0) {
             s_lo = 0xffffffffu;
             s_hi = 0u;
+            s_few_n = 0;
         }
         __syncthreads();
         const int bkt = s_bucket;
         rank -= s_before;
+        if (s_count <= kKthFew) {
+            // Few candidates left in the bucket: list them (in any order) and read the rank off by counting, instead
+            // of narrowing the range again. hist is free: the list lives in its first words.
+            float* few = reinterpret_cast<float*>(hist);
+            __syncthreads();
+            for (int i = tid; i < n; i += kSelThreads) {
+                const float v = x[i];
+                if (v >= lo && v <= hi && bucket_of(v) == bkt) few[atomicAdd(&s_few_n, 1)] = v;
+            }
+            __syncthreads();
+            const int c = s_few_n;
+            if (tid < c) {
+                const float v = few[tid];
+                int greater = 0, equal = 0;
+                for (int j = 0; j < c; j++) {
+                    greater += few[j] > v;
+                    equal += few[j] == v;
+                }
+                if (greater < rank && rank <= greater + equal) s_lo = ordered_key(v);  // (equal values write the same key)
+            }
+            __syncthreads();
+            return from_ordered_key(s_lo);
+        }
         {
             uint32_t klo = 0xffffffffu, khi = 0u;
             for (int i = tid; i < n; i += kSelThreads) {
@@ -951,99 +977,116 @@ __device__ __forceinline__ void record_pick(const SelectParams& p, int b, int* h
 // The rest of sample_from_logits (text_gen.cpp:156-208) when the top-k filter left n <= kSmallMax candidates: their
 // ids (ascending) in idx, their tempered logits in val; srt: room for the next power of two of floats. Softmax over
 // the candidates (every other entry is an exact zero), nucleus cutoff on the sorted values, renormalisation, draw --
-// the sums formed term by term in index order by one thread, as the reference forms them. x (vocabulary-sized) is
-// only used to lay out the probabilities when the caller asked for them. All threads call it; returns the pick.
+// the sums formed term by term in index order by one lane, as the reference forms them. x (vocabulary-sized) is
+// only used to lay out the probabilities when the caller asked for them. Called by ONE warp (warp barriers only);
+// every lane returns the pick.
 constexpr int kSmallMax = 256;
-__device__ int select_among_few(const SelectParams& p, int b, int n, const int* idx, float* val, float* srt, float* red_v,
+__device__ void sort_desc_warp(float* a, int n_pad) {  // bitonic, descending, n_pad a power of two, one warp
+    const int lane = threadIdx.x & 31;
+    for (int k = 2; k <= n_pad; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = lane; i < n_pad; i += 32) {
+                const int ixj = i ^ j;
+                if (ixj > i) {
+                    const float x = a[i], y = a[ixj];
+                    const bool desc = (i & k) == 0;
+                    if (desc ? (x < y) : (x > y)) {
+                        a[i] = y;
+                        a[ixj] = x;
+                    }
+                }
+            }
+            __syncwarp();
+        }
+    }
+}
+__device__ int select_among_few(const SelectParams& p, int b, int n, const int* idx, float* val, float* srt,
                                 const uint64_t* exp_tab, float* x) {
-    __shared__ float s_scalar;
-    __shared__ int s_pick;
-    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int lane = threadIdx.x & 31;
     // max (tensor.cpp:434-440; the filtered entries, -1e10, lie below every candidate)
     float m = -INFINITY;
-    for (int j = tid; j < n; j += kSelThreads) m = fmaxf(m, val[j]);
-    m = warp_max(m);
-    if (lane == 0) red_v[w] = m;
-    __syncthreads();
-    float mx = red_v[0];
-    for (int i = 1; i < kSelWarps; i++) mx = fmaxf(mx, red_v[i]);
-    for (int j = tid; j < n; j += kSelThreads) val[j] = expf_libm(__fsub_rn(val[j], mx), exp_tab);
-    __syncthreads();
-    if (tid == 0) {
-        float sum = 0.0f;
+    for (int j = lane; j < n; j += 32) m = fmaxf(m, val[j]);
+    const float mx = warp_max(m);
+    for (int j = lane; j < n; j += 32) val[j] = expf_libm(__fsub_rn(val[j], mx), exp_tab);
+    __syncwarp();
+    float sum = 0.0f;
+    if (lane == 0) {
         for (int j = 0; j < n; j++) sum = __fadd_rn(sum, val[j]);
-        s_scalar = sum;
     }
-    __syncthreads();
-    const float inv_sum = __fdiv_rn(1.0f, s_scalar);
-    for (int j = tid; j < n; j += kSelThreads) val[j] = __fmul_rn(val[j], inv_sum);
-    __syncthreads();
+    const float inv_sum = __fdiv_rn(1.0f, __shfl_sync(0xffffffffu, sum, 0));
+    for (int j = lane; j < n; j += 32) val[j] = __fmul_rn(val[j], inv_sum);
+    __syncwarp();
     if (p.top_p < 1.0f) {  // text_gen.cpp:158-193
         int n_pad = 2;
         while (n_pad < n) n_pad <<= 1;
-        for (int j = tid; j < n_pad; j += kSelThreads) srt[j] = j < n ? val[j] : -INFINITY;
-        __syncthreads();
-        sort_desc(srt, n_pad);
-        __syncthreads();
-        if (tid == 0) {
-            float sum = 0.0f;
+        for (int j = lane; j < n_pad; j += 32) srt[j] = j < n ? val[j] : -INFINITY;
+        __syncwarp();
+        sort_desc_warp(srt, n_pad);
+        float cutoff_prob = 0.0f;
+        if (lane == 0) {
+            float run = 0.0f;
             int cutoff = 0;  // stays 0 when the running sum never reaches p (the zeros after the candidates add nothing)
             for (int j = 0; j < n; j++) {
-                sum = __fadd_rn(sum, srt[j]);
-                if (sum >= p.top_p) {
+                run = __fadd_rn(run, srt[j]);
+                if (run >= p.top_p) {
                     cutoff = j;
                     break;
                 }
             }
-            s_scalar = srt[cutoff];
+            cutoff_prob = srt[cutoff];
         }
-        __syncthreads();
-        const float cutoff_prob = s_scalar;
-        for (int j = tid; j < n; j += kSelThreads) {
+        cutoff_prob = __shfl_sync(0xffffffffu, cutoff_prob, 0);
+        for (int j = lane; j < n; j += 32) {
             if (val[j] < cutoff_prob) val[j] = 0.0f;
         }
-        __syncthreads();
-        if (tid == 0) {
-            float sum = 0.0f;
-            for (int j = 0; j < n; j++) sum = __fadd_rn(sum, val[j]);
-            s_scalar = sum;
+        __syncwarp();
+        float kept = 0.0f;
+        if (lane == 0) {
+            for (int j = 0; j < n; j++) kept = __fadd_rn(kept, val[j]);
         }
-        __syncthreads();
-        const float kept = s_scalar;
+        kept = __shfl_sync(0xffffffffu, kept, 0);
         if (kept > 0.0f) {
-            for (int j = tid; j < n; j += kSelThreads) val[j] = __fdiv_rn(val[j], kept);
+            for (int j = lane; j < n; j += 32) val[j] = __fdiv_rn(val[j], kept);
         }
-        __syncthreads();
+        __syncwarp();
     }
     if (p.probs_out) {
-        for (int i = tid; i < p.V; i += kSelThreads) x[i] = 0.0f;
-        __syncthreads();
-        for (int j = tid; j < n; j += kSelThreads) x[idx[j]] = val[j];
-        __syncthreads();
-        for (int i = tid; i < p.V; i += kSelThreads) p.probs_out[(size_t)b * p.V + i] = x[i];
+        for (int i = lane; i < p.V; i += 32) x[i] = 0.0f;
+        __syncwarp();
+        for (int j = lane; j < n; j += 32) x[idx[j]] = val[j];
+        __syncwarp();
+        for (int i = lane; i < p.V; i += 32) p.probs_out[(size_t)b * p.V + i] = x[i];
     }
     // draw (text_gen.cpp:199-208): first index with u <= running sum, else the last id. Index 0 already satisfies
     // u <= 0 + x[0] when u is not positive, candidate or not.
-    if (tid == 0) {
+    int pick = p.V - 1;
+    if (lane == 0) {
         const float u = p.uniforms[(size_t)b * p.u_stride + (p.loop_mode ? p.gen[b] : 0)];
-        int pick = p.V - 1;
         if (u <= 0.0f) {
             pick = 0;
         } else {
-            float sum = 0.0f;
+            float run = 0.0f;
             for (int j = 0; j < n; j++) {
-                sum = __fadd_rn(sum, val[j]);
-                if (u <= sum) {
+                run = __fadd_rn(run, val[j]);
+                if (u <= run) {
                     pick = idx[j];
                     break;
                 }
             }
         }
-        s_pick = pick;
     }
-    __syncthreads();
-    return s_pick;
+    return __shfl_sync(0xffffffffu, pick, 0);
 }
+
+// Diagnostics build: clock cycles sequence 0's CTA spends per part of the sampled selection (gradb_diag_select_clocks).
+#if GRADB_DIAG
+__device__ unsigned long long g_sel_clock[16];
+#define SEL_CLK(x) const long long x = clock64()
+#define SEL_ADD(i, v) do { if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_sel_clock[i], (unsigned long long)(v)); } while (0)
+#else
+#define SEL_CLK(x)
+#define SEL_ADD(i, v)
+#endif
 
 // Sampled selection, one 512-thread CTA per sequence. Shared memory holds ONE vocabulary-sized array (so two
 // sequences share an SM): the values in index order, except while the nucleus cutoff is being found, when it holds
@@ -1059,6 +1102,7 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     pdl_trigger();
     pdl_wait();
     if (p.loop_mode && p.done[b]) return;
+    SEL_CLK(t0);
 
     float* x = smem;                                                        // [V] (+ slack the scans may read)
     uint32_t* work = reinterpret_cast<uint32_t*>(smem + p.n_pad);          // 4096 words: histograms, scan scratch
@@ -1067,6 +1111,9 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     for (int i = tid; i < V; i += kSelThreads) x[i] = lg[i];
     for (int i = V + tid; i < p.n_pad; i += kSelThreads) x[i] = 0.0f;
     __syncthreads();
+    SEL_CLK(t1);
+    SEL_ADD(0, 1);
+    SEL_ADD(1, t1 - t0);  // logits -> shared memory
 
     // ---- repetition penalty: last min(50, n) ids, once per occurrence, in order (text_gen.cpp:20-31)
     int* hist = p.hist + (size_t)b * p.hist_stride;
@@ -1099,35 +1146,37 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     }
     __syncthreads();
 
+    SEL_CLK(t2);
+    SEL_ADD(2, t2 - t1);  // penalty
     const float inv_t = __fdiv_rn(1.0f, p.temperature);  // text_gen.cpp:136
     const bool use_k = p.top_k > 0 && p.top_k < V;
     const bool use_p = p.top_p < 1.0f;
     for (int i = tid; i < V; i += kSelThreads) x[i] = __fmul_rn(x[i], inv_t);
     __syncthreads();
     if (use_k) {  // text_gen.cpp:138-154: below the k-th largest value -> -1e10, ties kept
+        SEL_CLK(t3);
+        SEL_ADD(3, t3 - t2);  // temperature
         const float kth = select_kth_desc(x, V, p.top_k, reinterpret_cast<int*>(work));
         __syncthreads();  // the histogram area is free again
+        SEL_CLK(t4);
+        SEL_ADD(4, t4 - t3);  // k-th value
         // Few survivors (the usual top-k): everything after the filter only ever sees them. The filtered entries
         // become exp(-1e10 - max) = +0 exactly, and adding +0 never changes a running sum, so the sequential sums
-        // of the reference are those of the survivors in index order; one thread forms them natively.
+        // of the reference are those of the survivors in index order; one warp does the rest of the stage.
         {
-            __shared__ int s_cnt[kSelWarps + 1];
-            const int per = (V + kSelThreads - 1) / kSelThreads;
-            const int lo = min(V, tid * per), hi = min(V, lo + per);
+            __shared__ int s_cnt[kSelWarps];
+            // each warp compacts a contiguous range, 32 consecutive values per step (ballot + popcount keep the order)
+            const int per_warp = ((V + kSelWarps - 1) / kSelWarps + 31) / 32 * 32;
+            const int w_lo = min(V, w * per_warp), w_hi = min(V, w_lo + per_warp);
             int cnt = 0;
             bool odd = false;  // a NaN among the values: leave it to the general path
-            for (int i = lo; i < hi; i++) {
-                const float v = x[i];
-                cnt += !(v < kth);
+            for (int base = w_lo; base < w_hi; base += 32) {
+                const int i = base + lane;
+                const float v = i < w_hi ? x[i] : -INFINITY;
                 odd |= v != v;
+                cnt += __popc(__ballot_sync(0xffffffffu, i < w_hi && !(v < kth)));
             }
-            int incl = cnt;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int up = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += up;
-            }
-            if (lane == 31) s_cnt[w] = incl;
+            if (lane == 0) s_cnt[w] = cnt;
             const bool any_odd = __syncthreads_or(odd);
             int before = 0, total = 0;
             for (int i = 0; i < kSelWarps; i++) {
@@ -1137,19 +1186,30 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
             if (!any_odd && total <= kSmallMax && kth > -1e10f) {
                 int* s_idx = reinterpret_cast<int*>(work);
                 float* s_val = reinterpret_cast<float*>(work + kSmallMax);
-                int at = before + incl - cnt;
-                for (int i = lo; i < hi; i++) {
-                    const float v = x[i];
-                    if (!(v < kth)) {
-                        s_idx[at] = i;
-                        s_val[at] = v;
-                        at++;
+                int at = before;
+                for (int base = w_lo; base < w_hi; base += 32) {
+                    const int i = base + lane;
+                    const float v = i < w_hi ? x[i] : -INFINITY;
+                    const bool keep = i < w_hi && !(v < kth);
+                    const uint32_t mask = __ballot_sync(0xffffffffu, keep);
+                    if (keep) {
+                        const int pos = at + __popc(mask & ((1u << lane) - 1u));
+                        s_idx[pos] = i;
+                        s_val[pos] = v;
                     }
+                    at += __popc(mask);
                 }
                 __syncthreads();
+                SEL_CLK(t5);
+                SEL_ADD(5, t5 - t4);  // count and compact the survivors
+                if (w != 0) return;   // one warp finishes the stage: no block-wide barrier from here on
                 const int pick = select_among_few(p, b, total, s_idx, s_val, reinterpret_cast<float*>(work + 2 * kSmallMax),
-                                                  red_v, s_exp_tab, x);
-                if (tid == 0) record_pick(p, b, hist, hlen, pick);
+                                                  s_exp_tab, x);
+                SEL_CLK(t6);
+                SEL_ADD(6, t6 - t5);  // the stage on the survivors
+                if (lane == 0) record_pick(p, b, hist, hlen, pick);
+                SEL_CLK(t7);
+                SEL_ADD(7, t7 - t6);  // bookkeeping
                 return;
             }
             __syncthreads();  // (s_cnt is read by all before anyone moves on)
@@ -1397,6 +1457,17 @@ void configure_select(int V) {
     GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                     (int)cudaSharedmemCarveoutMaxShared));
 }
+
+#if GRADB_DIAG
+void select_clocks_read(unsigned long long* out16, bool reset) {
+    GRADB_CUDA(cudaDeviceSynchronize());
+    GRADB_CUDA(cudaMemcpyFromSymbol(out16, g_sel_clock, sizeof(unsigned long long) * 16));
+    if (reset) {
+        unsigned long long zero[16] = {};
+        GRADB_CUDA(cudaMemcpyToSymbol(g_sel_clock, zero, sizeof(zero)));
+    }
+}
+#endif
 
 void launch_select(const SelectParams& p_in, int B, cudaStream_t st) {
     SelectParams p = p_in;

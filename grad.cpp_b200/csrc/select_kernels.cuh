@@ -44,6 +44,9 @@ size_t select_scratch_floats(int V);
 // Sampled selection keeps one sequence's values and their sorted copy in one CTA's shared memory.
 bool select_sampled_fits(int V);
 void configure_select(int V);
+#if GRADB_DIAG
+void select_clocks_read(unsigned long long* out16, bool reset);  // diagnostics build: per-part clocks of the sampled kernel
+#endif
 void launch_select(const SelectParams& p, int B, cudaStream_t st);
 
 }  // namespace gradb

@@ -207,5 +207,5 @@ def test_product_library_has_no_diagnostic_entry_points(pkg):
     import ctypes
     L = ctypes.CDLL(str(ROOT / "grad.cpp_b200" / "libgradb.so"))
     for name in ("gradb_session_stage_trace", "gradb_diag_attention_wait", "gradb_diag_poke_history",
-                 "gradb_diag_wide_clocks", "gradb_diag_attn_clocks"):
+                 "gradb_diag_wide_clocks", "gradb_diag_attn_clocks", "gradb_diag_select_clocks"):
         assert not hasattr(L, name), name
