@@ -1091,6 +1091,9 @@ __device__ unsigned long long g_sel_clock[16];
 // Sampled selection, one 512-thread CTA per sequence. Shared memory holds ONE vocabulary-sized array (so two
 // sequences share an SM): the values in index order, except while the nucleus cutoff is being found, when it holds
 // the sorted probabilities and the index-order copy waits in a global scratch row (L2 resident).
+// TOPK: compiled with or without the top-k filter and its few-candidates path, so that the registers those need do
+// not weigh on the plain nucleus path (the benchmark's) and the other way round.
+template <bool TOPK>
 __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectParams p) {
     extern __shared__ __align__(16) float smem[];
     __shared__ uint32_t scan_sh[2 * kSelWarps + 4];
@@ -1149,11 +1152,11 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     SEL_CLK(t2);
     SEL_ADD(2, t2 - t1);  // penalty
     const float inv_t = __fdiv_rn(1.0f, p.temperature);  // text_gen.cpp:136
-    const bool use_k = p.top_k > 0 && p.top_k < V;
+    const bool use_k = TOPK && p.top_k > 0 && p.top_k < V;
     const bool use_p = p.top_p < 1.0f;
     for (int i = tid; i < V; i += kSelThreads) x[i] = __fmul_rn(x[i], inv_t);
     __syncthreads();
-    if (use_k) {  // text_gen.cpp:138-154: below the k-th largest value -> -1e10, ties kept
+    if (TOPK && use_k) {  // text_gen.cpp:138-154: below the k-th largest value -> -1e10, ties kept
         SEL_CLK(t3);
         SEL_ADD(3, t3 - t2);  // temperature
         const float kth = select_kth_desc(x, V, p.top_k, reinterpret_cast<int*>(work));
@@ -1451,10 +1454,13 @@ bool select_sampled_fits(int V) { return select_smem_bytes(V, nullptr) <= 200 * 
 void configure_select(int V) {
     const size_t bytes = select_smem_bytes(V, nullptr);
     if (bytes > 48 * 1024 && bytes <= 200 * 1024) {
-        GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        GRADB_CUDA(cudaFuncSetAttribute(select_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        GRADB_CUDA(cudaFuncSetAttribute(select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
     // two sequences per SM need the large shared-memory configuration
-    GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+    GRADB_CUDA(cudaFuncSetAttribute(select_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    (int)cudaSharedmemCarveoutMaxShared));
+    GRADB_CUDA(cudaFuncSetAttribute(select_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                     (int)cudaSharedmemCarveoutMaxShared));
 }
 
@@ -1487,9 +1493,11 @@ void launch_select(const SelectParams& p_in, int B, cudaStream_t st) {
     p.scratch_stride = select_scratch_floats(p.V);
     p.n_sort = (int)(p.scratch_stride - (size_t)p.V);
     if (bytes > 48 * 1024 && !g_capturing) {
-        GRADB_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        GRADB_CUDA(cudaFuncSetAttribute(select_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        GRADB_CUDA(cudaFuncSetAttribute(select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     }
-    launch_kernel(select_kernel, dim3(B), dim3(kSelThreads), bytes, st, p);
+    if (p.top_k > 0 && p.top_k < p.V) launch_kernel(select_kernel<true>, dim3(B), dim3(kSelThreads), bytes, st, p);
+    else launch_kernel(select_kernel<false>, dim3(B), dim3(kSelThreads), bytes, st, p);
     count_launch();
     GRADB_CUDA(cudaGetLastError());
 }
