@@ -784,9 +784,12 @@ Session* create_session(const DeviceModel* m, int max_batch, int max_len, void* 
         }
         const char* ng = std::getenv("GRADB_NO_GRAPH");
         s->use_graph = !(ng && ng[0] == '1');
-        // Context splits only when sequences x heads alone cannot occupy the SMs about twice over
-        // (measured: at 32 sequences x 12 heads and context ~1100, one split per unit beats seven).
-        const int want = (2 * m->sm_count + s->B * s->H - 1) / (s->B * s->H);
+        // Context splits: as many as still give every warp of the persistent attention kernel (seven per SM) at most
+        // one (sequence, head, split) unit. Each warp keeps one 16 KB tile in flight, so the warps that have a unit
+        // set the bandwidth; a split count that spills into a second round of units loses more than it gains
+        // (32 sequences x 12 heads at contexts 1025..1280, attention per launch: 1 split 56 us, 2 splits 46, 3 splits
+        // 59, 4 splits 50, 6 splits 57).
+        const int want = (kAttnPipeWarps * m->sm_count) / (s->B * s->H);
         s->attn_splits = std::max(1, std::min({want, 16, (s->T + 31) / 32}));
 #if GRADB_DIAG
         if (const char* sp = std::getenv("GRADB_ATTN_SPLITS")) {

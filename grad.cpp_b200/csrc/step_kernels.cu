@@ -561,7 +561,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode64_kernel(const At
 // stream of a warp continues across unit boundaries instead of restarting per (sequence, head).
 // Scores: lane r owns row r of the tile and walks its 64 columns rotated by r, which keeps the
 // 128-bit shared-memory reads conflict free and needs no shuffles. P@V: lane owns two columns.
-constexpr int kPipeWarps = 7;   // independent warps per CTA: as many 2-stage rings as shared memory holds
+constexpr int kPipeWarps = kAttnPipeWarps;  // independent warps per CTA: as many 2-stage rings as shared memory holds
 constexpr int kPipeStages = 2;  // per warp: one tile being consumed, one in flight
 constexpr int kPipeTileRows = 32;
 constexpr int kPipeStageFloats = 2 * kPipeTileRows * 64;  // K tile then V tile

@@ -78,6 +78,9 @@ void launch_lse_combine(const float* part, int tiles, const float* tgt_logit, co
 void launch_advance(const int* tok, int* pos, int* hist, int* hist_len, int hist_stride, int B, cudaStream_t st);
 void launch_gemv(const GemvParams& p, int pro, int epi, bool bf16, int sm_count, cudaStream_t st);
 void launch_logits(const LogitsParams& p, bool bf16, cudaStream_t st);
+// Independent warps per CTA of the persistent cached-attention kernel (one CTA per SM); callers size their context
+// splits by it.
+constexpr int kAttnPipeWarps = 7;
 void launch_attention(const AttnParams& p, int B, int splits, cudaStream_t st);
 void attention_configure();
 // Same kernel with its scratch in a fixed device array (no allocation); see step_kernels.cu.
