@@ -974,6 +974,16 @@ __device__ __forceinline__ void record_pick(const SelectParams& p, int b, int* h
     }
 }
 
+// Diagnostics build: clock cycles sequence 0's CTA spends per part of the sampled selection (gradb_diag_select_clocks).
+#if GRADB_DIAG
+__device__ unsigned long long g_sel_clock[16];
+#define SEL_CLK(x) const long long x = clock64()
+#define SEL_ADD(i, v) do { if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_sel_clock[i], (unsigned long long)(v)); } while (0)
+#else
+#define SEL_CLK(x)
+#define SEL_ADD(i, v)
+#endif
+
 // The rest of sample_from_logits (text_gen.cpp:156-208) when the top-k filter left n <= kSmallMax candidates: their
 // ids (ascending) in idx, their tempered logits in val; srt: room for the next power of two of floats. Softmax over
 // the candidates (every other entry is an exact zero), nucleus cutoff on the sorted values, renormalisation, draw --
@@ -1000,9 +1010,27 @@ __device__ void sort_desc_warp(float* a, int n_pad) {  // bitonic, descending, n
         }
     }
 }
+// First j < n whose running sum v[0] + ... + v[j] (added one by one, in order) is >= thresh; n when none is. The
+// values are fetched eight at a time ahead of the dependent additions; a +0 past the end leaves the sum as it is.
+__device__ __forceinline__ int first_reaching(const float* v, int n, float thresh) {
+    float run = 0.0f;
+    int found = n;
+    for (int j0 = 0; j0 < n && found == n; j0 += 8) {
+        float r[8];
+#pragma unroll
+        for (int t = 0; t < 8; t++) r[t] = j0 + t < n ? v[j0 + t] : 0.0f;
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+            run = __fadd_rn(run, r[t]);
+            if (found == n && j0 + t < n && run >= thresh) found = j0 + t;
+        }
+    }
+    return found;
+}
 __device__ int select_among_few(const SelectParams& p, int b, int n, const int* idx, float* val, float* srt,
                                 const uint64_t* exp_tab, float* x) {
     const int lane = threadIdx.x & 31;
+    SEL_CLK(f0);
     // max (tensor.cpp:434-440; the filtered entries, -1e10, lie below every candidate)
     float m = -INFINITY;
     for (int j = lane; j < n; j += 32) m = fmaxf(m, val[j]);
@@ -1016,24 +1044,36 @@ __device__ int select_among_few(const SelectParams& p, int b, int n, const int* 
     const float inv_sum = __fdiv_rn(1.0f, __shfl_sync(0xffffffffu, sum, 0));
     for (int j = lane; j < n; j += 32) val[j] = __fmul_rn(val[j], inv_sum);
     __syncwarp();
+    SEL_CLK(f1);
+    SEL_ADD(8, f1 - f0);  // few: max, exp, sum, normalise
     if (p.top_p < 1.0f) {  // text_gen.cpp:158-193
-        int n_pad = 2;
-        while (n_pad < n) n_pad <<= 1;
-        for (int j = lane; j < n_pad; j += 32) srt[j] = j < n ? val[j] : -INFINITY;
-        __syncwarp();
-        sort_desc_warp(srt, n_pad);
+        if (n <= 64) {
+            // rank of each value among the candidates (equal values ordered by position): its place in the sorted row
+            const int j0 = lane, j1 = lane + 32;
+            const float v0 = j0 < n ? val[j0] : 0.0f, v1 = j1 < n ? val[j1] : 0.0f;
+            int r0 = 0, r1 = 0;
+            for (int t = 0; t < n; t++) {
+                const float o = val[t];
+                r0 += (o > v0) || (o == v0 && t < j0);
+                r1 += (o > v1) || (o == v1 && t < j1);
+            }
+            if (j0 < n) srt[r0] = v0;
+            if (j1 < n) srt[r1] = v1;
+            __syncwarp();
+        } else {
+            int n_pad = 128;
+            while (n_pad < n) n_pad <<= 1;
+            for (int j = lane; j < n_pad; j += 32) srt[j] = j < n ? val[j] : -INFINITY;
+            __syncwarp();
+            sort_desc_warp(srt, n_pad);
+        }
+        SEL_CLK(f2);
+        SEL_ADD(9, f2 - f1);  // few: sort
         float cutoff_prob = 0.0f;
         if (lane == 0) {
-            float run = 0.0f;
-            int cutoff = 0;  // stays 0 when the running sum never reaches p (the zeros after the candidates add nothing)
-            for (int j = 0; j < n; j++) {
-                run = __fadd_rn(run, srt[j]);
-                if (run >= p.top_p) {
-                    cutoff = j;
-                    break;
-                }
-            }
-            cutoff_prob = srt[cutoff];
+            // stays 0 when the running sum never reaches p (the zeros after the candidates add nothing)
+            const int reached = first_reaching(srt, n, p.top_p);
+            cutoff_prob = srt[reached < n ? reached : 0];
         }
         cutoff_prob = __shfl_sync(0xffffffffu, cutoff_prob, 0);
         for (int j = lane; j < n; j += 32) {
@@ -1050,6 +1090,8 @@ __device__ int select_among_few(const SelectParams& p, int b, int n, const int* 
         }
         __syncwarp();
     }
+    SEL_CLK(f3);
+    SEL_ADD(10, f3 - f0);  // few: everything up to here
     if (p.probs_out) {
         for (int i = lane; i < p.V; i += 32) x[i] = 0.0f;
         __syncwarp();
@@ -1065,28 +1107,14 @@ __device__ int select_among_few(const SelectParams& p, int b, int n, const int* 
         if (u <= 0.0f) {
             pick = 0;
         } else {
-            float run = 0.0f;
-            for (int j = 0; j < n; j++) {
-                run = __fadd_rn(run, val[j]);
-                if (u <= run) {
-                    pick = idx[j];
-                    break;
-                }
-            }
+            const int reached = first_reaching(val, n, u);
+            if (reached < n) pick = idx[reached];
         }
     }
+    SEL_CLK(f4);
+    SEL_ADD(11, f4 - f3);  // few: draw
     return __shfl_sync(0xffffffffu, pick, 0);
 }
-
-// Diagnostics build: clock cycles sequence 0's CTA spends per part of the sampled selection (gradb_diag_select_clocks).
-#if GRADB_DIAG
-__device__ unsigned long long g_sel_clock[16];
-#define SEL_CLK(x) const long long x = clock64()
-#define SEL_ADD(i, v) do { if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_sel_clock[i], (unsigned long long)(v)); } while (0)
-#else
-#define SEL_CLK(x)
-#define SEL_ADD(i, v)
-#endif
 
 // Sampled selection, one 512-thread CTA per sequence. Shared memory holds ONE vocabulary-sized array (so two
 // sequences share an SM): the values in index order, except while the nucleus cutoff is being found, when it holds
@@ -1111,6 +1139,13 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     uint32_t* work = reinterpret_cast<uint32_t*>(smem + p.n_pad);          // 4096 words: histograms, scan scratch
     float* g = p.scratch + (size_t)b * p.scratch_stride;                   // [V] index-order copy, then [n_sort] sort area
     const float* lg = p.logits + (size_t)b * V;
+    // the penalty window's ids are fetched alongside the logits (two dependent reads of global memory otherwise wait
+    // behind the barrier)
+    __shared__ int s_pen_id[kPenaltyWindow];
+    int* hist = p.hist + (size_t)b * p.hist_stride;
+    const int hlen = p.hist_len[b];
+    const int window = min(kPenaltyWindow, hlen);
+    if (p.penalty != 1.0f && tid < window) s_pen_id[tid] = hist[hlen - window + tid];
     for (int i = tid; i < V; i += kSelThreads) x[i] = lg[i];
     for (int i = V + tid; i < p.n_pad; i += kSelThreads) x[i] = 0.0f;
     __syncthreads();
@@ -1119,16 +1154,10 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     SEL_ADD(1, t1 - t0);  // logits -> shared memory
 
     // ---- repetition penalty: last min(50, n) ids, once per occurrence, in order (text_gen.cpp:20-31)
-    int* hist = p.hist + (size_t)b * p.hist_stride;
-    const int hlen = p.hist_len[b];
     if (p.penalty != 1.0f) {
         // The reference walks the window in order and penalises an id once per occurrence. Different ids do not
         // interact and the repeated penalties of one id are applied in sequence by one thread (the window position
         // of its first occurrence), so the positions work side by side with the reference's result.
-        __shared__ int s_pen_id[kPenaltyWindow];
-        const int window = min(kPenaltyWindow, hlen);
-        if (tid < window) s_pen_id[tid] = hist[hlen - window + tid];
-        __syncthreads();
         if (tid < window) {
             const int id = s_pen_id[tid];
             if (GRADB_INDEX_OK(id >= 0 && id < V, p.status, 901)) {
@@ -1154,11 +1183,101 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     const float inv_t = __fdiv_rn(1.0f, p.temperature);  // text_gen.cpp:136
     const bool use_k = TOPK && p.top_k > 0 && p.top_k < V;
     const bool use_p = p.top_p < 1.0f;
-    for (int i = tid; i < V; i += kSelThreads) x[i] = __fmul_rn(x[i], inv_t);
+    float own_max = -INFINITY;  // of this thread's values; NaNs aside
+    bool own_odd = false;       // a NaN among them
+    for (int i = tid; i < V; i += kSelThreads) {
+        const float v = __fmul_rn(x[i], inv_t);
+        x[i] = v;
+        if (TOPK) {
+            own_max = fmaxf(own_max, v);
+            own_odd |= v != v;
+        }
+    }
     __syncthreads();
     if (TOPK && use_k) {  // text_gen.cpp:138-154: below the k-th largest value -> -1e10, ties kept
         SEL_CLK(t3);
         SEL_ADD(3, t3 - t2);  // temperature
+        // Small k (the usual one): a threshold with at least k values at or above it comes from the threads' own maxima
+        // -- the j-th largest of each warp's 32, j = ceil(k / warps), and the smallest of those over the warps, so at
+        // least j * warps >= k maxima reach it. The few values that reach it are listed; the k-th largest and the
+        // survivors in index order are read off the list by counting. Anything unusual (a NaN, too many listed) leaves
+        // the row untouched for the search below.
+        constexpr int kListK = 256, kListMax = kSelThreads;
+        if (p.top_k <= kListK) {
+            __shared__ float s_warp_thr[kSelWarps];
+            __shared__ float s_kth;
+            __shared__ int s_listed;
+            const int j = (p.top_k + kSelWarps - 1) / kSelWarps;
+            float m = own_max, thr = -INFINITY;
+            for (int r = 0; r < j; r++) {
+                thr = warp_max(m);
+                const uint32_t holders = __ballot_sync(0xffffffffu, m == thr);
+                if (lane == __ffs(holders) - 1) m = -INFINITY;  // one holder of the maximum steps aside
+            }
+            if (lane == 0) s_warp_thr[w] = thr;
+            if (tid == 0) s_listed = 0;
+            const bool any_odd = __syncthreads_or(own_odd);
+            thr = s_warp_thr[0];
+            for (int i = 1; i < kSelWarps; i++) thr = fminf(thr, s_warp_thr[i]);
+            if (!any_odd && thr > -1e10f) {
+                float* l_val = reinterpret_cast<float*>(work);
+                int* l_idx = reinterpret_cast<int*>(work + kListMax);
+                int* s_idx = reinterpret_cast<int*>(work + 2 * kListMax);
+                float* s_val = reinterpret_cast<float*>(work + 2 * kListMax + kSmallMax);
+                float* s_srt = reinterpret_cast<float*>(work + 2 * kListMax + 2 * kSmallMax);
+                for (int i = tid; i < V; i += kSelThreads) {
+                    const float v = x[i];
+                    if (v >= thr) {
+                        const int at = atomicAdd(&s_listed, 1);
+                        if (at < kListMax) {
+                            l_val[at] = v;
+                            l_idx[at] = i;
+                        }
+                    }
+                }
+                __syncthreads();
+                const int listed = s_listed;
+                if (listed <= kListMax && listed >= p.top_k) {
+                    float v = 0.0f;
+                    int id = 0;
+                    if (tid < listed) {
+                        v = l_val[tid];
+                        id = l_idx[tid];
+                        int greater = 0, equal = 0;
+                        for (int t = 0; t < listed; t++) {
+                            const float o = l_val[t];
+                            greater += o > v;
+                            equal += o == v;
+                        }
+                        if (greater < p.top_k && p.top_k <= greater + equal) s_kth = v;  // (equal values write the same)
+                    }
+                    __syncthreads();
+                    const float kth = s_kth;
+                    const bool keep = tid < listed && !(v < kth);
+                    const int total = __syncthreads_count(keep);
+                    if (total <= kSmallMax && kth > -1e10f) {
+                        if (keep) {
+                            int at = 0;  // survivors with a smaller id
+                            for (int t = 0; t < listed; t++) at += !(l_val[t] < kth) && l_idx[t] < id;
+                            s_idx[at] = id;
+                            s_val[at] = v;
+                        }
+                        __syncthreads();
+                        SEL_CLK(t5);
+                        SEL_ADD(4, t5 - t3);  // threshold, list, k-th value, survivors in index order
+                        if (w != 0) return;   // one warp finishes the stage: no block-wide barrier from here on
+                        const int pick = select_among_few(p, b, total, s_idx, s_val, s_srt, s_exp_tab, x);
+                        SEL_CLK(t6);
+                        SEL_ADD(6, t6 - t5);  // the stage on the survivors
+                        if (lane == 0) record_pick(p, b, hist, hlen, pick);
+                        SEL_CLK(t7);
+                        SEL_ADD(7, t7 - t6);  // bookkeeping
+                        return;
+                    }
+                }
+            }
+            __syncthreads();  // the list area is free again
+        }
         const float kth = select_kth_desc(x, V, p.top_k, reinterpret_cast<int*>(work));
         __syncthreads();  // the histogram area is free again
         SEL_CLK(t4);

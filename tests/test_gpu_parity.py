@@ -177,6 +177,19 @@ def test_selection_stage_random_sweep_against_oracle(G, models, port):
         want, want_probs = port.sample(lg, t, k, p, u, want_probs=True)
         assert int(got[0]) == want, (i, t, k, p, u)
         assert np.array_equal(probs[0].view(np.uint32), want_probs.view(np.uint32)), i
+    # small k around the sizes where the k-th value is read off a short list of values above a threshold (k up to
+    # 256, one to sixteen maxima per warp), with and without equal values at the k-th place
+    for i, k in enumerate([2, 16, 17, 100, 256, 257, 40, 40, 3, 255]):
+        lg = rng.standard_normal(16000, dtype=np.float32) * np.float32([2.0, 0.55, 8.0][i % 3])
+        if i % 2 == 1:
+            lg = np.round(lg * 64) / 64
+        t = np.float32([0.8, 1.3][i % 2])
+        p = np.float32([0.9, 1.0, 0.3][i % 3])
+        u = np.float32(rng.random())
+        got, probs = s.select(G.Sampling(0, t, 1.0, k, p), uniforms=[u], logits=lg[None, :], want_probs=True)
+        want, want_probs = port.sample(lg, t, k, p, u, want_probs=True)
+        assert int(got[0]) == want, (i, k, t, p, u)
+        assert np.array_equal(probs[0].view(np.uint32), want_probs.view(np.uint32)), (i, k)
     # the ends of the draw: u = 0 is satisfied at index 0 whatever its probability, a draw beyond the total mass
     # falls through to the last id -- with few candidates after top-k (their own code path) and with all of them
     lg = rng.standard_normal(16000, dtype=np.float32) * np.float32(2.0)
