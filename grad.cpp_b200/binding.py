@@ -211,7 +211,10 @@ class GPTModel:
             self._h = None
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown: the module's globals may already be gone
+            pass
 
 
 class BatchSession:
@@ -231,7 +234,10 @@ class BatchSession:
             self._h = None
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown: the module's globals may already be gone
+            pass
 
     def reset(self):
         _check(lib().gradb_session_reset(self._h))
