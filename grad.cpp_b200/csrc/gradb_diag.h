@@ -47,7 +47,9 @@ gradb_status gradb_diag_attn_clocks(uint64_t* out16, int reset);
 
 /* Clock cycles sequence 0's CTA of the sampled selection kernel has spent per part since the last reset, for calls
  * that take the few-candidates path after top-k: [0] calls, [1] logits -> shared memory, [2] penalty, [3] temperature,
- * [4] k-th value, [5] count and compact, [6] softmax / nucleus / draw on the survivors, [7] bookkeeping. */
+ * [4] k-th value, [5] count and compact, [6] softmax / nucleus / draw on the survivors, [7] bookkeeping; and of those that
+ * run the stage on the full row: [8] maximum and exponentials, [9] softmax denominator, [10] probabilities, [11] sort,
+ * [12] nucleus cutoff, [13] mask + kept mass + renormalisation, [14] all of [8]-[13] and the draw. */
 gradb_status gradb_diag_select_clocks(uint64_t* out16, int reset);
 
 #ifdef __cplusplus

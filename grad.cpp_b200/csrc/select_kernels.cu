@@ -660,11 +660,26 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
     }
 }
 
+// Diagnostics build: clock cycles sequence 0's CTA spends per part of the sampled selection (gradb_diag_select_clocks).
+#if GRADB_DIAG
+__device__ unsigned long long g_sel_clock[16];
+#define SEL_CLK(x) const long long x = clock64()
+#define SEL_ADD(i, v) do { if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_sel_clock[i], (unsigned long long)(v)); } while (0)
+#define SEL_ANY(i, v) do { if (threadIdx.x == 0) atomicAdd(&g_sel_clock[i], (unsigned long long)(v)); } while (0)
+#define SEL_MAX(i, v) do { if (threadIdx.x == 0) atomicMax(&g_sel_clock[i], (unsigned long long)(v)); } while (0)
+#else
+#define SEL_CLK(x)
+#define SEL_ADD(i, v)
+#define SEL_ANY(i, v)
+#define SEL_MAX(i, v)
+#endif
+
 // The exact scan: the one-sweep fast path, or the pass-per-binade scan when it declines.
 template <typename Hit>
 __device__ ScanResult exact_scan(int n, const float* arr, Hit hit, bool has_predicate, uint32_t* sh, uint32_t* work) {
     ScanResult r;
     if (seq_scan_fast(n, arr, hit, has_predicate, work, r)) return r;
+    SEL_ANY(5, 1);  // sweeps abandoned, over all sequences
     __syncthreads();
     return seq_scan(n, [arr](int i) { return arr[i]; }, hit, sh);
 }
@@ -730,37 +745,122 @@ __device__ void bucket_starts(int* hist) {
     __syncthreads();
 }
 
+// Descending bitonic network on N (a power of two) bit patterns held in registers; every index is a compile-time
+// constant once unrolled.
+template <int N>
+__device__ __forceinline__ void sort_regs_desc(uint32_t (&v)[N]) {
+#pragma unroll
+    for (int k = 2; k <= N; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+#pragma unroll
+            for (int i = 0; i < N; i++) {
+                const int l = i ^ j;
+                if (l > i) {
+                    const uint32_t hi = max(v[i], v[l]), lo = min(v[i], v[l]);
+                    const bool desc = (i & k) == 0;
+                    v[i] = desc ? hi : lo;
+                    v[l] = desc ? lo : hi;
+                }
+            }
+        }
+    }
+}
+// A bucket of 2..N positive floats x[lo..lo+n): fetched side by side, sorted in registers, written back.
+template <int N>
+__device__ __forceinline__ void sort_bucket_regs(float* x, int lo, int n) {
+    uint32_t v[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) v[i] = i < n ? __float_as_uint(x[lo + i]) : 0u;  // (0 sorts behind every positive value)
+    sort_regs_desc<N>(v);
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        if (i < n) x[lo + i] = __uint_as_float(v[i]);
+    }
+}
+
+// Exclusive prefix sum over 2 * kBuckets 16-bit counts packed two to a word (sums below 65536), in place.
+__device__ void bucket_starts16(uint32_t* hist) {
+    __shared__ int wsum16[kSelWarps];
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    constexpr int kPer = kBuckets / kSelThreads;  // words per thread
+    uint32_t c[kPer];
+    int tot = 0;
+#pragma unroll
+    for (int i = 0; i < kPer; i++) {
+        c[i] = hist[tid * kPer + i];
+        tot += (int)(c[i] & 0xffffu) + (int)(c[i] >> 16);
+    }
+    int inc = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+    }
+    if (lane == 31) wsum16[w] = inc;
+    __syncthreads();
+    int wv = lane < kSelWarps ? wsum16[lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, wv, o);
+        if (lane >= o) wv += v;
+    }
+    int base = __shfl_sync(0xffffffffu, wv, (w + 31) & 31);
+    if (w == 0) base = 0;
+    base += inc - tot;
+#pragma unroll
+    for (int i = 0; i < kPer; i++) {
+        const int lo = base, hi = base + (int)(c[i] & 0xffffu);
+        base = hi + (int)(c[i] >> 16);
+        hist[tid * kPer + i] = (uint32_t)lo | ((uint32_t)hi << 16);
+    }
+    __syncthreads();
+}
+
 // Descending sort of n probabilities (non-negative, finite). On entry x[0..n) (shared) and g[0..n) (global) hold the
 // same values in index order; on return x holds them sorted, g is untouched. Positive floats order like their bit
-// patterns, so a bucket is a range of bit patterns (an equal share of each binade: the values are exponentials of
-// roughly bell-shaped logits); zeros go to the tail unsorted; a histogram + prefix sum places the buckets, the
-// scatter reads the index-order copy in g while it overwrites x, and each small bucket is finished by insertion.
-// Buckets of many equal values (coarse logits) need no work. Returns false, with x unspecified, when the values are
-// not finite or too clustered; the caller then sorts g's copy bitonically.
-__device__ bool sort_probs_desc(float* x, const float* g, int n, int* hist) {
+// patterns, so a bucket is a range of bit patterns. The buckets follow the values' own distribution: a coarse
+// histogram (kCoarse equal ranges of bit patterns) gives every range a power-of-two share of the 2 * kBuckets fine
+// buckets in proportion to its count, so a fine bucket holds a few values wherever they crowd (exponentials of
+// bell-shaped logits crowd in the middle). Zeros go to the tail unsorted; a histogram + prefix sum (16-bit counts,
+// two to a word) places the buckets, the scatter reads the index-order copy in g while it overwrites x, and each
+// bucket is finished by insertion. Buckets of many equal values (coarse logits) need no work. Returns false, with x
+// unspecified, when the values are not finite or too clustered; the caller then sorts g's copy bitonically.
+constexpr int kCoarse = 256;
+constexpr int kFineBuckets = 2 * kBuckets;
+constexpr int kFineTarget = 6144;  // fine buckets handed out in proportion (each range gets at least one on top)
+struct ProbStats {  // of one thread's share of the probabilities: bit patterns of the non-zero ones
+    uint32_t kmin = 0xffffffffu, kmax = 0u;
+    int nnz = 0, bad = 0;  // bad: a NaN, an infinity or a negative value
+    __device__ __forceinline__ void add(float pr) {
+        const uint32_t k = __float_as_uint(pr);
+        if (k >= 0x7f800000u) bad = 1;
+        if (k != 0u) {
+            kmin = min(kmin, k);
+            kmax = max(kmax, k);
+            nnz++;
+        }
+    }
+};
+__device__ bool sort_probs_desc(float* x, const float* g, int n, int* hist_words, ProbStats own) {
     __shared__ uint32_t s_kmin, s_kmax;
     __shared__ int s_nnz, s_bad;
+    __shared__ int s_coarse[kCoarse];  // counts, then (first fine bucket << 5) | shift inside the range
+    uint32_t* hist = reinterpret_cast<uint32_t*>(hist_words);
     const int tid = threadIdx.x;
+    if (n >= 65536) return false;  // (16-bit bucket positions; a row in shared memory is shorter anyway)
     if (tid == 0) {
         s_kmin = 0xffffffffu;
         s_kmax = 0u;
         s_nnz = 0;
         s_bad = 0;
     }
-    for (int i = tid; i < kBuckets; i += kSelThreads) hist[i] = 0;
+    for (int i = tid; i < kBuckets; i += kSelThreads) hist[i] = 0u;
+    if (tid < kCoarse) s_coarse[tid] = 0;
     __syncthreads();
     {
-        uint32_t kmin = 0xffffffffu, kmax = 0u;
-        int nnz = 0, bad = 0;
-        for (int i = tid; i < n; i += kSelThreads) {
-            const uint32_t k = __float_as_uint(x[i]);
-            if (k >= 0x7f800000u) bad = 1;  // NaN, infinity or a negative value
-            if (k != 0u) {
-                kmin = min(kmin, k);
-                kmax = max(kmax, k);
-                nnz++;
-            }
-        }
+        uint32_t kmin = own.kmin, kmax = own.kmax;
+        int nnz = own.nnz, bad = own.bad;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
@@ -780,24 +880,77 @@ __device__ bool sort_probs_desc(float* x, const float* g, int n, int* hist) {
     const int nnz = s_nnz;
     if (nnz == 0) return true;  // all zero: sorted as it stands
     const uint32_t kmax = s_kmax, span = kmax - s_kmin;
-    int shift = 0;
-    while ((span >> shift) >= (uint32_t)kBuckets) shift++;
+    int cshift = 0;
+    while ((span >> cshift) >= (uint32_t)kCoarse) cshift++;
+    const uint32_t cmask = (1u << cshift) - 1u;
     for (int i = tid; i < n; i += kSelThreads) {
         const uint32_t k = __float_as_uint(x[i]);
-        if (k != 0u) atomicAdd(&hist[(kmax - k) >> shift], 1);
+        if (k != 0u) atomicAdd(&s_coarse[(kmax - k) >> cshift], 1);
     }
     __syncthreads();
-    bucket_starts(hist);
+    if (tid < 32) {  // one warp: fine buckets per range (a power of two), their starts
+        constexpr int kPerLane = kCoarse / 32;
+        int bits[kPerLane], tot = 0;
+        const float per_value = (float)kFineTarget / (float)nnz;  // (rounding may add one bucket per range: there is room)
+#pragma unroll
+        for (int i = 0; i < kPerLane; i++) {
+            const int cnt = s_coarse[tid * kPerLane + i];
+            const int share = max(1, (int)((float)cnt * per_value));
+            bits[i] = min(31 - __clz(share), cshift);  // 2^bits <= share; no finer than single bit patterns
+            tot += 1 << bits[i];
+        }
+        int inc = tot;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, inc, o);
+            if (tid >= o) inc += v;
+        }
+        int start = inc - tot;
+#pragma unroll
+        for (int i = 0; i < kPerLane; i++) {
+            s_coarse[tid * kPerLane + i] = (start << 5) | (cshift - bits[i]);
+            start += 1 << bits[i];
+        }
+    }
+    __syncthreads();
+    auto bucket_of = [&](uint32_t k) {
+        const uint32_t d = kmax - k;
+        const int e = s_coarse[d >> cshift];
+        return (e >> 5) + (int)((d & cmask) >> (e & 31));
+    };
+    for (int i = tid; i < n; i += kSelThreads) {
+        const uint32_t k = __float_as_uint(x[i]);
+        if (k != 0u) {
+            const int fb = bucket_of(k);
+            atomicAdd(&hist[fb >> 1], 1u << ((fb & 1) * 16));
+        }
+    }
+    __syncthreads();
+    bucket_starts16(hist);
     for (int i = tid; i < n; i += kSelThreads) {
         const float v = g[i];
         const uint32_t k = __float_as_uint(v);
-        if (k != 0u) x[atomicAdd(&hist[(kmax - k) >> shift], 1)] = v;
+        if (k != 0u) {
+            const int fb = bucket_of(k);
+            const uint32_t old = atomicAdd(&hist[fb >> 1], 1u << ((fb & 1) * 16));
+            x[(old >> ((fb & 1) * 16)) & 0xffffu] = v;
+        }
     }
     for (int i = nnz + tid; i < n; i += kSelThreads) x[i] = 0.0f;
     __syncthreads();
-    // hist[b] is now the END of bucket b; finish each bucket by insertion (descending)
-    for (int bkt = tid; bkt < kBuckets; bkt += kSelThreads) {
-        const int lo = bkt == 0 ? 0 : hist[bkt - 1], hi = hist[bkt];
+    // each half word is now the END of its bucket; finish each bucket: a network in registers for up to 16 values, insertion beyond
+    const uint16_t* ends = reinterpret_cast<const uint16_t*>(hist);
+    for (int bkt = tid; bkt < kFineBuckets; bkt += kSelThreads) {
+        const int lo = bkt == 0 ? 0 : ends[bkt - 1], hi = ends[bkt];
+        if (hi - lo <= 1) continue;
+        if (hi - lo <= 8) {
+            sort_bucket_regs<8>(x, lo, hi - lo);
+            continue;
+        }
+        if (hi - lo <= 16) {
+            sort_bucket_regs<16>(x, lo, hi - lo);
+            continue;
+        }
         if (hi - lo > kBucketMax) {
             const float first = x[lo];
             bool same = true;
@@ -974,16 +1127,6 @@ __device__ __forceinline__ void record_pick(const SelectParams& p, int b, int* h
     }
 }
 
-// Diagnostics build: clock cycles sequence 0's CTA spends per part of the sampled selection (gradb_diag_select_clocks).
-#if GRADB_DIAG
-__device__ unsigned long long g_sel_clock[16];
-#define SEL_CLK(x) const long long x = clock64()
-#define SEL_ADD(i, v) do { if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_sel_clock[i], (unsigned long long)(v)); } while (0)
-#else
-#define SEL_CLK(x)
-#define SEL_ADD(i, v)
-#endif
-
 // The rest of sample_from_logits (text_gen.cpp:156-208) when the top-k filter left n <= kSmallMax candidates: their
 // ids (ascending) in idx, their tempered logits in val; srt: room for the next power of two of floats. Softmax over
 // the candidates (every other entry is an exact zero), nucleus cutoff on the sorted values, renormalisation, draw --
@@ -1030,7 +1173,6 @@ __device__ __forceinline__ int first_reaching(const float* v, int n, float thres
 __device__ int select_among_few(const SelectParams& p, int b, int n, const int* idx, float* val, float* srt,
                                 const uint64_t* exp_tab, float* x) {
     const int lane = threadIdx.x & 31;
-    SEL_CLK(f0);
     // max (tensor.cpp:434-440; the filtered entries, -1e10, lie below every candidate)
     float m = -INFINITY;
     for (int j = lane; j < n; j += 32) m = fmaxf(m, val[j]);
@@ -1044,8 +1186,6 @@ __device__ int select_among_few(const SelectParams& p, int b, int n, const int* 
     const float inv_sum = __fdiv_rn(1.0f, __shfl_sync(0xffffffffu, sum, 0));
     for (int j = lane; j < n; j += 32) val[j] = __fmul_rn(val[j], inv_sum);
     __syncwarp();
-    SEL_CLK(f1);
-    SEL_ADD(8, f1 - f0);  // few: max, exp, sum, normalise
     if (p.top_p < 1.0f) {  // text_gen.cpp:158-193
         if (n <= 64) {
             // rank of each value among the candidates (equal values ordered by position): its place in the sorted row
@@ -1067,8 +1207,6 @@ __device__ int select_among_few(const SelectParams& p, int b, int n, const int* 
             __syncwarp();
             sort_desc_warp(srt, n_pad);
         }
-        SEL_CLK(f2);
-        SEL_ADD(9, f2 - f1);  // few: sort
         float cutoff_prob = 0.0f;
         if (lane == 0) {
             // stays 0 when the running sum never reaches p (the zeros after the candidates add nothing)
@@ -1090,8 +1228,6 @@ __device__ int select_among_few(const SelectParams& p, int b, int n, const int* 
         }
         __syncwarp();
     }
-    SEL_CLK(f3);
-    SEL_ADD(10, f3 - f0);  // few: everything up to here
     if (p.probs_out) {
         for (int i = lane; i < p.V; i += 32) x[i] = 0.0f;
         __syncwarp();
@@ -1111,8 +1247,6 @@ __device__ int select_among_few(const SelectParams& p, int b, int n, const int* 
             if (reached < n) pick = idx[reached];
         }
     }
-    SEL_CLK(f4);
-    SEL_ADD(11, f4 - f3);  // few: draw
     return __shfl_sync(0xffffffffu, pick, 0);
 }
 
@@ -1341,6 +1475,7 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
         }
         __syncthreads();
     }
+    SEL_CLK(g0);
     float mx;
     {
         float m = -INFINITY;
@@ -1355,19 +1490,30 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     // softmax (tensor.cpp:434-448): exp(x - max), sequential sum in index order, times 1/sum
     for (int i = tid; i < V; i += kSelThreads) x[i] = expf_libm(__fsub_rn(x[i], mx), s_exp_tab);
     __syncthreads();
+    SEL_CLK(g1);
+    SEL_ADD(8, g1 - g0);  // maximum and exponentials
     const ScanResult den = exact_scan(V, x, [](float) { return false; }, false, scan_sh, work);
+    SEL_CLK(g2);
+    SEL_ADD(9, g2 - g1);  // denominator (exact scan)
     const float inv_sum = __fdiv_rn(1.0f, den.sum);
+    ProbStats stats;
     for (int i = tid; i < V; i += kSelThreads) {
         const float pr = __fmul_rn(x[i], inv_sum);
         x[i] = pr;
-        if (use_p) g[i] = pr;
+        if (use_p) {
+            g[i] = pr;
+            stats.add(pr);
+        }
     }
     __syncthreads();
+    SEL_CLK(g3);
+    SEL_ADD(10, g3 - g2);  // probabilities (and their index-order copy)
 
     if (use_p) {  // text_gen.cpp:158-193
         // The reference sorts (probability, id) pairs; only the sorted VALUES enter its running sum, so the
         // probabilities are sorted directly.
-        if (!sort_probs_desc(x, g, V, reinterpret_cast<int*>(work))) {
+        if (!sort_probs_desc(x, g, V, reinterpret_cast<int*>(work), stats)) {
+            SEL_ANY(4, 1);  // sorts redone bitonically, over all sequences
             __syncthreads();
             float* area = g + V;  // bitonic sort of a padded copy in global memory: slow, and rare
             for (int i = tid; i < p.n_sort; i += kSelThreads) area[i] = i < V ? g[i] : -INFINITY;
@@ -1376,11 +1522,15 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
             for (int i = tid; i < V; i += kSelThreads) x[i] = area[i];
             __syncthreads();
         }
+        SEL_CLK(g4);
+        SEL_ADD(11, g4 - g3);  // sort
         const float top_p = p.top_p;
         const ScanResult cut = exact_scan(V, x, [top_p](float s) { return s >= top_p; }, true, scan_sh, work);
         const int cutoff = cut.hit < V ? cut.hit : 0;  // never reached: index stays 0
         const float cutoff_prob = x[cutoff];
         __syncthreads();
+        SEL_CLK(g5);
+        SEL_ADD(12, g5 - g4);  // nucleus cutoff (exact scan with a predicate)
         for (int i = tid; i < V; i += kSelThreads) {
             const float pr = g[i];
             x[i] = pr < cutoff_prob ? 0.0f : pr;
@@ -1392,6 +1542,8 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
             for (int i = tid; i < V; i += kSelThreads) x[i] = __fdiv_rn(x[i], tk);
         }
         __syncthreads();
+        SEL_CLK(g6);
+        SEL_ADD(13, g6 - g5);  // mask, kept mass (exact scan), renormalisation
     }
     if (p.probs_out) {
         for (int i = tid; i < V; i += kSelThreads) p.probs_out[(size_t)b * V + i] = x[i];
@@ -1400,6 +1552,9 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     const float u = p.uniforms[(size_t)b * p.u_stride + (p.loop_mode ? p.gen[b] : 0)];
     const ScanResult dr = exact_scan(V, x, [u](float s) { return u <= s; }, true, scan_sh, work);
     const int pick = dr.hit < V ? dr.hit : V - 1;
+    SEL_CLK(g7);
+    SEL_ADD(14, g7 - g0);  // the whole stage on the full row, draw included
+    SEL_MAX(15, g7 - g0);  // the slowest sequence's
 
     if (tid == 0) record_pick(p, b, hist, hlen, pick);
 }
