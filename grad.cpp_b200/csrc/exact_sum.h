@@ -58,4 +58,18 @@ GRADB_HD IncPair term_inc(uint32_t bits, int ue) {
 
 GRADB_HD uint32_t step_S(uint32_t S, IncPair t) { return S + ((S & 1u) ? t.o : t.e); }
 
+// The same term when it is not a tie: its increment does not depend on the parity of S, so the increments of a
+// run of such terms simply add up (saturating once at the end: each is at most kBinadeEnd). *tie is set when the
+// term IS a tie (the returned value is then meaningless and the caller composes the run's maps with term_inc).
+GRADB_HD uint32_t term_inc_plain(uint32_t bits, int ue, uint32_t* tie) {
+    const uint32_t exf = (bits >> 23) & 0xffu;
+    const uint32_t man = (bits & 0x7fffffu) | (exf ? 0x800000u : 0u);
+    const int ex = exf ? (int)exf : 1;
+    const int shift = ue - (ex - 150);
+    const int sh = shift < 1 ? 1 : (shift > 26 ? 26 : shift);
+    const uint32_t rem = man & ((1u << sh) - 1u), half = 1u << (sh - 1);
+    *tie |= (rem == half && shift > 0) ? 1u : 0u;
+    return shift <= 0 ? kBinadeEnd : (man >> sh) + (rem > half ? 1u : 0u);
+}
+
 }  // namespace gradb

@@ -367,6 +367,15 @@ __device__ __forceinline__ SegVal seg_shfl_up(const SegVal& v, int o) {
     return r;
 }
 
+// The parity -> increment map of terms [from, end) of a chunk that starts at beg, composed term by term: the rare
+// chunk with a tie among its terms. Kept out of line so that its registers do not weigh on the sweep.
+__device__ __noinline__ IncPair chunk_map_with_ties(const float* arr, int beg, int from, int end, int ue) {
+    IncPair m = {0u, 0u};
+    (void)beg;
+    for (int i = from; i < end; i++) m = compose(m, term_inc(__float_as_uint(arr[i]), ue));
+    return m;
+}
+
 // work: 4096 words of shared scratch (the sort's histogram is dead by the time scans run).
 // Returns false when the sweep had to be abandoned; the caller then runs seq_scan.
 template <typename Hit>
@@ -500,13 +509,22 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
     const float lo = P * (1.0f - 1.0f / 512.0f), hi = (P + dsum) * (1.0f + 1.0f / 512.0f);
     const int elo = (int)(__float_as_uint(lo) >> 23), ehi = (int)(__float_as_uint(hi) >> 23);
     const bool used = beg < end && beg + kFastPer > start;
-    const bool safe = used && elo == ehi && elo >= 30 && elo < 254;
+    uint32_t sign_seen = 0u;
+#pragma unroll
+    for (int i = 0; i < kFastPer; i++) sign_seen |= __float_as_uint(a[i]);
+    // (a chunk with a negative term is left to the native adds of the walk below: the sums of a safe chunk never decrease)
+    const bool safe = used && elo == ehi && elo >= 30 && elo < 254 && (sign_seen >> 31) == 0u;
     SegVal sv;
     sv.m.e = sv.m.o = 0u;
     if (safe) {
+        // Without a tie among the chunk's terms (the usual case: a tie needs the bits below the sum's unit to be
+        // exactly one half) the increments do not look at the parity and just add up; with one, the maps are composed.
         const int ue = elo - 150;
+        uint32_t total = 0u, tie = 0u;
 #pragma unroll
-        for (int i = 0; i < kFastPer; i++) sv.m = compose(sv.m, term_inc(__float_as_uint(a[i]), ue));
+        for (int i = 0; i < kFastPer; i++) total += term_inc_plain(__float_as_uint(a[i]), ue, &tie);
+        sv.m.e = sv.m.o = sat(total);
+        if (tie != 0u) sv.m = chunk_map_with_ties(arr, beg, max(beg, start), end, ue);  // (fetches the terms again)
     }
     info[tid] = safe ? elo : -1;
     __syncthreads();
@@ -642,15 +660,24 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
             ex.o = seg_o[tid - 1];
         }
         uint32_t S = step_S(S0, ex);
-        int mine = 0x7fffffff;
+        IncPair through;  // the head's start to this chunk's end
+        through.e = seg_e[tid];
+        through.o = seg_o[tid];
+        const uint32_t S_end = step_S(S0, through);
+        auto as_sum = [elo](uint32_t Sx) { return __uint_as_float(((uint32_t)elo << 23) | (Sx & 0x7fffffu)); };
+        // The terms are non-negative, so the sums never decrease, and the predicate stays true once it is: the first
+        // hit of a run lies in the one chunk whose start does not satisfy it and whose end does. Only that chunk walks.
+        if (!hit(as_sum(S)) && hit(as_sum(S_end))) {
+            int mine = 0x7fffffff;
 #pragma unroll
-        for (int i = 0; i < kFastPer; i++) {
-            if (mine == 0x7fffffff && beg + i >= start && beg + i < end) {
-                S = step_S(S, term_inc(__float_as_uint(a[i]), elo - 150));
-                if (hit(__uint_as_float(((uint32_t)elo << 23) | (S & 0x7fffffu)))) mine = beg + i;
+            for (int i = 0; i < kFastPer; i++) {
+                if (mine == 0x7fffffff && beg + i >= start && beg + i < end) {
+                    S = step_S(S, term_inc(__float_as_uint(a[i]), elo - 150));
+                    if (hit(as_sum(S))) mine = beg + i;
+                }
             }
+            if (mine != 0x7fffffff) atomicMin(&f_hit, mine);
         }
-        if (mine != 0x7fffffff) atomicMin(&f_hit, mine);
     }
     __syncthreads();
     // this window is done: the next one starts where it ended, from its exact sum
@@ -665,21 +692,19 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
 __device__ unsigned long long g_sel_clock[16];
 #define SEL_CLK(x) const long long x = clock64()
 #define SEL_ADD(i, v) do { if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_sel_clock[i], (unsigned long long)(v)); } while (0)
-#define SEL_ANY(i, v) do { if (threadIdx.x == 0) atomicAdd(&g_sel_clock[i], (unsigned long long)(v)); } while (0)
 #define SEL_MAX(i, v) do { if (threadIdx.x == 0) atomicMax(&g_sel_clock[i], (unsigned long long)(v)); } while (0)
 #else
 #define SEL_CLK(x)
 #define SEL_ADD(i, v)
-#define SEL_ANY(i, v)
 #define SEL_MAX(i, v)
 #endif
 
-// The exact scan: the one-sweep fast path, or the pass-per-binade scan when it declines.
+// The exact scan: the one-sweep fast path, or the pass-per-binade scan when it declines. The terms are non-negative
+// and `hit` is monotone (true for every sum above one it is true for).
 template <typename Hit>
 __device__ ScanResult exact_scan(int n, const float* arr, Hit hit, bool has_predicate, uint32_t* sh, uint32_t* work) {
     ScanResult r;
     if (seq_scan_fast(n, arr, hit, has_predicate, work, r)) return r;
-    SEL_ANY(5, 1);  // sweeps abandoned, over all sequences
     __syncthreads();
     return seq_scan(n, [arr](int i) { return arr[i]; }, hit, sh);
 }
@@ -1513,7 +1538,6 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
         // The reference sorts (probability, id) pairs; only the sorted VALUES enter its running sum, so the
         // probabilities are sorted directly.
         if (!sort_probs_desc(x, g, V, reinterpret_cast<int*>(work), stats)) {
-            SEL_ANY(4, 1);  // sorts redone bitonically, over all sequences
             __syncthreads();
             float* area = g + V;  // bitonic sort of a padded copy in global memory: slow, and rare
             for (int i = tid; i < p.n_sort; i += kSelThreads) area[i] = i < V ? g[i] : -INFINITY;

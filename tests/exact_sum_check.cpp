@@ -147,7 +147,21 @@ static bool emulated_fast(const std::vector<float>& a, int mode, float thr, Resu
         const bool safe = elo == ehi && elo >= 30 && elo < 254;
         info[c] = safe ? elo : -1;
         IncPair m = {0u, 0u};
-        if (safe) for (int k = b; k < e; k++) m = compose(m, term_inc(fbits(a[k]), elo - 150));
+        if (safe) {  // as the kernel builds it: increments added up when no term is a tie, maps composed otherwise
+            uint32_t total = 0u, tie = 0u;
+            for (int k = b; k < e; k++) total += term_inc_plain(fbits(a[k]), elo - 150, &tie);
+            IncPair composed = {0u, 0u};
+            for (int k = b; k < e; k++) composed = compose(composed, term_inc(fbits(a[k]), elo - 150));
+            if (tie == 0u) {
+                m.e = m.o = sat(total);
+                if (composed.e != m.e || composed.o != m.o) {
+                    std::fprintf(stderr, "PLAIN MAP MISMATCH chunk %d\n", c);
+                    std::exit(1);
+                }
+            } else {
+                m = composed;
+            }
+        }
         cmap[c] = m;
         P += d;
         if (!safe) (*unsafe_chunks)++;
