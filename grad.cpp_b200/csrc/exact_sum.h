@@ -59,17 +59,30 @@ GRADB_HD IncPair term_inc(uint32_t bits, int ue) {
 GRADB_HD uint32_t step_S(uint32_t S, IncPair t) { return S + ((S & 1u) ? t.o : t.e); }
 
 // The same term when it is not a tie: its increment does not depend on the parity of S, so the increments of a
-// run of such terms simply add up (saturating once at the end: each is at most kBinadeEnd). *tie is set when the
-// term IS a tie (the returned value is then meaningless and the caller composes the run's maps with term_inc).
-GRADB_HD uint32_t term_inc_plain(uint32_t bits, int ue, uint32_t* tie) {
-    const uint32_t exf = (bits >> 23) & 0xffu;
-    const uint32_t man = (bits & 0x7fffffu) | (exf ? 0x800000u : 0u);
-    const int ex = exf ? (int)exf : 1;
-    const int shift = ue - (ex - 150);
-    const int sh = shift < 1 ? 1 : (shift > 26 ? 26 : shift);
-    const uint32_t rem = man & ((1u << sh) - 1u), half = 1u << (sh - 1);
-    *tie |= (rem == half && shift > 0) ? 1u : 0u;
-    return shift <= 0 ? kBinadeEnd : (man >> sh) + (rem > half ? 1u : 0u);
+// run of such terms simply add up. In floating point: a / u is exact (u is a power of two; a product that underflows
+// is far below one half either way), adding and subtracting 2^23 rounds it to the nearest integer for a / u < 2^22,
+// and the distance to that integer tells a tie. Returns the increment as a float (an integer below 2^22: four of them
+// add up exactly); *slow is set for a tie, a term of 2^22 units or more, an infinity or a NaN — the caller then
+// composes the run's maps with term_inc, which covers every case. inv_u = 1 / u.
+GRADB_HD float term_inc_float(float a, float inv_u, uint32_t* slow) {
+#if defined(__CUDA_ARCH__)
+    const float t = __fmul_rn(a, inv_u);
+    const float r = __fadd_rn(__fadd_rn(t, 8388608.0f), -8388608.0f);
+    const float d = __fadd_rn(t, -r);
+#else
+    volatile float tv = a * inv_u;  // (volatile: the host compiler must not fold the rounding away)
+    const float t = tv;
+    volatile float up = t + 8388608.0f;
+    const float r = up - 8388608.0f;
+    const float d = t - r;
+#endif
+    *slow |= (!(t < 4194304.0f) || d == 0.5f || d == -0.5f) ? 1u : 0u;
+    return r;
+}
+GRADB_HD float unit_reciprocal(int ue) {  // 1 / 2^ue for -127 < ue < 127
+    union { uint32_t u; float f; } v;
+    v.u = (uint32_t)(127 - ue) << 23;
+    return v.f;
 }
 
 }  // namespace gradb

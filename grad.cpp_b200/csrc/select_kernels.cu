@@ -518,13 +518,21 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
     sv.m.e = sv.m.o = 0u;
     if (safe) {
         // Without a tie among the chunk's terms (the usual case: a tie needs the bits below the sum's unit to be
-        // exactly one half) the increments do not look at the parity and just add up; with one, the maps are composed.
+        // exactly one half) the increments do not look at the parity and just add up, and each is a / u rounded to
+        // the nearest integer: a handful of floating-point operations per term. With a tie, or a term that is not
+        // small against the sum, the maps are composed term by term.
         const int ue = elo - 150;
-        uint32_t total = 0u, tie = 0u;
+        const float inv_u = unit_reciprocal(ue);
+        uint32_t total = 0u, slow = 0u;
 #pragma unroll
-        for (int i = 0; i < kFastPer; i++) total += term_inc_plain(__float_as_uint(a[i]), ue, &tie);
+        for (int q = 0; q < kFastPer / 4; q++) {  // four increments below 2^22 add up exactly in a float
+            float four = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; i++) four = __fadd_rn(four, term_inc_float(a[4 * q + i], inv_u, &slow));
+            total += (uint32_t)four;
+        }
         sv.m.e = sv.m.o = sat(total);
-        if (tie != 0u) sv.m = chunk_map_with_ties(arr, beg, max(beg, start), end, ue);  // (fetches the terms again)
+        if (slow != 0u) sv.m = chunk_map_with_ties(arr, beg, max(beg, start), end, ue);  // (fetches the terms again)
     }
     info[tid] = safe ? elo : -1;
     __syncthreads();

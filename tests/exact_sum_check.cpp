@@ -149,7 +149,12 @@ static bool emulated_fast(const std::vector<float>& a, int mode, float thr, Resu
         IncPair m = {0u, 0u};
         if (safe) {  // as the kernel builds it: increments added up when no term is a tie, maps composed otherwise
             uint32_t total = 0u, tie = 0u;
-            for (int k = b; k < e; k++) total += term_inc_plain(fbits(a[k]), elo - 150, &tie);
+            const float inv_u = unit_reciprocal(elo - 150);
+            for (int k0 = b; k0 < e; k0 += 4) {  // four at a time, as the kernel adds them
+                float four = 0.0f;
+                for (int k = k0; k < std::min(e, k0 + 4); k++) four += term_inc_float(a[k], inv_u, &tie);
+                total += (uint32_t)four;
+            }
             IncPair composed = {0u, 0u};
             for (int k = b; k < e; k++) composed = compose(composed, term_inc(fbits(a[k]), elo - 150));
             if (tie == 0u) {
