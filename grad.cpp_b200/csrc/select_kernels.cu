@@ -1571,7 +1571,10 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
         const ScanResult kept = exact_scan(V, x, [](float) { return false; }, false, scan_sh, work);
         if (kept.sum > 0.0f) {
             const float tk = kept.sum;
-            for (int i = tid; i < V; i += kSelThreads) x[i] = __fdiv_rn(x[i], tk);
+            for (int i = tid; i < V; i += kSelThreads) {
+                const float v = x[i];
+                if (v != 0.0f) x[i] = __fdiv_rn(v, tk);  // (a zero numerator would send the whole warp down the division's slow path)
+            }
         }
         __syncthreads();
         SEL_CLK(g6);
