@@ -1257,7 +1257,9 @@ __device__ int select_among_few(const SelectParams& p, int b, int n, const int* 
         }
         kept = __shfl_sync(0xffffffffu, kept, 0);
         if (kept > 0.0f) {
-            for (int j = lane; j < n; j += 32) val[j] = __fdiv_rn(val[j], kept);
+            for (int j = lane; j < n; j += 32) {
+                if (val[j] != 0.0f) val[j] = __fdiv_rn(val[j], kept);  // (zeros stay zero without the division's slow path)
+            }
         }
         __syncwarp();
     }
