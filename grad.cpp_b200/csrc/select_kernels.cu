@@ -334,15 +334,16 @@ __device__ ScanResult seq_scan(int n, Term term, Hit hit, uint32_t* sh) {
 // ---------------------------------------------------------------------------------------------
 // Fast path of the exact sequential sum: one sweep instead of one pass per binade.
 //
-// A cheap double-precision prefix sum predicts, for every 16-term chunk, an interval that is
+// A cheap prefix sum (pairwise fp32) predicts, for every 16-term chunk, an interval that is
 // GUARANTEED to contain the sequential fp32 running sum throughout the chunk (sequential
 // summation of n non-negative terms is within (n-1) * 2^-24 of the exact sum, under 2^-10 for
 // n <= 16384; the interval is widened by 2^-9). A chunk whose interval lies inside one binade is
 // "safe": its binade is known in advance and nothing can leave it, so its parity -> increment map
 // can be built immediately. Runs of safe chunks that share a binade are composed by a segmented
 // scan; the few chunks that straddle a power of two are added natively. One thread then walks
-// the resulting short list (tens of items) carrying the exact sum, and finally every thread
-// walks its own chunk from its exact start to test the predicate. Any surprise (a start outside
+// the resulting short list (tens of items) carrying the exact sum, and finally the one chunk of a
+// run whose start misses the predicate and whose end meets it walks its terms from its exact start
+// (the sums never decrease and the predicate is monotone). Any surprise (a start outside
 // the predicted binade, an unexpected exit) abandons the sweep and the pass-per-binade scan above
 // redoes the work, so exactness never rests on the prediction.
 constexpr int kFastPer = 16;
