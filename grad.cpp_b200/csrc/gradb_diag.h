@@ -47,10 +47,11 @@ gradb_status gradb_diag_attn_clocks(uint64_t* out16, int reset);
 
 /* Clock cycles sequence 0's CTA of the sampled selection kernel has spent per part since the last reset, for calls
  * that take the few-candidates path after top-k: [0] calls, [1] logits -> shared memory, [2] penalty, [3] temperature,
- * [4] k-th value (for k <= 256: threshold, list, k-th value and the survivors' order, and [5] stays zero), [5] count and compact, [6] softmax / nucleus / draw on the survivors, [7] bookkeeping; and of those that
- * run the stage on the full row: [8] maximum and exponentials, [9] softmax denominator, [10] probabilities, [11] sort,
- * [12] nucleus cutoff, [13] mask + kept mass + renormalisation, [14] all of [8]-[13] and the draw; [15] the largest [14]
- * of any sequence's CTA in one call (the kernel lasts as long as its slowest sequence). */
+ * [4] k-th value (for k <= 256: threshold, list, k-th value and the survivors' order; [5] then stays zero),
+ * [5] count and compact, [6] softmax / nucleus / draw on the survivors, [7] bookkeeping; and of those that run the
+ * stage on the full row: [8] maximum and exponentials, [9] softmax denominator, [10] probabilities, [11] sort,
+ * [12] nucleus cutoff, [13] mask + kept mass + renormalisation, [14] all of [8]-[13] and the draw; [15] the largest
+ * [14] of any sequence's CTA in one call (the kernel lasts as long as its slowest sequence). */
 gradb_status gradb_diag_select_clocks(uint64_t* out16, int reset);
 
 #ifdef __cplusplus
