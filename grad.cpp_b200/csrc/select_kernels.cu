@@ -368,6 +368,31 @@ __device__ __forceinline__ SegVal seg_shfl_up(const SegVal& v, int o) {
     return r;
 }
 
+// Adds v[0..K) to s natively, in order. Returns the position of the first term after which hit(sum) holds (s is then
+// the sum after that term), or K (s the sum after all of them). Non-negative terms never lower the sum and the
+// predicate is monotone, so only the last sum is tested unless it hits; a group with a negative term or a NaN sum is
+// tested term by term.
+template <int K, typename Hit>
+__device__ __forceinline__ int add_group(float& s, const float (&v)[K], bool has_predicate, Hit& hit) {
+    uint32_t signs = 0u;
+    float t = s;
+#pragma unroll
+    for (int k = 0; k < K; k++) {
+        signs |= __float_as_uint(v[k]);
+        t = __fadd_rn(t, v[k]);
+    }
+    if (!has_predicate || ((signs >> 31) == 0u && t == t && !hit(t))) {
+        s = t;
+        return K;
+    }
+#pragma unroll
+    for (int k = 0; k < K; k++) {
+        s = __fadd_rn(s, v[k]);
+        if (hit(s)) return k;
+    }
+    return K;
+}
+
 // The parity -> increment map of terms [from, end) of a chunk that starts at beg, composed term by term: the rare
 // chunk with a tie among its terms. Kept out of line so that its registers do not weigh on the sweep.
 __device__ __noinline__ IncPair chunk_map_with_ties(const float* arr, int beg, int from, int end, int ue) {
@@ -424,13 +449,8 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
                 float v[8];
 #pragma unroll
                 for (int k = 0; k < 8; k++) v[k] = term(i + k);
-#pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    if (h == n) {
-                        s = __fadd_rn(s, v[k]);
-                        if (has_predicate && hit(s)) h = i + k;
-                    }
-                }
+                const int at = add_group<8>(s, v, has_predicate, hit);
+                if (at < 8) h = i + at;
                 i = h == n ? i + 8 : h + 1;
             }
             while (i < stop && h == n) {
@@ -617,13 +637,9 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
                 float v[kFastPer];
 #pragma unroll
                 for (int i = 0; i < kFastPer; i++) v[i] = (b0 + i >= start && b0 + i < e0) ? term(b0 + i) : 0.0f;  // loads first
-#pragma unroll
-                for (int i = 0; i < kFastPer; i++) {
-                    if (b0 + i >= start && b0 + i < e0 && h == n) {
-                        s = __fadd_rn(s, v[i]);
-                        if (has_predicate && hit(s)) h = b0 + i;
-                    }
-                }
+                // (the terms outside [start, e0) are +0 here and leave the sum as it is)
+                const int at = add_group<kFastPer>(s, v, has_predicate, hit);
+                if (at < kFastPer) h = b0 + at;
             } else {  // run of safe chunks t .. nxt-1 in binade e
                 const uint32_t sb = __float_as_uint(s);
                 if ((int)(sb >> 23) != e) {
@@ -678,11 +694,26 @@ __device__ bool seq_scan_fast(int n, const float* arr, Hit hit, bool has_predica
         // hit of a run lies in the one chunk whose start does not satisfy it and whose end does. Only that chunk walks.
         if (!hit(as_sum(S)) && hit(as_sum(S_end))) {
             int mine = 0x7fffffff;
+            // tie-free chunk: the increments do not look at the parity of S
+            const float inv_u = unit_reciprocal(elo - 150);
+            uint32_t slow = 0u, inc[kFastPer];
 #pragma unroll
-            for (int i = 0; i < kFastPer; i++) {
-                if (mine == 0x7fffffff && beg + i >= start && beg + i < end) {
-                    S = step_S(S, term_inc(__float_as_uint(a[i]), elo - 150));
-                    if (hit(as_sum(S))) mine = beg + i;
+            for (int i = 0; i < kFastPer; i++) inc[i] = (uint32_t)term_inc_float(a[i], inv_u, &slow);
+            if (slow == 0u) {
+#pragma unroll
+                for (int i = 0; i < kFastPer; i++) {
+                    if (mine == 0x7fffffff && beg + i >= start && beg + i < end) {
+                        S += inc[i];
+                        if (hit(as_sum(S))) mine = beg + i;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < kFastPer; i++) {
+                    if (mine == 0x7fffffff && beg + i >= start && beg + i < end) {
+                        S = step_S(S, term_inc(__float_as_uint(a[i]), elo - 150));
+                        if (hit(as_sum(S))) mine = beg + i;
+                    }
                 }
             }
             if (mine != 0x7fffffff) atomicMin(&f_hit, mine);
