@@ -397,8 +397,11 @@ __device__ __forceinline__ int add_group(float& s, const float (&v)[K], bool has
 // chunk with a tie among its terms. Kept out of line so that its registers do not weigh on the sweep.
 __device__ __noinline__ IncPair chunk_map_with_ties(const float* arr, int beg, int from, int end, int ue) {
     IncPair m = {0u, 0u};
-    (void)beg;
-    for (int i = from; i < end; i++) m = compose(m, term_inc(__float_as_uint(arr[i]), ue));
+    float v[kFastPer];
+#pragma unroll
+    for (int i = 0; i < kFastPer; i++) v[i] = (beg + i >= from && beg + i < end) ? arr[beg + i] : 0.0f;  // loads first
+#pragma unroll
+    for (int i = 0; i < kFastPer; i++) m = compose(m, term_inc(__float_as_uint(v[i]), ue));  // (+0 is the identity map)
     return m;
 }
 
@@ -893,7 +896,7 @@ __device__ void bucket_starts16(uint32_t* hist) {
 // unspecified, when the values are not finite or too clustered; the caller then sorts g's copy bitonically.
 constexpr int kCoarse = 256;
 constexpr int kFineBuckets = 2 * kBuckets;
-constexpr int kFineTarget = 6144;  // fine buckets handed out in proportion (each range gets at least one on top)
+constexpr int kFineTarget = 7424;  // fine buckets handed out in proportion (each range gets at least one on top)
 struct ProbStats {  // of one thread's share of the probabilities: bit patterns of the non-zero ones
     uint32_t kmin = 0xffffffffu, kmax = 0u;
     int nnz = 0, bad = 0;  // bad: a NaN, an infinity or a negative value
