@@ -190,6 +190,23 @@ def test_selection_stage_random_sweep_against_oracle(G, models, port):
         want, want_probs = port.sample(lg, t, k, p, u, want_probs=True)
         assert int(got[0]) == want, (i, k, t, p, u)
         assert np.array_equal(probs[0].view(np.uint32), want_probs.view(np.uint32)), (i, k)
+    # tight clusters far apart: the probabilities crowd into a few of the sort's buckets, whatever their layout, and
+    # the stage has to fall back on its slow sort; a single cluster of nearly equal values; one dominant id
+    for i in range(4):
+        jitter = rng.standard_normal(16000, dtype=np.float32) * np.float32(1e-4)
+        if i < 2:
+            lg = np.where(rng.random(16000) < 0.5, np.float32(-4.0), np.float32(3.0)).astype(np.float32) + jitter
+        elif i == 2:
+            lg = np.float32(1.5) + jitter
+        else:
+            lg = jitter.copy()
+            lg[123] = np.float32(30.0)
+        p = np.float32([0.9, 0.5, 0.9, 0.9][i])
+        u = np.float32(rng.random())
+        got, probs = s.select(G.Sampling(0, np.float32(1.0), 1.0, 0, p), uniforms=[u], logits=lg[None, :], want_probs=True)
+        want, want_probs = port.sample(lg, np.float32(1.0), 0, p, u, want_probs=True)
+        assert int(got[0]) == want, (i, p, u)
+        assert np.array_equal(probs[0].view(np.uint32), want_probs.view(np.uint32)), i
     # the ends of the draw: u = 0 is satisfied at index 0 whatever its probability, a draw beyond the total mass
     # falls through to the last id -- with few candidates after top-k (their own code path) and with all of them
     lg = rng.standard_normal(16000, dtype=np.float32) * np.float32(2.0)
