@@ -1392,10 +1392,8 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
     for (int i = tid; i < V; i += kSelThreads) {
         const float v = __fmul_rn(x[i], inv_t);
         x[i] = v;
-        if (TOPK) {
-            own_max = fmaxf(own_max, v);
-            own_odd |= v != v;
-        }
+        own_max = fmaxf(own_max, v);
+        if (TOPK) own_odd |= v != v;
     }
     __syncthreads();
     if (TOPK && use_k) {  // text_gen.cpp:138-154: below the k-th largest value -> -1e10, ties kept
@@ -1541,16 +1539,18 @@ __global__ void __launch_bounds__(kSelThreads, 2) select_kernel(const SelectPara
             __syncthreads();  // (s_cnt is read by all before anyone moves on)
         }
         for (int i = tid; i < V; i += kSelThreads) {
-            if (x[i] < kth) x[i] = -1e10f;
+            if (x[i] < kth) {
+                x[i] = -1e10f;
+                own_max = fmaxf(own_max, -1e10f);  // (only matters when every survivor lies below the sentinel)
+            }
         }
         __syncthreads();
     }
     SEL_CLK(g0);
     float mx;
     {
-        float m = -INFINITY;
-        for (int i = tid; i < V; i += kSelThreads) m = fmaxf(m, x[i]);
-        m = warp_max(m);
+        // (each thread's maximum of its tempered values, with the top-k sentinel where it wrote one)
+        float m = warp_max(own_max);
         if (lane == 0) red_v[w] = m;
         __syncthreads();
         m = red_v[0];

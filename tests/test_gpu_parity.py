@@ -207,6 +207,15 @@ def test_selection_stage_random_sweep_against_oracle(G, models, port):
         want, want_probs = port.sample(lg, np.float32(1.0), 0, p, u, want_probs=True)
         assert int(got[0]) == want, (i, p, u)
         assert np.array_equal(probs[0].view(np.uint32), want_probs.view(np.uint32)), i
+    # every logit below the top-k sentinel (-1e10): the filtered entries end up ABOVE the survivors, as in the reference
+    lg = (np.float32(-2e10) - np.abs(rng.standard_normal(16000, dtype=np.float32)) * np.float32(1e9)).astype(np.float32)
+    for k in (300, 40):
+        u = np.float32(rng.random())
+        got, probs = s.select(G.Sampling(0, np.float32(1.0), 1.0, k, np.float32(0.9)), uniforms=[u], logits=lg[None, :],
+                              want_probs=True)
+        want, want_probs = port.sample(lg, np.float32(1.0), k, np.float32(0.9), u, want_probs=True)
+        assert int(got[0]) == want, (k, u, int(got[0]), want)
+        assert np.array_equal(probs[0].view(np.uint32), want_probs.view(np.uint32)), k
     # the ends of the draw: u = 0 is satisfied at index 0 whatever its probability, a draw beyond the total mass
     # falls through to the last id -- with few candidates after top-k (their own code path) and with all of them
     lg = rng.standard_normal(16000, dtype=np.float32) * np.float32(2.0)
